@@ -1,0 +1,142 @@
+/*
+ * xn_mm.h -- C ABI of the B200 (sm_100a) matmul engine for xn.
+ *
+ * Every entry point takes plain pointers and sizes.  Device pointers are CUDA
+ * device addresses on the current device; `stream` is a cudaStream_t passed as
+ * void* (NULL = the default stream, which is what xn-core's Device uses,
+ * xn-core/src/cuda_backend.rs:52).  All work is enqueued asynchronously; the
+ * caller synchronises (xn-core/src/cuda_backend.rs:427-430).  Sizes, strides
+ * and offsets are in ELEMENTS unless a name ends in _bytes.
+ *
+ * Return value: 0 on success, otherwise an xn_status code; a human-readable
+ * message for the calling thread's last failure is returned by
+ * xn_mm_last_error().  Arguments are validated on the host before any launch;
+ * no entry point traps on the device.  Entry points may be called from many
+ * host threads at once (the reference's Backend is Send + Sync,
+ * xn-core/src/backend.rs:4).
+ */
+#ifndef XN_MM_H
+#define XN_MM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types Backend::gemm accepts on CUDA (xn-core/src/cuda_backend.rs:803-862);
+ * numbering is this library's own. */
+typedef enum { XN_F32 = 0, XN_F16 = 1, XN_BF16 = 2 } xn_dtype;
+
+typedef enum {
+    XN_OK = 0,
+    XN_ERR_INVALID = 1,     /* shape / stride / null / alignment problem: the Rust side's bail!() */
+    XN_ERR_UNSUPPORTED = 2, /* dtype or size outside what the engine implements */
+    XN_ERR_CUDA = 3,        /* a CUDA runtime call failed (Error::CudaDriver in the reference) */
+    XN_ERR_WORKSPACE = 4    /* caller-provided workspace too small */
+} xn_status;
+
+const char *xn_mm_last_error(void);
+/* Library version, bumped when the ABI changes. */
+int xn_mm_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Backend::gemm -- replaces the body of CudaDevice's `gemm` (xn-core/src/cuda_backend.rs:787-865,
+ * which calls cublasGemmStridedBatchedEx at :2109/:2170/:2231); signature mirrors the trait
+ * method xn-core/src/backend.rs:135-148 argument for argument, plus dtype and stream.
+ *
+ *   for b < lhs_b, i < m, j < n:
+ *     dst[b*m*n + i*dst_rs + j*dst_cs] =
+ *        sum_{p<k} lhs[lhs_off + b*lhs_b_stride + i*lhs_rs + p*lhs_cs]
+ *                * rhs[rhs_off + b*rhs_b_stride + p*rhs_rs + j*rhs_cs]
+ *
+ * f32 accumulation, dst overwritten (it arrives uninitialised, xn-core/src/ops.rs:697).
+ * rhs_b_stride == 0 shares rhs across the batch.  This is also the grouped / per-codebook
+ * form: one call, lhs_b groups.  Every stride pattern is accepted (the reference's CUDA path
+ * rejects patterns cuBLAS cannot express, xn-core/src/cuda_backend.rs:208-223; its CPU path
+ * accepts all of them).  dst must not overlap lhs or rhs.
+ * ------------------------------------------------------------------------------------------ */
+int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const void *rhs,
+               size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b, size_t lhs_b_stride,
+               size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs,
+               size_t rhs_cs, size_t rhs_rs, void *stream);
+
+/* Host-only: Tensor::matmul_'s lowering of two views to the gemm arguments
+ * (xn-core/src/inplace_ops.rs:318-436, shape rules of xn-core/src/ops.rs:640-700).
+ * out12 = {m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs, lhs_cs, lhs_rs,
+ * rhs_cs, rhs_rs}.  dst_capacity is the element count of the destination storage
+ * (inplace_ops.rs:371-383).  XN_ERR_INVALID on rank < 2, inner-dimension mismatch, batch
+ * mismatch or a destination that is too small. */
+int xn_mm_matmul_plan(size_t lhs_rank, const size_t *lhs_dims, const size_t *lhs_strides,
+                      size_t rhs_rank, const size_t *rhs_dims, const size_t *rhs_strides,
+                      int rhs_t, size_t dst_capacity, size_t *out12);
+
+/* ------------------------------------------------------------------------------------------
+ * Block-quantized integer weights.  No counterpart in the reference (its DType has no
+ * quantized member, xn-core/src/dtype.rs:4-10); these follow the operand specification of the
+ * int4 decode configuration.
+ *
+ * Weights W [n,k], k in 32-element blocks, scale = max|w|/7 (int4) or /127 (int8) per block,
+ * q = clamp(round_half_even(w/scale)).  Activations: int8 per row, scale = max|x|/127.
+ *   P[i,j,blk] = sum_32 xq*wq   (int32, exact)
+ *   y[i,j]     = x_scale[i] * sum_blk (float)P[i,j,blk] * w_scale[j,blk]
+ *
+ * Packed int4 storage ("q4 tiles"): rows padded to a multiple of 16, k a multiple of 128.
+ * Tile (r/16, kk/128) is 1024 bytes = 64 chunks of 16 bytes; chunk 32*h + 4*g + t holds, for
+ * row 16*(r/16) + 8*h + g, four u32 words, word j for 32-block j of the 128-k group; in a
+ * word, byte i = element 4*t+i of the block in its low nibble and element 16+4*t+i in its
+ * high nibble, 4-bit two's complement.  Tiles are ordered [r/16][kk/128].
+ * Scales use the same tiling: tile (r/16, kk/128) = 16 rows x 4 blocks of f32, row-major.
+ * xn_mm_q4_packed_bytes / xn_mm_q4_scale_count give the buffer sizes.
+ * ------------------------------------------------------------------------------------------ */
+size_t xn_mm_q4_packed_bytes(size_t n, size_t k);
+size_t xn_mm_q4_scale_count(size_t n, size_t k);
+
+/* Device: quantize + pack W (dtype f32/f16/bf16, row-major [n,k]) into q4 tiles. */
+int xn_mm_quantize_weights_q4(void *wq_packed, float *w_scale_tiled, const void *w,
+                              xn_dtype dtype, size_t n, size_t k, void *stream);
+/* Host: logical int8 values in [-7,7], row-major [n,k] <-> q4 tiles; row-major scales <-> tiled. */
+int xn_mm_pack_q4_host(uint8_t *wq_packed, const int8_t *q, size_t n, size_t k);
+int xn_mm_unpack_q4_host(int8_t *q, const uint8_t *wq_packed, size_t n, size_t k);
+int xn_mm_tile_scales_host(float *tiled, const float *row_major, size_t n, size_t k, int inverse);
+
+/* Device: dynamic per-row int8 activation quantization of x [m,k] (dtype f32/f16/bf16). */
+int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype dtype, size_t m,
+                           size_t k, void *stream);
+
+/* Device: y [m,n] f32 = int4 linear as specified above.  partials (optional, may be NULL)
+ * receives the int32 block sums as [m][n][k/32].  Any m >= 1; rows are processed 16 at a
+ * time with the weights streamed once per 16 rows. */
+int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed,
+                    const float *w_scale_tiled, size_t m, size_t n, size_t k, int32_t *partials,
+                    void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * fp8-e4m3 weights with one f32 scale per output channel.  No counterpart in the reference.
+ *   scale[j] = max_p |w[j,p]| / 448 ; wq = e4m3_rn_satfinite(w / scale)   (row-major [n,k] bytes)
+ *   y[i,j]   = bf16( scale[j] * sum_p x[i,p] * wq[j,p] ),  f32 accumulation
+ * Activations reach the fp8 tensor-core path as e4m3 pieces of x / s_i, s_i a power of two
+ * with max|x_i| / s_i in (224, 448]:  hi = e4m3(x/s), lo = e4m3(x/s - hi).
+ *   variant 0 ("W8A16"): hi and lo are both used; x = s*(hi+lo) holds exactly for every
+ *                        bf16 x within 2^-11 of the row maximum and to 2^-10 * s otherwise.
+ *   variant 1 ("W8A8"):  hi only.
+ * ------------------------------------------------------------------------------------------ */
+int xn_mm_quantize_weights_fp8(uint8_t *wq, float *w_scale, const void *w, xn_dtype dtype,
+                               size_t n, size_t k, void *stream);
+int xn_mm_split_rows_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const void *x,
+                          xn_dtype dtype, size_t m, size_t k, void *stream);
+/* x_lo == NULL selects variant 1. y is bf16 [m,n]. */
+int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const uint8_t *x_lo,
+                            const float *x_scale, const uint8_t *wq, const float *w_scale,
+                            size_t m, size_t n, size_t k, void *stream);
+/* Convenience: split + linear.  workspace must hold xn_mm_linear_fp8_workspace_bytes(m,k). */
+size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k);
+int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
+                     size_t m, size_t n, size_t k, int variant, void *workspace,
+                     size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XN_MM_H */

@@ -1,0 +1,127 @@
+"""GPU: Backend::gemm through the C ABI against the oracle -- the reference's known-answer tests,
+every call-site stride pattern, all three element types, and seeded larger shapes."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import kats
+
+pytestmark = pytest.mark.gpu
+_TORCH = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
+TOL = {0: 1e-4, 1: 1e-2, 2: 1e-2}
+
+
+def _to_dev(dt, flat, dev):
+    t = torch.from_numpy(np.ascontiguousarray(flat))
+    if dt != 0:
+        t = t.view(torch.int16).view(_TORCH[dt])
+    return t.to(dev)
+
+
+def _to_host(dt, t):
+    t = t.cpu()
+    if dt != 0:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()
+
+
+class AbiBackend:
+    """kats backend that calls xn_mm_matmul_plan / xn_mm_gemm on the device."""
+
+    def __init__(self, xn, dev):
+        self.xn, self.dev = xn, dev
+
+    def plan(self, ld, ls, rd, rs, rhs_t, cap):
+        out = (C.c_size_t * 12)()
+        arr = lambda v: (C.c_size_t * len(v))(*v)
+        self.xn._lib.check(self.xn.lib().xn_mm_matmul_plan(len(ld), arr(ld), arr(ls), len(rd), arr(rd), arr(rs),
+                                                          int(rhs_t), cap, out))
+        return [int(v) for v in out]
+
+    def gemm(self, dt, dst_len, lhs, lhs_off, rhs, rhs_off, *a):
+        dl, dr = _to_dev(dt, lhs, self.dev), _to_dev(dt, rhs, self.dev)
+        # poison the output: every element must be overwritten (dst arrives uninitialised, ops.rs:697)
+        dst = torch.full((dst_len,), float("nan"), dtype=_TORCH[dt], device=self.dev)
+        self.xn._lib.check(self.xn.lib().xn_mm_gemm(dt, dst.data_ptr(), dl.data_ptr(), lhs_off, dr.data_ptr(), rhs_off,
+                                                    *a, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        return _to_host(dt, dst)
+
+
+def test_reference_kats_through_the_c_abi(xn, cuda):
+    assert kats.run_all(AbiBackend(xn, cuda)) == 12
+
+
+@pytest.mark.parametrize("dt", [0, 1, 2])
+def test_call_site_views_match_oracle(xn, oracle, cuda, dt):
+    rng = np.random.default_rng(10 + dt)
+    be, ob = AbiBackend(xn, cuda), kats.OracleBackend()
+    for name, ld, ls, loff, rd, rs, roff, rhs_t in kats.view_cases():
+        lhs = rng.standard_normal(kats.storage_len(ld, ls, loff)).astype(np.float32)
+        rhs = rng.standard_normal(kats.storage_len(rd, rs, roff)).astype(np.float32)
+        lhs, rhs = oracle.to_f32(dt, oracle.from_f32(dt, lhs)), oracle.to_f32(dt, oracle.from_f32(dt, rhs))
+        dims, got = kats.view_matmul(be, dt, lhs, ld, ls, loff, rhs, rd, rs, roff, rhs_t)
+        _, want = kats.view_matmul(ob, dt, lhs, ld, ls, loff, rhs, rd, rs, roff, rhs_t)
+        truth = kats.reference_from_views(lhs, ld, ls, loff, rhs, rd, rs, roff, rhs_t)
+        assert not np.isnan(got).any(), name
+        assert oracle.rel_err(got, truth) < TOL[dt], (name, oracle.rel_err(got, truth))
+        assert oracle.rel_err(got, want) < 2 * TOL[dt], name
+
+
+def test_python_mirror_on_torch_views(xn, oracle, cuda):
+    """matmul / matmul_t / Linear on torch views (transpose, narrow, batched) vs float64."""
+    g = torch.Generator(device="cpu").manual_seed(3)
+    q = torch.randn(2, 3, 5, 16, generator=g).to(cuda)
+    k = torch.randn(2, 3, 11, 16, generator=g).to(cuda)
+    v1 = xn.matmul(q, k.transpose(2, 3))
+    v2 = xn.matmul_t(q, k)
+    ref = (q.double() @ k.double().transpose(2, 3)).cpu().numpy()
+    assert v1.shape == (2, 3, 5, 11)
+    assert oracle.rel_err(v1.cpu().numpy(), ref) < 1e-4 and oracle.rel_err(v2.cpu().numpy(), ref) < 1e-4
+    w = torch.randn(24, 16, generator=g).to(cuda)
+    b = torch.randn(24, generator=g).to(cuda)
+    y = xn.Linear(w, b)(q)
+    assert oracle.rel_err(y.cpu().numpy(), (q.double() @ w.double().T + b.double()).cpu().numpy()) < 1e-4
+    big = torch.randn(8, 40, generator=g).to(cuda)
+    nar = big.narrow(1, 4, 16)  # non-zero offset, row stride 40
+    y2 = xn.matmul_t(nar, w)
+    assert oracle.rel_err(y2.cpu().numpy(), (nar.double() @ w.double().T).cpu().numpy()) < 1e-4
+    with pytest.raises(xn.XnError):
+        xn.matmul(q, torch.randn(2, 3, 17, 4, device=cuda))
+    with pytest.raises(xn.XnError):
+        xn.matmul(q.long(), k.long().transpose(2, 3))
+
+
+def test_config1_f32_linear_full_size(xn, oracle, cuda):
+    """x [16,4096] N(0,1), W [11264,4096] N(0,0.02), seed 0, y = x W^T; judged against the
+    f64-accumulated oracle at tolerance 1e-4."""
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((16, 4096)).astype(np.float32)
+    w = (rng.standard_normal((11264, 4096)) * 0.02).astype(np.float32)
+    y = xn.matmul_t(torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda)).cpu().numpy()
+    truth = oracle.gemm_f64(0, x.reshape(-1), 0, w.reshape(-1), 0, 16, 11264, 4096, 1, 0, 0, (1, 4096), (4096, 1))
+    assert oracle.rel_err(y, truth) < 1e-4
+
+
+@pytest.mark.parametrize("dt,m,n,k", [(2, 64, 256, 512), (1, 33, 130, 200), (0, 130, 70, 300), (2, 1, 512, 1024),
+                                      (2, 16, 384, 2048)])
+def test_seeded_linear_shapes(xn, oracle, cuda, dt, m, n, k):
+    rng = np.random.default_rng(100 + m)
+    x = oracle.from_f32(dt, rng.standard_normal((m, k)).astype(np.float32))
+    w = oracle.from_f32(dt, (rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+    y = xn.matmul_t(_to_dev(dt, x, cuda), _to_dev(dt, w, cuda))
+    truth = oracle.gemm_f64(dt, x.reshape(-1), 0, w.reshape(-1), 0, m, n, k, 1, 0, 0, (1, k), (k, 1))
+    assert oracle.rel_err(oracle.to_f32(dt, _to_host(dt, y).reshape(-1)), truth) < TOL[dt]
+
+
+def test_grouped_codebook_config_shape(xn, oracle, cuda):
+    """16 groups, x [B=64,16,1024] bf16 viewed [16,64,1024], W [16,1024,1024] bf16: one call."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(64, 16, 1024, generator=g).bfloat16().to(cuda)
+    w = (torch.randn(16, 1024, 1024, generator=g) * 0.03).bfloat16().to(cuda)
+    y = xn.matmul_t(x.transpose(0, 1), w)
+    assert y.shape == (16, 64, 1024)
+    ref = torch.einsum("bgk,gnk->gbn", x.double(), w.double()).cpu().numpy()
+    assert oracle.rel_err(y.float().cpu().numpy(), ref) < 1e-2

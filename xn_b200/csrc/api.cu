@@ -1,0 +1,155 @@
+// Host side of the C ABI: error reporting, argument validation, kernel selection for
+// Backend::gemm, and the host-only restatement of Tensor::matmul_'s stride lowering.
+#include <stdarg.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace xn {
+
+std::string &last_error() {
+    static thread_local std::string msg;
+    return msg;
+}
+
+int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return code;
+}
+
+int sm_count() {
+    // Cached per device; devices are few and the table is written once per entry.
+    static int cache[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cache[dev] = v;
+    }
+    return cache[dev];
+}
+
+}  // namespace xn
+
+using namespace xn;
+
+extern "C" const char *xn_mm_last_error(void) { return last_error().c_str(); }
+extern "C" int xn_mm_abi_version(void) { return 1; }
+
+extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const void *rhs,
+                          size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b,
+                          size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_cs, size_t dst_rs,
+                          size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream) {
+    // Same refusal as the reference for element types it has no GEMM for
+    // (xn-core/src/cuda_backend.rs:862).
+    if (!valid_dtype(dtype)) return fail(XN_ERR_UNSUPPORTED, "GEMM not supported for dtype %d", (int)dtype);
+    if (lhs_b == 0 || m == 0 || n == 0) return XN_OK;  // nothing to write
+    XN_REQUIRE(dst && lhs && rhs, "gemm: null pointer (dst=%p lhs=%p rhs=%p)", dst, lhs, rhs);
+    const size_t es = dtype_size(dtype);
+    XN_REQUIRE(aligned(dst, es) && aligned(lhs, es) && aligned(rhs, es), "gemm: operand not aligned to its element size");
+    // Distinct (i,j) must map to distinct dst elements inside one batch slab of m*n elements.
+    XN_REQUIRE((dst_cs == 1 && dst_rs >= n) || (dst_rs == 1 && dst_cs >= m) || m == 1 || n == 1,
+               "gemm: unsupported dst strides (%zu, %zu) for m:%zu n:%zu", dst_cs, dst_rs, m, n);
+    const char *l = static_cast<const char *>(lhs) + lhs_off * es;
+    const char *r = static_cast<const char *>(rhs) + rhs_off * es;
+    return launch_gemm_generic(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
+                               lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
+}
+
+extern "C" int xn_mm_matmul_plan(size_t lhs_rank, const size_t *lhs_dims, const size_t *lhs_strides,
+                                 size_t rhs_rank, const size_t *rhs_dims, const size_t *rhs_strides,
+                                 int rhs_t, size_t dst_capacity, size_t *out) {
+    XN_REQUIRE(lhs_dims && lhs_strides && rhs_dims && rhs_strides && out, "matmul: null pointer");
+    XN_REQUIRE(lhs_rank >= 2 && rhs_rank >= 2, "matmul requires at least 2D tensors, got lhs rank %zu, rhs rank %zu",
+               lhs_rank, rhs_rank);
+    const size_t *ld = lhs_dims + lhs_rank - 2, *rd = rhs_dims + rhs_rank - 2;
+    const size_t m = ld[0], k = ld[1];
+    const size_t rk = rhs_t ? rd[1] : rd[0], n = rhs_t ? rd[0] : rd[1];
+    XN_REQUIRE(k == rk, "matmul inner dimension mismatch: lhs k=%zu, rhs k=%zu, rhs_t=%d", k, rk, rhs_t);
+    size_t lb = 1, rb = 1;
+    for (size_t i = 0; i + 2 < lhs_rank; ++i) lb *= lhs_dims[i];
+    for (size_t i = 0; i + 2 < rhs_rank; ++i) rb *= rhs_dims[i];
+    if (rhs_rank > 2) {
+        bool same = rhs_rank == lhs_rank;
+        for (size_t i = 0; same && i + 2 < rhs_rank; ++i) same = rhs_dims[i] == lhs_dims[i];
+        XN_REQUIRE(same, "batch dimensions do not match in matmul");
+    }
+    if (lb < 1) lb = 1;
+    if (rb < 1) rb = 1;
+    XN_REQUIRE(lb * m * n <= dst_capacity, "matmul dst is too small, dst %zu < %zu", dst_capacity, lb * m * n);
+    const size_t *ls = lhs_strides + lhs_rank, *rs = rhs_strides + rhs_rank;
+    size_t lhs_b_stride = lhs_rank >= 3 ? ls[-3] : m * k;
+    size_t rhs_b_stride = rb == 1 ? 0 : (rhs_rank >= 3 ? rs[-3] : rd[0] * rd[1]);
+    size_t mm = m, batch = lb;
+    if (lhs_b_stride == m * ls[-2] && rb == 1) {  // one flat GEMM over all lhs rows
+        batch = 1;
+        rhs_b_stride = 1;
+        mm = lb * m;
+    }
+    out[0] = mm; out[1] = n; out[2] = k; out[3] = batch; out[4] = lhs_b_stride; out[5] = rhs_b_stride;
+    out[6] = 1; out[7] = n; out[8] = ls[-1]; out[9] = ls[-2];
+    out[10] = rhs_t ? rs[-2] : rs[-1];
+    out[11] = rhs_t ? rs[-1] : rs[-2];
+    return XN_OK;
+}
+
+// ---- host-side q4 tile packing (layout documented in include/xn_mm.h) ----
+static inline size_t q4_byte_index(size_t r, size_t kk, size_t k) {
+    const size_t tile = (r / 16) * (k / 128) + kk / 128;
+    const size_t rr = r % 16, h = rr / 8, g = rr % 8, j = (kk % 128) / 32, e = kk % 32;
+    const size_t t = (e % 16) / 4, i = e % 4;
+    return tile * 1024 + (32 * h + 4 * g + t) * 16 + j * 4 + i;
+}
+
+extern "C" int xn_mm_pack_q4_host(uint8_t *packed, const int8_t *q, size_t n, size_t k) {
+    XN_REQUIRE(k % 128 == 0, "pack_q4: k=%zu must be a multiple of 128", k);
+    if (n == 0 || k == 0) return XN_OK;
+    XN_REQUIRE(packed && q, "pack_q4: null pointer");
+    memset(packed, 0, xn_mm_q4_packed_bytes(n, k));
+    for (size_t r = 0; r < n; ++r)
+        for (size_t kk = 0; kk < k; ++kk) {
+            const int v = q[r * k + kk];
+            XN_REQUIRE(v >= -8 && v <= 7, "pack_q4: value %d at (%zu,%zu) does not fit in 4 bits", v, r, kk);
+            const uint8_t nib = (uint8_t)v & 0xF;
+            uint8_t &b = packed[q4_byte_index(r, kk, k)];
+            b = (kk % 32) / 16 ? (uint8_t)(b | (nib << 4)) : (uint8_t)(b | nib);
+        }
+    return XN_OK;
+}
+
+extern "C" int xn_mm_unpack_q4_host(int8_t *q, const uint8_t *packed, size_t n, size_t k) {
+    XN_REQUIRE(k % 128 == 0, "unpack_q4: k=%zu must be a multiple of 128", k);
+    if (n == 0 || k == 0) return XN_OK;
+    XN_REQUIRE(packed && q, "unpack_q4: null pointer");
+    for (size_t r = 0; r < n; ++r)
+        for (size_t kk = 0; kk < k; ++kk) {
+            const uint8_t b = packed[q4_byte_index(r, kk, k)];
+            int v = (kk % 32) / 16 ? (b >> 4) : (b & 0xF);
+            q[r * k + kk] = (int8_t)(v >= 8 ? v - 16 : v);
+        }
+    return XN_OK;
+}
+
+extern "C" int xn_mm_tile_scales_host(float *dst, const float *src, size_t n, size_t k, int inverse) {
+    XN_REQUIRE(k % 128 == 0, "tile_scales: k=%zu must be a multiple of 128", k);
+    if (n == 0 || k == 0) return XN_OK;
+    XN_REQUIRE(dst && src, "tile_scales: null pointer");
+    const size_t nblk = k / 32, bt = nblk / 4;
+    if (!inverse) memset(dst, 0, xn_mm_q4_scale_count(n, k) * sizeof(float));
+    for (size_t r = 0; r < n; ++r)
+        for (size_t b = 0; b < nblk; ++b) {
+            const size_t idx = ((r / 16) * bt + b / 4) * 64 + (r % 16) * 4 + b % 4;
+            if (inverse) dst[r * nblk + b] = src[idx];
+            else dst[idx] = src[r * nblk + b];
+        }
+    return XN_OK;
+}

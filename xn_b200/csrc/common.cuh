@@ -1,0 +1,85 @@
+// Shared host/device helpers of the sm_100a matmul engine.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/xn_mm.h"
+
+namespace xn {
+
+// Thread-local message returned by xn_mm_last_error().
+std::string &last_error();
+int fail(int code, const char *fmt, ...);
+
+#define XN_CHECK_CUDA(expr)                                                                   \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess)                                                                \
+            return ::xn::fail(XN_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                    \
+                              cudaGetErrorString(_e), __FILE__, __LINE__);                    \
+    } while (0)
+
+#define XN_REQUIRE(cond, ...)                                                                 \
+    do {                                                                                      \
+        if (!(cond)) return ::xn::fail(XN_ERR_INVALID, __VA_ARGS__);                          \
+    } while (0)
+
+inline size_t dtype_size(xn_dtype dt) { return dt == XN_F32 ? 4 : 2; }
+inline bool valid_dtype(int dt) { return dt == XN_F32 || dt == XN_F16 || dt == XN_BF16; }
+inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int sm_count();
+
+// Element widening / narrowing (round to nearest even), the same conversions crate `half`
+// performs for the reference (xn-core/src/dtype.rs:92-131).
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Streaming 128-bit global load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ldg_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// Dispatch a functor template over the three element types.
+#define XN_DISPATCH_DTYPE(dt, T, ...)                                                         \
+    do {                                                                                      \
+        if ((dt) == XN_F32) { using T = float; __VA_ARGS__; }                                 \
+        else if ((dt) == XN_F16) { using T = __half; __VA_ARGS__; }                           \
+        else { using T = __nv_bfloat16; __VA_ARGS__; }                                        \
+    } while (0)
+
+// ---- kernel launchers implemented in the other translation units ----
+int launch_gemm_generic(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n,
+                        size_t k, size_t lhs_b, size_t lhs_b_stride, size_t rhs_b_stride,
+                        size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs, size_t rhs_cs,
+                        size_t rhs_rs, cudaStream_t st);
+
+}  // namespace xn

@@ -1,0 +1,52 @@
+// Entry points of the fp8-e4m3 weight linear: validation, workspace carving, regime selection
+// (decode-sized batches -> weight-streaming kernel; larger batches -> tensor-core GEMM).
+#include "common.cuh"
+
+namespace xn {
+int launch_linear_fp8_gemv(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
+                           const uint8_t *wq, const float *w_scale, int m, size_t n, int k, cudaStream_t st);
+
+static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}  // namespace xn
+
+using namespace xn;
+
+extern "C" int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const uint8_t *x_lo,
+                                       const float *x_scale, const uint8_t *wq, const float *w_scale,
+                                       size_t m, size_t n, size_t k, void *stream) {
+    XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8: k=%zu must be a positive multiple of 16", k);
+    XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull, "linear_fp8: dimension too large");
+    if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(y_bf16 && x_hi && x_scale && wq && w_scale, "linear_fp8: null pointer");
+    XN_REQUIRE(aligned(wq, 16) && aligned(x_hi, 16) && (!x_lo || aligned(x_lo, 16)),
+               "linear_fp8: weights and activation pieces must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    for (size_t i0 = 0; i0 < m; i0 += 16) {
+        const int mc = (int)((m - i0) < 16 ? (m - i0) : 16);
+        int rc = launch_linear_fp8_gemv((char *)y_bf16 + i0 * n * 2, x_hi + i0 * k, x_lo ? x_lo + i0 * k : nullptr,
+                                        x_scale + i0, wq, w_scale, mc, n, (int)k, st);
+        if (rc) return rc;
+    }
+    return XN_OK;
+}
+
+extern "C" size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k) {
+    return 2 * round_up(m * k, 256) + round_up(m * sizeof(float), 256);
+}
+
+extern "C" int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
+                                size_t m, size_t n, size_t k, int variant, void *workspace,
+                                size_t workspace_bytes, void *stream) {
+    XN_REQUIRE(variant == 0 || variant == 1, "linear_fp8: variant must be 0 (W8A16) or 1 (W8A8), got %d", variant);
+    if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(workspace && aligned(workspace, 256), "linear_fp8: workspace must be a 256-byte aligned device buffer");
+    if (workspace_bytes < xn_mm_linear_fp8_workspace_bytes(m, k))
+        return fail(XN_ERR_WORKSPACE, "linear_fp8: workspace of %zu bytes is smaller than the %zu needed",
+                    workspace_bytes, xn_mm_linear_fp8_workspace_bytes(m, k));
+    uint8_t *hi = (uint8_t *)workspace;
+    uint8_t *lo = hi + round_up(m * k, 256);
+    float *xs = (float *)(lo + round_up(m * k, 256));
+    int rc = xn_mm_split_rows_e4m3(hi, variant == 0 ? lo : nullptr, xs, x_bf16, XN_BF16, m, k, stream);
+    if (rc) return rc;
+    return xn_mm_linear_fp8_pieces(y_bf16, hi, variant == 0 ? lo : nullptr, xs, wq, w_scale, m, n, k, stream);
+}

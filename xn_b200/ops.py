@@ -1,0 +1,224 @@
+"""Host-side mirror of xn's matmul interface over the C ABI.
+
+Names and argument meaning follow the reference: ``matmul`` / ``matmul_t`` / ``matmul_with_t``
+(xn-core/src/ops.rs:631-714), the in-place ``matmul_`` (xn-core/src/inplace_ops.rs:318-436) and
+``Linear`` (xn-core/src/nn/linear.rs:4-71).  A ``torch.Tensor`` on a CUDA device plays the role of
+xn's ``Tensor`` / ``TensorView``: its storage pointer, ``storage_offset()``, ``stride()`` and
+``shape`` are exactly the (storage, start_offset, strides, dims) a TensorView carries
+(xn-core/src/tensor_view.rs:103-109), so transposed / narrowed views reach the kernels zero-copy.
+torch is used for device memory and streams only; all arithmetic happens in libxn_mm.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import BF16, F16, F32, XnError, check, lib
+
+_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype not in _DT:
+        # the reference refuses other element types at the same point (cuda_backend.rs:862)
+        raise XnError(_lib.ERR_UNSUPPORTED, f"GEMM not supported for dtype {t.dtype}")
+    return _DT[t.dtype]
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_cuda:
+            raise XnError(_lib.ERR_INVALID, "xn_b200 runs on CUDA tensors only; there is no CPU path")
+
+
+def _base_ptr(t: torch.Tensor) -> int:
+    return t.untyped_storage().data_ptr()
+
+
+def _arr(vals):
+    return (C.c_size_t * len(vals))(*[int(v) for v in vals])
+
+
+def matmul_plan(lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool, dst_capacity: int):
+    """The 12 ``Backend::gemm`` arguments for two views (xn_mm_matmul_plan)."""
+    out = (C.c_size_t * 12)()
+    check(lib().xn_mm_matmul_plan(lhs.dim(), _arr(lhs.shape), _arr(lhs.stride()), rhs.dim(), _arr(rhs.shape),
+                                  _arr(rhs.stride()), int(rhs_t), dst_capacity, out))
+    return [int(v) for v in out]
+
+
+def gemm(dst: torch.Tensor, lhs: torch.Tensor, lhs_off: int, rhs: torch.Tensor, rhs_off: int, m, n, k, lhs_b,
+         lhs_b_stride, rhs_b_stride, dst_strides, lhs_strides, rhs_strides) -> None:
+    """``Backend::gemm`` on flat storages (xn-core/src/backend.rs:135-148)."""
+    _require_cuda(dst, lhs, rhs)
+    dt = _dtype_code(dst)
+    check(lib().xn_mm_gemm(dt, dst.data_ptr(), lhs.data_ptr(), lhs_off, rhs.data_ptr(), rhs_off, m, n, k, lhs_b,
+                           lhs_b_stride, rhs_b_stride, dst_strides[0], dst_strides[1], lhs_strides[0],
+                           lhs_strides[1], rhs_strides[0], rhs_strides[1], _stream()))
+
+
+def matmul_(dst: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool) -> None:
+    """``Tensor::matmul_``: dst (a whole contiguous tensor) = lhs @ rhs or lhs @ rhs^T."""
+    _require_cuda(dst, lhs, rhs)
+    if not (dst.dtype == lhs.dtype == rhs.dtype):
+        raise XnError(_lib.ERR_INVALID, f"matmul dtype mismatch: {dst.dtype}, {lhs.dtype}, {rhs.dtype}")
+    dt = _dtype_code(dst)
+    a = matmul_plan(lhs, rhs, rhs_t, dst.numel())
+    check(lib().xn_mm_gemm(dt, dst.data_ptr(), _base_ptr(lhs), lhs.storage_offset(), _base_ptr(rhs),
+                           rhs.storage_offset(), *a, _stream()))
+
+
+def matmul_with_t(lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool) -> torch.Tensor:
+    """``ops::matmul_with_t``: output shape = lhs batch dims + [M, N], allocated uninitialised."""
+    if lhs.dim() < 2 or rhs.dim() < 2:
+        raise XnError(_lib.ERR_INVALID, "matmul requires at least 2D tensors")
+    n = rhs.shape[-2] if rhs_t else rhs.shape[-1]
+    out = torch.empty(*lhs.shape[:-2], lhs.shape[-2], n, dtype=lhs.dtype, device=lhs.device)
+    matmul_(out, lhs, rhs, rhs_t)
+    return out
+
+
+def matmul(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
+    return matmul_with_t(lhs, rhs, False)
+
+
+def matmul_t(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
+    return matmul_with_t(lhs, rhs, True)
+
+
+class Linear:
+    """``nn::Linear``: weight (out_features, in_features), optional bias (out_features)."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None):
+        self.weight, self.bias = weight, bias
+
+    def with_bias(self, bias: torch.Tensor) -> "Linear":
+        self.bias = bias
+        return self
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = matmul_t(x, self.weight)
+        if self.bias is not None:
+            y += self.bias  # the reference's separate broadcast_add (nn/linear.rs:61-64)
+        return y
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------------------------
+# Quantized linears (no counterpart in the reference): same forward(x) signature as Linear.
+# ---------------------------------------------------------------------------------------------
+def quantize_rows_i8(x: torch.Tensor):
+    _require_cuda(x)
+    x = x.contiguous()
+    m, k = x.shape
+    xq = torch.empty(m, k, dtype=torch.int8, device=x.device)
+    xs = torch.empty(m, dtype=torch.float32, device=x.device)
+    check(lib().xn_mm_quantize_rows_i8(xq.data_ptr(), xs.data_ptr(), x.data_ptr(), _dtype_code(x), m, k, _stream()))
+    return xq, xs
+
+
+def quantize_weights_q4(w: torch.Tensor):
+    """W [n,k] -> (packed q4 tiles as uint8, tiled f32 scales)."""
+    _require_cuda(w)
+    w = w.contiguous()
+    n, k = w.shape
+    packed = torch.empty(lib().xn_mm_q4_packed_bytes(n, k), dtype=torch.uint8, device=w.device)
+    scales = torch.empty(lib().xn_mm_q4_scale_count(n, k), dtype=torch.float32, device=w.device)
+    check(lib().xn_mm_quantize_weights_q4(packed.data_ptr(), scales.data_ptr(), w.data_ptr(), _dtype_code(w), n, k,
+                                          _stream()))
+    return packed, scales
+
+
+def linear_q4(xq: torch.Tensor, x_scale: torch.Tensor, wq_packed: torch.Tensor, w_scale_tiled: torch.Tensor, n: int,
+              partials: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(xq, wq_packed)
+    m, k = xq.shape
+    y = out if out is not None else torch.empty(m, n, dtype=torch.float32, device=xq.device)
+    check(lib().xn_mm_linear_q4(y.data_ptr(), xq.data_ptr(), x_scale.data_ptr(), wq_packed.data_ptr(),
+                                w_scale_tiled.data_ptr(), m, n, k,
+                                partials.data_ptr() if partials is not None else None, _stream()))
+    return y
+
+
+class LinearQ4:
+    """int4 block-quantized linear: forward(x) quantizes x per row to int8, returns f32."""
+
+    def __init__(self, wq_packed, w_scale_tiled, out_features: int, in_features: int):
+        self.wq, self.ws, self.n, self.k = wq_packed, w_scale_tiled, out_features, in_features
+
+    @classmethod
+    def from_weight(cls, w: torch.Tensor) -> "LinearQ4":
+        p, s = quantize_weights_q4(w)
+        return cls(p, s, w.shape[0], w.shape[1])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        xq, xs = quantize_rows_i8(x.reshape(-1, self.k))
+        return linear_q4(xq, xs, self.wq, self.ws, self.n).reshape(*lead, self.n)
+
+    __call__ = forward
+
+
+def quantize_weights_fp8(w: torch.Tensor):
+    _require_cuda(w)
+    w = w.contiguous()
+    n, k = w.shape
+    wq = torch.empty(n, k, dtype=torch.uint8, device=w.device)
+    ws = torch.empty(n, dtype=torch.float32, device=w.device)
+    check(lib().xn_mm_quantize_weights_fp8(wq.data_ptr(), ws.data_ptr(), w.data_ptr(), _dtype_code(w), n, k, _stream()))
+    return wq, ws
+
+
+def split_rows_e4m3(x: torch.Tensor, want_lo: bool = True):
+    _require_cuda(x)
+    x = x.contiguous()
+    m, k = x.shape
+    hi = torch.empty(m, k, dtype=torch.uint8, device=x.device)
+    lo = torch.empty(m, k, dtype=torch.uint8, device=x.device) if want_lo else None
+    xs = torch.empty(m, dtype=torch.float32, device=x.device)
+    check(lib().xn_mm_split_rows_e4m3(hi.data_ptr(), lo.data_ptr() if want_lo else None, xs.data_ptr(), x.data_ptr(),
+                                      _dtype_code(x), m, k, _stream()))
+    return hi, lo, xs
+
+
+def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, variant: int = 0,
+               workspace: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y bf16 [m,n] = fp8 linear of bf16 x [m,k]; variant 0 = W8A16, 1 = W8A8."""
+    _require_cuda(x, wq)
+    if x.dtype != torch.bfloat16:
+        raise XnError(_lib.ERR_INVALID, "linear_fp8 takes bf16 activations")
+    x = x.contiguous()
+    m, k = x.shape
+    n = wq.shape[0]
+    need = lib().xn_mm_linear_fp8_workspace_bytes(m, k)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    y = out if out is not None else torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    check(lib().xn_mm_linear_fp8(y.data_ptr(), x.data_ptr(), wq.data_ptr(), w_scale.data_ptr(), m, n, k, variant,
+                                 workspace.data_ptr(), workspace.numel(), _stream()))
+    return y
+
+
+class LinearFp8:
+    """fp8-e4m3 per-channel linear: forward(x bf16) -> bf16."""
+
+    def __init__(self, wq: torch.Tensor, w_scale: torch.Tensor, variant: int = 0):
+        self.wq, self.ws, self.variant = wq, w_scale, variant
+
+    @classmethod
+    def from_weight(cls, w: torch.Tensor, variant: int = 0) -> "LinearFp8":
+        q, s = quantize_weights_fp8(w)
+        return cls(q, s, variant)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        return linear_fp8(x.reshape(-1, x.shape[-1]), self.wq, self.ws, self.variant).reshape(*lead, self.wq.shape[0])
+
+    __call__ = forward
