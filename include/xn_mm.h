@@ -83,23 +83,24 @@ int xn_mm_matmul_plan(size_t lhs_rank, const size_t *lhs_dims, const size_t *lhs
  *   y[i,j]     = x_scale[i] * sum_blk (float)P[i,j,blk] * w_scale[j,blk]
  *
  * Packed int4 storage ("q4 tiles"): rows padded to a multiple of 16, k a multiple of 128.
- * Tile (r/16, kk/128) is 1024 bytes = 64 chunks of 16 bytes; chunk 32*h + 4*g + t holds, for
- * row 16*(r/16) + 8*h + g, four u32 words, word j for 32-block j of the 128-k group; in a
- * word, byte i = element 4*t+i of the block in its low nibble and element 16+4*t+i in its
- * high nibble, 4-bit two's complement.  Tiles are ordered [r/16][kk/128].
- * Scales use the same tiling: tile (r/16, kk/128) = 16 rows x 4 blocks of f32, row-major.
- * xn_mm_q4_packed_bytes / xn_mm_q4_scale_count give the buffer sizes.
+ * Tile (r/16, kk/128) is 1280 bytes; tiles are ordered [r/16][kk/128].
+ *   bytes 0..1023: 64 chunks of 16 bytes; chunk 32*h + 4*g + t holds, for row 16*(r/16) + 8*h + g,
+ *     four u32 words, word j for 32-block j of the 128-k group; in a word, byte i = element 4*t+i
+ *     of the block in its low nibble and element 16+4*t+i in its high nibble, 4-bit two's
+ *     complement.
+ *   bytes 1024..1279: 64 f32 scales; entry (4*g + j)*2 + h is the scale of row 16*(r/16) + 8*h + g,
+ *     32-block j of the 128-k group.
+ * xn_mm_q4_packed_bytes gives the buffer size (pad rows are zero).
  * ------------------------------------------------------------------------------------------ */
 size_t xn_mm_q4_packed_bytes(size_t n, size_t k);
-size_t xn_mm_q4_scale_count(size_t n, size_t k);
 
 /* Device: quantize + pack W (dtype f32/f16/bf16, row-major [n,k]) into q4 tiles. */
-int xn_mm_quantize_weights_q4(void *wq_packed, float *w_scale_tiled, const void *w,
-                              xn_dtype dtype, size_t n, size_t k, void *stream);
-/* Host: logical int8 values in [-7,7], row-major [n,k] <-> q4 tiles; row-major scales <-> tiled. */
-int xn_mm_pack_q4_host(uint8_t *wq_packed, const int8_t *q, size_t n, size_t k);
-int xn_mm_unpack_q4_host(int8_t *q, const uint8_t *wq_packed, size_t n, size_t k);
-int xn_mm_tile_scales_host(float *tiled, const float *row_major, size_t n, size_t k, int inverse);
+int xn_mm_quantize_weights_q4(void *wq_packed, const void *w, xn_dtype dtype, size_t n, size_t k,
+                              void *stream);
+/* Host: logical int8 values in [-7,7] and f32 block scales, both row-major ([n,k], [n,k/32])
+ * <-> q4 tiles. */
+int xn_mm_pack_q4_host(uint8_t *wq_packed, const int8_t *q, const float *scales, size_t n, size_t k);
+int xn_mm_unpack_q4_host(int8_t *q, float *scales, const uint8_t *wq_packed, size_t n, size_t k);
 
 /* Device: dynamic per-row int8 activation quantization of x [m,k] (dtype f32/f16/bf16). */
 int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype dtype, size_t m,
@@ -108,9 +109,8 @@ int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype d
 /* Device: y [m,n] f32 = int4 linear as specified above.  partials (optional, may be NULL)
  * receives the int32 block sums as [m][n][k/32].  Any m >= 1; rows are processed 16 at a
  * time with the weights streamed once per 16 rows. */
-int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed,
-                    const float *w_scale_tiled, size_t m, size_t n, size_t k, int32_t *partials,
-                    void *stream);
+int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
+                    size_t n, size_t k, int32_t *partials, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * fp8-e4m3 weights with one f32 scale per output channel.  No counterpart in the reference.

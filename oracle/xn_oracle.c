@@ -245,33 +245,39 @@ void xo_quantize_rows_i8(const float *x, size_t m, size_t k, int8_t *q, float *s
 }
 
 /* Physical int4 layout used by the engine ("q4 tiles", documented in include/xn_mm.h):
- * rows padded to a multiple of 16, k a multiple of 128.  Tile (r/16, kk/128) = 1024 bytes =
- * 64 chunks of 16 bytes; chunk 32*h + 4*g + t belongs to row 16*(r/16) + 8*h + g and holds
- * four u32 words, word j for 32-block j of the 128-k group.  In word j, byte i carries
+ * rows padded to a multiple of 16, k a multiple of 128.  Tile (r/16, kk/128) = 1280 bytes.
+ * Bytes 0..1023 = 64 chunks of 16 bytes; chunk 32*h + 4*g + t belongs to row 16*(r/16) + 8*h + g
+ * and holds four u32 words, word j for 32-block j of the 128-k group.  In word j, byte i carries
  * element 4*t+i (low nibble) and element 16+4*t+i (high nibble) of that block, each as 4-bit
- * two's complement.  Scales follow the same tiling: tile = 16 rows x 4 blocks of f32.
- * `packed` must hold ceil(n/16)*16*k/2 bytes and is fully written (pad rows are zero). */
+ * two's complement.  Bytes 1024..1279 = 64 f32 scales; entry (4*g + j)*2 + h is the scale of row
+ * 8*h + g, block j.  `packed` must hold ceil(n/16)*(k/128)*1280 bytes and is fully written. */
 static size_t q4_pos(size_t r, size_t kk, size_t k, int *hi) {
     size_t tile = (r / 16) * (k / 128) + kk / 128;
     size_t rr = r % 16, h = rr / 8, g = rr % 8, j = (kk % 128) / 32, e = kk % 32;
     size_t t = (e % 16) / 4, i = e % 4;
     *hi = (int)(e / 16);
-    return tile * 1024 + (32 * h + 4 * g + t) * 16 + j * 4 + i;
+    return tile * 1280 + (32 * h + 4 * g + t) * 16 + j * 4 + i;
+}
+static size_t q4_scale_pos(size_t r, size_t blk, size_t k) {
+    size_t tile = (r / 16) * (k / 128) + blk / 4;
+    return tile * 1280 + 1024 + 4 * ((4 * (r % 8) + blk % 4) * 2 + (r % 16) / 8);
 }
 
-void xo_pack_q4(const int8_t *q, size_t n, size_t k, uint8_t *packed) {
-    memset(packed, 0, ((n + 15) / 16) * 16 * k / 2);
-    for (size_t r = 0; r < n; ++r)
+void xo_pack_q4(const int8_t *q, const float *scales, size_t n, size_t k, uint8_t *packed) {
+    memset(packed, 0, ((n + 15) / 16) * (k / 128) * 1280);
+    for (size_t r = 0; r < n; ++r) {
         for (size_t kk = 0; kk < k; ++kk) {
             int hi;
             size_t byte = q4_pos(r, kk, k, &hi);
             uint8_t nib = (uint8_t)q[r * k + kk] & 0xF;
             packed[byte] |= hi ? (uint8_t)(nib << 4) : nib;
         }
+        for (size_t b = 0; b < k / 32; ++b) memcpy(packed + q4_scale_pos(r, b, k), &scales[r * (k / 32) + b], 4);
+    }
 }
 
-void xo_unpack_q4(const uint8_t *packed, size_t n, size_t k, int8_t *q) {
-    for (size_t r = 0; r < n; ++r)
+void xo_unpack_q4(const uint8_t *packed, size_t n, size_t k, int8_t *q, float *scales) {
+    for (size_t r = 0; r < n; ++r) {
         for (size_t kk = 0; kk < k; ++kk) {
             int hi;
             uint8_t b = packed[q4_pos(r, kk, k, &hi)];
@@ -279,17 +285,8 @@ void xo_unpack_q4(const uint8_t *packed, size_t n, size_t k, int8_t *q) {
             if (v >= 8) v -= 16;
             q[r * k + kk] = (int8_t)v;
         }
-}
-
-/* Row-major [n, k/32] scales -> the tiled order described above (inverse != 0: back). */
-void xo_tile_scales(const float *s, size_t n, size_t nblk, float *out, int inverse) {
-    size_t bt = nblk / 4;
-    for (size_t r = 0; r < n; ++r)
-        for (size_t b = 0; b < nblk; ++b) {
-            size_t idx = ((r / 16) * bt + b / 4) * 64 + (r % 16) * 4 + b % 4;
-            if (inverse) out[r * nblk + b] = s[idx];
-            else out[idx] = s[r * nblk + b];
-        }
+        for (size_t b = 0; b < k / 32; ++b) memcpy(&scales[r * (k / 32) + b], packed + q4_scale_pos(r, b, k), 4);
+    }
 }
 
 /* Quantized linear: P[i,j,blk] = sum over the block of xq*wq as int32,

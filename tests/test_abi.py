@@ -20,7 +20,7 @@ def _declared_symbols():
 
 def test_library_exports_every_declared_symbol(xn):
     names = _declared_symbols()
-    assert len(names) >= 15
+    assert len(names) >= 14
     h = C.CDLL(xn.LIB_PATH)
     for n in names:
         assert hasattr(h, n), f"{n} declared in include/xn_mm.h but not exported"
@@ -81,9 +81,9 @@ def test_gemm_argument_validation_happens_on_the_host(xn):
     # empty problem: nothing to do, no pointer is touched
     assert lib.xn_mm_gemm(0, None, None, 0, None, 0, 0, 4, 4, 1, 0, 0, 1, 4, 1, 4, 4, 1, None) == 0
     # quantized entry points
-    assert lib.xn_mm_linear_q4(None, None, None, None, None, 1, 16, 100, None, None) == 1
+    assert lib.xn_mm_linear_q4(None, None, None, None, 1, 16, 100, None, None) == 1
     assert b"multiple of 128" in lib.xn_mm_last_error()
-    assert lib.xn_mm_linear_q4(None, None, None, None, None, 0, 16, 128, None, None) == 0
+    assert lib.xn_mm_linear_q4(None, None, None, None, 0, 16, 128, None, None) == 0
     assert lib.xn_mm_linear_fp8(None, None, None, None, 1, 16, 128, 5, None, 0, None) == 1
     assert lib.xn_mm_linear_fp8(1, 1, 1, 1, 1, 16, 128, 0, 256, 10, None) == 4  # workspace too small
     assert lib.xn_mm_linear_fp8_workspace_bytes(16, 4096) == 2 * 65536 + 256
@@ -93,22 +93,16 @@ def test_q4_host_packing_matches_oracle_layout(xn, oracle):
     rng = np.random.default_rng(0)
     n, k = 41, 384
     q = rng.integers(-7, 8, size=(n, k)).astype(np.int8)
+    sc = rng.standard_normal((n, k // 32)).astype(np.float32)
     lib = xn.lib()
     nbytes = lib.xn_mm_q4_packed_bytes(n, k)
-    assert nbytes == 48 * k // 2 and lib.xn_mm_q4_scale_count(n, k) == 48 * k // 32
+    assert nbytes == 3 * 3 * 1280
     packed = np.full(nbytes, 0xAB, dtype=np.uint8)
-    assert lib.xn_mm_pack_q4_host(packed.ctypes.data, q.ctypes.data, n, k) == 0
-    assert np.array_equal(packed, oracle.pack_q4(q))
-    back = np.zeros_like(q)
-    assert lib.xn_mm_unpack_q4_host(back.ctypes.data, packed.ctypes.data, n, k) == 0
-    assert np.array_equal(back, q)
-    s = rng.standard_normal((n, k // 32)).astype(np.float32)
-    tiled = np.zeros(48 * k // 32, np.float32)
-    assert lib.xn_mm_tile_scales_host(tiled.ctypes.data, s.ctypes.data, n, k, 0) == 0
-    assert np.array_equal(tiled, oracle.tile_scales(s))
-    s2 = np.zeros_like(s)
-    assert lib.xn_mm_tile_scales_host(s2.ctypes.data, tiled.ctypes.data, n, k, 1) == 0
-    assert np.array_equal(s2, s)
+    assert lib.xn_mm_pack_q4_host(packed.ctypes.data, q.ctypes.data, sc.ctypes.data, n, k) == 0
+    assert np.array_equal(packed, oracle.pack_q4(q, sc))
+    back, sback = np.zeros_like(q), np.zeros_like(sc)
+    assert lib.xn_mm_unpack_q4_host(back.ctypes.data, sback.ctypes.data, packed.ctypes.data, n, k) == 0
+    assert np.array_equal(back, q) and np.array_equal(sback, sc)
     bad = q.copy()
     bad[0, 0] = 9
-    assert lib.xn_mm_pack_q4_host(packed.ctypes.data, bad.ctypes.data, n, k) == 1
+    assert lib.xn_mm_pack_q4_host(packed.ctypes.data, bad.ctypes.data, sc.ctypes.data, n, k) == 1

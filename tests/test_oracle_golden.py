@@ -81,11 +81,10 @@ def test_block_quantizers(oracle):
     assert np.max(np.abs(deq - blocks)) <= 0.5 * s.max() * 1.0001
     # pack / unpack round trip, ragged row count (pads to 16)
     q2 = q[:41]
-    packed = oracle.pack_q4(q2)
-    assert packed.size == 48 * 256 // 2
-    assert np.array_equal(oracle.unpack_q4(packed, 41, 256), q2)
-    t = oracle.tile_scales(s[:41])
-    assert np.array_equal(oracle.untile_scales(t, 41, 8), s[:41])
+    packed = oracle.pack_q4(q2, s[:41])
+    assert packed.size == 3 * 2 * 1280
+    uq, us = oracle.unpack_q4(packed, 41, 256)
+    assert np.array_equal(uq, q2) and np.array_equal(us, s[:41])
     # int8 rows
     x = rng.standard_normal((5, 256)).astype(np.float32)
     xq, xs = oracle.quantize_rows_i8(x)

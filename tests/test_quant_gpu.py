@@ -25,10 +25,9 @@ def test_quantize_weights_q4_bit_exact(xn, oracle, cuda, n, k):
     g = torch.Generator().manual_seed(2)
     w = torch.randn(n, k, generator=g) * 0.02
     w[1, 32:64] = 0
-    packed, scales = xn.quantize_weights_q4(w.to(cuda))
+    packed = xn.quantize_weights_q4(w.to(cuda))
     q, s = oracle.quantize_q4(w.numpy())
-    assert np.array_equal(packed.cpu().numpy(), oracle.pack_q4(q))
-    assert np.array_equal(scales.cpu().numpy(), oracle.tile_scales(s))
+    assert np.array_equal(packed.cpu().numpy(), oracle.pack_q4(q, s))
 
 
 def _q4_case(xn, oracle, cuda, m, n, k, seed, partials=True):
@@ -38,14 +37,13 @@ def _q4_case(xn, oracle, cuda, m, n, k, seed, partials=True):
     q, s = oracle.quantize_q4(w)
     xq, xs = oracle.quantize_rows_i8(x)
     want_y, want_p = oracle.linear_q(xq, xs, q, s, want_partials=partials)
-    dq = torch.from_numpy(oracle.pack_q4(q)).to(cuda)
-    ds = torch.from_numpy(oracle.tile_scales(s)).to(cuda)
+    dq = torch.from_numpy(oracle.pack_q4(q, s)).to(cuda)
     dxq, dxs = torch.from_numpy(xq).to(cuda), torch.from_numpy(xs).to(cuda)
     part = torch.full((m, n, k // 32), -12345, dtype=torch.int32, device=cuda) if partials else None
     y = torch.full((m, n), float("nan"), device=cuda)
-    xn.linear_q4(dxq, dxs, dq, ds, n, partials=part, out=y)
+    xn.linear_q4(dxq, dxs, dq, n, partials=part, out=y)
     # the run without the debug output must give the same floats
-    y2 = xn.linear_q4(dxq, dxs, dq, ds, n)
+    y2 = xn.linear_q4(dxq, dxs, dq, n)
     torch.cuda.synchronize()
     if partials:
         assert np.array_equal(part.cpu().numpy(), want_p), "int32 block sums must match bit for bit"
@@ -86,10 +84,10 @@ def test_linear_q4_is_linear_in_the_scales(xn, oracle, cuda):
     lin = xn.LinearQ4.from_weight(w)
     xq = torch.from_numpy(rng.integers(-127, 128, (m, k)).astype(np.int8)).to(cuda)
     xs = torch.rand(m, device=cuda) + 0.5
-    y1 = xn.linear_q4(xq, xs, lin.wq, lin.ws, n)
-    y2 = xn.linear_q4(xq, xs * 2, lin.wq, lin.ws, n)
+    y1 = xn.linear_q4(xq, xs, lin.wq, n)
+    y2 = xn.linear_q4(xq, xs * 2, lin.wq, n)
     assert torch.equal(y1 * 2, y2)
-    y0 = xn.linear_q4(torch.zeros_like(xq), xs, lin.wq, lin.ws, n)
+    y0 = xn.linear_q4(torch.zeros_like(xq), xs, lin.wq, n)
     assert not y0.any()
 
 

@@ -30,13 +30,11 @@ SIGNATURES = {
     "xn_mm_gemm": (_i, [_i, _p, _p, _sz, _p, _sz] + [_sz] * 12 + [_p]),
     "xn_mm_matmul_plan": (_i, [_sz, _p, _p, _sz, _p, _p, _i, _sz, _p]),
     "xn_mm_q4_packed_bytes": (_sz, [_sz, _sz]),
-    "xn_mm_q4_scale_count": (_sz, [_sz, _sz]),
-    "xn_mm_quantize_weights_q4": (_i, [_p, _p, _p, _i, _sz, _sz, _p]),
-    "xn_mm_pack_q4_host": (_i, [_p, _p, _sz, _sz]),
-    "xn_mm_unpack_q4_host": (_i, [_p, _p, _sz, _sz]),
-    "xn_mm_tile_scales_host": (_i, [_p, _p, _sz, _sz, _i]),
+    "xn_mm_quantize_weights_q4": (_i, [_p, _p, _i, _sz, _sz, _p]),
+    "xn_mm_pack_q4_host": (_i, [_p, _p, _p, _sz, _sz]),
+    "xn_mm_unpack_q4_host": (_i, [_p, _p, _p, _sz, _sz]),
     "xn_mm_quantize_rows_i8": (_i, [_p, _p, _p, _i, _sz, _sz, _p]),
-    "xn_mm_linear_q4": (_i, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _p, _p]),
+    "xn_mm_linear_q4": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p, _p]),
     "xn_mm_quantize_weights_fp8": (_i, [_p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_split_rows_e4m3": (_i, [_p, _p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_linear_fp8_pieces": (_i, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),

@@ -1,6 +1,8 @@
 // Host side of the C ABI: error reporting, argument validation, kernel selection for
 // Backend::gemm, and the host-only restatement of Tensor::matmul_'s stride lowering.
 #include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -36,6 +38,27 @@ int sm_count() {
         cache[dev] = v;
     }
     return cache[dev];
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("XN_MM_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+int ensure_dynamic_smem(const void *kernel, int *slot, size_t bytes) {
+    int dev = 0;
+    XN_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (bytes <= 32 * 1024) return XN_OK;  // leaves room for static shared memory under the 48 KB default
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if ((size_t)slot[dev] >= bytes) return XN_OK;
+    XN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    slot[dev] = (int)bytes;
+    return XN_OK;
 }
 
 }  // namespace xn
@@ -107,15 +130,19 @@ static inline size_t q4_byte_index(size_t r, size_t kk, size_t k) {
     const size_t tile = (r / 16) * (k / 128) + kk / 128;
     const size_t rr = r % 16, h = rr / 8, g = rr % 8, j = (kk % 128) / 32, e = kk % 32;
     const size_t t = (e % 16) / 4, i = e % 4;
-    return tile * 1024 + (32 * h + 4 * g + t) * 16 + j * 4 + i;
+    return tile * 1280 + (32 * h + 4 * g + t) * 16 + j * 4 + i;
+}
+static inline size_t q4_scale_offset(size_t r, size_t blk, size_t k) {  // byte offset of a block scale
+    const size_t tile = (r / 16) * (k / 128) + blk / 4;
+    return tile * 1280 + 1024 + ((4 * (r % 8) + blk % 4) * 2 + (r % 16) / 8) * 4;
 }
 
-extern "C" int xn_mm_pack_q4_host(uint8_t *packed, const int8_t *q, size_t n, size_t k) {
+extern "C" int xn_mm_pack_q4_host(uint8_t *packed, const int8_t *q, const float *scales, size_t n, size_t k) {
     XN_REQUIRE(k % 128 == 0, "pack_q4: k=%zu must be a multiple of 128", k);
     if (n == 0 || k == 0) return XN_OK;
-    XN_REQUIRE(packed && q, "pack_q4: null pointer");
+    XN_REQUIRE(packed && q && scales, "pack_q4: null pointer");
     memset(packed, 0, xn_mm_q4_packed_bytes(n, k));
-    for (size_t r = 0; r < n; ++r)
+    for (size_t r = 0; r < n; ++r) {
         for (size_t kk = 0; kk < k; ++kk) {
             const int v = q[r * k + kk];
             XN_REQUIRE(v >= -8 && v <= 7, "pack_q4: value %d at (%zu,%zu) does not fit in 4 bits", v, r, kk);
@@ -123,33 +150,24 @@ extern "C" int xn_mm_pack_q4_host(uint8_t *packed, const int8_t *q, size_t n, si
             uint8_t &b = packed[q4_byte_index(r, kk, k)];
             b = (kk % 32) / 16 ? (uint8_t)(b | (nib << 4)) : (uint8_t)(b | nib);
         }
+        for (size_t blk = 0; blk < k / 32; ++blk)
+            memcpy(packed + q4_scale_offset(r, blk, k), &scales[r * (k / 32) + blk], 4);
+    }
     return XN_OK;
 }
 
-extern "C" int xn_mm_unpack_q4_host(int8_t *q, const uint8_t *packed, size_t n, size_t k) {
+extern "C" int xn_mm_unpack_q4_host(int8_t *q, float *scales, const uint8_t *packed, size_t n, size_t k) {
     XN_REQUIRE(k % 128 == 0, "unpack_q4: k=%zu must be a multiple of 128", k);
     if (n == 0 || k == 0) return XN_OK;
-    XN_REQUIRE(packed && q, "unpack_q4: null pointer");
-    for (size_t r = 0; r < n; ++r)
+    XN_REQUIRE(packed && q && scales, "unpack_q4: null pointer");
+    for (size_t r = 0; r < n; ++r) {
         for (size_t kk = 0; kk < k; ++kk) {
             const uint8_t b = packed[q4_byte_index(r, kk, k)];
             int v = (kk % 32) / 16 ? (b >> 4) : (b & 0xF);
             q[r * k + kk] = (int8_t)(v >= 8 ? v - 16 : v);
         }
-    return XN_OK;
-}
-
-extern "C" int xn_mm_tile_scales_host(float *dst, const float *src, size_t n, size_t k, int inverse) {
-    XN_REQUIRE(k % 128 == 0, "tile_scales: k=%zu must be a multiple of 128", k);
-    if (n == 0 || k == 0) return XN_OK;
-    XN_REQUIRE(dst && src, "tile_scales: null pointer");
-    const size_t nblk = k / 32, bt = nblk / 4;
-    if (!inverse) memset(dst, 0, xn_mm_q4_scale_count(n, k) * sizeof(float));
-    for (size_t r = 0; r < n; ++r)
-        for (size_t b = 0; b < nblk; ++b) {
-            const size_t idx = ((r / 16) * bt + b / 4) * 64 + (r % 16) * 4 + b % 4;
-            if (inverse) dst[r * nblk + b] = src[idx];
-            else dst[idx] = src[r * nblk + b];
-        }
+        for (size_t blk = 0; blk < k / 32; ++blk)
+            memcpy(&scales[r * (k / 32) + blk], packed + q4_scale_offset(r, blk, k), 4);
+    }
     return XN_OK;
 }

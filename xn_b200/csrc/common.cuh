@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <string>
 
@@ -35,6 +36,19 @@ inline bool valid_dtype(int dt) { return dt == XN_F32 || dt == XN_F16 || dt == X
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 int sm_count();
+// Programmatic dependent launch for the weight-streaming kernels (on unless XN_MM_PDL=0): a kernel
+// may begin, and prefetch weights, while its predecessor in the stream is still draining.
+bool pdl_enabled();
+
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device); later calls with a
+// size already covered cost one atomic load.  `slot` is a per-kernel table of 64 ints.
+int ensure_dynamic_smem(const void *kernel, int *slot, size_t bytes);
+#define XN_ENSURE_SMEM(kern, bytes)                                                           \
+    do {                                                                                      \
+        static int _slot[64];                                                                 \
+        int _rc = ::xn::ensure_dynamic_smem((const void *)(kern), _slot, (bytes));            \
+        if (_rc) return _rc;                                                                  \
+    } while (0)
 
 // Element widening / narrowing (round to nearest even), the same conversions crate `half`
 // performs for the reference (xn-core/src/dtype.rs:92-131).

@@ -31,8 +31,11 @@ gemm_generic_kernel(T *__restrict__ dst, const T *__restrict__ lhs, const T *__r
     for (size_t b = blockIdx.y; b < lhs_b; b += gridDim.y) {
         const T *A = lhs + b * lhs_b_stride;
         const T *B = rhs + b * rhs_b_stride;
+        // Two-level accumulation: each 16-deep slice is summed on its own and then added to the
+        // running total, which keeps the f32 rounding error near eps*sqrt(k/16) instead of eps*sqrt(k).
         float acc[4][4] = {};
         for (size_t p0 = 0; p0 < k; p0 += BK) {
+            float part[4][4] = {};
 #pragma unroll
             for (int e = tid; e < BM * BK; e += NT) {
                 int ii, pp;
@@ -58,8 +61,12 @@ gemm_generic_kernel(T *__restrict__ dst, const T *__restrict__ lhs, const T *__r
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(a[r], bb[c], acc[r][c]);
+                    for (int c = 0; c < 4; ++c) part[r][c] = fmaf(a[r], bb[c], part[r][c]);
             }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] += part[r][c];
             __syncthreads();
         }
         T *D = dst + b * m * n;

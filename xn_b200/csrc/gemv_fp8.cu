@@ -183,7 +183,7 @@ int launch(__nv_bfloat16 *y, const uint8_t *x_hi, const uint8_t *x_lo, const flo
     const int grid = (tiles + tpc - 1) / tpc;
     const size_t smem = (size_t)pieces * MT * 8 * x_row_stride(kchunk) + (size_t)warps * MT * 4 * 32 * sizeof(float);
     auto kern = linear_fp8_gemv_kernel<MT, LO>;
-    XN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    XN_ENSURE_SMEM(kern, smem);
     kern<<<grid, warps * 32, smem, st>>>(y, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, kchunk, tiles, tpc,
                                          slots, ksplit);
     XN_CHECK_CUDA(cudaGetLastError());

@@ -46,8 +46,8 @@ __global__ void quantize_rows_i8_kernel(int8_t *__restrict__ xq, float *__restri
 // One warp per (row, 32-block): lane e owns element e of the block.
 // Output layout: see "q4 tiles" in include/xn_mm.h.
 template <typename T>
-__global__ void quantize_weights_q4_kernel(uint8_t *__restrict__ packed, float *__restrict__ scales,
-                                           const T *__restrict__ w, size_t n, size_t n_pad, size_t k) {
+__global__ void quantize_weights_q4_kernel(uint8_t *__restrict__ packed, const T *__restrict__ w, size_t n,
+                                           size_t n_pad, size_t k) {
     const size_t nblk = k / 32;
     const size_t warp = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (warp >= n_pad * nblk) return;
@@ -72,9 +72,9 @@ __global__ void quantize_weights_q4_kernel(uint8_t *__restrict__ packed, float *
     if (e < 16 && (e & 3) == 0) {
         unsigned t = e >> 2;
         unsigned word = byte | (b1 << 8) | (b2 << 16) | (b3 << 24);
-        *reinterpret_cast<unsigned *>(packed + tile * 1024 + (32 * h + 4 * g + t) * 16 + j * 4) = word;
+        *reinterpret_cast<unsigned *>(packed + tile * 1280 + (32 * h + 4 * g + t) * 16 + j * 4) = word;
     }
-    if (e == 0) scales[tile * 64 + rr * 4 + j] = scale;
+    if (e == 0) reinterpret_cast<float *>(packed + tile * 1280 + 1024)[(4 * g + j) * 2 + h] = scale;
 }
 
 // One CTA per output channel.  scale = max|w| / 448, q = e4m3(w / scale).
@@ -147,15 +147,14 @@ extern "C" int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x,
     return XN_OK;
 }
 
-extern "C" size_t xn_mm_q4_packed_bytes(size_t n, size_t k) { return ((n + 15) / 16) * 16 * k / 2; }
-extern "C" size_t xn_mm_q4_scale_count(size_t n, size_t k) { return ((n + 15) / 16) * 16 * (k / 32); }
+extern "C" size_t xn_mm_q4_packed_bytes(size_t n, size_t k) { return ((n + 15) / 16) * (k / 128) * 1280; }
 
-extern "C" int xn_mm_quantize_weights_q4(void *wq_packed, float *w_scale_tiled, const void *w,
-                                         xn_dtype dtype, size_t n, size_t k, void *stream) {
+extern "C" int xn_mm_quantize_weights_q4(void *wq_packed, const void *w, xn_dtype dtype, size_t n, size_t k,
+                                         void *stream) {
     XN_REQUIRE(valid_dtype(dtype), "quantize_weights_q4: unknown dtype %d", (int)dtype);
     XN_REQUIRE(k % 128 == 0 && k > 0, "quantize_weights_q4: k=%zu must be a positive multiple of 128", k);
     if (n == 0) return XN_OK;
-    XN_REQUIRE(wq_packed && w_scale_tiled && w, "quantize_weights_q4: null pointer");
+    XN_REQUIRE(wq_packed && w, "quantize_weights_q4: null pointer");
     XN_REQUIRE(aligned(wq_packed, 16), "quantize_weights_q4: packed buffer must be 16-byte aligned");
     size_t n_pad = (n + 15) / 16 * 16;
     size_t warps = n_pad * (k / 32);
@@ -164,7 +163,7 @@ extern "C" int xn_mm_quantize_weights_q4(void *wq_packed, float *w_scale_tiled, 
     cudaStream_t st = (cudaStream_t)stream;
     XN_DISPATCH_DTYPE(dtype, T,
         quantize_weights_q4_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
-            (uint8_t *)wq_packed, w_scale_tiled, (const T *)w, n, n_pad, k));
+            (uint8_t *)wq_packed, (const T *)w, n, n_pad, k));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }

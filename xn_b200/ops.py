@@ -124,25 +124,22 @@ def quantize_rows_i8(x: torch.Tensor):
     return xq, xs
 
 
-def quantize_weights_q4(w: torch.Tensor):
-    """W [n,k] -> (packed q4 tiles as uint8, tiled f32 scales)."""
+def quantize_weights_q4(w: torch.Tensor) -> torch.Tensor:
+    """W [n,k] -> q4 tiles (uint8 buffer holding nibbles and block scales)."""
     _require_cuda(w)
     w = w.contiguous()
     n, k = w.shape
     packed = torch.empty(lib().xn_mm_q4_packed_bytes(n, k), dtype=torch.uint8, device=w.device)
-    scales = torch.empty(lib().xn_mm_q4_scale_count(n, k), dtype=torch.float32, device=w.device)
-    check(lib().xn_mm_quantize_weights_q4(packed.data_ptr(), scales.data_ptr(), w.data_ptr(), _dtype_code(w), n, k,
-                                          _stream()))
-    return packed, scales
+    check(lib().xn_mm_quantize_weights_q4(packed.data_ptr(), w.data_ptr(), _dtype_code(w), n, k, _stream()))
+    return packed
 
 
-def linear_q4(xq: torch.Tensor, x_scale: torch.Tensor, wq_packed: torch.Tensor, w_scale_tiled: torch.Tensor, n: int,
+def linear_q4(xq: torch.Tensor, x_scale: torch.Tensor, wq_packed: torch.Tensor, n: int,
               partials: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     _require_cuda(xq, wq_packed)
     m, k = xq.shape
     y = out if out is not None else torch.empty(m, n, dtype=torch.float32, device=xq.device)
-    check(lib().xn_mm_linear_q4(y.data_ptr(), xq.data_ptr(), x_scale.data_ptr(), wq_packed.data_ptr(),
-                                w_scale_tiled.data_ptr(), m, n, k,
+    check(lib().xn_mm_linear_q4(y.data_ptr(), xq.data_ptr(), x_scale.data_ptr(), wq_packed.data_ptr(), m, n, k,
                                 partials.data_ptr() if partials is not None else None, _stream()))
     return y
 
@@ -150,18 +147,17 @@ def linear_q4(xq: torch.Tensor, x_scale: torch.Tensor, wq_packed: torch.Tensor, 
 class LinearQ4:
     """int4 block-quantized linear: forward(x) quantizes x per row to int8, returns f32."""
 
-    def __init__(self, wq_packed, w_scale_tiled, out_features: int, in_features: int):
-        self.wq, self.ws, self.n, self.k = wq_packed, w_scale_tiled, out_features, in_features
+    def __init__(self, wq_packed, out_features: int, in_features: int):
+        self.wq, self.n, self.k = wq_packed, out_features, in_features
 
     @classmethod
     def from_weight(cls, w: torch.Tensor) -> "LinearQ4":
-        p, s = quantize_weights_q4(w)
-        return cls(p, s, w.shape[0], w.shape[1])
+        return cls(quantize_weights_q4(w), w.shape[0], w.shape[1])
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         xq, xs = quantize_rows_i8(x.reshape(-1, self.k))
-        return linear_q4(xq, xs, self.wq, self.ws, self.n).reshape(*lead, self.n)
+        return linear_q4(xq, xs, self.wq, self.n).reshape(*lead, self.n)
 
     __call__ = forward
 
