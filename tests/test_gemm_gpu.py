@@ -125,3 +125,36 @@ def test_grouped_codebook_config_shape(xn, oracle, cuda):
     assert y.shape == (16, 64, 1024)
     ref = torch.einsum("bgk,gnk->gbn", x.double(), w.double()).cpu().numpy()
     assert oracle.rel_err(y.float().cpu().numpy(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("dt", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(17, 72, 64), (128, 256, 128), (200, 328, 1032), (512, 1024, 4096), (4096, 4096, 1024)])
+def test_dense_16bit_tensor_core_path(xn, oracle, cuda, dt, m, n, k):
+    """Linear::forward's form (x [m,k], W [n,k], both k-contiguous) on the tcgen05 kernel; sampled
+    rows/columns are recomputed by the oracle with f64 accumulation."""
+    g = torch.Generator(device=cuda).manual_seed(m + n)
+    x = torch.randn(m, k, generator=g, device=cuda).to(_TORCH[dt])
+    w = (torch.randn(n, k, generator=g, device=cuda) * 0.05).to(_TORCH[dt])
+    y = torch.full((m, n), float("nan"), dtype=_TORCH[dt], device=cuda)
+    xn.matmul_(y, x, w, True)
+    torch.cuda.synchronize()
+    assert not torch.isnan(y).any()
+    rng = np.random.default_rng(m)
+    rows = np.unique(np.concatenate([[0, m - 1], rng.choice(m, size=min(40, m), replace=False)]))
+    cols = np.unique(np.concatenate([[0, n - 1], rng.choice(n, size=min(96, n), replace=False)]))
+    xs = _to_host(dt, x[torch.from_numpy(rows).to(cuda)].contiguous())
+    ws = _to_host(dt, w[torch.from_numpy(cols).to(cuda)].contiguous())
+    truth = oracle.gemm_f64(dt, xs.reshape(-1), 0, ws.reshape(-1), 0, len(rows), len(cols), k, 1, 0, 0, (1, k), (k, 1))
+    got = y[torch.from_numpy(rows).to(cuda)][:, torch.from_numpy(cols).to(cuda)].float().cpu().numpy()
+    assert oracle.rel_err(got, truth) < TOL[dt]
+
+
+def test_dense_16bit_views_with_row_pitch(xn, oracle, cuda):
+    """narrow()-ed operands: row pitches larger than k, non-zero offsets (multiples of 8 elements)."""
+    g = torch.Generator(device=cuda).manual_seed(5)
+    xb = torch.randn(96, 320, generator=g, device=cuda).bfloat16()
+    wb = (torch.randn(144, 384, generator=g, device=cuda) * 0.05).bfloat16()
+    x, w = xb.narrow(1, 64, 256), wb.narrow(1, 128, 256)
+    y = xn.matmul_t(x, w)
+    ref = (x.double() @ w.double().T).cpu().numpy()
+    assert oracle.rel_err(y.float().cpu().numpy(), ref) < 1e-2

@@ -164,3 +164,49 @@ def test_linear_fp8_ragged(xn, oracle, cuda, n, k):
 @pytest.mark.parametrize("m", [1, 16])
 def test_linear_fp8_transformer_shapes_decode(xn, oracle, cuda, n, k, m):
     _fp8_case(xn, oracle, cuda, m, n, k, seed=2)
+
+
+def _fp8_gemm_sampled(xn, oracle, cuda, m, n, k, variant, seed=2, n_cols=192, n_rows=48):
+    """Full-size run on the device; the oracle recomputes a random sample of rows x channels."""
+    g = torch.Generator(device=cuda).manual_seed(seed)
+    x = torch.randn(m, k, generator=g, device=cuda).bfloat16()
+    w = torch.randn(n, k, generator=g, device=cuda) * 0.02
+    wq, ws = xn.quantize_weights_fp8(w)
+    del w
+    y = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda)
+    xn.linear_fp8(x, wq, ws, variant, out=y)
+    torch.cuda.synchronize()
+    assert not torch.isnan(y).any()
+    rng = np.random.default_rng(seed)
+    rows = np.sort(rng.choice(m, size=min(n_rows, m), replace=False))
+    cols = np.sort(rng.choice(n, size=min(n_cols, n), replace=False))
+    # always include the corners and tile edges
+    rows[0], rows[-1] = 0, m - 1
+    cols[0], cols[-1] = 0, n - 1
+    xb = _bf16_bits(x[torch.from_numpy(rows).to(cuda)])
+    wq_s = wq[torch.from_numpy(cols).to(cuda)].cpu().numpy()
+    ws_s = ws[torch.from_numpy(cols).to(cuda)].cpu().numpy()
+    _, want32 = oracle.linear_fp8(xb, wq_s, ws_s, variant)
+    got = y[torch.from_numpy(rows).to(cuda)][:, torch.from_numpy(cols).to(cuda)].float().cpu().numpy()
+    err = oracle.rel_err(got, want32)
+    assert err < 1e-2, err
+    return y
+
+
+@pytest.mark.parametrize("m", [64, 100, 256])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_linear_fp8_gemm_small_shapes_full_check(xn, oracle, cuda, m, variant):
+    # every output checked; ragged n and k exercise the zero-filled tile edges
+    _fp8_case(xn, oracle, cuda, m, 200, 1040, seed=m, variant=variant)
+    _fp8_case(xn, oracle, cuda, m, 520, 256, seed=m + 1, variant=variant)
+
+
+@pytest.mark.parametrize("n,k", [(12288, 4096), (4096, 4096), (22528, 4096), (4096, 11264)])
+@pytest.mark.parametrize("m", [64, 256, 1024, 4096])
+def test_linear_fp8_transformer_shapes_prefill(xn, oracle, cuda, n, k, m):
+    y0 = _fp8_gemm_sampled(xn, oracle, cuda, m, n, k, 0)
+    if m == 256:
+        # run-to-run identical, and the W8A8 form on the same shape
+        y1 = _fp8_gemm_sampled(xn, oracle, cuda, m, n, k, 0)
+        assert torch.equal(y0, y1)
+        _fp8_gemm_sampled(xn, oracle, cuda, m, n, k, 1)

@@ -84,6 +84,12 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                "gemm: unsupported dst strides (%zu, %zu) for m:%zu n:%zu", dst_cs, dst_rs, m, n);
     const char *l = static_cast<const char *>(lhs) + lhs_off * es;
     const char *r = static_cast<const char *>(rhs) + rhs_off * es;
+    // Linear::forward's form with 16-bit elements -- both operands k-contiguous, rows of dst
+    // contiguous -- goes to the tcgen05 kernel when TMA can address it (16-byte pitches and bases).
+    if (dtype != XN_F32 && lhs_b == 1 && m > 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
+        lhs_rs % 8 == 0 && rhs_cs % 8 == 0 && aligned(l, 16) && aligned(r, 16) && m <= 0x7fffffff &&
+        n <= 0x7fffffff && k <= 0x7fffffff && dst_rs <= 0x7fffffff)
+        return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, (cudaStream_t)stream);
     return launch_gemm_generic(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
                                lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
 }

@@ -1,0 +1,366 @@
+// Dense tensor-core GEMM for the `matmul_t` form, D[M,N] = A[M,K] * B[N,K]^T with both operands
+// K-contiguous -- the shape every Linear::forward produces (xn-core/src/nn/linear.rs:56-66), which
+// the reference sends to cublasGemmStridedBatchedEx (xn-core/src/cuda_backend.rs:2109-2133).
+// Written for sm_100a: TMA (cp.async.bulk.tensor, no multicast) stages 128-byte-swizzled tiles in
+// shared memory, one elected thread issues tcgen05.mma with the accumulators in tensor memory, and
+// four epilogue warps read them back with tcgen05.ld.
+//
+//   warp 0      producer: TMA loads into a ring of NSTAGE stages, mbarrier full/empty pairs
+//   warp 1      tensor-memory allocation; MMA issue; tcgen05.commit releases stages / publishes tiles
+//   warps 2..5  epilogue: TMEM -> registers -> scale/convert -> global (each warp owns the 32 TMEM
+//               lanes of its warp-id-mod-4 quarter)
+//
+// The kernel is persistent (grid = #SMs, tiles round-robin) and keeps two accumulator buffers in
+// TMEM so the epilogue of one tile overlaps the MMAs of the next.
+//
+// Operand kinds
+//   FP8 pieces: A is one (W8A8) or two (W8A16: hi + lo) e4m3 matrices, B the e4m3 weights;
+//               kind::f8f6f4, the two pieces accumulate into the same TMEM tile, the epilogue
+//               applies x_scale[m] * w_scale[n] and rounds to bf16.
+//   BF16 / F16: kind::f16, the epilogue rounds the f32 accumulator to the element type.
+//
+// Every mbarrier wait is bounded; a wait that gives up records it in g_gemm_wait_timeouts and the
+// CTA drains through its common exit (tensor memory is always released).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace xn {
+namespace {
+
+constexpr int BM = 128;        // rows of A per tile = TMEM lanes
+constexpr int BKB = 128;       // bytes of K per stage = one 128-byte swizzle atom
+constexpr int UMMA_KB = 32;    // bytes of K per tcgen05.mma (32 x 8-bit or 16 x 16-bit)
+constexpr int NTHREADS = 192;
+constexpr unsigned WAIT_LIMIT = 1u << 26;
+
+__device__ unsigned g_gemm_wait_timeouts;
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *b, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *b, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        unsigned ok;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(smem_u32(b)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    atomicAdd(&g_gemm_wait_timeouts, 1u);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(const void *tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)0 << 16;                             // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                             // descriptor version
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D = f32, A/B formats, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int n) {
+    return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+template <bool F8>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    if (F8)
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+            : "memory");
+    else
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+            : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+    void *y;              // [M, N] output, row stride ldy elements
+    const float *x_scale; // FP8 only: per activation row
+    const float *w_scale; // FP8 only: per output channel
+    int M, N, K;          // K in elements
+    int ldy;
+};
+
+// KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16
+template <int KIND, int BN, int NA, int NSTAGE>
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
+                    const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
+    constexpr bool F8 = KIND == 0;
+    constexpr int ELEM = F8 ? 1 : 2;
+    constexpr int BK = BKB / ELEM;  // K elements per stage
+    constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB;
+    constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES;
+    constexpr uint32_t IDESC = F8 ? instr_desc(0, 0, BN) : (KIND == 1 ? instr_desc(1, 1, BN) : instr_desc(0, 0, BN));
+    constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full[NSTAGE], empty[NSTAGE], tmem_full[2], tmem_empty[2];
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_m = (args.M + BM - 1) / BM, num_n = (args.N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = (args.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int it = 0;  // running k-block count across tiles: stage = it % NSTAGE
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_blk = tile % num_m, n_blk = tile / num_m;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % NSTAGE;
+                    const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(st, &map_a0, kb * BK, m_blk * BM, &full[s]);
+                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_a1, kb * BK, m_blk * BM, &full[s]);
+                    tma_load_2d(st + NA * A_BYTES, &map_b, kb * BK, n_blk * BN, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int it = 0, t_local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
+                const int acc = t_local & 1;
+                const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % NSTAGE;
+                    const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
+                    if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    const uint64_t da0 = smem_desc(st), da1 = smem_desc(st + A_BYTES), db = smem_desc(st + NA * A_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
+                        const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
+                        umma<F8>(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
+                        if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + adv, IDESC, 1u);
+                    }
+                    umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(&tmem_full[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int t_local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
+            const int m_blk = tile % num_m, n_blk = tile / num_m;
+            const int acc = t_local & 1;
+            const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
+            if (!mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m_blk * BM + q * 32 + lane;
+            float xs = 1.0f;
+            if (F8 && row < args.M) xs = __ldg(args.x_scale + row);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+                const int col0 = n_blk * BN + c * 32;
+                if (row < args.M && col0 < args.N) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float f0 = __uint_as_float(v[2 * j]), f1 = __uint_as_float(v[2 * j + 1]);
+                        if (F8) {
+                            const int c0 = min(col0 + 2 * j, args.N - 1), c1 = min(col0 + 2 * j + 1, args.N - 1);
+                            f0 = __ldg(args.w_scale + c0) * (xs * f0);
+                            f1 = __ldg(args.w_scale + c1) * (xs * f1);
+                        }
+                        if (KIND == 2) {
+                            __half2 h = __floats2half2_rn(f0, f1);
+                            packed[j] = *reinterpret_cast<uint32_t *>(&h);
+                        } else {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                            packed[j] = *reinterpret_cast<uint32_t *>(&h);
+                        }
+                    }
+                    uint16_t *dst = reinterpret_cast<uint16_t *>(args.y) + (size_t)row * args.ldy + col0;
+                    if (col0 + 32 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            reinterpret_cast<uint4 *>(dst)[j] =
+                                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < args.N; ++j)
+                            dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// 2-D row-major [rows, k] tensor with `elem` bytes per element and a row pitch of ld elements;
+// box = 128 bytes of k by box_rows rows, 128-byte swizzle, out-of-range reads give zeros.
+int make_map(CUtensorMap *map, const void *base, int elem, size_t rows, size_t k, size_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem};
+    cuuint32_t box[2] = {(cuuint32_t)(BKB / elem), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return XN_OK;
+}
+
+template <int KIND, int BN, int NA>
+int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
+               cudaStream_t st) {
+    constexpr int ELEM = KIND == 0 ? 1 : 2;
+    constexpr int STAGE_BYTES = NA * BM * BKB + BN * BKB;
+    constexpr int NSTAGE = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+    CUtensorMap ma0, ma1, mb;
+    int rc = make_map(&ma0, a0, ELEM, args.M, args.K, lda, BM);
+    if (rc) return rc;
+    rc = make_map(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM);
+    if (rc) return rc;
+    rc = make_map(&mb, b, ELEM, args.N, args.K, ldb, BN);
+    if (rc) return rc;
+    auto kern = gemm_tcgen05_kernel<KIND, BN, NA, NSTAGE>;
+    const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 1024;
+    XN_ENSURE_SMEM(kern, smem);
+    const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN);
+    const int sms = sm_count();
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, NTHREADS, smem, st>>>(ma0, ma1, mb, args);
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+template <int KIND, int NA>
+int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
+                cudaStream_t st) {
+    // Wide tiles when there are enough of them to fill the machine, narrower ones otherwise.
+    const int sms = sm_count();
+    const long m_tiles = (args.M + BM - 1) / BM;
+    if (m_tiles * ((args.N + 255) / 256) >= sms) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st);
+    if (m_tiles * ((args.N + 127) / 128) >= sms) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st);
+    return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st);
+}
+
+}  // namespace
+
+// y bf16 [m,n] = x_scale[m] * w_scale[n] * (x_hi (+ x_lo)) * wq^T, all operands row-major e4m3.
+int launch_linear_fp8_gemm(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
+                           const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
+    GemmArgs a{y, x_scale, w_scale, (int)m, (int)n, (int)k, (int)n};
+    return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
+}
+
+// dst [m,n] (row stride ldd) = lhs [m,k] (row stride lda) * rhs [n,k]^T (row stride ldb); dt BF16 or F16.
+int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
+                         size_t lda, size_t ldb, size_t ldd, cudaStream_t st) {
+    GemmArgs a{dst, nullptr, nullptr, (int)m, (int)n, (int)k, (int)ldd};
+    return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st)
+                         : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st);
+}
+
+}  // namespace xn

@@ -6,6 +6,9 @@ namespace xn {
 int launch_linear_fp8_gemv(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
                            const uint8_t *wq, const float *w_scale, int m, size_t n, int k, cudaStream_t st);
 
+int launch_linear_fp8_gemm(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
+                           const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st);
+
 static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 }  // namespace xn
 
@@ -21,6 +24,9 @@ extern "C" int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const 
     XN_REQUIRE(aligned(wq, 16) && aligned(x_hi, 16) && (!x_lo || aligned(x_lo, 16)),
                "linear_fp8: weights and activation pieces must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
+    // Decode-sized batches stream the weights once through the GEMV kernel; anything larger goes to
+    // the tensor-memory GEMM (which pads the last row tile).
+    if (m > 16) return launch_linear_fp8_gemm(y_bf16, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
     for (size_t i0 = 0; i0 < m; i0 += 16) {
         const int mc = (int)((m - i0) < 16 ? (m - i0) : 16);
         int rc = launch_linear_fp8_gemv((char *)y_bf16 + i0 * n * 2, x_hi + i0 * k, x_lo ? x_lo + i0 * k : nullptr,
