@@ -1,0 +1,180 @@
+"""Shape sweeps behind the benchmark tables: fp8 transformer linears, grouped per-codebook matmul,
+the f32 linear, and the 16-bit dense GEMM, each with its roofline and (where the reference has a
+GPU path) the same call through cuBLAS as xn issues it (torch.matmul -> cublasGemmEx, f32 accumulate).
+
+    python -m xn_b200.sweep [--what fp8|dense|grouped|f32|all] [--json out.json]
+
+Timing: CUDA events around a CUDA-graph replay of `reps` launches that rotate over enough distinct
+weight copies to exceed the L2 several times for the bandwidth-bound points.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import xn_b200 as xn  # noqa: E402
+
+NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "fp8_tflops": 4500.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
+
+
+def time_graph(fns, reps_per_fn=1, iters=5):
+    """fns: list of callables (one per operand replica). Returns seconds per call."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(reps_per_fn):
+                for f in fns:
+                    f()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / (iters * reps_per_fn * len(fns))
+
+
+def replicas_for(nbytes, target=600e6, lo=1, hi=32):
+    return int(max(lo, min(hi, -(-target // nbytes))))
+
+
+def sweep_fp8(out, dev, pk):
+    shapes = [(12288, 4096, "qkv"), (4096, 4096, "out_proj"), (22528, 4096, "ffn_up"), (4096, 11264, "ffn_down")]
+    for n, k, name in shapes:
+        R = replicas_for(n * k)
+        ws = []
+        for _ in range(R):
+            w = torch.randn(n, k, device=dev) * 0.02
+            ws.append(xn.quantize_weights_fp8(w))
+            del w
+        wb = [(q.view(torch.float8_e4m3fn)) for q, _ in ws]
+        for m in (1, 16, 64, 256, 1024, 4096):
+            x = torch.randn(m, k, device=dev).bfloat16()
+            y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+            wsp = torch.empty(xn.lib().xn_mm_linear_fp8_workspace_bytes(m, k), dtype=torch.uint8, device=dev)
+            flops = 2.0 * m * n * k
+            byts = n * k + 4 * n + 2 * m * k + 2 * m * n
+            reps = 1 if m >= 1024 else 2
+            row = {"config": "fp8_linear", "name": name, "m": m, "n": n, "k": k, "replicas": R}
+            for variant, tag in ((0, "w8a16"), (1, "w8a8")):
+                t_full = time_graph([lambda q=q, s=s: xn.linear_fp8(x, q, s, variant, workspace=wsp, out=y) for q, s in ws], reps)
+                hi, lo, xs = xn.split_rows_e4m3(x, want_lo=(variant == 0))
+                from xn_b200._lib import check
+                L = xn.lib()
+                st = lambda: torch.cuda.current_stream().cuda_stream
+                t_mm = time_graph([lambda q=q, s=s: check(L.xn_mm_linear_fp8_pieces(
+                    y.data_ptr(), hi.data_ptr(), lo.data_ptr() if lo is not None else None, xs.data_ptr(), q.data_ptr(),
+                    s.data_ptr(), m, n, k, st())) for q, s in ws], reps)
+                peak_t = (pk["bf16_tflops"] if variant == 0 else 2 * pk["bf16_tflops"]) * 1e12
+                roof = max(byts / (pk["hbm_gbs"] * 1e9), flops / peak_t)
+                row[tag] = {"us_full": t_full * 1e6, "us_matmul": t_mm * 1e6, "tflops": flops / t_mm / 1e12,
+                            "gbs": byts / t_mm / 1e9, "roofline_us": roof * 1e6, "frac_of_roofline": roof / t_mm}
+            # the reference's GPU path for a bf16 weight of the same shape: cuBLAS bf16 GEMM, f32 accumulate
+            wbf = [torch.randn(n, k, device=dev).bfloat16() for _ in range(min(R, max(1, R // 2)))]
+            t_cublas = time_graph([lambda w=w: torch.matmul(x, w.t(), out=y) for w in wbf], reps)
+            row["cublas_bf16_us"] = t_cublas * 1e6
+            del wbf
+            out.append(row)
+            print(json.dumps(row), flush=True)
+        del ws, wb
+        torch.cuda.empty_cache()
+
+
+def sweep_dense(out, dev, pk):
+    for dt in (torch.bfloat16, torch.float16):
+        for m, n, k in ((4096, 4096, 4096), (8192, 8192, 8192), (1024, 12288, 4096), (256, 12288, 4096), (64, 12288, 4096)):
+            R = replicas_for(2 * n * k, hi=8)
+            ws = [(torch.randn(n, k, device=dev) * 0.05).to(dt) for _ in range(R)]
+            x = torch.randn(m, k, device=dev).to(dt)
+            y = torch.empty(m, n, device=dev, dtype=dt)
+            flops = 2.0 * m * n * k
+            byts = 2 * (n * k + m * k + m * n)
+            t = time_graph([lambda w=w: xn.matmul_(y, x, w, True) for w in ws], 1)
+            t_ref = time_graph([lambda w=w: torch.matmul(x, w.t(), out=y) for w in ws], 1)
+            roof = max(byts / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12))
+            row = {"config": "dense_16bit", "dtype": str(dt), "m": m, "n": n, "k": k, "us": t * 1e6,
+                   "tflops": flops / t / 1e12, "cublas_us": t_ref * 1e6, "cublas_tflops": flops / t_ref / 1e12,
+                   "frac_of_roofline": roof / t}
+            out.append(row)
+            print(json.dumps(row), flush=True)
+            del ws
+
+
+def sweep_grouped(out, dev, pk):
+    G, B = 16, 64
+    for n, k, name in ((1024, 1024, "stage1"), (4096, 1024, "ffn_up"), (1024, 2048, "ffn_down")):
+        R = replicas_for(2 * G * n * k, hi=16)
+        ws = [(torch.randn(G, n, k, device=dev) * 0.03).bfloat16() for _ in range(R)]
+        x = torch.randn(B, G, k, device=dev).bfloat16()
+        xt = x.transpose(0, 1)
+        y = torch.empty(G, B, n, device=dev, dtype=torch.bfloat16)
+        t = time_graph([lambda w=w: xn.matmul_(y, xt, w, True) for w in ws], 2)
+        t_ref = time_graph([lambda w=w: torch.bmm(xt, w.transpose(1, 2), out=y) for w in ws], 2)
+        byts = 2 * (G * n * k + B * G * k + B * G * n)
+        row = {"config": "grouped_codebooks", "name": name, "groups": G, "b": B, "n": n, "k": k, "us": t * 1e6,
+               "gbs": byts / t / 1e9, "frac_of_hbm": byts / t / 1e9 / pk["hbm_gbs"], "cublas_us": t_ref * 1e6}
+        out.append(row)
+        print(json.dumps(row), flush=True)
+        del ws
+
+
+def sweep_f32(out, dev, pk):
+    m, n, k = 16, 11264, 4096
+    R = 4
+    ws = [torch.randn(n, k, device=dev) * 0.02 for _ in range(R)]
+    x = torch.randn(m, k, device=dev)
+    y = torch.empty(m, n, device=dev)
+    t = time_graph([lambda w=w: xn.matmul_(y, x, w, True) for w in ws], 2)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False  # the reference keeps full-precision f32 by default
+    t_ref = time_graph([lambda w=w: torch.matmul(x, w.t(), out=y) for w in ws], 2)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    byts = 4 * (n * k + m * k + m * n)
+    row = {"config": "f32_linear", "m": m, "n": n, "k": k, "us": t * 1e6, "gbs": byts / t / 1e9,
+           "frac_of_hbm": byts / t / 1e9 / pk["hbm_gbs"], "cublas_us": t_ref * 1e6}
+    out.append(row)
+    print(json.dumps(row), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="all")
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    pk = peaks()
+    out = [{"peaks": pk, "nominal": NOMINAL}]
+    print(json.dumps(out[0]), flush=True)
+    for name, fn in (("fp8", sweep_fp8), ("dense", sweep_dense), ("grouped", sweep_grouped), ("f32", sweep_f32)):
+        if a.what in ("all", name):
+            fn(out, dev, pk)
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump(out, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()
