@@ -22,8 +22,8 @@ def oracle():
 @pytest.fixture(scope="session")
 def xn():
     """The engine package; building the library is the session's first act."""
-    from xn_b200 import build as b
-    b.build()
+    import __graft_entry__
+    __graft_entry__.load_builder().build()
     import xn_b200
     return xn_b200
 

@@ -1,6 +1,6 @@
 """Builds libxn_mm.so (the C-ABI engine) in-tree with nvcc for sm_100a.
 
-    python -m xn_b200.build [--force] [--verbose]
+    python xn_b200/build.py [--force] [--verbose]
 
 The library links only the CUDA runtime; it has no Python or torch dependency.
 """
