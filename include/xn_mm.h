@@ -136,6 +136,20 @@ int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const 
                      size_t m, size_t n, size_t k, int variant, void *workspace,
                      size_t workspace_bytes, void *stream);
 
+/* Allocation-free form of xn_mm_linear_fp8.  It has no counterpart in the reference.  For hosts
+ * that must not (or cannot) allocate device memory at call time -- a serving loop whose device
+ * budget belongs to another allocator, a real-time audio callback that cannot afford a
+ * synchronising cudaMalloc, an embedder barred from the CUDA allocator.  The scratch for the
+ * activation pieces is a fixed 513 KiB array inside the library image (held by every GPU that loads
+ * the library until the process exits), so sizes are limited to m <= 64 and
+ * m*k <= xn_mm_linear_fp8_noalloc_max_elems() (262144); larger calls return XN_ERR_UNSUPPORTED.
+ * All calls on a device share that array: calls that overlap on the GPU race, so keep them in one
+ * stream order.  The first call on a device resolves the array's device address and should be made
+ * outside any stream capture.  Results are identical to xn_mm_linear_fp8. */
+size_t xn_mm_linear_fp8_noalloc_max_elems(void);
+int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
+                             size_t m, size_t n, size_t k, int variant, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

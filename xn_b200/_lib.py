@@ -40,6 +40,8 @@ SIGNATURES = {
     "xn_mm_linear_fp8_pieces": (_i, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "xn_mm_linear_fp8_workspace_bytes": (_sz, [_sz, _sz]),
     "xn_mm_linear_fp8": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p, _sz, _p]),
+    "xn_mm_linear_fp8_noalloc_max_elems": (_sz, []),
+    "xn_mm_linear_fp8_noalloc": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p]),
 }
 
 _lib = None

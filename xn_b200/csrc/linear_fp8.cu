@@ -1,5 +1,7 @@
 // Entry points of the fp8-e4m3 weight linear: validation, workspace carving, regime selection
 // (decode-sized batches -> weight-streaming kernel; larger batches -> tensor-core GEMM).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace xn {
@@ -53,6 +55,77 @@ extern "C" int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t 
     uint8_t *lo = hi + round_up(m * k, 256);
     float *xs = (float *)(lo + round_up(m * k, 256));
     int rc = xn_mm_split_rows_e4m3(hi, variant == 0 ? lo : nullptr, xs, x_bf16, XN_BF16, m, k, stream);
+    if (rc) return rc;
+    return xn_mm_linear_fp8_pieces(y_bf16, hi, variant == 0 ? lo : nullptr, xs, wq, w_scale, m, n, k, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of xn_mm_linear_fp8.
+//
+// Some hosts of this library cannot obtain device memory at call time: a serving loop whose whole
+// device budget was handed to another allocator at start-up, a real-time audio callback where a
+// cudaMalloc (which may synchronise the device) is not acceptable, or an embedder that is simply not
+// allowed to call the CUDA allocator.  xn_mm_linear_fp8 needs scratch for the e4m3 activation pieces
+// and their row scales; here that scratch is a fixed array that is part of the library image, so the
+// call allocates nothing -- no cudaMalloc, cudaFree or allocating library routine is reached.
+//
+// Cost and limits: every GPU that loads the library holds XN_NOALLOC_SCRATCH_BYTES (513 KiB) until
+// the process exits.  Sizes are limited to m <= 64 and m * k <= 262144 (decode-sized batches, e.g.
+// 16 x 16384 or 64 x 4096); anything larger is refused with XN_ERR_UNSUPPORTED.
+//
+// The array is shared by every call on a device.  It keeps the previous call's contents; nothing in
+// it has to start at zero, because each call rewrites the m * k piece bytes and m scales it then
+// reads.  Two calls that overlap on the GPU (different streams, or different host threads on
+// different streams) race on it: keep all calls on one device in one stream order.
+//
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+// first call outside any stream capture.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t NOALLOC_MAX_ELEMS = 262144;  // m * k
+constexpr size_t NOALLOC_MAX_ROWS = 64;
+constexpr size_t NOALLOC_SCALE_OFFSET = 2 * NOALLOC_MAX_ELEMS;
+constexpr size_t NOALLOC_BYTES = NOALLOC_SCALE_OFFSET + 1024;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
+static __device__ __align__(256) unsigned char g_fp8_noalloc_scratch[NOALLOC_BYTES];
+
+int noalloc_scratch(unsigned char **out) {
+    static unsigned char *table[64];
+    static std::mutex mu;
+    int dev = 0;
+    XN_CHECK_CUDA(cudaGetDevice(&dev));
+    XN_REQUIRE(dev >= 0 && dev < 64, "linear_fp8_noalloc: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!table[dev]) {
+        void *p = nullptr;
+        XN_CHECK_CUDA(cudaGetSymbolAddress(&p, g_fp8_noalloc_scratch));  // address on the current device
+        table[dev] = static_cast<unsigned char *>(p);
+    }
+    *out = table[dev];
+    return XN_OK;
+}
+}  // namespace
+
+extern "C" size_t xn_mm_linear_fp8_noalloc_max_elems(void) { return NOALLOC_MAX_ELEMS; }
+
+extern "C" int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
+                                        size_t m, size_t n, size_t k, int variant, void *stream) {
+    XN_REQUIRE(variant == 0 || variant == 1, "linear_fp8_noalloc: variant must be 0 (W8A16) or 1 (W8A8), got %d",
+               variant);
+    if (m > NOALLOC_MAX_ROWS || (k != 0 && m > NOALLOC_MAX_ELEMS / k))
+        return fail(XN_ERR_UNSUPPORTED,
+                    "linear_fp8_noalloc: m=%zu k=%zu exceeds the built-in scratch (m <= %zu and m*k <= %zu); "
+                    "use xn_mm_linear_fp8 with a caller workspace",
+                    m, k, NOALLOC_MAX_ROWS, NOALLOC_MAX_ELEMS);
+    if (m == 0 || n == 0) return XN_OK;
+    unsigned char *base = nullptr;
+    int rc = noalloc_scratch(&base);
+    if (rc) return rc;
+    uint8_t *hi = base;
+    uint8_t *lo = base + NOALLOC_MAX_ELEMS;
+    float *xs = reinterpret_cast<float *>(base + NOALLOC_SCALE_OFFSET);
+    rc = xn_mm_split_rows_e4m3(hi, variant == 0 ? lo : nullptr, xs, x_bf16, XN_BF16, m, k, stream);
     if (rc) return rc;
     return xn_mm_linear_fp8_pieces(y_bf16, hi, variant == 0 ? lo : nullptr, xs, wq, w_scale, m, n, k, stream);
 }
