@@ -129,6 +129,52 @@ __global__ void split_rows_e4m3_kernel(uint8_t *__restrict__ x_hi, uint8_t *__re
     }
 }
 
+// Fast path of the split for 16-bit rows: 256 threads per row, each holds up to VPT 8-element vectors of
+// the row in registers between the maximum and the rounding pass (one read of x), 8-byte stores.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+split_rows_e4m3_vec_kernel(uint8_t *__restrict__ x_hi, uint8_t *__restrict__ x_lo, float *__restrict__ x_scale,
+                           const T *__restrict__ x, size_t k) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + row * k);
+    const int nvec = (int)(k / 8);
+    uint4 v[VPT];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = i * 256 + threadIdx.x;
+        v[i] = idx < nvec ? __ldg(src + idx) : make_uint4(0, 0, 0, 0);
+        const T *e = reinterpret_cast<const T *>(&v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(to_f32(e[j])));
+    }
+    amax = block_max(amax, red);
+    float s = 1.0f;
+    if (amax != 0.0f && isfinite(amax)) {
+        int ex;
+        float f = frexpf(amax, &ex);
+        s = ldexpf(1.0f, f <= 0.875f ? ex - 9 : ex - 8);
+    }
+    if (threadIdx.x == 0) x_scale[row] = s;
+    const float inv = 1.0f / s;  // exact: s is a power of two
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = i * 256 + threadIdx.x;
+        if (idx >= nvec) continue;
+        const T *e = reinterpret_cast<const T *>(&v[i]);
+        uint8_t h[8], l[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float val = to_f32(e[j]) * inv;
+            h[j] = (uint8_t)__nv_cvt_float_to_fp8(val, __NV_SATFINITE, __NV_E4M3);
+            l[j] = (uint8_t)__nv_cvt_float_to_fp8(val - e4m3_to_f32(h[j]), __NV_SATFINITE, __NV_E4M3);
+        }
+        reinterpret_cast<uint2 *>(x_hi + row * k)[idx] = *reinterpret_cast<const uint2 *>(h);
+        if (x_lo) reinterpret_cast<uint2 *>(x_lo + row * k)[idx] = *reinterpret_cast<const uint2 *>(l);
+    }
+}
+
 }  // namespace
 }  // namespace xn
 
@@ -188,6 +234,19 @@ extern "C" int xn_mm_split_rows_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scal
     XN_REQUIRE(x_hi && x_scale && x, "split_rows_e4m3: null pointer");
     XN_REQUIRE(m <= 0x7fffffffull, "split_rows_e4m3: m too large");
     cudaStream_t st = (cudaStream_t)stream;
+    if (dtype != XN_F32 && k % 8 == 0 && k <= 8 * 256 * 8 && aligned(x, 16) && aligned(x_hi, 8) &&
+        (!x_lo || aligned(x_lo, 8))) {
+        const bool small = k <= 8 * 256 * 2;
+        if (dtype == XN_BF16) {
+            if (small) split_rows_e4m3_vec_kernel<__nv_bfloat16, 2><<<(unsigned)m, 256, 0, st>>>(x_hi, x_lo, x_scale, (const __nv_bfloat16 *)x, k);
+            else split_rows_e4m3_vec_kernel<__nv_bfloat16, 8><<<(unsigned)m, 256, 0, st>>>(x_hi, x_lo, x_scale, (const __nv_bfloat16 *)x, k);
+        } else {
+            if (small) split_rows_e4m3_vec_kernel<__half, 2><<<(unsigned)m, 256, 0, st>>>(x_hi, x_lo, x_scale, (const __half *)x, k);
+            else split_rows_e4m3_vec_kernel<__half, 8><<<(unsigned)m, 256, 0, st>>>(x_hi, x_lo, x_scale, (const __half *)x, k);
+        }
+        XN_CHECK_CUDA(cudaGetLastError());
+        return XN_OK;
+    }
     XN_DISPATCH_DTYPE(dtype, T,
         split_rows_e4m3_kernel<T><<<(unsigned)m, 256, 0, st>>>(x_hi, x_lo, x_scale, (const T *)x, k));
     XN_CHECK_CUDA(cudaGetLastError());
