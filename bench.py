@@ -300,7 +300,9 @@ def main() -> None:
             "gpu_launches": args.steps * launches_per_step,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "traffic": None, "kernel": "linear_q4_kernel",
+                         "peak_kind": f"of {peak_kind}", "traffic": 28878848,
+                         "traffic_source": "dram__bytes_read+write per launch, ncu capture in profiles/linear_q4_kernel_int4_decode_gemv.md",
+                         "kernel": "linear_q4_kernel",
                          "algorithmic_bytes_per_launch": alg, "us_per_launch": launch_s * 1e6},
             "cpu_baseline": {"value": cpu_gbs, "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": f"{passes} pass(es) of M in {{1,4,16}} over one weight copy, {cpu_dt:.1f} s"},
