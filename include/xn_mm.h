@@ -136,6 +136,44 @@ int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const 
                      size_t m, size_t n, size_t k, int variant, void *workspace,
                      size_t workspace_bytes, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Row operations around the matmuls of a decoder step, with the reference's semantics (f32 math on
+ * widened elements, rounded to the element type where the reference rounds).  Contiguous rows.
+ *   rms_norm   Backend::rms_norm, xn-core/src/cpu_backend.rs:766-784 (cuda-kernels/reduce.cu:139-181)
+ *   softmax    Backend::softmax,  xn-core/src/cpu_backend.rs:742-764 (reduce.cu:185-225)
+ *   silu_mul   Mlp::Gating's silu(x1) * x2 over the two halves of a [rows, 2*hidden] tensor,
+ *              xn-moshi/src/transformer.rs:239-245 (silu: xn-core/src/cpu_backend.rs:216-218)
+ *   add        the residual add (binary Add), xn-moshi/src/batched_transformer.rs:259,266
+ *   kv_append  ScatteredKvCache::append = scatter_set along the context axis of a
+ *              (batch, heads, context, head_dim) cache, xn-core/src/models/kv_cache.rs:352-366;
+ *              src is (batch, heads, 1, head_dim) with a batch stride of src_batch_stride elements
+ *              (a narrow()-ed view of the fused qkv projection), index[b] the context slot of stream b
+ * ------------------------------------------------------------------------------------------ */
+int xn_mm_rms_norm(xn_dtype dtype, void *dst, const void *src, const void *alpha, size_t rows, size_t cols,
+                   float eps, void *stream);
+int xn_mm_softmax(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t cols, void *stream);
+int xn_mm_silu_mul(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t hidden, void *stream);
+int xn_mm_add(xn_dtype dtype, void *dst, const void *a, const void *b, size_t len, void *stream);
+int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_batch_stride, const int64_t *index,
+                    size_t batch, size_t heads, size_t context, size_t head_dim, void *stream);
+
+/* Fusions with no counterpart in the reference (it runs every op as its own kernel):
+ * the norm / the gating write the e4m3 activation pieces (and power-of-two row scale) of the next
+ * fp8 linear directly -- identical to running the plain op and then xn_mm_split_rows_e4m3;
+ * x_lo may be NULL (W8A8), dst_or_null additionally receives the rounded row. */
+int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *dst_or_null, const void *src,
+                              const void *alpha, xn_dtype dtype, size_t rows, size_t cols, float eps, void *stream);
+int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const void *src, xn_dtype dtype,
+                              size_t rows, size_t hidden, void *stream);
+/* Single-token attention in one pass over the cache: replaces q.matmul_t(k) -> scale -> +mask ->
+ * softmax -> matmul(v) (xn-moshi/src/batched_transformer.rs:174-190) for T = 1.  q: (batch, heads,
+ * 128) bf16 with a batch stride of q_batch_stride elements; out: contiguous (batch, heads, 128) bf16;
+ * caches (batch, heads, context, 128) bf16; mask (optional) f32
+ * [batch, context], added to the scaled scores (0 / -inf as IndicesAndMask builds it).  f32 math. */
+int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t q_batch_stride, const void *k_cache_bf16,
+                           const void *v_cache_bf16, const float *mask_or_null, size_t batch, size_t heads,
+                           size_t context, size_t head_dim, float scale, void *stream);
+
 /* Allocation-free form of xn_mm_linear_fp8.  It has no counterpart in the reference.  For hosts
  * that must not (or cannot) allocate device memory at call time -- a serving loop whose device
  * budget belongs to another allocator, a real-time audio callback that cannot afford a

@@ -1,0 +1,142 @@
+"""GPU: the row operations around the matmuls and one reduced-size decoder step against the oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+_T = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
+
+
+def _bits(t):
+    return t.cpu().view(torch.int16).numpy().view(np.uint16) if t.dtype != torch.float32 else t.cpu().numpy()
+
+
+def _dev(dt, arr, cuda):
+    t = torch.from_numpy(np.ascontiguousarray(arr))
+    return (t.view(torch.int16).view(_T[dt]) if dt != 0 else t).to(cuda)
+
+
+@pytest.mark.parametrize("dt", [0, 1, 2])
+def test_row_ops_match_oracle(xn, oracle, cuda, dt):
+    rng = np.random.default_rng(dt)
+    x = oracle.from_f32(dt, rng.standard_normal((7, 384)).astype(np.float32) * 2)
+    a = oracle.from_f32(dt, (1 + 0.1 * rng.standard_normal(384)).astype(np.float32))
+    tol = 1e-5 if dt == 0 else 8e-3  # one element-type ulp of slack for expf / division differences
+    got = oracle.to_f32(dt, _bits(xn.ops.rms_norm(_dev(dt, x, cuda), _dev(dt, a, cuda), 1e-5)).reshape(7, 384))
+    want = oracle.to_f32(dt, oracle.rms_norm(dt, x, a, 1e-5))
+    assert np.max(np.abs(got - want) / (np.abs(want) + 1e-3)) < tol
+    got = oracle.to_f32(dt, _bits(xn.ops.softmax(_dev(dt, x, cuda))).reshape(7, 384))
+    want = oracle.to_f32(dt, oracle.softmax(dt, x))
+    assert np.max(np.abs(got - want)) < tol * max(1e-3, want.max())  + 1e-7
+    got = oracle.to_f32(dt, _bits(xn.ops.silu_mul(_dev(dt, x, cuda))).reshape(7, 192))
+    want = oracle.to_f32(dt, oracle.silu_mul(dt, x))
+    assert np.max(np.abs(got - want) / (np.abs(want) + 1e-3)) < tol
+    y = oracle.from_f32(dt, rng.standard_normal((7, 384)).astype(np.float32))
+    got = oracle.to_f32(dt, _bits(xn.ops.add(_dev(dt, x, cuda), _dev(dt, y, cuda))).reshape(7, 384))
+    assert np.array_equal(got, oracle.to_f32(dt, oracle.from_f32(dt, oracle.to_f32(dt, x) + oracle.to_f32(dt, y))))
+
+
+def test_fused_split_equals_op_then_split(xn, oracle, cuda):
+    """rms_norm_split / silu_mul_split == plain op followed by xn_mm_split_rows_e4m3, bit for bit."""
+    g = torch.Generator(device=cuda).manual_seed(0)
+    lib, chk = xn.lib(), xn._lib.check
+    s = torch.cuda.current_stream().cuda_stream
+    x = (torch.randn(5, 1024, generator=g, device=cuda) * 3).bfloat16()
+    al = (1 + 0.1 * torch.randn(1024, generator=g, device=cuda)).bfloat16()
+    hi, lo = torch.empty(5, 1024, dtype=torch.uint8, device=cuda), torch.empty(5, 1024, dtype=torch.uint8, device=cuda)
+    xs = torch.empty(5, device=cuda)
+    chk(lib.xn_mm_rms_norm_split_e4m3(hi.data_ptr(), lo.data_ptr(), xs.data_ptr(), None, x.data_ptr(), al.data_ptr(), 2, 5,
+                                      1024, 1e-5, s))
+    h2, l2, s2 = xn.split_rows_e4m3(xn.ops.rms_norm(x, al, 1e-5))
+    assert torch.equal(hi, h2) and torch.equal(lo, l2) and torch.equal(xs, s2)
+    hh = torch.randn(5, 2048, generator=g, device=cuda).bfloat16()
+    chk(lib.xn_mm_silu_mul_split_e4m3(hi.data_ptr(), lo.data_ptr(), xs.data_ptr(), hh.data_ptr(), 2, 5, 1024, s))
+    h2, l2, s2 = xn.split_rows_e4m3(xn.ops.silu_mul(hh))
+    assert torch.equal(hi, h2) and torch.equal(lo, l2) and torch.equal(xs, s2)
+
+
+def test_kv_append_is_scatter_set_on_the_context_axis(xn, cuda):
+    g = torch.Generator(device=cuda).manual_seed(1)
+    B, H, ctx, hd = 3, 4, 10, 128
+    cache = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    ref = cache.clone()
+    qkv = torch.randn(B, 3 * H * hd, generator=g, device=cuda).bfloat16()
+    idx = torch.tensor([9, 0, 4], dtype=torch.int64, device=cuda)
+    xn._lib.check(xn.lib().xn_mm_kv_append(2, cache.data_ptr(), qkv.data_ptr() + 2 * H * hd, 3 * H * hd, idx.data_ptr(), B, H,
+                                           ctx, hd, torch.cuda.current_stream().cuda_stream))
+    src = qkv[:, H * hd:2 * H * hd].reshape(B, H, hd)
+    for b in range(B):
+        ref[b, :, int(idx[b])] = src[b]
+    assert torch.equal(cache, ref)
+
+
+@pytest.mark.parametrize("ctx", [1, 33, 300, 3000])
+def test_decode_attention_vs_float64(xn, oracle, cuda, ctx):
+    g = torch.Generator(device=cuda).manual_seed(ctx)
+    B, H, hd = 3, 4, 128
+    q = torch.randn(B, H * hd, generator=g, device=cuda).bfloat16()
+    k = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    v = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    mask = torch.zeros(B, ctx, device=cuda)
+    if ctx > 2:
+        mask[1, ctx // 2:] = float("-inf")  # stream 1 sees only the first half of its context
+    out = torch.empty(B, H * hd, dtype=torch.bfloat16, device=cuda)
+    xn._lib.check(xn.lib().xn_mm_decode_attention(out.data_ptr(), q.data_ptr(), H * hd, k.data_ptr(), v.data_ptr(),
+                                                  mask.data_ptr(), B, H, ctx, hd, 1 / math.sqrt(hd),
+                                                  torch.cuda.current_stream().cuda_stream))
+    sc = torch.einsum("bhd,bhcd->bhc", q.double().view(B, H, hd), k.double()) / math.sqrt(hd) + mask.double()[:, None, :]
+    ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(sc, -1), v.double()).reshape(B, H * hd).cpu().numpy()
+    assert oracle.rel_err(out.float().cpu().numpy(), ref) < 1e-2
+    # and the same through Backend::gemm + softmax, the reference's unfused route
+    scores = xn.matmul_t(q.view(B, H, 1, hd), k)
+    scores = (scores.float() / math.sqrt(hd) + mask[:, None, None, :]).bfloat16()
+    p = xn.ops.softmax(scores)
+    o2 = xn.matmul(p, v).reshape(B, H * hd)
+    # this route rounds scores and probabilities to bf16 between the ops (as the reference does), so
+    # it is judged on its rms error rather than element by element
+    o2 = o2.float().cpu().numpy()
+    assert np.sqrt(np.mean((o2 - ref) ** 2)) < 2e-2 * np.sqrt(np.mean(ref ** 2))
+
+
+def test_decoder_step_reduced_size(xn, oracle, cuda):
+    """2 layers, 4 streams, context 300, full width: the device step against a float64 restatement
+    built from the same quantized weights."""
+    from xn_b200.decoder import DecoderStack
+    st = DecoderStack(2, 4096, 32, 11264, 4, 300, cuda, seed=4)
+    g = torch.Generator(device=cuda).manual_seed(9)
+    x = torch.randn(4, 4096, generator=g, device=cuda).bfloat16()
+    caches = [(l["k"].clone(), l["v"].clone()) for l in st.layers]
+    y = st.step(x).float().cpu().numpy()
+    torch.cuda.synchronize()
+    tab = torch.from_numpy(oracle.e4m3_decode_table()).double().to(cuda)
+
+    def deq(qs):
+        q, s = qs
+        return tab[q.long()] * s.double()[:, None]
+
+    def rms(t):
+        return t / torch.sqrt((t * t).mean(-1, keepdim=True) + 1e-5)
+
+    cur = x.double()
+    for lay, (k0, v0) in zip(st.layers, caches):
+        qkv = rms(cur) @ deq(lay["in_proj"]).T
+        q, kn, vn = qkv[:, :4096], qkv[:, 4096:8192], qkv[:, 8192:]
+        k, v = k0.double(), v0.double()
+        k[:, :, 299] = kn.view(4, 32, 128)
+        v[:, :, 299] = vn.view(4, 32, 128)
+        sc = torch.einsum("bhd,bhcd->bhc", q.view(4, 32, 128), k) / math.sqrt(128)
+        att = torch.einsum("bhc,bhcd->bhd", torch.softmax(sc, -1), v).reshape(4, 4096)
+        mid = cur + att @ deq(lay["out_proj"]).T
+        h = rms(mid) @ deq(lay["linear_in"]).T
+        gate = torch.nn.functional.silu(h[:, :11264]) * h[:, 11264:]
+        cur = mid + gate @ deq(lay["linear_out"]).T
+    ref = cur.cpu().numpy()
+    # The device rounds to bf16 at every op boundary (as the reference does) while this restatement
+    # keeps float64 throughout, so ~20 roundings of 2^-9 accumulate over the two layers: the step is
+    # judged on its rms error and on its largest error relative to the rms of the output.
+    rms = np.sqrt(np.mean(ref ** 2))
+    err_rms, err_max = np.sqrt(np.mean((y - ref) ** 2)) / rms, np.max(np.abs(y - ref)) / rms
+    print("decoder step: rms err", err_rms, "max err / rms", err_max)
+    assert err_rms < 1e-2 and err_max < 6e-2

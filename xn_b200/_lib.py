@@ -40,6 +40,14 @@ SIGNATURES = {
     "xn_mm_linear_fp8_pieces": (_i, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "xn_mm_linear_fp8_workspace_bytes": (_sz, [_sz, _sz]),
     "xn_mm_linear_fp8": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p, _sz, _p]),
+    "xn_mm_rms_norm": (_i, [_i, _p, _p, _p, _sz, _sz, C.c_float, _p]),
+    "xn_mm_softmax": (_i, [_i, _p, _p, _sz, _sz, _p]),
+    "xn_mm_silu_mul": (_i, [_i, _p, _p, _sz, _sz, _p]),
+    "xn_mm_add": (_i, [_i, _p, _p, _p, _sz, _p]),
+    "xn_mm_kv_append": (_i, [_i, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _p]),
+    "xn_mm_rms_norm_split_e4m3": (_i, [_p, _p, _p, _p, _p, _p, _i, _sz, _sz, C.c_float, _p]),
+    "xn_mm_silu_mul_split_e4m3": (_i, [_p, _p, _p, _p, _i, _sz, _sz, _p]),
+    "xn_mm_decode_attention": (_i, [_p, _p, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, C.c_float, _p]),
     "xn_mm_linear_fp8_noalloc_max_elems": (_sz, []),
     "xn_mm_linear_fp8_noalloc": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p]),
 }

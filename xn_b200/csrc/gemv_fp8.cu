@@ -205,15 +205,18 @@ int launch(__nv_bfloat16 *y, const uint8_t *x_hi, const uint8_t *x_lo, const flo
 
 }  // namespace
 
-// y [m,n] bf16 from row-major e4m3 pieces; m <= 16.
+// y [m,n] bf16 from row-major e4m3 pieces; m <= 32.
 int launch_linear_fp8_gemv(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
                            const uint8_t *wq, const float *w_scale, int m, size_t n, int k, cudaStream_t st) {
     __nv_bfloat16 *yy = (__nv_bfloat16 *)y;
     if (m <= 8)
         return x_lo ? launch<1, true>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st)
                     : launch<1, false>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
-    return x_lo ? launch<2, true>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st)
-                : launch<2, false>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
+    if (m <= 16)
+        return x_lo ? launch<2, true>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st)
+                    : launch<2, false>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
+    return x_lo ? launch<4, true>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st)
+                : launch<4, false>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
 }
 
 }  // namespace xn

@@ -1,0 +1,370 @@
+// Row operations a decoder step needs around its matmuls, with the reference's semantics (f32
+// math on widened elements, one rounding to the element type where the reference rounds):
+//   rms_norm   xn-core/src/cpu_backend.rs:766-784 (CUDA: cuda-kernels/reduce.cu:139-181)
+//   softmax    xn-core/src/cpu_backend.rs:742-764 (reduce.cu:185-225)
+//   silu * mul the gating of Mlp::Gating, xn-moshi/src/transformer.rs:239-245 (silu: cpu_backend.rs:216-218)
+//   add        the residual adds, xn-moshi/src/batched_transformer.rs:259,266
+//   kv_append  ScatteredKvCache::append's scatter_set along the context axis,
+//              xn-core/src/models/kv_cache.rs:352-366, xn-core/src/cpu_backend.rs:673-697
+// plus two fusions that have no counterpart in the reference:
+//   *_split_e4m3      the norm / gating writes the fp8 activation pieces of the next linear directly
+//   decode_attention  q.k^T -> scale -> +mask -> softmax -> .v (batched_transformer.rs:174-190) in
+//                     one pass over the (batch, heads, context, head_dim) cache
+// All of them are bandwidth-bound; one CTA per row (or per (stream, head)), 128-bit accesses.
+#include "common.cuh"
+
+namespace xn {
+namespace {
+
+constexpr int NT = 256;
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = (threadIdx.x < nw) ? red[threadIdx.x] : 0.0f;
+    if (w == 0) {
+        r = warp_sum(r);
+        if (lane == 0) red[0] = r;
+    }
+    __syncthreads();
+    r = red[0];
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_max2(float v, float *red) {
+    v = warp_max(v);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = (threadIdx.x < nw) ? red[threadIdx.x] : -INFINITY;
+    if (w == 0) {
+        r = warp_max(r);
+        if (lane == 0) red[0] = r;
+    }
+    __syncthreads();
+    r = red[0];
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float e4m3_f32(uint8_t b) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    return __half2float(__half(h));
+}
+
+// Writes the e4m3 pieces of one row held as f32 values v[i] at columns c(i) (already rounded to
+// bf16): s = power of two with max|v|/s in (224, 448]; hi = e4m3(v/s), lo = e4m3(v/s - hi).
+__device__ __forceinline__ float pow2_scale(float amax) {
+    if (amax == 0.0f || !isfinite(amax)) return 1.0f;
+    int ex;
+    const float f = frexpf(amax, &ex);
+    return ldexpf(1.0f, f <= 0.875f ? ex - 9 : ex - 8);
+}
+
+// y = x / sqrt(mean(x^2) + eps) * alpha, rounded to T.  Optionally also the e4m3 pieces of y.
+template <typename T, bool SPLIT>
+__global__ void __launch_bounds__(NT)
+rms_norm_kernel(T *__restrict__ dst, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo, float *__restrict__ scale,
+                const T *__restrict__ src, const T *__restrict__ alpha, size_t cols, float eps) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const T *x = src + row * cols;
+    float s2 = 0.0f;
+    for (size_t c = threadIdx.x; c < cols; c += NT) {
+        const float v = to_f32(x[c]);
+        s2 += v * v;
+    }
+    s2 = block_sum(s2, red);
+    const float denom = sqrtf(s2 / (float)cols + eps);
+    float amax = 0.0f;
+    for (size_t c = threadIdx.x; c < cols; c += NT) {
+        const T y = from_f32<T>(to_f32(x[c]) / denom * to_f32(alpha[c]));
+        if (dst) dst[row * cols + c] = y;
+        if (SPLIT) amax = fmaxf(amax, fabsf(to_f32(y)));
+    }
+    if (SPLIT) {
+        amax = block_max2(amax, red);
+        const float s = pow2_scale(amax), inv = 1.0f / s;
+        if (threadIdx.x == 0) scale[row] = s;
+        for (size_t c = threadIdx.x; c < cols; c += NT) {
+            const float y = to_f32(from_f32<T>(to_f32(x[c]) / denom * to_f32(alpha[c]))) * inv;
+            const uint8_t h = (uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+            hi[row * cols + c] = h;
+            if (lo) lo[row * cols + c] = (uint8_t)__nv_cvt_float_to_fp8(y - e4m3_f32(h), __NV_SATFINITE, __NV_E4M3);
+        }
+    }
+}
+
+// One warp per row: max-subtract, exp rounded to T, f32 sum of the rounded values, divide.
+template <typename T>
+__global__ void softmax_kernel(T *__restrict__ dst, const T *__restrict__ src, size_t rows, size_t cols) {
+    const size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const T *x = src + row * cols;
+    T *y = dst + row * cols;
+    float mx = -INFINITY;
+    for (size_t c = lane; c < cols; c += 32) mx = fmaxf(mx, to_f32(x[c]));
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (size_t c = lane; c < cols; c += 32) {
+        const T e = from_f32<T>(expf(to_f32(x[c]) - mx));
+        y[c] = e;
+        sum += to_f32(e);
+    }
+    sum = warp_sum(sum);
+    for (size_t c = lane; c < cols; c += 32) y[c] = from_f32<T>(to_f32(y[c]) / sum);
+}
+
+// out[r, c] = T(silu(a)) * b with a = src[r, c], b = src[r, hidden + c]; optionally the e4m3 pieces.
+template <typename T, bool SPLIT>
+__global__ void __launch_bounds__(NT)
+silu_mul_kernel(T *__restrict__ dst, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo, float *__restrict__ scale,
+                const T *__restrict__ src, size_t hidden) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const T *a = src + row * 2 * hidden, *b = a + hidden;
+    auto f = [&](size_t c) {
+        const float av = to_f32(a[c]);
+        const float s = to_f32(from_f32<T>(av / (1.0f + expf(-av))));
+        return from_f32<T>(s * to_f32(b[c]));
+    };
+    float amax = 0.0f;
+    for (size_t c = threadIdx.x; c < hidden; c += NT) {
+        const T y = f(c);
+        if (dst) dst[row * hidden + c] = y;
+        if (SPLIT) amax = fmaxf(amax, fabsf(to_f32(y)));
+    }
+    if (SPLIT) {
+        amax = block_max2(amax, red);
+        const float s = pow2_scale(amax), inv = 1.0f / s;
+        if (threadIdx.x == 0) scale[row] = s;
+        for (size_t c = threadIdx.x; c < hidden; c += NT) {
+            const float y = to_f32(f(c)) * inv;
+            const uint8_t h = (uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+            hi[row * hidden + c] = h;
+            if (lo) lo[row * hidden + c] = (uint8_t)__nv_cvt_float_to_fp8(y - e4m3_f32(h), __NV_SATFINITE, __NV_E4M3);
+        }
+    }
+}
+
+template <typename T>
+__global__ void add_kernel(T *__restrict__ dst, const T *__restrict__ a, const T *__restrict__ b, size_t len) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < len) dst[i] = from_f32<T>(to_f32(a[i]) + to_f32(b[i]));
+}
+
+// cache [batch, heads, context, hd] <- src [batch, heads, 1, hd] at context index idx[batch].
+template <typename T>
+__global__ void kv_append_kernel(T *__restrict__ cache, const T *__restrict__ src, const int64_t *__restrict__ idx,
+                                 size_t heads, size_t context, size_t hd, size_t src_batch_stride, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t d = i % hd, h = (i / hd) % heads, b = i / (hd * heads);
+    const int64_t p = idx[b];
+    if (p < 0 || (size_t)p >= context) return;  // out-of-range index: nothing is written
+    cache[((b * heads + h) * context + (size_t)p) * hd + d] = src[b * src_batch_stride + h * hd + d];
+}
+
+// Fused single-token attention over a (batch, heads, context, 128) bf16 cache.  One CTA of 4 warps per
+// (stream, head); a half-warp owns a key/value row (16 lanes x 16 bytes = 128 bf16), so a warp
+// handles two rows per step; online softmax per half-warp, merged at the end.  f32 throughout.
+constexpr int HD = 128;
+__global__ void __launch_bounds__(128)
+decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ q,
+                        const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
+                        const float *__restrict__ mask, size_t heads, size_t context, size_t q_batch_stride,
+                        float scale) {
+    const size_t bh = blockIdx.x, b = bh / heads;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4, l16 = lane & 15;
+    const int group = warp * 2 + half;  // 8 half-warps stride over the rows
+    float qv[8];
+    {
+        const uint4 t = *reinterpret_cast<const uint4 *>(q + b * q_batch_stride + (bh % heads) * HD + l16 * 8);
+        const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qv[j] = __bfloat162float(e[j]) * scale;
+    }
+    const __nv_bfloat16 *kb = kc + bh * context * HD, *vb = vc + bh * context * HD;
+    const float *mrow = mask ? mask + b * context : nullptr;
+    float m_run = -INFINITY, l_run = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    constexpr int U = 4;
+    for (size_t base = 0; base < context; base += 8 * U) {  // uniform trip count across the CTA
+        const size_t r0 = base + group;
+        uint4 kr[U], vr[U];
+        float s[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t r = r0 + 8 * u;
+            if (r < context) {
+                kr[u] = ldg_stream(kb + r * HD + l16 * 8);
+                vr[u] = ldg_stream(vb + r * HD + l16 * 8);
+            } else {
+                kr[u] = make_uint4(0, 0, 0, 0);
+                vr[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&kr[u]);
+            float d = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d = fmaf(qv[j], __bfloat162float(e[j]), d);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);  // within the half-warp
+            const size_t r = r0 + 8 * u;
+            if (r >= context) d = -INFINITY;
+            else if (mrow) d += mrow[r];
+            s[u] = d;
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int u = 0; u < U; ++u) m_new = fmaxf(m_new, s[u]);
+        if (m_new == -INFINITY) continue;  // everything masked so far
+        const float corr = __expf(m_run - m_new);
+        l_run *= corr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= corr;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float p = __expf(s[u] - m_new);
+            l_run += p;
+            const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&vr[u]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(p, __bfloat162float(e[j]), acc[j]);
+        }
+        m_run = m_new;
+    }
+    // merge the 8 half-warp states
+    __shared__ float sm_m[8], sm_l[8], sm_acc[8][HD];
+    if (l16 == 0) { sm_m[group] = m_run; sm_l[group] = l_run; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm_acc[group][l16 * 8 + j] = acc[j];
+    __syncthreads();
+    if (threadIdx.x < HD) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int gI = 0; gI < 8; ++gI) mx = fmaxf(mx, sm_m[gI]);
+        float l = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int gI = 0; gI < 8; ++gI) {
+            const float w = sm_m[gI] == -INFINITY ? 0.0f : __expf(sm_m[gI] - mx);
+            l += w * sm_l[gI];
+            o += w * sm_acc[gI][threadIdx.x];
+        }
+        out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
+    }
+}
+
+}  // namespace
+}  // namespace xn
+
+using namespace xn;
+
+extern "C" int xn_mm_rms_norm(xn_dtype dtype, void *dst, const void *src, const void *alpha, size_t rows, size_t cols,
+                              float eps, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "rms_norm: unknown dtype %d", (int)dtype);
+    if (rows == 0 || cols == 0) return XN_OK;
+    XN_REQUIRE(dst && src && alpha, "rms_norm: null pointer");
+    XN_REQUIRE(rows <= 0x7fffffffull, "rms_norm: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, false><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                                    (T *)dst, nullptr, nullptr, nullptr, (const T *)src, (const T *)alpha, cols, eps));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *dst_or_null,
+                                         const void *src, const void *alpha, xn_dtype dtype, size_t rows, size_t cols,
+                                         float eps, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "rms_norm_split: unknown dtype %d", (int)dtype);
+    if (rows == 0 || cols == 0) return XN_OK;
+    XN_REQUIRE(x_hi && x_scale && src && alpha, "rms_norm_split: null pointer");
+    XN_REQUIRE(rows <= 0x7fffffffull, "rms_norm_split: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                                    (T *)dst_or_null, x_hi, x_lo, x_scale, (const T *)src, (const T *)alpha, cols, eps));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_softmax(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t cols, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "softmax: unknown dtype %d", (int)dtype);
+    if (rows == 0 || cols == 0) return XN_OK;
+    XN_REQUIRE(dst && src, "softmax: null pointer");
+    const size_t blocks = (rows + 7) / 8;
+    XN_REQUIRE(blocks <= 0x7fffffffull, "softmax: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, softmax_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+                                    (T *)dst, (const T *)src, rows, cols));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_silu_mul(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t hidden, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "silu_mul: unknown dtype %d", (int)dtype);
+    if (rows == 0 || hidden == 0) return XN_OK;
+    XN_REQUIRE(dst && src, "silu_mul: null pointer");
+    XN_REQUIRE(rows <= 0x7fffffffull, "silu_mul: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T, false><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                                    (T *)dst, nullptr, nullptr, nullptr, (const T *)src, hidden));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const void *src,
+                                         xn_dtype dtype, size_t rows, size_t hidden, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "silu_mul_split: unknown dtype %d", (int)dtype);
+    if (rows == 0 || hidden == 0) return XN_OK;
+    XN_REQUIRE(x_hi && x_scale && src, "silu_mul_split: null pointer");
+    XN_REQUIRE(rows <= 0x7fffffffull, "silu_mul_split: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                                    (T *)nullptr, x_hi, x_lo, x_scale, (const T *)src, hidden));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_add(xn_dtype dtype, void *dst, const void *a, const void *b, size_t len, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "add: unknown dtype %d", (int)dtype);
+    if (len == 0) return XN_OK;
+    XN_REQUIRE(dst && a && b, "add: null pointer");
+    const size_t blocks = (len + 255) / 256;
+    XN_REQUIRE(blocks <= 0x7fffffffull, "add: too many elements");
+    XN_DISPATCH_DTYPE(dtype, T, add_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+                                    (T *)dst, (const T *)a, (const T *)b, len));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_batch_stride,
+                               const int64_t *index, size_t batch, size_t heads, size_t context, size_t head_dim,
+                               void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "kv_append: unknown dtype %d", (int)dtype);
+    const size_t total = batch * heads * head_dim;
+    if (total == 0) return XN_OK;
+    XN_REQUIRE(cache && src && index, "kv_append: null pointer");
+    const size_t blocks = (total + 255) / 256;
+    XN_REQUIRE(blocks <= 0x7fffffffull, "kv_append: too many elements");
+    XN_DISPATCH_DTYPE(dtype, T, kv_append_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+                                    (T *)cache, (const T *)src, index, heads, context, head_dim, src_batch_stride, total));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t q_batch_stride,
+                                      const void *k_cache_bf16, const void *v_cache_bf16, const float *mask_or_null,
+                                      size_t batch, size_t heads, size_t context, size_t head_dim, float scale,
+                                      void *stream) {
+    XN_REQUIRE(head_dim == 128, "decode_attention: head_dim %zu is not supported (128 only)", head_dim);
+    if (batch == 0 || heads == 0) return XN_OK;
+    XN_REQUIRE(context > 0, "decode_attention: empty context");
+    XN_REQUIRE(out_bf16 && q_bf16 && k_cache_bf16 && v_cache_bf16, "decode_attention: null pointer");
+    XN_REQUIRE(aligned(q_bf16, 16) && aligned(k_cache_bf16, 16) && aligned(v_cache_bf16, 16) && q_batch_stride % 8 == 0,
+               "decode_attention: q and the caches must be 16-byte aligned (q_batch_stride a multiple of 8)");
+    XN_REQUIRE(batch * heads <= 0x7fffffffull, "decode_attention: too many (stream, head) pairs");
+    decode_attention_kernel<<<(unsigned)(batch * heads), 128, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16 *)out_bf16, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_cache_bf16,
+        (const __nv_bfloat16 *)v_cache_bf16, mask_or_null, heads, context, q_batch_stride, scale);
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}

@@ -218,3 +218,41 @@ class LinearFp8:
         return linear_fp8(x.reshape(-1, x.shape[-1]), self.wq, self.ws, self.variant).reshape(*lead, self.wq.shape[0])
 
     __call__ = forward
+
+
+# ---------------------------------------------------------------------------------------------
+# Row operations of a decoder step (xn_mm_rms_norm & co.): thin wrappers used by decoder.py and tests.
+# ---------------------------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, alpha: torch.Tensor, eps: float) -> torch.Tensor:
+    _require_cuda(x, alpha)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    rows, cols = x.numel() // x.shape[-1], x.shape[-1]
+    check(lib().xn_mm_rms_norm(_dtype_code(x), out.data_ptr(), x.data_ptr(), alpha.data_ptr(), rows, cols, eps, _stream()))
+    return out
+
+
+def softmax(x: torch.Tensor) -> torch.Tensor:
+    _require_cuda(x)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    rows, cols = x.numel() // x.shape[-1], x.shape[-1]
+    check(lib().xn_mm_softmax(_dtype_code(x), out.data_ptr(), x.data_ptr(), rows, cols, _stream()))
+    return out
+
+
+def silu_mul(x: torch.Tensor) -> torch.Tensor:
+    _require_cuda(x)
+    x = x.contiguous()
+    hidden = x.shape[-1] // 2
+    rows = x.numel() // x.shape[-1]
+    out = torch.empty(*x.shape[:-1], hidden, dtype=x.dtype, device=x.device)
+    check(lib().xn_mm_silu_mul(_dtype_code(x), out.data_ptr(), x.data_ptr(), rows, hidden, _stream()))
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    _require_cuda(a, b)
+    out = torch.empty_like(a)
+    check(lib().xn_mm_add(_dtype_code(a), out.data_ptr(), a.contiguous().data_ptr(), b.contiguous().data_ptr(), a.numel(), _stream()))
+    return out
