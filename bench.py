@@ -162,6 +162,42 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def measure_decode(args, dev, world, rank, timed):
+    """Decoder-stack configuration: 32 layers, d_model 4096, 32 heads x 128, gated SiLU FFN hidden 11264,
+    fp8-e4m3 weights (W8A16 form), 32 independent streams per GPU each with a 3000-token bf16 KV cache.
+    One step = one token for every stream, replayed as a CUDA graph.  Streams are sharded over the
+    GPUs with no communication, so the whole-job figure is the sum over ranks."""
+    import torch
+
+    from xn_b200.decoder import DecoderStack
+    streams, ctx = 32, 3000
+    try:
+        st = DecoderStack(32, 4096, 32, 11264, streams, ctx, dev, seed=4 + rank)
+    except torch.cuda.OutOfMemoryError:
+        return {"unavailable": "not enough free device memory for the 57 GB decode working set"}
+    x = torch.randn(streams, 4096, device=dev).bfloat16()
+    st.step(x)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            st.step(x)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    ms = timed(graph.replay, args.decode_steps)
+    per_step = ms / args.decode_steps
+    b = st.bytes_per_step()
+    peak, kind = measured_peak_gbs()
+    return {"ms_per_step": per_step, "steps_per_s_per_gpu": 1e3 / per_step, "streams_per_gpu": streams,
+            "tokens_per_s_all_gpus": world * streams * 1e3 / per_step, "context": ctx,
+            "bytes_per_step_per_gpu": b["total"], "gb_per_s_per_gpu": b["total"] / (per_step * 1e-3) / 1e9,
+            "frac_of_hbm_peak": b["total"] / (per_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}",
+            "launches_per_step": st.launches_per_step(), "variant": "W8A16",
+            "l2": "working set 57 GB per GPU, far larger than L2"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,6 +207,9 @@ def main() -> None:
     ap.add_argument("--replicas", type=int, default=24)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--sweeps", type=int, default=16, help="passes over all replicas and M values per step")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decoder-stack step measurement")
+    ap.add_argument("--decode-steps", type=int, default=8)
+    ap.add_argument("--decode-only", action="store_true", help="measure only the decoder-stack step (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -190,6 +229,35 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    if args.decode_only:
+        d = measure_decode(args, dev, world, rank, timed)
+        if rank == 0:
+            print(json.dumps({"decode_step": d}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- synthetic operands, resident in HBM ----
     g = torch.Generator(device=dev).manual_seed(1 + rank)
@@ -237,27 +305,6 @@ def main() -> None:
                 host_y[m].copy_(outs[m], non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the step's result is on the host
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        barrier()
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
     for _ in range(warmup):
         step()
     sampler = ClockSampler(local)
@@ -271,6 +318,12 @@ def main() -> None:
         step_e2e()
     e2e_steps = max(3, min(args.steps, 20))
     ms_e2e = timed(step_e2e, e2e_steps)
+
+    decode = None
+    if not args.no_decode:
+        del lins, graph
+        torch.cuda.empty_cache()
+        decode = measure_decode(args, dev, world, rank, timed)
 
     wb = weight_bytes()
     total_weight_bytes = world * args.steps * launches_per_step * wb
@@ -298,6 +351,7 @@ def main() -> None:
                     "d2h_bytes_per_step": R * sum(m * N_OUT * 4 for m in MS), "steps": e2e_steps,
                     "ms_per_step": ms_e2e / e2e_steps},
             "gpu_launches": args.steps * launches_per_step,
+            "decode_step": decode,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "traffic": 28878848,

@@ -130,6 +130,16 @@ int xn_mm_split_rows_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const vo
 int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const uint8_t *x_lo,
                             const float *x_scale, const uint8_t *wq, const float *w_scale,
                             size_t m, size_t n, size_t k, void *stream);
+/* Column-parallel prefill (no counterpart in the reference, which has no multi-GPU path): this rank
+ * owns output channels [col_offset, col_offset + n) of an [m, ldy] result and writes its slice into
+ * every one of the num_dst (<= 8) destination buffers -- its own and its peers', mapped into this
+ * process (CUDA IPC / symmetric memory) -- with plain stores from the GEMM epilogue, so the
+ * "all-gather" travels over NVLink tile by tile while the tensor cores work on the next tile.
+ * The caller synchronises the ranks before the result is read. */
+int xn_mm_linear_fp8_pieces_scatter(void *const *y_dsts, size_t num_dst, size_t ldy, size_t col_offset,
+                                    const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
+                                    const uint8_t *wq, const float *w_scale, size_t m, size_t n, size_t k,
+                                    void *stream);
 /* Convenience: split + linear.  workspace must hold xn_mm_linear_fp8_workspace_bytes(m,k). */
 size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k);
 int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,

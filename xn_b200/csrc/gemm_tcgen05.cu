@@ -119,8 +119,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+constexpr int MAX_DST = 8;
 struct GemmArgs {
-    void *y;              // [M, N] output, row stride ldy elements
+    void *y[MAX_DST];     // ndst destinations for the [M, N] result (own buffer and, in the column-parallel
+                          // prefill, the peers' buffers mapped into this process); row stride ldy elements
+    int ndst;
+    int col_offset;       // first output column inside each destination row
     const float *x_scale; // FP8 only: per activation row
     const float *w_scale; // FP8 only: per output channel
     int M, N, K;          // K in elements
@@ -252,15 +256,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                             packed[j] = *reinterpret_cast<uint32_t *>(&h);
                         }
                     }
-                    uint16_t *dst = reinterpret_cast<uint16_t *>(args.y) + (size_t)row * args.ldy + col0;
-                    if (col0 + 32 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    for (int p = 0; p < args.ndst; ++p) {
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)row * args.ldy + args.col_offset + col0;
+                        if (col0 + 32 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            reinterpret_cast<uint4 *>(dst)[j] =
-                                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < args.N; ++j)
-                            dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                            for (int j = 0; j < 4; ++j)
+                                reinterpret_cast<uint4 *>(dst)[j] =
+                                    make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < args.N; ++j)
+                                dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                        }
                     }
                 }
             }
@@ -351,14 +357,30 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
 // y bf16 [m,n] = x_scale[m] * w_scale[n] * (x_hi (+ x_lo)) * wq^T, all operands row-major e4m3.
 int launch_linear_fp8_gemm(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
                            const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
-    GemmArgs a{y, x_scale, w_scale, (int)m, (int)n, (int)k, (int)n};
+    GemmArgs a{};
+    a.y[0] = y; a.ndst = 1; a.col_offset = 0;
+    a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)n;
+    return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
+}
+
+// Column-parallel form: this rank's [m, n] slice is written at column col_offset of every destination
+// (row stride ldy).  Destinations may live on peer GPUs (plain stores over NVLink).
+int launch_linear_fp8_gemm_scatter(void *const *y_dsts, int ndst, size_t ldy, size_t col_offset, const uint8_t *x_hi,
+                                   const uint8_t *x_lo, const float *x_scale, const uint8_t *wq, const float *w_scale,
+                                   size_t m, size_t n, size_t k, cudaStream_t st) {
+    GemmArgs a{};
+    for (int p = 0; p < ndst; ++p) a.y[p] = y_dsts[p];
+    a.ndst = ndst; a.col_offset = (int)col_offset;
+    a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldy;
     return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
 }
 
 // dst [m,n] (row stride ldd) = lhs [m,k] (row stride lda) * rhs [n,k]^T (row stride ldb); dt BF16 or F16.
 int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
                          size_t lda, size_t ldb, size_t ldd, cudaStream_t st) {
-    GemmArgs a{dst, nullptr, nullptr, (int)m, (int)n, (int)k, (int)ldd};
+    GemmArgs a{};
+    a.y[0] = dst; a.ndst = 1; a.col_offset = 0;
+    a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
     return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st)
                          : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st);
 }

@@ -11,6 +11,10 @@ int launch_linear_fp8_gemv(void *y, const uint8_t *x_hi, const uint8_t *x_lo, co
 int launch_linear_fp8_gemm(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
                            const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st);
 
+int launch_linear_fp8_gemm_scatter(void *const *y_dsts, int ndst, size_t ldy, size_t col_offset, const uint8_t *x_hi,
+                                   const uint8_t *x_lo, const float *x_scale, const uint8_t *wq, const float *w_scale,
+                                   size_t m, size_t n, size_t k, cudaStream_t st);
+
 static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 }  // namespace xn
 
@@ -36,6 +40,24 @@ extern "C" int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const 
         if (rc) return rc;
     }
     return XN_OK;
+}
+
+extern "C" int xn_mm_linear_fp8_pieces_scatter(void *const *y_dsts, size_t num_dst, size_t ldy, size_t col_offset,
+                                               const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
+                                               const uint8_t *wq, const float *w_scale, size_t m, size_t n, size_t k,
+                                               void *stream) {
+    XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_scatter: k=%zu must be a positive multiple of 16", k);
+    XN_REQUIRE(num_dst >= 1 && num_dst <= 8, "linear_fp8_scatter: %zu destinations (1..8 supported)", num_dst);
+    XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull && ldy <= 0x7ffffff0ull, "linear_fp8_scatter: dimension too large");
+    XN_REQUIRE(col_offset + n <= ldy, "linear_fp8_scatter: columns [%zu, %zu) do not fit a row of %zu", col_offset,
+               col_offset + n, ldy);
+    if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(y_dsts && x_hi && x_scale && wq && w_scale, "linear_fp8_scatter: null pointer");
+    for (size_t p = 0; p < num_dst; ++p) XN_REQUIRE(y_dsts[p], "linear_fp8_scatter: destination %zu is null", p);
+    XN_REQUIRE(aligned(wq, 16) && aligned(x_hi, 16) && (!x_lo || aligned(x_lo, 16)),
+               "linear_fp8_scatter: weights and activation pieces must be 16-byte aligned");
+    return launch_linear_fp8_gemm_scatter(y_dsts, (int)num_dst, ldy, col_offset, x_hi, x_lo, x_scale, wq, w_scale, m, n, k,
+                                          (cudaStream_t)stream);
 }
 
 extern "C" size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k) {
