@@ -146,6 +146,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char *epi_smem = smem + (size_t)NSTAGE * STAGE_BYTES;  // 4 epilogue slabs of 32 rows x 256 bytes
     __shared__ __align__(8) uint64_t full[NSTAGE], empty[NSTAGE], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_slot;
 
@@ -233,12 +234,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             const int row = m_blk * BM + q * 32 + lane;
             float xs = 1.0f;
             if (F8 && row < args.M) xs = __ldg(args.x_scale + row);
+            // Column groups of GC: the warp's 32 x GC slab goes through shared memory (16-byte chunks
+            // XOR-swizzled by row) so that global stores are whole row segments of GC*2 bytes instead of
+            // 16 bytes per row -- this matters most when the destination is a peer GPU.
+            constexpr int GC = BN < 128 ? BN : 128;     // columns per group
+            constexpr int CPR = GC / 8;                 // 16-byte chunks per slab row
+            constexpr int RPI = 32 / CPR;               // rows written per store instruction
+            unsigned char *slab = epi_smem + (size_t)(warp - 2) * 32 * 256;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-                const int col0 = n_blk * BN + c * 32;
-                if (row < args.M && col0 < args.N) {
+            for (int g0 = 0; g0 < BN; g0 += GC) {
+#pragma unroll 1
+                for (int c = 0; c < GC / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + g0 + c * 32), v);
+                    const int col0 = n_blk * BN + g0 + c * 32;
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -256,19 +265,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                             packed[j] = *reinterpret_cast<uint32_t *>(&h);
                         }
                     }
-                    for (int p = 0; p < args.ndst; ++p) {
-                        uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)row * args.ldy + args.col_offset + col0;
-                        if (col0 + 32 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<uint4 *>(dst)[j] =
-                                    make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                        } else {
-                            for (int j = 0; j < 32 && col0 + j < args.N; ++j)
-                                dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk = (c * 4 + j) ^ (lane & (CPR - 1));
+                        *reinterpret_cast<uint4 *>(slab + lane * (GC * 2) + chunk * 16) =
+                            make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    }
+                }
+                __syncwarp();
+                const int sub = lane / CPR, ch = lane % CPR;  // this lane's row within a store instruction, chunk
+#pragma unroll 1
+                for (int r0 = 0; r0 < 32; r0 += RPI) {
+                    const int r = r0 + sub;
+                    const uint4 val = *reinterpret_cast<const uint4 *>(slab + r * (GC * 2) + ((ch ^ (r & (CPR - 1))) * 16));
+                    const int grow = m_blk * BM + q * 32 + r;
+                    const int gcol = n_blk * BN + g0 + ch * 8;
+                    if (grow < args.M && gcol < args.N) {
+                        for (int p = 0; p < args.ndst; ++p) {
+                            uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)grow * args.ldy + args.col_offset + gcol;
+                            if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                *reinterpret_cast<uint4 *>(dst) = val;
+                            } else {
+                                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                                for (int j = 0; j < 8 && gcol + j < args.N; ++j)
+                                    dst[j] = (uint16_t)(w4[j >> 1] >> ((j & 1) * 16));
+                            }
                         }
                     }
                 }
+                __syncwarp();
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -322,7 +347,7 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
                cudaStream_t st) {
     constexpr int ELEM = KIND == 0 ? 1 : 2;
     constexpr int STAGE_BYTES = NA * BM * BKB + BN * BKB;
-    constexpr int NSTAGE = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+    constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
     CUtensorMap ma0, ma1, mb;
     int rc = make_map(&ma0, a0, ELEM, args.M, args.K, lda, BM);
     if (rc) return rc;
@@ -331,7 +356,7 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     rc = make_map(&mb, b, ELEM, args.N, args.K, ldb, BN);
     if (rc) return rc;
     auto kern = gemm_tcgen05_kernel<KIND, BN, NA, NSTAGE>;
-    const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 1024;
+    const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 4 * 32 * 256 + 1024;
     XN_ENSURE_SMEM(kern, smem);
     const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN);
     const int sms = sm_count();
