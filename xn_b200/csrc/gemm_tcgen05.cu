@@ -309,6 +309,221 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Skinny form for 16 < M <= 128 (weights >> activations, HBM-bound): the operands swap roles.  The
+// 128 TMEM lanes carry 128 output channels (a 16 KB weight tile per 128-byte k stage) and the MMA's N
+// dimension carries the M activation rows (one or two e4m3 pieces of MB rows each), so almost all
+// bytes in flight are weight bytes and a deep ring (up to 8 stages) keeps ~100 KB of them in flight
+// per SM.  D[n, m] is written transposed: lane = output channel, column = activation row.
+// ---------------------------------------------------------------------------------------------
+struct SkinnyArgs {
+    __nv_bfloat16 *y;
+    const float *x_scale, *w_scale;
+    float *partials;     // scratch: [2 * grid][MB][128] f32 partial accumulators of split tiles
+    unsigned *counters;  // scratch: [tiles][4] arrival counts per (tile, lane quarter); zero between launches
+    int M, N, K;
+    int MB;      // MMA N dimension: M rounded up to 16
+    int nstage;
+    int np;      // pieces (1 or 2)
+};
+
+// Work is cut at k-stage granularity ("stream-K"): total = tiles * num_kb stage units, CTA c owns the
+// contiguous unit range [c*total/G, (c+1)*total/G), i.e. a run of segments (tile, kb0..kb1).  A tile
+// that is covered by several CTAs is finished by whichever of them arrives last (per lane quarter):
+// every contributor stores its f32 partial to scratch, and the finisher adds all partials in k order
+// -- a fixed order, so the result does not depend on which CTA happens to be last.
+__device__ __forceinline__ long long unit_begin(int c, int G, long long total) { return (long long)c * total / G; }
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x0,
+                           const __grid_constant__ CUtensorMap map_x1, const SkinnyArgs args) {
+    constexpr int W_BYTES = BM * BKB;
+    const int X_BYTES = args.MB * BKB;
+    const int STAGE_BYTES = W_BYTES + args.np * X_BYTES;
+    const int NSTAGE = args.nstage;
+    const uint32_t IDESC = instr_desc(0, 0, args.MB);
+    const int TMEM_COLS = 2 * args.MB <= 32 ? 32 : (2 * args.MB <= 64 ? 64 : (2 * args.MB <= 128 ? 128 : (2 * args.MB <= 256 ? 256 : 512)));
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full[8], empty[8], tmem_full[2], tmem_empty[2];
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = (args.N + BM - 1) / BM;
+    const int num_kb = (args.K + BKB - 1) / BKB;
+    const int G = gridDim.x;
+    const long long total = (long long)num_tiles * num_kb;
+    const long long u0 = unit_begin(blockIdx.x, G, total), u1 = unit_begin(blockIdx.x + 1, G, total);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (long long u = u0; u < u1 && ok;) {
+                const int tile = (int)(u / num_kb), kb0 = (int)(u % num_kb);
+                const int kb1 = (int)min((long long)num_kb, kb0 + (u1 - u));
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % NSTAGE;
+                    const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(st, &map_w, kb * BKB, tile * BM, &full[s]);
+                    tma_load_2d(st + W_BYTES, &map_x0, kb * BKB, 0, &full[s]);
+                    if (args.np == 2) tma_load_2d(st + W_BYTES + X_BYTES, &map_x1, kb * BKB, 0, &full[s]);
+                }
+                u += kb1 - kb0;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, t_local = 0;
+            bool ok = true;
+            for (long long u = u0; u < u1 && ok; ++t_local) {
+                const int kb0 = (int)(u % num_kb);
+                const int kb1 = (int)min((long long)num_kb, kb0 + (u1 - u));
+                const int acc = t_local & 1;
+                const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * args.MB);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % NSTAGE;
+                    const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
+                    if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    const uint64_t dw = smem_desc(st), dx0 = smem_desc(st + W_BYTES), dx1 = smem_desc(st + W_BYTES + X_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
+                        const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
+                        umma<true>(d_tmem, dw + adv, dx0 + adv, IDESC, (kb > kb0) || ks != 0);
+                        if (args.np == 2) umma<true>(d_tmem, dw + adv, dx1 + adv, IDESC, 1u);
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&tmem_full[acc]);
+                u += kb1 - kb0;
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int t_local = 0;
+        bool ok = true;
+        const size_t slot_elems = (size_t)args.MB * BM;
+        for (long long u = u0; u < u1 && ok; ++t_local) {
+            const int tile = (int)(u / num_kb), kb0 = (int)(u % num_kb);
+            const int kb1 = (int)min((long long)num_kb, kb0 + (u1 - u));
+            const bool whole = kb0 == 0 && kb1 == num_kb;
+            const int acc = t_local & 1;
+            const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
+            if (!mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int ch = tile * BM + q * 32 + lane;  // output channel of this lane
+            const float ws = ch < args.N ? __ldg(args.w_scale + ch) : 0.0f;
+            // a split tile's segment is this CTA's first one iff its range starts inside that tile
+            const int my_slot = 2 * blockIdx.x + ((u == u0) ? 0 : 1);
+            float *mine = args.partials + (size_t)my_slot * slot_elems + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < args.MB; c += 16) {
+                uint32_t v[16];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                    : "r"(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * args.MB + c)));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (whole) {
+                    if (ch < args.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int mrow = c + j;
+                            if (mrow < args.M)  // 32 lanes = 32 consecutive channels of one activation row
+                                args.y[(size_t)mrow * args.N + ch] =
+                                    __float2bfloat16_rn(ws * (__ldg(args.x_scale + mrow) * __uint_as_float(v[j])));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * BM] = __uint_as_float(v[j]);
+                }
+            }
+            // the accumulator buffer can be reused as soon as it has been read
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+
+            if (!whole) {
+                // contributors of this tile: the CTAs whose unit ranges intersect [tile*num_kb, (tile+1)*num_kb)
+                const long long t0 = (long long)tile * num_kb, t1 = t0 + num_kb;
+                int c_first = (int)((t0 * G) / total);
+                while (c_first > 0 && unit_begin(c_first, G, total) > t0) --c_first;
+                while (unit_begin(c_first + 1, G, total) <= t0) ++c_first;
+                int c_last = c_first;
+                while (c_last + 1 < G && unit_begin(c_last + 1, G, total) < t1) ++c_last;
+                const unsigned ncontrib = (unsigned)(c_last - c_first + 1);
+                __threadfence();
+                __syncwarp();
+                unsigned old = 0;
+                if (lane == 0) old = atomicAdd(args.counters + (size_t)tile * 4 + q, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == ncontrib - 1) {  // last arriver of this quarter: reduce in k order and store
+                    __threadfence();
+                    if (lane == 0) args.counters[(size_t)tile * 4 + q] = 0;  // ready for the next launch
+                    if (ch < args.N) {
+                        // 32 activation rows at a time: 32 independent loads in flight per contributor
+                        for (int m0 = 0; m0 < args.M; m0 += 32) {
+                            float sum[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) sum[j] = 0.0f;
+                            for (int cc = c_first; cc <= c_last; ++cc) {
+                                const int slot = 2 * cc + (unit_begin(cc, G, total) >= t0 ? 0 : 1);
+                                const float *src = args.partials + (size_t)slot * slot_elems + (size_t)m0 * BM + q * 32 + lane;
+                                float tv[32];
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) tv[j] = (m0 + j < args.MB) ? __ldcg(src + (size_t)j * BM) : 0.0f;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) sum[j] += tv[j];
+                            }
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (m0 + j < args.M)
+                                    args.y[(size_t)(m0 + j) * args.N + ch] =
+                                        __float2bfloat16_rn(ws * (__ldg(args.x_scale + m0 + j) * sum[j]));
+                        }
+                    }
+                }
+            }
+            u += kb1 - kb0;
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ----
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -379,9 +594,78 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
 
 }  // namespace
 
+// Per-device scratch of the skinny path (partial accumulators + arrival counters).  One buffer per
+// device, grown on demand; calls that use it must be stream-ordered with respect to each other on a
+// device, which is how xn drives a device (one stream per Device, xn-core/src/cuda_backend.rs:52).
+struct SkinnyScratch { float *partials = nullptr; size_t partial_bytes = 0; unsigned *counters = nullptr; size_t ncounters = 0; };
+int skinny_scratch(size_t partial_bytes, size_t ncounters, SkinnyScratch *out) {
+    static SkinnyScratch table[64];
+    static std::mutex mu;
+    int dev = 0;
+    XN_CHECK_CUDA(cudaGetDevice(&dev));
+    XN_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    SkinnyScratch &s = table[dev];
+    if (s.partial_bytes < partial_bytes) {
+        if (s.partials) { XN_CHECK_CUDA(cudaDeviceSynchronize()); XN_CHECK_CUDA(cudaFree(s.partials)); s.partials = nullptr; s.partial_bytes = 0; }
+        XN_CHECK_CUDA(cudaMalloc(&s.partials, partial_bytes));
+        s.partial_bytes = partial_bytes;
+    }
+    if (s.ncounters < ncounters) {
+        if (s.counters) { XN_CHECK_CUDA(cudaDeviceSynchronize()); XN_CHECK_CUDA(cudaFree(s.counters)); s.counters = nullptr; s.ncounters = 0; }
+        XN_CHECK_CUDA(cudaMalloc(&s.counters, ncounters * sizeof(unsigned)));
+        XN_CHECK_CUDA(cudaMemset(s.counters, 0, ncounters * sizeof(unsigned)));
+        XN_CHECK_CUDA(cudaDeviceSynchronize());
+        s.ncounters = ncounters;
+    }
+    *out = s;
+    return XN_OK;
+}
+
+// Skinny path: 16 < m <= 128.
+int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
+                             const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
+    SkinnyArgs a{};
+    a.y = (__nv_bfloat16 *)y; a.x_scale = x_scale; a.w_scale = w_scale;
+    a.M = (int)m; a.N = (int)n; a.K = (int)k;
+    a.MB = (int)((m + 15) / 16 * 16);
+    a.np = x_lo ? 2 : 1;
+    const int stage = BM * BKB + a.np * a.MB * BKB;
+    a.nstage = (196 * 1024) / stage > 8 ? 8 : (196 * 1024) / stage;
+    const int tiles = (int)((n + BM - 1) / BM);
+    const int num_kb = (int)((k + BKB - 1) / BKB);
+    const int sms = sm_count();
+    const long long total = (long long)tiles * num_kb;
+    // at least 4 k stages per CTA, so that a split never degenerates into single-stage crumbs
+    long long grid = total / 4 < 1 ? 1 : total / 4;
+    if (grid > sms) grid = sms;
+    // Whole tiles (no fix-up pass) when they already fill most of the machine; otherwise split at k-stage
+    // granularity so that every SM streams its share of the weights.
+    if (tiles <= sms && tiles * 100 >= sms * 64) grid = tiles;
+    SkinnyScratch sc;
+    int rc = skinny_scratch((size_t)2 * grid * a.MB * BM * sizeof(float), (size_t)tiles * 4, &sc);
+    if (rc) return rc;
+    a.partials = sc.partials;
+    a.counters = sc.counters;
+    CUtensorMap mw, mx0, mx1;
+    rc = make_map(&mw, wq, 1, n, k, k, BM);
+    if (rc) return rc;
+    rc = make_map(&mx0, x_hi, 1, m, k, k, a.MB);
+    if (rc) return rc;
+    rc = make_map(&mx1, x_lo ? x_lo : x_hi, 1, m, k, k, a.MB);
+    if (rc) return rc;
+    const size_t smem = (size_t)a.nstage * stage + 1024;
+    XN_ENSURE_SMEM(gemm_tcgen05_skinny_kernel, smem);
+    gemm_tcgen05_skinny_kernel<<<(unsigned)grid, NTHREADS, smem, st>>>(mw, mx0, mx1, a);
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
 // y bf16 [m,n] = x_scale[m] * w_scale[n] * (x_hi (+ x_lo)) * wq^T, all operands row-major e4m3.
 int launch_linear_fp8_gemm(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
                            const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
+    static const size_t skinny_max = [] { const char *e = getenv("XN_FP8_SKINNY_MAX_M"); return e ? (size_t)atoi(e) : (size_t)64; }();
+    if (m <= skinny_max) return launch_linear_fp8_skinny(y, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
     GemmArgs a{};
     a.y[0] = y; a.ndst = 1; a.col_offset = 0;
     a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)n;

@@ -16,7 +16,7 @@
 namespace xn {
 namespace {
 
-constexpr int NT = 256;
+constexpr int NT = 1024;  // one CTA per row: decode has few rows, so each gets a full SM
 
 __device__ __forceinline__ float block_sum(float v, float *red) {
     v = warp_sum(v);

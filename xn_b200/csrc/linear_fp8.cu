@@ -32,7 +32,8 @@ extern "C" int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const 
     cudaStream_t st = (cudaStream_t)stream;
     // Decode-sized batches stream the weights once through the GEMV kernel; anything larger goes to
     // the tensor-memory GEMM (which pads the last row tile).
-    if (m > 32) return launch_linear_fp8_gemm(y_bf16, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
+    static const size_t gemv_max_m = [] { const char *e = getenv("XN_FP8_GEMV_MAX_M"); return e ? (size_t)atoi(e) : (size_t)16; }();
+    if (m > gemv_max_m) return launch_linear_fp8_gemm(y_bf16, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
     for (size_t i0 = 0; i0 < m; i0 += 32) {
         const int mc = (int)((m - i0) < 32 ? (m - i0) : 32);
         int rc = launch_linear_fp8_gemv((char *)y_bf16 + i0 * n * 2, x_hi + i0 * k, x_lo ? x_lo + i0 * k : nullptr,
