@@ -158,3 +158,21 @@ def test_dense_16bit_views_with_row_pitch(xn, oracle, cuda):
     y = xn.matmul_t(x, w)
     ref = (x.double() @ w.double().T).cpu().numpy()
     assert oracle.rel_err(y.float().cpu().numpy(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("dt", [1, 2])
+def test_strided_batched_16bit_one_launch(xn, oracle, cuda, dt):
+    """lhs_b > 1 with per-batch rhs on the tensor-core path: contiguous batches and the transposed
+    (grouped per-codebook) view, plus a ragged second stage shape of the grouped configuration."""
+    g = torch.Generator(device=cuda).manual_seed(11)
+    a = torch.randn(5, 40, 64, generator=g, device=cuda).to(_TORCH[dt])
+    b = (torch.randn(5, 24, 64, generator=g, device=cuda) * 0.1).to(_TORCH[dt])
+    y = xn.matmul_t(a, b)
+    ref = torch.einsum("gmk,gnk->gmn", a.double(), b.double()).cpu().numpy()
+    assert oracle.rel_err(y.float().cpu().numpy(), ref) < TOL[dt]
+    x = torch.randn(64, 16, 1024, generator=g, device=cuda).to(_TORCH[dt])   # [B, G, K]
+    w = (torch.randn(16, 4096, 1024, generator=g, device=cuda) * 0.03).to(_TORCH[dt])  # gated-FFN up
+    y = xn.matmul_t(x.transpose(0, 1), w)
+    ref = torch.einsum("bgk,gnk->gbn", x.double(), w.double()).cpu().numpy()
+    assert y.shape == (16, 64, 4096)
+    assert oracle.rel_err(y.float().cpu().numpy(), ref) < TOL[dt]

@@ -84,12 +84,25 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                "gemm: unsupported dst strides (%zu, %zu) for m:%zu n:%zu", dst_cs, dst_rs, m, n);
     const char *l = static_cast<const char *>(lhs) + lhs_off * es;
     const char *r = static_cast<const char *>(rhs) + rhs_off * es;
+    // Decode-sized matmul_t (m <= 16, both operands k-contiguous): the weight-streaming kernel with exact f32
+    // products, for all three element types and any batch count.
+    {
+        const size_t v = 16 / es;
+        if (m <= 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % v == 0 && lhs_rs % v == 0 && rhs_cs % v == 0 &&
+            (lhs_b == 1 || (lhs_b_stride % v == 0 && rhs_b_stride % v == 0)) && aligned(l, 16) && aligned(r, 16))
+            return launch_gemv_dense(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_rs, lhs_rs, rhs_cs,
+                                     (cudaStream_t)stream);
+    }
     // Linear::forward's form with 16-bit elements -- both operands k-contiguous, rows of dst
     // contiguous -- goes to the tcgen05 kernel when TMA can address it (16-byte pitches and bases).
-    if (dtype != XN_F32 && lhs_b == 1 && m > 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
+    // The strided-batched / grouped form (lhs_b > 1 with per-batch weights) is one launch as well.
+    if (dtype != XN_F32 && m > 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
         lhs_rs % 8 == 0 && rhs_cs % 8 == 0 && aligned(l, 16) && aligned(r, 16) && m <= 0x7fffffff &&
-        n <= 0x7fffffff && k <= 0x7fffffff && dst_rs <= 0x7fffffff)
-        return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, (cudaStream_t)stream);
+        n <= 0x7fffffff && k <= 0x7fffffff && dst_rs <= 0x7fffffff &&
+        (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 && rhs_b_stride != 0 &&
+                        lhs_b_stride != 0)))
+        return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
+                                    (cudaStream_t)stream);
     return launch_gemm_generic(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
                                lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
 }

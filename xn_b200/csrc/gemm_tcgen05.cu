@@ -62,6 +62,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity) {
     return false;
 }
 
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -129,6 +136,9 @@ struct GemmArgs {
     const float *w_scale; // FP8 only: per output channel
     int M, N, K;          // K in elements
     int ldy;
+    int batch;            // strided-batched / grouped form: `batch` independent problems in one launch
+    long long y_batch_stride;  // elements between consecutive outputs (m * n in Backend::gemm)
+    int a_batch_inner, b_batch_inner;  // the tensor map's dimension order is (k, batch, rows) instead of (k, rows, batch)
 };
 
 // KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16
@@ -152,7 +162,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_m = (args.M + BM - 1) / BM, num_n = (args.N + BN - 1) / BN;
-    const int num_tiles = num_m * num_n;
+    const int tiles_per_batch = num_m * num_n;
+    const int num_tiles = tiles_per_batch * args.batch;
     const int num_kb = (args.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -178,16 +189,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             int it = 0;  // running k-block count across tiles: stage = it % NSTAGE
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m_blk = tile % num_m, n_blk = tile / num_m;
+                const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
+                const int m_blk = tin % num_m, n_blk = tin / num_m;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(st, &map_a0, kb * BK, m_blk * BM, &full[s]);
-                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_a1, kb * BK, m_blk * BM, &full[s]);
-                    tma_load_2d(st + NA * A_BYTES, &map_b, kb * BK, n_blk * BN, &full[s]);
+                    const int ay = args.a_batch_inner ? g : m_blk * BM, az = args.a_batch_inner ? m_blk * BM : g;
+                    const int by = args.b_batch_inner ? g : n_blk * BN, bz = args.b_batch_inner ? n_blk * BN : g;
+                    tma_load_3d(st, &map_a0, kb * BK, ay, az, &full[s]);
+                    if (NA == 2) tma_load_3d(st + A_BYTES, &map_a1, kb * BK, ay, az, &full[s]);
+                    tma_load_3d(st + NA * A_BYTES, &map_b, kb * BK, by, bz, &full[s]);
                 }
             }
         }
@@ -226,7 +240,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         int t_local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
-            const int m_blk = tile % num_m, n_blk = tile / num_m;
+            const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
+            const int m_blk = tin % num_m, n_blk = tin / num_m;
             const int acc = t_local & 1;
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
             if (!mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
@@ -282,7 +297,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     const int gcol = n_blk * BN + g0 + ch * 8;
                     if (grow < args.M && gcol < args.N) {
                         for (int p = 0; p < args.ndst; ++p) {
-                            uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)grow * args.ldy + args.col_offset + gcol;
+                            uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
+                                            (size_t)grow * args.ldy + args.col_offset + gcol;
                             if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                                 *reinterpret_cast<uint4 *>(dst) = val;
                             } else {
@@ -543,6 +559,28 @@ EncodeTiledFn encode_fn() {
 
 // 2-D row-major [rows, k] tensor with `elem` bytes per element and a row pitch of ld elements;
 // box = 128 bytes of k by box_rows rows, 128-byte swizzle, out-of-range reads give zeros.
+// 3-D form of the same map: `batch` matrices `batch_stride` elements apart (box covers one of them).
+// Dimensions are ordered by increasing stride: when the batch stride is smaller than the row pitch (a
+// transposed view such as [groups, rows, k] over storage [rows, groups, k]) the map is (k, batch, rows) and
+// *batch_inner is set; the shared-memory image of a box is the same either way.
+int make_map3(CUtensorMap *map, const void *base, int elem, size_t rows, size_t k, size_t ld, int box_rows,
+              size_t batch, size_t batch_stride, int *batch_inner) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if (batch <= 1) { batch = 1; batch_stride = rows * ld; }
+    const bool inner = batch_stride < ld;
+    *batch_inner = inner ? 1 : 0;
+    cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)(inner ? batch : rows), (cuuint64_t)(inner ? rows : batch)};
+    cuuint64_t strides[2] = {(cuuint64_t)(inner ? batch_stride : ld) * elem, (cuuint64_t)(inner ? ld : batch_stride) * elem};
+    cuuint32_t box[3] = {(cuuint32_t)(BKB / elem), (cuuint32_t)(inner ? 1 : box_rows), (cuuint32_t)(inner ? box_rows : 1)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMapDataType dt = elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    CUresult r = fn(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with code %d", (int)r);
+    return XN_OK;
+}
+
 int make_map(CUtensorMap *map, const void *base, int elem, size_t rows, size_t k, size_t ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -557,39 +595,42 @@ int make_map(CUtensorMap *map, const void *base, int elem, size_t rows, size_t k
     return XN_OK;
 }
 
+struct BatchGeom { size_t batch = 1, a_stride = 0, b_stride = 0; };
+
 template <int KIND, int BN, int NA>
 int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
-               cudaStream_t st) {
+               cudaStream_t st, const BatchGeom &bg = BatchGeom()) {
     constexpr int ELEM = KIND == 0 ? 1 : 2;
     constexpr int STAGE_BYTES = NA * BM * BKB + BN * BKB;
     constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
     CUtensorMap ma0, ma1, mb;
-    int rc = make_map(&ma0, a0, ELEM, args.M, args.K, lda, BM);
+    GemmArgs args2 = args;
+    int rc = make_map3(&ma0, a0, ELEM, args.M, args.K, lda, BM, bg.batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
-    rc = make_map(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM);
+    rc = make_map3(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM, bg.batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
-    rc = make_map(&mb, b, ELEM, args.N, args.K, ldb, BN);
+    rc = make_map3(&mb, b, ELEM, args.N, args.K, ldb, BN, bg.batch, bg.b_stride, &args2.b_batch_inner);
     if (rc) return rc;
     auto kern = gemm_tcgen05_kernel<KIND, BN, NA, NSTAGE>;
     const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 4 * 32 * 256 + 1024;
     XN_ENSURE_SMEM(kern, smem);
-    const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN);
+    const long long tiles = (long long)((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) * args.batch;
     const int sms = sm_count();
-    const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, NTHREADS, smem, st>>>(ma0, ma1, mb, args);
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    kern<<<grid, NTHREADS, smem, st>>>(ma0, ma1, mb, args2);
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
 
 template <int KIND, int NA>
 int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
-                cudaStream_t st) {
+                cudaStream_t st, const BatchGeom &bg = BatchGeom()) {
     // Wide tiles when there are enough of them to fill the machine, narrower ones otherwise.
     const int sms = sm_count();
-    const long m_tiles = (args.M + BM - 1) / BM;
-    if (m_tiles * ((args.N + 255) / 256) >= sms) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st);
-    if (m_tiles * ((args.N + 127) / 128) >= sms) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st);
-    return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st);
+    const long long m_tiles = (long long)((args.M + BM - 1) / BM) * args.batch;
+    if (m_tiles * ((args.N + 255) / 256) >= sms) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    if (m_tiles * ((args.N + 127) / 128) >= sms) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
 }
 
 }  // namespace
@@ -667,7 +708,7 @@ int launch_linear_fp8_gemm(void *y, const uint8_t *x_hi, const uint8_t *x_lo, co
     static const size_t skinny_max = [] { const char *e = getenv("XN_FP8_SKINNY_MAX_M"); return e ? (size_t)atoi(e) : (size_t)64; }();
     if (m <= skinny_max) return launch_linear_fp8_skinny(y, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
     GemmArgs a{};
-    a.y[0] = y; a.ndst = 1; a.col_offset = 0;
+    a.y[0] = y; a.ndst = 1; a.col_offset = 0; a.batch = 1; a.y_batch_stride = 0;
     a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)n;
     return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
 }
@@ -679,19 +720,22 @@ int launch_linear_fp8_gemm_scatter(void *const *y_dsts, int ndst, size_t ldy, si
                                    size_t m, size_t n, size_t k, cudaStream_t st) {
     GemmArgs a{};
     for (int p = 0; p < ndst; ++p) a.y[p] = y_dsts[p];
-    a.ndst = ndst; a.col_offset = (int)col_offset;
+    a.ndst = ndst; a.col_offset = (int)col_offset; a.batch = 1; a.y_batch_stride = 0;
     a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldy;
     return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
 }
 
-// dst [m,n] (row stride ldd) = lhs [m,k] (row stride lda) * rhs [n,k]^T (row stride ldb); dt BF16 or F16.
+// dst [b][m,n] (row stride ldd, batch stride m*n) = lhs [b][m,k] (row stride lda, batch stride lhs_bs) *
+// rhs [b][n,k]^T (row stride ldb, batch stride rhs_bs); dt BF16 or F16; one launch for all batches.
 int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
-                         size_t lda, size_t ldb, size_t ldd, cudaStream_t st) {
+                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st) {
     GemmArgs a{};
-    a.y[0] = dst; a.ndst = 1; a.col_offset = 0;
+    a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
-    return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st)
-                         : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st);
+    BatchGeom bg;
+    bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;
+    return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
+                         : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
 }
 
 }  // namespace xn
