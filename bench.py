@@ -335,9 +335,12 @@ def main() -> None:
         launch_s = ms * 1e-3 / (args.steps * launches_per_step)
         alg = sum(algorithmic_bytes(m) for m in MS) / len(MS)
         achieved = alg / launch_s / 1e9
-        port = CpuPort()
-        cpu_gbs, passes, cpu_dt = port.throughput(args.cpu_seconds)
-        threads = port.threads
+        cpu_baseline = None
+        if world == 1:  # the CPU leg runs at N = 1 only (torchrun pins OMP to one thread per rank)
+            port = CpuPort()
+            cpu_gbs, passes, cpu_dt = port.throughput(args.cpu_seconds)
+            cpu_baseline = {"value": cpu_gbs, "unit": UNIT, "cores": port.threads, "kind": "port",
+                            "sample": f"{passes} pass(es) of M in {{1,4,16}} over one weight copy, {cpu_dt:.1f} s"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -358,8 +361,7 @@ def main() -> None:
                          "traffic_source": "dram__bytes_read+write per launch, ncu capture in profiles/linear_q4_kernel_int4_decode_gemv.md",
                          "kernel": "linear_q4_kernel",
                          "algorithmic_bytes_per_launch": alg, "us_per_launch": launch_s * 1e6},
-            "cpu_baseline": {"value": cpu_gbs, "unit": UNIT, "cores": threads, "kind": "port",
-                             "sample": f"{passes} pass(es) of M in {{1,4,16}} over one weight copy, {cpu_dt:.1f} s"},
+            "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
