@@ -106,3 +106,23 @@ def test_q4_host_packing_matches_oracle_layout(xn, oracle):
     bad = q.copy()
     bad[0, 0] = 9
     assert lib.xn_mm_pack_q4_host(packed.ctypes.data, bad.ctypes.data, sc.ctypes.data, n, k) == 1
+
+
+def test_row_op_and_scatter_validation_on_the_host(xn):
+    lib = xn.lib()
+    assert lib.xn_mm_rms_norm(9, 1, 1, 1, 4, 4, 1e-5, None) == 1
+    assert lib.xn_mm_rms_norm(0, None, None, None, 4, 4, 1e-5, None) == 1
+    assert lib.xn_mm_rms_norm(0, None, None, None, 0, 4, 1e-5, None) == 0
+    assert lib.xn_mm_softmax(2, None, None, 3, 0, None) == 0
+    assert lib.xn_mm_silu_mul(2, None, None, 3, 8, None) == 1
+    assert lib.xn_mm_add(1, None, None, None, 0, None) == 0
+    assert lib.xn_mm_kv_append(2, None, None, 0, None, 0, 4, 8, 128, None) == 0
+    assert lib.xn_mm_decode_attention(1, 1, 0, 1, 1, None, 2, 4, 16, 64, 0.1, None) == 1
+    assert b"head_dim" in lib.xn_mm_last_error()
+    assert lib.xn_mm_decode_attention(None, None, 0, None, None, None, 0, 4, 16, 128, 0.1, None) == 0
+    import ctypes as C
+    ptrs = (C.c_void_p * 2)(1, 2)
+    assert lib.xn_mm_linear_fp8_pieces_scatter(ptrs, 9, 64, 0, 1, 1, 1, 1, 1, 64, 32, 128, None) == 1
+    assert lib.xn_mm_linear_fp8_pieces_scatter(ptrs, 2, 40, 16, 1, 1, 1, 1, 1, 64, 32, 128, None) == 1
+    assert b"do not fit" in lib.xn_mm_last_error()
+    assert lib.xn_mm_linear_fp8_noalloc(None, None, None, None, 65, 16, 128, 0, None) == 2

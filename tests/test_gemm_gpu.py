@@ -176,3 +176,34 @@ def test_strided_batched_16bit_one_launch(xn, oracle, cuda, dt):
     ref = torch.einsum("bgk,gnk->gbn", x.double(), w.double()).cpu().numpy()
     assert y.shape == (16, 64, 4096)
     assert oracle.rel_err(y.float().cpu().numpy(), ref) < TOL[dt]
+
+
+def test_gemm_is_reentrant_from_many_host_threads(xn, oracle, cuda):
+    """The reference's Backend is Send + Sync and its examples/cuda_thread_test.rs hammers one device
+    from 32 threads; the entry points must give the same answers under that load."""
+    import threading
+    g = torch.Generator(device=cuda).manual_seed(21)
+    a = torch.randn(24, 96, generator=g, device=cuda)
+    b = torch.randn(40, 96, generator=g, device=cuda)
+    ref = (a.double() @ b.double().T).cpu().numpy()
+    errs = []
+
+    def work(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(10):
+                    y = xn.matmul_t(a, b)
+                st.synchronize()
+            if oracle.rel_err(y.cpu().numpy(), ref) >= 1e-4:
+                errs.append((i, "mismatch"))
+        except Exception as e:  # noqa: BLE001
+            errs.append((i, repr(e)))
+
+    torch.cuda.synchronize()
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(32)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs

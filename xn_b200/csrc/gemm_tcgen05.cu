@@ -627,9 +627,15 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
                 cudaStream_t st, const BatchGeom &bg = BatchGeom()) {
     // Wide tiles when there are enough of them to fill the machine, narrower ones otherwise.
     const int sms = sm_count();
+    static const int force_bn = [] { const char *e = getenv("XN_GEMM_BN"); return e ? atoi(e) : 0; }();
+    if (force_bn == 256) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    if (force_bn == 128) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    if (force_bn == 64) return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
     const long long m_tiles = (long long)((args.M + BM - 1) / BM) * args.batch;
-    if (m_tiles * ((args.N + 255) / 256) >= sms) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
-    if (m_tiles * ((args.N + 127) / 128) >= sms) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    // (measured on the transformer shapes: the widest tile that still gives ~0.55 tiles per SM wins, because
+    // every extra column tile re-reads the activation tile from L2)
+    if (m_tiles * ((args.N + 255) / 256) * 100 >= sms * 55) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    if (m_tiles * ((args.N + 127) / 128) * 100 >= sms * 55) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
     return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
 }
 

@@ -79,12 +79,12 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     extern __shared__ __align__(128) unsigned char smem[];
     const int nblk = k / 32, nsb = k / 128;
     const int nwarps = blockDim.x >> 5;
-    // [rings: nwarps * depth slots of upc units][B fragments: nblk * 32 * MT uint2][red: nwarps * MT*4*32 f32][mbarriers]
+    // [rings: nwarps * depth slots of upc units, reused as red: nwarps * MT*4*32 f32][B fragments: nblk * 32 * MT uint2][mbarriers]
     unsigned char *rings = smem;
     const int slot_bytes = upc * UNIT_BYTES;
     uint2 *sB = reinterpret_cast<uint2 *>(smem + (size_t)nwarps * depth * slot_bytes);
-    float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(sB) + (size_t)nblk * 32 * MT * sizeof(uint2));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(red + (size_t)nwarps * MT * 4 * 32);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(sB) + (size_t)nblk * 32 * MT * sizeof(uint2));
+    float *red = reinterpret_cast<float *>(rings);  // the rings are dead once every warp has left its unit loop
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -210,9 +210,18 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
             const unsigned a0 = (wa[j] << 4) & 0xF0F0F0F0u, a2 = wa[j] & 0xF0F0F0F0u;
             const unsigned a1 = (wb[j] << 4) & 0xF0F0F0F0u, a3 = wb[j] & 0xF0F0F0F0u;
             const int kb = (sb0 + i) * 4 + j;
+            // both column groups' fragments sit side by side: one 128-bit shared-memory read for MT = 2
+            uint2 bfrag[MT];
+            if (MT == 2) {
+                const uint4 t4 = *reinterpret_cast<const uint4 *>(sB + ((size_t)kb * 32 + lane) * 2);
+                bfrag[0] = make_uint2(t4.x, t4.y);
+                bfrag[MT - 1] = make_uint2(t4.z, t4.w);
+            } else {
+                bfrag[0] = sB[(size_t)kb * 32 + lane];
+            }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                const uint2 bb = sB[((size_t)kb * 32 + lane) * MT + mt];
+                const uint2 bb = bfrag[mt];
                 int d[4];
                 mma_s8(d, a0, a1, a2, a3, bb.x, bb.y);
                 acc[mt][0] = fmaf(__int_as_float(d[0]) - MAGIC_F, sc[j].x, acc[mt][0]);
@@ -244,6 +253,7 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
 
     // Fixed-order reduction over the ksplit warps of a tile.
     if (ksplit > 1) {
+        __syncthreads();  // all unit loops are over: the ring area becomes the reduction buffer
         if (ks > 0) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
@@ -279,21 +289,24 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     const int nsb = k / 128;
     const int sms = sm_count();
     int tpc = (tiles + sms - 1) / sms;
-    if (tpc > MAX_WARPS) tpc = MAX_WARPS;  // very tall weights: more CTAs than SMs
-    int ksplit = MAX_WARPS / tpc;
+    static const int maxw = [] { const char *e = getenv("XN_Q4_MAXW"); int v = e ? atoi(e) : MAX_WARPS; return v < 1 ? 1 : (v > MAX_WARPS ? MAX_WARPS : v); }();
+    static const size_t smem_cap = [] { const char *e = getenv("XN_Q4_SMEM_KB"); return (size_t)(e ? atoi(e) : 227) * 1024; }();
+    if (tpc > maxw) tpc = maxw;  // very tall weights: more CTAs than SMs
+    int ksplit = maxw / tpc;
     if (ksplit > nsb) ksplit = nsb;
     const int warps = tpc * ksplit;
     const int grid = (tiles + tpc - 1) / tpc;
-    const size_t fixed = (size_t)(k / 32) * 32 * MT * sizeof(uint2) + (size_t)warps * MT * 4 * 32 * sizeof(float) +
-                         (size_t)warps * 8 * sizeof(uint64_t);
-    if (fixed + (size_t)warps * UNIT_BYTES > 227 * 1024)
+    const size_t fixed = (size_t)(k / 32) * 32 * MT * sizeof(uint2) + (size_t)warps * 8 * sizeof(uint64_t);
+    if (fixed + (size_t)warps * UNIT_BYTES > 227 * 1024)  // hard limit of the part
         return fail(XN_ERR_UNSUPPORTED, "linear_q4: k=%d needs more than 232448 bytes of shared memory", k);
     const int per_warp = (nsb + ksplit - 1) / ksplit;
     static const int upc_env = [] { const char *e = getenv("XN_Q4_UPC"); return e ? atoi(e) : 0; }();
     int upc = upc_env > 0 ? upc_env : 2;  // units per bulk copy
     if (upc > per_warp) upc = per_warp;
-    while (upc > 1 && fixed + (size_t)warps * 2 * upc * UNIT_BYTES > 227 * 1024) --upc;
-    int depth = (int)((227 * 1024 - fixed) / ((size_t)warps * upc * UNIT_BYTES));
+    const size_t cap = smem_cap > fixed + (size_t)warps * UNIT_BYTES ? smem_cap : fixed + (size_t)warps * UNIT_BYTES;
+    while (upc > 1 && fixed + (size_t)warps * 2 * upc * UNIT_BYTES > cap) --upc;
+    int depth = (int)((cap - fixed) / ((size_t)warps * upc * UNIT_BYTES));
+    if (depth < 1) depth = 1;
     if (depth > (per_warp + upc - 1) / upc) depth = (per_warp + upc - 1) / upc;
     if (depth > 8) depth = 8;
     const size_t smem = fixed + (size_t)warps * depth * upc * UNIT_BYTES;
