@@ -112,6 +112,19 @@ int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype d
 int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
                     size_t n, size_t k, int32_t *partials, void *stream);
 
+/* int8 block-quantized weights: the same scheme with scale = max|w|/127 and one byte per weight.
+ * "q8 tiles": tile (r/16, kk/128) is 2304 bytes, ordered [r/16][kk/128]; bytes 0..2047 = for each
+ * 32-block j (512 bytes) and each lane 4*g + t (16 bytes) the four MMA A-operand words
+ * {row g, k 4t..4t+3}, {row g+8, k 4t..}, {row g, k 16+4t..}, {row g+8, k 16+4t..}; bytes
+ * 2048..2303 = 64 f32 scales laid out as in the q4 tiles. */
+size_t xn_mm_q8_packed_bytes(size_t n, size_t k);
+int xn_mm_quantize_weights_q8(void *wq_packed, const void *w, xn_dtype dtype, size_t n, size_t k,
+                              void *stream);
+int xn_mm_pack_q8_host(uint8_t *wq_packed, const int8_t *q, const float *scales, size_t n, size_t k);
+int xn_mm_unpack_q8_host(int8_t *q, float *scales, const uint8_t *wq_packed, size_t n, size_t k);
+int xn_mm_linear_q8(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
+                    size_t n, size_t k, int32_t *partials, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * fp8-e4m3 weights with one f32 scale per output channel.  No counterpart in the reference.
  *   scale[j] = max_p |w[j,p]| / 448 ; wq = e4m3_rn_satfinite(w / scale)   (row-major [n,k] bytes)

@@ -184,6 +184,13 @@ def pack_q4(q: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return out
 
 
+def pack_q8(q: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    n, k = q.shape
+    out = np.zeros((n + 15) // 16 * (k // 128) * 2304, dtype=np.uint8)
+    lib().xo_pack_q8(_p(np.ascontiguousarray(q)), _p(np.ascontiguousarray(scales, dtype=np.float32)), *_sz(n, k), _p(out))
+    return out
+
+
 def unpack_q4(packed: np.ndarray, n: int, k: int):
     q = np.zeros((n, k), dtype=np.int8)
     s = np.zeros((n, k // 32), dtype=np.float32)

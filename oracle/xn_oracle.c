@@ -289,6 +289,26 @@ void xo_unpack_q4(const uint8_t *packed, size_t n, size_t k, int8_t *q, float *s
     }
 }
 
+/* int8 block tiles ("q8 tiles"): tile (r/16, kk/128) = 2304 bytes; for 32-block j and lane 4*g + t the 16
+ * bytes at j*512 + (4*g+t)*16 are the words {row g, k 4t..}, {row g+8, k 4t..}, {row g, k 16+4t..},
+ * {row g+8, k 16+4t..}; scales at +2048 as in the q4 tiles. */
+static size_t q8_pos(size_t r, size_t kk, size_t k) {
+    size_t tile = (r / 16) * (k / 128) + kk / 128;
+    size_t rr = r % 16, h = rr / 8, g = rr % 8, j = (kk % 128) / 32, e = kk % 32;
+    size_t t = (e % 16) / 4, i = e % 4, hi = e / 16;
+    return tile * 2304 + j * 512 + (4 * g + t) * 16 + (h + 2 * hi) * 4 + i;
+}
+void xo_pack_q8(const int8_t *q, const float *scales, size_t n, size_t k, uint8_t *packed) {
+    memset(packed, 0, ((n + 15) / 16) * (k / 128) * 2304);
+    for (size_t r = 0; r < n; ++r) {
+        for (size_t kk = 0; kk < k; ++kk) packed[q8_pos(r, kk, k)] = (uint8_t)q[r * k + kk];
+        for (size_t b = 0; b < k / 32; ++b) {
+            size_t tile = (r / 16) * (k / 128) + b / 4;
+            memcpy(packed + tile * 2304 + 2048 + 4 * ((4 * (r % 8) + b % 4) * 2 + (r % 16) / 8), &scales[r * (k / 32) + b], 4);
+        }
+    }
+}
+
 /* Quantized linear: P[i,j,blk] = sum over the block of xq*wq as int32,
  * y[i,j] = x_scale[i] * sum_blk (float)P * w_scale[j,blk]  (f32, blocks in order).
  * partials may be NULL. wq is the logical (one value per int8) form. */

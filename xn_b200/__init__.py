@@ -10,5 +10,5 @@ lib()  # fail loudly at import time when the CUDA library has not been built
 
 from . import ops  # noqa: E402
 from .ops import (Linear, LinearFp8, LinearQ4, gemm, linear_fp8, linear_q4, matmul, matmul_, matmul_plan,  # noqa: E402
-                  matmul_t, matmul_with_t, quantize_rows_i8, quantize_weights_fp8, quantize_weights_q4,
+                  matmul_t, matmul_with_t, quantize_rows_i8, quantize_weights_fp8, quantize_weights_q4, quantize_weights_q8, linear_q8,
                   split_rows_e4m3)

@@ -35,6 +35,11 @@ SIGNATURES = {
     "xn_mm_unpack_q4_host": (_i, [_p, _p, _p, _sz, _sz]),
     "xn_mm_quantize_rows_i8": (_i, [_p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_linear_q4": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p, _p]),
+    "xn_mm_q8_packed_bytes": (_sz, [_sz, _sz]),
+    "xn_mm_quantize_weights_q8": (_i, [_p, _p, _i, _sz, _sz, _p]),
+    "xn_mm_pack_q8_host": (_i, [_p, _p, _p, _sz, _sz]),
+    "xn_mm_unpack_q8_host": (_i, [_p, _p, _p, _sz, _sz]),
+    "xn_mm_linear_q8": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p, _p]),
     "xn_mm_quantize_weights_fp8": (_i, [_p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_split_rows_e4m3": (_i, [_p, _p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_linear_fp8_pieces": (_i, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),

@@ -190,3 +190,40 @@ extern "C" int xn_mm_unpack_q4_host(int8_t *q, float *scales, const uint8_t *pac
     }
     return XN_OK;
 }
+
+// ---- host-side q8 tile packing ----
+static inline size_t q8_byte_index(size_t r, size_t kk, size_t k) {
+    const size_t tile = (r / 16) * (k / 128) + kk / 128;
+    const size_t rr = r % 16, h = rr / 8, g = rr % 8, j = (kk % 128) / 32, e = kk % 32;
+    const size_t t = (e % 16) / 4, i = e % 4, hi = e / 16;
+    return tile * 2304 + j * 512 + (4 * g + t) * 16 + (h + 2 * hi) * 4 + i;
+}
+static inline size_t q8_scale_offset(size_t r, size_t blk, size_t k) {
+    const size_t tile = (r / 16) * (k / 128) + blk / 4;
+    return tile * 2304 + 2048 + ((4 * (r % 8) + blk % 4) * 2 + (r % 16) / 8) * 4;
+}
+
+extern "C" int xn_mm_pack_q8_host(uint8_t *packed, const int8_t *q, const float *scales, size_t n, size_t k) {
+    XN_REQUIRE(k % 128 == 0, "pack_q8: k=%zu must be a multiple of 128", k);
+    if (n == 0 || k == 0) return XN_OK;
+    XN_REQUIRE(packed && q && scales, "pack_q8: null pointer");
+    memset(packed, 0, xn_mm_q8_packed_bytes(n, k));
+    for (size_t r = 0; r < n; ++r) {
+        for (size_t kk = 0; kk < k; ++kk) packed[q8_byte_index(r, kk, k)] = (uint8_t)q[r * k + kk];
+        for (size_t blk = 0; blk < k / 32; ++blk)
+            memcpy(packed + q8_scale_offset(r, blk, k), &scales[r * (k / 32) + blk], 4);
+    }
+    return XN_OK;
+}
+
+extern "C" int xn_mm_unpack_q8_host(int8_t *q, float *scales, const uint8_t *packed, size_t n, size_t k) {
+    XN_REQUIRE(k % 128 == 0, "unpack_q8: k=%zu must be a multiple of 128", k);
+    if (n == 0 || k == 0) return XN_OK;
+    XN_REQUIRE(packed && q && scales, "unpack_q8: null pointer");
+    for (size_t r = 0; r < n; ++r) {
+        for (size_t kk = 0; kk < k; ++kk) q[r * k + kk] = (int8_t)packed[q8_byte_index(r, kk, k)];
+        for (size_t blk = 0; blk < k / 32; ++blk)
+            memcpy(&scales[r * (k / 32) + blk], packed + q8_scale_offset(r, blk, k), 4);
+    }
+    return XN_OK;
+}

@@ -28,7 +28,7 @@ namespace xn {
 namespace {
 
 constexpr int MAX_WARPS = 20;
-constexpr int UNIT_BYTES = 1024 + 256;
+template <int BITS> struct Tile { static constexpr int W = BITS == 4 ? 1024 : 2048, UNIT = W + 256; };  // bytes
 constexpr int MAGIC_I = 0x4B400000;
 constexpr float MAGIC_F = 12582912.0f;
 constexpr unsigned WAIT_LIMIT = 1u << 24;  // polls of one mbarrier before the warp gives up
@@ -71,11 +71,12 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], unsigned a0, unsigned a1, un
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(MAGIC_I));
 }
 
-template <int MT, bool DUMP>
+template <int MT, bool DUMP, int BITS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
 linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const float *__restrict__ x_scale,
                  const unsigned char *__restrict__ wq, int m, size_t n, int k, int tiles, int tpc, int ksplit,
                  int depth, int upc, int32_t *__restrict__ partials) {
+    constexpr int UNIT_BYTES = Tile<BITS>::UNIT, W_BYTES = Tile<BITS>::W;
     extern __shared__ __align__(128) unsigned char smem[];
     const int nblk = k / 32, nsb = k / 128;
     const int nwarps = blockDim.x >> 5;
@@ -193,22 +194,33 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
             break;
         }
         const unsigned char *u = ring + (size_t)slot * slot_bytes + (size_t)(i % upc) * UNIT_BYTES;
-        const uint4 w0 = *reinterpret_cast<const uint4 *>(u + lane * 16);        // row g:   four 32-blocks
-        const uint4 w1 = *reinterpret_cast<const uint4 *>(u + 512 + lane * 16);  // row g+8
-        float2 sc[4];                                                            // {scale[g][j], scale[g+8][j]}
+        uint4 wv[4];  // int4: wv[0] = row g, wv[1] = row g+8 (four 32-blocks each); int8: wv[j] = block j's {a0,a1,a2,a3}
+        if (BITS == 4) {
+            wv[0] = *reinterpret_cast<const uint4 *>(u + lane * 16);
+            wv[1] = *reinterpret_cast<const uint4 *>(u + 512 + lane * 16);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) sc[j] = *reinterpret_cast<const float2 *>(u + 1024 + (4 * g + j) * 8);
+            for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const uint4 *>(u + j * 512 + lane * 16);
+        }
+        float2 sc[4];  // {scale[g][j], scale[g+8][j]}
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sc[j] = *reinterpret_cast<const float2 *>(u + W_BYTES + (4 * g + j) * 8);
         if (i % upc == upc - 1 || i == nu - 1) {
             __syncwarp();  // every lane holds its part of the slot: it can be refilled
             if (lane == 0 && c + depth < nchunk) issue(c + depth);
         }
 
-        const unsigned wa[4] = {w0.x, w0.y, w0.z, w0.w};
-        const unsigned wb[4] = {w1.x, w1.y, w1.z, w1.w};
+        const unsigned wa[4] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w};
+        const unsigned wb[4] = {wv[1].x, wv[1].y, wv[1].z, wv[1].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const unsigned a0 = (wa[j] << 4) & 0xF0F0F0F0u, a2 = wa[j] & 0xF0F0F0F0u;
-            const unsigned a1 = (wb[j] << 4) & 0xF0F0F0F0u, a3 = wb[j] & 0xF0F0F0F0u;
+            unsigned a0, a1, a2, a3;
+            if (BITS == 4) {
+                a0 = (wa[j] << 4) & 0xF0F0F0F0u; a2 = wa[j] & 0xF0F0F0F0u;
+                a1 = (wb[j] << 4) & 0xF0F0F0F0u; a3 = wb[j] & 0xF0F0F0F0u;
+            } else {
+                a0 = wv[j].x; a1 = wv[j].y; a2 = wv[j].z; a3 = wv[j].w;
+            }
             const int kb = (sb0 + i) * 4 + j;
             // both column groups' fragments sit side by side: one 128-bit shared-memory read for MT = 2
             uint2 bfrag[MT];
@@ -235,7 +247,7 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
                         const size_t row_n = (size_t)tile * 16 + g + 8 * (e >> 1);
                         const int row_m = 8 * mt + 2 * t + (e & 1);
                         if (row_n < n && row_m < m)
-                            partials[((size_t)row_m * n + row_n) * nblk + kb] = (d[e] - MAGIC_I) >> 4;
+                            partials[((size_t)row_m * n + row_n) * nblk + kb] = (d[e] - MAGIC_I) >> (BITS == 4 ? 4 : 0);
                     }
                 }
             }
@@ -277,14 +289,15 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
             for (int e = 0; e < 4; ++e) {
                 const size_t row_n = (size_t)tile * 16 + g + 8 * (e >> 1);
                 const int row_m = 8 * mt + 2 * t + (e & 1);
-                if (row_n < n && row_m < m) y[(size_t)row_m * n + row_n] = xs_reg[mt][e & 1] * (acc[mt][e] * 0.0625f);
+                if (row_n < n && row_m < m) y[(size_t)row_m * n + row_n] = xs_reg[mt][e & 1] * (acc[mt][e] * (BITS == 4 ? 0.0625f : 1.0f));
             }
     }
 }
 
-template <int MT, bool DUMP>
+template <int MT, bool DUMP, int BITS>
 int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int m, size_t n, int k,
            int32_t *partials, cudaStream_t st) {
+    constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
     const int tiles = (int)((n + 15) / 16);
     const int nsb = k / 128;
     const int sms = sm_count();
@@ -310,7 +323,7 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     if (depth > (per_warp + upc - 1) / upc) depth = (per_warp + upc - 1) / upc;
     if (depth > 8) depth = 8;
     const size_t smem = fixed + (size_t)warps * depth * upc * UNIT_BYTES;
-    auto kern = linear_q4_kernel<MT, DUMP>;
+    auto kern = linear_q4_kernel<MT, DUMP, BITS>;
     XN_ENSURE_SMEM(kern, smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
@@ -332,26 +345,37 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
 
 using namespace xn;
 
-extern "C" int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed,
-                               size_t m, size_t n, size_t k, int32_t *partials, void *stream) {
-    XN_REQUIRE(k > 0 && k % 128 == 0, "linear_q4: k=%zu must be a positive multiple of 128", k);
-    XN_REQUIRE(k <= 0x7fffffffull && n <= 0x7ffffff0ull, "linear_q4: dimension too large");
+template <int BITS>
+static int linear_q(const char *name, float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
+                    size_t n, size_t k, int32_t *partials, void *stream) {
+    XN_REQUIRE(k > 0 && k % 128 == 0, "%s: k=%zu must be a positive multiple of 128", name, k);
+    XN_REQUIRE(k <= 0x7fffffffull && n <= 0x7ffffff0ull, "%s: dimension too large", name);
     if (m == 0 || n == 0) return XN_OK;
-    XN_REQUIRE(y && xq && x_scale && wq_packed, "linear_q4: null pointer");
-    XN_REQUIRE(aligned(wq_packed, 16), "linear_q4: packed weights must be 16-byte aligned");
-    XN_REQUIRE(aligned(xq, 16), "linear_q4: xq must be 16-byte aligned");
+    XN_REQUIRE(y && xq && x_scale && wq_packed, "%s: null pointer", name);
+    XN_REQUIRE(aligned(wq_packed, 16), "%s: packed weights must be 16-byte aligned", name);
+    XN_REQUIRE(aligned(xq, 16), "%s: xq must be 16-byte aligned", name);
     cudaStream_t st = (cudaStream_t)stream;
     for (size_t i0 = 0; i0 < m; i0 += 16) {
         const int mc = (int)((m - i0) < 16 ? (m - i0) : 16);
         int32_t *pp = partials ? partials + i0 * n * (k / 32) : nullptr;
         int rc;
         if (mc <= 8)
-            rc = pp ? launch<1, true>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st)
-                    : launch<1, false>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st);
+            rc = pp ? launch<1, true, BITS>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st)
+                    : launch<1, false, BITS>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st);
         else
-            rc = pp ? launch<2, true>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st)
-                    : launch<2, false>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st);
+            rc = pp ? launch<2, true, BITS>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st)
+                    : launch<2, false, BITS>(y + i0 * n, xq + i0 * k, x_scale + i0, wq_packed, mc, n, (int)k, pp, st);
         if (rc) return rc;
     }
     return XN_OK;
+}
+
+extern "C" int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
+                               size_t n, size_t k, int32_t *partials, void *stream) {
+    return linear_q<4>("linear_q4", y, xq, x_scale, wq_packed, m, n, k, partials, stream);
+}
+
+extern "C" int xn_mm_linear_q8(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
+                               size_t n, size_t k, int32_t *partials, void *stream) {
+    return linear_q<8>("linear_q8", y, xq, x_scale, wq_packed, m, n, k, partials, stream);
 }

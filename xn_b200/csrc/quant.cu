@@ -77,6 +77,28 @@ __global__ void quantize_weights_q4_kernel(uint8_t *__restrict__ packed, const T
     if (e == 0) reinterpret_cast<float *>(packed + tile * 1280 + 1024)[(4 * g + j) * 2 + h] = scale;
 }
 
+// int8 block tiles ("q8 tiles", include/xn_mm.h): one warp per (row, 32-block), lane e owns element e.
+template <typename T>
+__global__ void quantize_weights_q8_kernel(uint8_t *__restrict__ packed, const T *__restrict__ w, size_t n,
+                                           size_t n_pad, size_t k) {
+    const size_t nblk = k / 32;
+    const size_t warp = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (warp >= n_pad * nblk) return;
+    const int e = threadIdx.x & 31;
+    const size_t r = warp / nblk, blk = warp % nblk;
+    float v = (r < n) ? to_f32(w[r * k + blk * 32 + e]) : 0.0f;
+    float amax = warp_max(fabsf(v));
+    float scale = __fdiv_rn(amax, 127.0f);
+    float qf = 0.0f;
+    if (scale != 0.0f) qf = rintf(__fdiv_rn(v, scale));
+    qf = fminf(fmaxf(qf, -127.0f), 127.0f);
+    const size_t tile = (r / 16) * (k / 128) + blk / 4;
+    const size_t rr = r % 16, h = rr / 8, g = rr % 8, j = blk % 4;
+    const size_t t = (e % 16) / 4, i = e % 4, hi = e / 16;
+    packed[tile * 2304 + j * 512 + (4 * g + t) * 16 + (h + 2 * hi) * 4 + i] = (uint8_t)(int8_t)qf;
+    if (e == 0) reinterpret_cast<float *>(packed + tile * 2304 + 2048)[(4 * g + j) * 2 + h] = scale;
+}
+
 // One CTA per output channel.  scale = max|w| / 448, q = e4m3(w / scale).
 template <typename T>
 __global__ void quantize_weights_fp8_kernel(uint8_t *__restrict__ wq, float *__restrict__ w_scale,
@@ -210,6 +232,26 @@ extern "C" int xn_mm_quantize_weights_q4(void *wq_packed, const void *w, xn_dtyp
     XN_DISPATCH_DTYPE(dtype, T,
         quantize_weights_q4_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
             (uint8_t *)wq_packed, (const T *)w, n, n_pad, k));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" size_t xn_mm_q8_packed_bytes(size_t n, size_t k) { return ((n + 15) / 16) * (k / 128) * 2304; }
+
+extern "C" int xn_mm_quantize_weights_q8(void *wq_packed, const void *w, xn_dtype dtype, size_t n, size_t k,
+                                         void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "quantize_weights_q8: unknown dtype %d", (int)dtype);
+    XN_REQUIRE(k % 128 == 0 && k > 0, "quantize_weights_q8: k=%zu must be a positive multiple of 128", k);
+    if (n == 0) return XN_OK;
+    XN_REQUIRE(wq_packed && w, "quantize_weights_q8: null pointer");
+    XN_REQUIRE(aligned(wq_packed, 16), "quantize_weights_q8: packed buffer must be 16-byte aligned");
+    size_t n_pad = (n + 15) / 16 * 16;
+    size_t warps = n_pad * (k / 32);
+    size_t blocks = (warps + 7) / 8;
+    XN_REQUIRE(blocks <= 0x7fffffffull, "quantize_weights_q8: matrix too large");
+    cudaStream_t st = (cudaStream_t)stream;
+    XN_DISPATCH_DTYPE(dtype, T,
+        quantize_weights_q8_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((uint8_t *)wq_packed, (const T *)w, n, n_pad, k));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }

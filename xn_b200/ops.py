@@ -144,6 +144,26 @@ def linear_q4(xq: torch.Tensor, x_scale: torch.Tensor, wq_packed: torch.Tensor, 
     return y
 
 
+def quantize_weights_q8(w: torch.Tensor) -> torch.Tensor:
+    """W [n,k] -> q8 tiles (int8 block-quantized, scale = max|w|/127 per 32-block)."""
+    _require_cuda(w)
+    w = w.contiguous()
+    n, k = w.shape
+    packed = torch.empty(lib().xn_mm_q8_packed_bytes(n, k), dtype=torch.uint8, device=w.device)
+    check(lib().xn_mm_quantize_weights_q8(packed.data_ptr(), w.data_ptr(), _dtype_code(w), n, k, _stream()))
+    return packed
+
+
+def linear_q8(xq: torch.Tensor, x_scale: torch.Tensor, wq_packed: torch.Tensor, n: int,
+              partials: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(xq, wq_packed)
+    m, k = xq.shape
+    y = out if out is not None else torch.empty(m, n, dtype=torch.float32, device=xq.device)
+    check(lib().xn_mm_linear_q8(y.data_ptr(), xq.data_ptr(), x_scale.data_ptr(), wq_packed.data_ptr(), m, n, k,
+                                partials.data_ptr() if partials is not None else None, _stream()))
+    return y
+
+
 class LinearQ4:
     """int4 block-quantized linear: forward(x) quantizes x per row to int8, returns f32."""
 
