@@ -140,3 +140,20 @@ def test_decoder_step_reduced_size(xn, oracle, cuda):
     err_rms, err_max = np.sqrt(np.mean((y - ref) ** 2)) / rms, np.max(np.abs(y - ref)) / rms
     print("decoder step: rms err", err_rms, "max err / rms", err_max)
     assert err_rms < 1e-2 and err_max < 6e-2
+
+
+def test_decode_attention_full_width_slice(xn, oracle, cuda):
+    """8 streams x 32 heads x 3000 tokens (393 MB of K/V): the per-GPU decode shape at a quarter of the
+    streams, against float64 on the device."""
+    g = torch.Generator(device=cuda).manual_seed(77)
+    B, H, ctx, hd = 8, 32, 3000, 128
+    qkv = torch.randn(B, 3 * H * hd, generator=g, device=cuda).bfloat16()
+    k = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    v = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    out = torch.empty(B, H * hd, dtype=torch.bfloat16, device=cuda)
+    xn._lib.check(xn.lib().xn_mm_decode_attention(out.data_ptr(), qkv.data_ptr(), 3 * H * hd, k.data_ptr(), v.data_ptr(), None,
+                                                  B, H, ctx, hd, 1 / math.sqrt(hd), torch.cuda.current_stream().cuda_stream))
+    q = qkv[:, : H * hd].double().view(B, H, hd)
+    sc = torch.einsum("bhd,bhcd->bhc", q, k.double()) / math.sqrt(hd)
+    ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(sc, -1), v.double()).reshape(B, H * hd).cpu().numpy()
+    assert oracle.rel_err(out.float().cpu().numpy(), ref) < 1e-2
