@@ -71,20 +71,95 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], unsigned a0, unsigned a1, un
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(MAGIC_I));
 }
 
+__device__ __forceinline__ unsigned long long pack_f2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// (int bits read as float) - 1.5 * 2^23 for two accumulator elements in one packed instruction
+__device__ __forceinline__ void unmagic2(int d0, int d1, float &f0, float &f1) {
+    unsigned long long v, r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(d0), "r"(d1));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(v), "l"(pack_f2(-MAGIC_F, -MAGIC_F)));
+    unpack_f2(r, f0, f1);
+}
+
+// One unit (16 weight rows x 128 k, at u in shared memory) against the activation words of its four
+// 32-blocks: b[mt][2j] = {x[8mt+g][32j+4t..+3]}, b[mt][2j+1] = {x[8mt+g][32j+16+4t..+3]} of the unit's k range.
+// acc[mt][e]: e = 0,1 -> weight row g, activation rows 8mt+2t, +1; e = 2,3 -> weight row g+8.
+template <int MT, bool DUMP, int BITS>
+__device__ __forceinline__ void unit_mma(const unsigned char *u, const unsigned (&b)[MT][8], float (&acc)[MT][4], int lane,
+                                         int tile, int kb0, int m, size_t n, int nblk, int32_t *__restrict__ partials) {
+    constexpr int W_BYTES = Tile<BITS>::W;
+    const int g = lane >> 2, t = lane & 3;
+    uint4 wv[4];  // int4: wv[0] = row g, wv[1] = row g+8 (four blocks each); int8: wv[j] = block j's {a0,a1,a2,a3}
+    if (BITS == 4) {
+        wv[0] = *reinterpret_cast<const uint4 *>(u + lane * 16);
+        wv[1] = *reinterpret_cast<const uint4 *>(u + 512 + lane * 16);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const uint4 *>(u + j * 512 + lane * 16);
+    }
+    // {scale[g][j], scale[g+8][j]} for j = 0..3: 32 contiguous bytes
+    const float4 s01 = *reinterpret_cast<const float4 *>(u + W_BYTES + g * 32);
+    const float4 s23 = *reinterpret_cast<const float4 *>(u + W_BYTES + g * 32 + 16);
+    const float sx[4] = {s01.x, s01.z, s23.x, s23.z}, sy[4] = {s01.y, s01.w, s23.y, s23.w};
+    const unsigned wa[4] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w};
+    const unsigned wb[4] = {wv[1].x, wv[1].y, wv[1].z, wv[1].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        unsigned a0, a1, a2, a3;
+        if (BITS == 4) {
+            a0 = (wa[j] << 4) & 0xF0F0F0F0u; a2 = wa[j] & 0xF0F0F0F0u;
+            a1 = (wb[j] << 4) & 0xF0F0F0F0u; a3 = wb[j] & 0xF0F0F0F0u;
+        } else {
+            a0 = wv[j].x; a1 = wv[j].y; a2 = wv[j].z; a3 = wv[j].w;
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            int d[4];
+            mma_s8(d, a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
+            float f0, f1, f2, f3;
+            unmagic2(d[0], d[1], f0, f1);
+            unmagic2(d[2], d[3], f2, f3);
+            acc[mt][0] = fmaf(f0, sx[j], acc[mt][0]);
+            acc[mt][1] = fmaf(f1, sx[j], acc[mt][1]);
+            acc[mt][2] = fmaf(f2, sy[j], acc[mt][2]);
+            acc[mt][3] = fmaf(f3, sy[j], acc[mt][3]);
+            if (DUMP) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const size_t row_n = (size_t)tile * 16 + g + 8 * (e >> 1);
+                    const int row_m = 8 * mt + 2 * t + (e & 1);
+                    if (row_n < n && row_m < m)
+                        partials[((size_t)row_m * n + row_n) * nblk + kb0 + j] = (d[e] - MAGIC_I) >> (BITS == 4 ? 4 : 0);
+                }
+            }
+        }
+    }
+}
+
 template <int MT, bool DUMP, int BITS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
 linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const float *__restrict__ x_scale,
                  const unsigned char *__restrict__ wq, int m, size_t n, int k, int tiles, int tpc, int ksplit,
-                 int depth, int upc, int32_t *__restrict__ partials) {
-    constexpr int UNIT_BYTES = Tile<BITS>::UNIT, W_BYTES = Tile<BITS>::W;
+                 int depth, int32_t *__restrict__ partials) {
+    constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
+    constexpr int UPC = 2;  // units per bulk copy and ring slot
     extern __shared__ __align__(128) unsigned char smem[];
     const int nblk = k / 32, nsb = k / 128;
     const int nwarps = blockDim.x >> 5;
-    // [rings: nwarps * depth slots of upc units, reused as red: nwarps * MT*4*32 f32][B fragments: nblk * 32 * MT uint2][mbarriers]
+    // [rings: nwarps * depth slots of UPC units, reused as red: nwarps * MT*4*32 f32]
+    // [activations: 8*MT rows of k int8 at a pitch of k+16 bytes][mbarriers: nwarps * depth, then one for the activations]
     unsigned char *rings = smem;
-    const int slot_bytes = upc * UNIT_BYTES;
-    uint2 *sB = reinterpret_cast<uint2 *>(smem + (size_t)nwarps * depth * slot_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(sB) + (size_t)nblk * 32 * MT * sizeof(uint2));
+    constexpr int slot_bytes = UPC * UNIT_BYTES;
+    unsigned char *sX = smem + (size_t)nwarps * depth * slot_bytes;
+    const int pitch = k + 16;  // rows 16 bytes apart modulo 128: the 8 rows of an ldmatrix tile hit distinct banks
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sX + (size_t)8 * MT * pitch);
+    uint64_t *xbar = bars + (size_t)nwarps * depth;
     float *red = reinterpret_cast<float *>(rings);  // the rings are dead once every warp has left its unit loop
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -98,33 +173,33 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     unsigned char *ring = rings + (size_t)warp * depth * slot_bytes;
     uint64_t *bar = bars + (size_t)warp * depth;
     const unsigned char *wsrc = wq + ((size_t)tile * nsb + sb0) * UNIT_BYTES;
-    const int nchunk = (nu + upc - 1) / upc;
-    auto issue = [&](int c) {  // lane 0 only: fetch chunk c (upc consecutive units) into slot c % depth
-        const int slot = c % depth;
-        const unsigned bytes = (unsigned)min(upc, nu - c * upc) * UNIT_BYTES;
+    const int nchunk = (nu + UPC - 1) / UPC;
+    auto issue = [&](int c, int slot) {  // lane 0 only: fetch chunk c (UPC consecutive units) into its slot (c % depth)
+        const unsigned bytes = (unsigned)min(UPC, nu - c * UPC) * UNIT_BYTES;
         mbar_expect_tx(&bar[slot], bytes);
         bulk_load(ring + (size_t)slot * slot_bytes, wsrc + (size_t)c * slot_bytes, bytes, &bar[slot]);
     };
     if (lane == 0) {
         for (int s = 0; s < depth; ++s) mbar_init(&bar[s], 1);
+        if (warp == 0) mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (nchunk > 0) issue(0);
+        if (nchunk > 0) issue(0, 0);
     }
-    __syncwarp();
+    __syncthreads();  // the activation barrier is initialised before any warp can wait on it
 
     // Everything above read only the weights; the activations may come from the previous kernel.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // Activation loads go out next, ahead of the bulk of the weight traffic, so that they are not
-    // queued behind ~150 KB of copies per SM; rows >= m read as zero.
-    // One work item = one (row group g, 32-block): 2*MT 128-bit loads (rows g and, for MT = 2,
-    // g + 8), then 32*MT contiguous bytes of fragments: entry (kb, lane = 4*g + t, mt) =
-    // {xq[8mt+g][32kb+4t..], xq[8mt+g][32kb+16+4t..]}.
-    constexpr int STAGE_ITEMS = 2;  // items per thread and pass
-    const int items = nblk * 8;
-    float xs_reg[MT][2];            // x_scale of the activation rows this lane stores at the end
+    // The activations come in as one bulk copy per row, row-major; rows >= m stay unwritten: their
+    // columns of the product are computed from whatever the shared memory holds and never stored.
+    if (tid == 0) {
+        const int rows = min(m, 8 * MT);
+        mbar_expect_tx(xbar, (unsigned)rows * (unsigned)k);
+        for (int r = 0; r < rows; ++r) bulk_load(sX + (size_t)r * pitch, xq + (size_t)r * k, (unsigned)k, xbar);
+    }
+    float xs_reg[MT][2];  // x_scale of the activation rows this lane stores at the end
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -132,125 +207,57 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
             const int row_m = 8 * mt + 2 * t + e;
             xs_reg[mt][e] = row_m < m ? __ldg(x_scale + row_m) : 0.0f;
         }
-    for (int base = 0; base < items; base += STAGE_ITEMS * (int)blockDim.x) {
-        uint4 lo[STAGE_ITEMS][MT], hi[STAGE_ITEMS][MT];
-#pragma unroll
-        for (int q = 0; q < STAGE_ITEMS; ++q) {
-            const int idx = base + q * (int)blockDim.x + tid;
-            const int gg = idx & 7, kb = idx >> 3;
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                lo[q][mt] = make_uint4(0u, 0u, 0u, 0u);
-                hi[q][mt] = lo[q][mt];
-                const int row = 8 * mt + gg;
-                if (idx < items && row < m) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)row * k + 32 * kb);
-                    lo[q][mt] = __ldg(src);
-                    hi[q][mt] = __ldg(src + 1);
-                }
-            }
-        }
-        if (base == 0 && lane == 0) {
-            for (int c = 1; c < depth && c < nchunk; ++c) issue(c);  // the rest of the first ring-full
-            // What does not fit in the ring yet is pulled into L2 now, so that the refills of the
-            // ring are L2 hits instead of a second round trip to HBM.
-            if (nchunk > depth) {
-                const unsigned rest = (unsigned)(nu - depth * upc) * UNIT_BYTES;
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wsrc + (size_t)depth * slot_bytes), "r"(rest)
-                             : "memory");
-            }
-        }
-#pragma unroll
-        for (int q = 0; q < STAGE_ITEMS; ++q) {
-            const int idx = base + q * (int)blockDim.x + tid;
-            if (idx >= items) continue;
-            const int gg = idx & 7, kb = idx >> 3;
-            uint2 *dst = sB + ((size_t)kb * 32 + 4 * gg) * MT;
-#pragma unroll
-            for (int tt = 0; tt < 4; ++tt) {
-                const int t2 = (tt + gg) & 3;  // rotate the order per lane: fewer bank conflicts
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const unsigned a = t2 == 0 ? lo[q][mt].x : t2 == 1 ? lo[q][mt].y : t2 == 2 ? lo[q][mt].z : lo[q][mt].w;
-                    const unsigned bq = t2 == 0 ? hi[q][mt].x : t2 == 1 ? hi[q][mt].y : t2 == 2 ? hi[q][mt].z : hi[q][mt].w;
-                    dst[t2 * MT + mt] = make_uint2(a, bq);
-                }
-            }
+    if (lane == 0) {
+        for (int c = 1; c < depth && c < nchunk; ++c) issue(c, c);  // the rest of the first ring-full
+        // What does not fit in the ring yet is pulled into L2 now, so that the refills of the
+        // ring are L2 hits instead of a second round trip to HBM.
+        if (nchunk > depth) {
+            const unsigned rest = (unsigned)(nu - depth * UPC) * UNIT_BYTES;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wsrc + (size_t)depth * slot_bytes), "r"(rest)
+                         : "memory");
         }
     }
-    __syncthreads();
+    // ldmatrix row address of this lane: matrix lane/8 = {block lo, block hi, next block lo, next block hi}, row lane%8
+    unsigned xaddr[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) xaddr[mt] = smem_u32(sX) + (unsigned)(8 * mt + (lane & 7)) * (unsigned)pitch + 16u * (lane >> 3);
 
     float acc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-    bool timed_out = false;
+    bool timed_out = nu > 0 && !mbar_wait(xbar, 0);
 
-    for (int i = 0; i < nu; ++i) {
-        const int c = i / upc, slot = c % depth;
-        if (i % upc == 0 && !mbar_wait(&bar[slot], (unsigned)(c / depth) & 1u)) {
+    // Chunks of UPC units walk the ring; slot and phase advance without divisions.
+    int slot = 0;
+    unsigned phase = 0;
+    for (int c = 0; c < nchunk && !timed_out; ++c) {
+        const int cu = min(UPC, nu - c * UPC);
+        if (!mbar_wait(&bar[slot], phase)) {
             timed_out = true;
             break;
         }
-        const unsigned char *u = ring + (size_t)slot * slot_bytes + (size_t)(i % upc) * UNIT_BYTES;
-        uint4 wv[4];  // int4: wv[0] = row g, wv[1] = row g+8 (four 32-blocks each); int8: wv[j] = block j's {a0,a1,a2,a3}
-        if (BITS == 4) {
-            wv[0] = *reinterpret_cast<const uint4 *>(u + lane * 16);
-            wv[1] = *reinterpret_cast<const uint4 *>(u + 512 + lane * 16);
-        } else {
+        const unsigned char *base = ring + (size_t)slot * slot_bytes;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const uint4 *>(u + j * 512 + lane * 16);
+        for (int iu = 0; iu < UPC; ++iu) {
+            if (iu >= cu) break;
+            const int kb0 = (sb0 + c * UPC + iu) * 4;
+            unsigned b[MT][8];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(b[mt][4 * h]), "=r"(b[mt][4 * h + 1]), "=r"(b[mt][4 * h + 2]), "=r"(b[mt][4 * h + 3])
+                                 : "r"(xaddr[mt] + (unsigned)kb0 * 32u + 64u * h));
+            unit_mma<MT, DUMP, BITS>(base + iu * UNIT_BYTES, b, acc, lane, tile, kb0, m, n, nblk, partials);
         }
-        float2 sc[4];  // {scale[g][j], scale[g+8][j]}
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sc[j] = *reinterpret_cast<const float2 *>(u + W_BYTES + (4 * g + j) * 8);
-        if (i % upc == upc - 1 || i == nu - 1) {
-            __syncwarp();  // every lane holds its part of the slot: it can be refilled
-            if (lane == 0 && c + depth < nchunk) issue(c + depth);
-        }
-
-        const unsigned wa[4] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w};
-        const unsigned wb[4] = {wv[1].x, wv[1].y, wv[1].z, wv[1].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            unsigned a0, a1, a2, a3;
-            if (BITS == 4) {
-                a0 = (wa[j] << 4) & 0xF0F0F0F0u; a2 = wa[j] & 0xF0F0F0F0u;
-                a1 = (wb[j] << 4) & 0xF0F0F0F0u; a3 = wb[j] & 0xF0F0F0F0u;
-            } else {
-                a0 = wv[j].x; a1 = wv[j].y; a2 = wv[j].z; a3 = wv[j].w;
-            }
-            const int kb = (sb0 + i) * 4 + j;
-            // both column groups' fragments sit side by side: one 128-bit shared-memory read for MT = 2
-            uint2 bfrag[MT];
-            if (MT == 2) {
-                const uint4 t4 = *reinterpret_cast<const uint4 *>(sB + ((size_t)kb * 32 + lane) * 2);
-                bfrag[0] = make_uint2(t4.x, t4.y);
-                bfrag[MT - 1] = make_uint2(t4.z, t4.w);
-            } else {
-                bfrag[0] = sB[(size_t)kb * 32 + lane];
-            }
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint2 bb = bfrag[mt];
-                int d[4];
-                mma_s8(d, a0, a1, a2, a3, bb.x, bb.y);
-                acc[mt][0] = fmaf(__int_as_float(d[0]) - MAGIC_F, sc[j].x, acc[mt][0]);
-                acc[mt][1] = fmaf(__int_as_float(d[1]) - MAGIC_F, sc[j].x, acc[mt][1]);
-                acc[mt][2] = fmaf(__int_as_float(d[2]) - MAGIC_F, sc[j].y, acc[mt][2]);
-                acc[mt][3] = fmaf(__int_as_float(d[3]) - MAGIC_F, sc[j].y, acc[mt][3]);
-                if (DUMP) {
-                    // d[0],d[1]: weight row g, activation rows 8mt+2t, +1; d[2],d[3]: weight row g+8
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const size_t row_n = (size_t)tile * 16 + g + 8 * (e >> 1);
-                        const int row_m = 8 * mt + 2 * t + (e & 1);
-                        if (row_n < n && row_m < m)
-                            partials[((size_t)row_m * n + row_n) * nblk + kb] = (d[e] - MAGIC_I) >> (BITS == 4 ? 4 : 0);
-                    }
-                }
-            }
+        __syncwarp();  // every lane is done with the slot: it can be refilled
+        if (lane == 0 && c + depth < nchunk) issue(c + depth, slot);
+        if (++slot == depth) {
+            slot = 0;
+            phase ^= 1u;
         }
     }
     if (timed_out) {
@@ -294,10 +301,176 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// One small CTA per 16-row tile band ("tile kernel").  KS warps split the band's k range; each warp
+// pulls its run of units into a private two-slot ring with bulk copies (for k = 4096 the whole run is
+// in flight from the first instruction), reads the activation fragments straight from global memory
+// (L1-resident: 8 or 16 rows of int8) and the KS partial sums meet in shared memory in a fixed order.
+// No CTA-wide staging and 40-odd KB of shared memory per CTA: about five CTAs share an SM, they start
+// and finish independently, and the CTAs of the next launch in the stream (programmatic dependent
+// launch) move in as soon as individual CTAs of this one retire -- the hand-over between consecutive
+// launches is staggered like that of a plain copy kernel instead of a full-SM barrier.
+// ---------------------------------------------------------------------------------------------
+constexpr int TK_WARPS = 4;    // k split inside a CTA
+
+template <int MT, bool DUMP, int BITS>
+__global__ void __launch_bounds__(TK_WARPS * 32, 5)
+linear_q_tile_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const float *__restrict__ x_scale,
+                     const unsigned char *__restrict__ wq, int m, size_t n, int k, int32_t *__restrict__ partials) {
+    constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
+    constexpr int SU = BITS == 4 ? 4 : 2;  // units per ring slot: 5 KB either way (static shared memory < 48 KB)
+    constexpr int SLOT_BYTES = SU * UNIT_BYTES;
+    constexpr int G = MT == 1 ? SU : SU / 2;  // units whose activation words are in registers at a time
+    __shared__ __align__(128) unsigned char rings[TK_WARPS][2][SLOT_BYTES];
+    __shared__ __align__(8) uint64_t bars[TK_WARPS][2];
+    __shared__ float red[TK_WARPS][MT * 4][32];
+
+    const int nblk = k / 32, nsb = k / 128;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x;
+    const int sb0 = (int)((long long)nsb * warp / TK_WARPS), sb1 = (int)((long long)nsb * (warp + 1) / TK_WARPS);
+    const int nu = sb1 - sb0;
+    const int nchunk = (nu + SU - 1) / SU;
+    const unsigned char *wsrc = wq + ((size_t)tile * nsb + sb0) * UNIT_BYTES;
+    auto issue = [&](int c) {  // lane 0 only
+        const int slot = c & 1;
+        const unsigned bytes = (unsigned)min(SU, nu - c * SU) * UNIT_BYTES;
+        mbar_expect_tx(&bars[warp][slot], bytes);
+        bulk_load(&rings[warp][slot][0], wsrc + (size_t)c * SLOT_BYTES, bytes, &bars[warp][slot]);
+    };
+    if (lane == 0) {
+        mbar_init(&bars[warp][0], 1);
+        mbar_init(&bars[warp][1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (nchunk > 0) issue(0);
+        if (nchunk > 1) issue(1);
+    }
+    __syncwarp();
+    // Only weights were touched so far; the activations may be produced by the previous kernel.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // Activation words of block kb for column group mt: {xq[8mt+g][32kb+4t..], xq[8mt+g][32kb+16+4t..]}.
+    // Rows past m are clamped to row m-1: their columns of the product are computed and dropped.
+    const int8_t *xrow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) xrow[mt] = xq + (size_t)min(8 * mt + g, m - 1) * k + (size_t)sb0 * 128 + 4 * t;
+
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
+    bool timed_out = false;
+
+    auto unit_math = [&](const unsigned char *u, const unsigned (&b)[MT][8], int kb0) {
+        unit_mma<MT, DUMP, BITS>(u, b, acc, lane, tile, kb0, m, n, nblk, partials);
+    };
+    auto fetch_unit = [&](unsigned (&b)[MT][8], int i) {  // unit i of this warp's run
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const unsigned *src = reinterpret_cast<const unsigned *>(xrow[mt] + (size_t)i * 128);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b[mt][2 * j] = __ldg(src + 8 * j);
+                b[mt][2 * j + 1] = __ldg(src + 8 * j + 4);
+            }
+        }
+    };
+
+    for (int c = 0; c < nchunk && !timed_out; ++c) {
+        const int slot = c & 1;
+        const int cu = min(SU, nu - c * SU);  // units in this chunk
+        const unsigned char *base = &rings[warp][slot][0];
+        if (cu == SU) {
+            // full chunk: the activation loads of G units go out together, ahead of the wait for the weights
+#pragma unroll
+            for (int h = 0; h < SU / G; ++h) {
+                unsigned b[G][MT][8];
+#pragma unroll
+                for (int ug = 0; ug < G; ++ug) fetch_unit(b[ug], c * SU + h * G + ug);
+                if (h == 0 && !mbar_wait(&bars[warp][slot], (unsigned)(c >> 1) & 1u)) {
+                    timed_out = true;
+                    break;
+                }
+#pragma unroll
+                for (int ug = 0; ug < G; ++ug)
+                    unit_math(base + (h * G + ug) * UNIT_BYTES, b[ug], (sb0 + c * SU + h * G + ug) * 4);
+            }
+        } else {
+            if (!mbar_wait(&bars[warp][slot], (unsigned)(c >> 1) & 1u)) {
+                timed_out = true;
+                break;
+            }
+            for (int iu = 0; iu < cu; ++iu) {
+                unsigned b[MT][8];
+                fetch_unit(b, c * SU + iu);
+                unit_math(base + iu * UNIT_BYTES, b, (sb0 + c * SU + iu) * 4);
+            }
+        }
+        __syncwarp();  // every lane is done with the slot: it can be refilled
+        if (lane == 0 && c + 2 < nchunk) issue(c + 2);
+    }
+    if (timed_out) {
+        if (lane == 0) atomicAdd(&g_q4_wait_timeouts, 1u);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mt][e] = __int_as_float(0x7fc00000);
+    }
+    if (warp > 0) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red[warp][mt * 4 + e][lane] = acc[mt][e];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int o = 1; o < TK_WARPS; ++o)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[mt][e] += red[o][mt * 4 + e][lane];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const size_t row_n = (size_t)tile * 16 + g + 8 * (e >> 1);
+                const int row_m = 8 * mt + 2 * t + (e & 1);
+                if (row_n < n && row_m < m)
+                    y[(size_t)row_m * n + row_n] = __ldg(x_scale + row_m) * (acc[mt][e] * (BITS == 4 ? 0.0625f : 1.0f));
+            }
+    }
+}
+
+template <int MT, bool DUMP, int BITS>
+int launch_tile(float *y, const int8_t *xq, const float *x_scale, const void *wq, int m, size_t n, int k,
+                int32_t *partials, cudaStream_t st) {
+    const int tiles = (int)((n + 15) / 16);
+    auto kern = linear_q_tile_kernel<MT, DUMP, BITS>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tiles);
+    cfg.blockDim = dim3(TK_WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, xq, x_scale, (const unsigned char *)wq, m, n, k, partials));
+    return XN_OK;
+}
+
 template <int MT, bool DUMP, int BITS>
 int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int m, size_t n, int k,
            int32_t *partials, cudaStream_t st) {
     constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
+    static const int tile_max_m = [] { const char *e = getenv("XN_Q4_TILE_MAX_M"); return e ? atoi(e) : 0; }();
+    if (m <= tile_max_m) return launch_tile<MT, DUMP, BITS>(y, xq, x_scale, wq, m, n, k, partials, st);
     const int tiles = (int)((n + 15) / 16);
     const int nsb = k / 128;
     const int sms = sm_count();
@@ -309,17 +482,12 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     if (ksplit > nsb) ksplit = nsb;
     const int warps = tpc * ksplit;
     const int grid = (tiles + tpc - 1) / tpc;
-    const size_t fixed = (size_t)(k / 32) * 32 * MT * sizeof(uint2) + (size_t)warps * 8 * sizeof(uint64_t);
-    if (fixed + (size_t)warps * UNIT_BYTES > 227 * 1024)  // hard limit of the part
-        return fail(XN_ERR_UNSUPPORTED, "linear_q4: k=%d needs more than 232448 bytes of shared memory", k);
+    const size_t fixed = (size_t)8 * MT * (k + 16) + ((size_t)warps * 8 + 1) * sizeof(uint64_t);
+    if (fixed + (size_t)warps * 2 * UNIT_BYTES > smem_cap)  // activations of a very long k leave no room for the rings
+        return launch_tile<MT, DUMP, BITS>(y, xq, x_scale, wq, m, n, k, partials, st);
     const int per_warp = (nsb + ksplit - 1) / ksplit;
-    static const int upc_env = [] { const char *e = getenv("XN_Q4_UPC"); return e ? atoi(e) : 0; }();
-    int upc = upc_env > 0 ? upc_env : 2;  // units per bulk copy
-    if (upc > per_warp) upc = per_warp;
-    const size_t cap = smem_cap > fixed + (size_t)warps * UNIT_BYTES ? smem_cap : fixed + (size_t)warps * UNIT_BYTES;
-    while (upc > 1 && fixed + (size_t)warps * 2 * upc * UNIT_BYTES > cap) --upc;
-    int depth = (int)((cap - fixed) / ((size_t)warps * upc * UNIT_BYTES));
-    if (depth < 1) depth = 1;
+    constexpr int upc = 2;  // units per bulk copy and ring slot (the kernel's UPC)
+    int depth = (int)((smem_cap - fixed) / ((size_t)warps * upc * UNIT_BYTES));
     if (depth > (per_warp + upc - 1) / upc) depth = (per_warp + upc - 1) / upc;
     if (depth > 8) depth = 8;
     const size_t smem = fixed + (size_t)warps * depth * upc * UNIT_BYTES;
@@ -336,7 +504,7 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, xq, x_scale, (const unsigned char *)wq, m, n, k, tiles, tpc,
-                                     ksplit, depth, upc, partials));
+                                     ksplit, depth, partials));
     return XN_OK;
 }
 
