@@ -9,19 +9,28 @@
 // nibbles becomes two int8x4 operands with two logic ops: (w << 4) & 0xF0F0F0F0 and
 // w & 0xF0F0F0F0 are the low / high nibbles times 16 as signed bytes; the factor 16 is removed
 // exactly at the end (power of two).  The MMA's accumulator input is the bit pattern of
-// 1.5 * 2^23, so the int32 result read as a float is exactly 12582912 + sum and one full-rate
-// FADD replaces the slow int-to-float conversion before the block scale is applied.
+// 1.5 * 2^23, so the int32 result read as a float is exactly 12582912 + sum and one packed
+// full-rate add (add.f32x2, two elements per instruction) replaces the slow int-to-float
+// conversion before the block scale is applied.
 //
-// Data movement.  The kernel lasts a few microseconds, so it is organised like a copy engine:
+// Data movement.  The kernel lasts a few microseconds and issues about as many instructions as the
+// SM can retire in that time, so it is organised like a copy engine with a lean inner loop:
 // one CTA per SM; a "unit" is one 1280-byte q4 tile (1 KB of nibbles + its 256 bytes of scales);
 // every warp owns a run of consecutive units of one 16-row tile band and a private ring of slots
-// in shared memory which lane 0 fills with bulk asynchronous copies (cp.async.bulk + mbarrier), re-arming a slot as soon as the
-// warp has read it.  The first ring-full of copies is issued before anything else -- before the
-// dependency wait of a programmatic dependent launch and before the activations are staged -- so
-// about 150 KB per SM are in flight without holding a single register.  The int8 activations are
-// staged once per CTA in shared memory in B-fragment order.  Warps that share a tile (k split)
-// combine their partial sums through shared memory in a fixed order: results are run-to-run
-// identical.
+// in shared memory which lane 0 fills with bulk asynchronous copies (cp.async.bulk + mbarrier),
+// re-arming a slot as soon as the warp is done with it.  The first copy of every warp is issued
+// before anything else -- before the dependency wait of a programmatic dependent launch -- and the
+// rest of the ring right after the activation copies, so about 150 KB per SM are in flight
+// without holding a single register.  The int8 activations arrive by bulk copies too, row-major
+// at a pitch of k + 16 bytes, and are read in B-fragment order with ldmatrix (the pitch spreads the
+// 8 rows of a fragment over distinct banks): no staging code, no CTA-wide barrier before the math.
+// The unit loop has no divisions and no per-unit address arithmetic beyond two adds.  Warps that
+// share a tile (k split) combine their partial sums through shared memory in a fixed order:
+// results are run-to-run identical.
+//
+// When k is so long that the activations leave no room for the rings, a second kernel with one small
+// CTA per 16-row band takes over: it reads the activation fragments straight from global memory
+// and has no limit on k.
 #include "common.cuh"
 
 namespace xn {
@@ -146,29 +155,30 @@ template <int MT, bool DUMP, int BITS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
 linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const float *__restrict__ x_scale,
                  const unsigned char *__restrict__ wq, int m, size_t n, int k, int tiles, int tpc, int ksplit,
-                 int depth, int32_t *__restrict__ partials) {
+                 int usplit, int urem, int depth, int32_t *__restrict__ partials) {
     constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
     constexpr int UPC = 2;  // units per bulk copy and ring slot
     extern __shared__ __align__(128) unsigned char smem[];
     const int nblk = k / 32, nsb = k / 128;
     const int nwarps = blockDim.x >> 5;
     // [rings: nwarps * depth slots of UPC units, reused as red: nwarps * MT*4*32 f32]
-    // [activations: 8*MT rows of k int8 at a pitch of k+16 bytes][mbarriers: nwarps * depth, then one for the activations]
+    // [activations: 8*MT rows of k int8 at a pitch of k+16 bytes][mbarriers: nwarps * depth, then one per k slice for the activations]
     unsigned char *rings = smem;
     constexpr int slot_bytes = UPC * UNIT_BYTES;
     unsigned char *sX = smem + (size_t)nwarps * depth * slot_bytes;
     const int pitch = k + 16;  // rows 16 bytes apart modulo 128: the 8 rows of an ldmatrix tile hit distinct banks
     uint64_t *bars = reinterpret_cast<uint64_t *>(sX + (size_t)8 * MT * pitch);
-    uint64_t *xbar = bars + (size_t)nwarps * depth;
+    uint64_t *xbars = bars + (size_t)nwarps * depth;
     float *red = reinterpret_cast<float *>(rings);  // the rings are dead once every warp has left its unit loop
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int tl = warp / ksplit, ks = warp % ksplit;
+    // warp -> (tile of this CTA, k slice): slice ks covers usplit units, the first urem slices one more
+    const int tl = (int)((unsigned)warp / (unsigned)ksplit), ks = warp - tl * ksplit;
     const int tile = blockIdx.x * tpc + tl;
     const bool valid = tile < tiles;
-    const int sb0 = (int)((long long)nsb * ks / ksplit), sb1 = (int)((long long)nsb * (ks + 1) / ksplit);
-    const int nu = valid ? sb1 - sb0 : 0;
+    const int sb0 = ks * usplit + min(ks, urem);
+    const int nu = valid ? usplit + (ks < urem ? 1 : 0) : 0;
 
     unsigned char *ring = rings + (size_t)warp * depth * slot_bytes;
     uint64_t *bar = bars + (size_t)warp * depth;
@@ -181,7 +191,7 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     };
     if (lane == 0) {
         for (int s = 0; s < depth; ++s) mbar_init(&bar[s], 1);
-        if (warp == 0) mbar_init(xbar, 1);
+        if (tl == 0) mbar_init(&xbars[ks], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (nchunk > 0) issue(0, 0);
@@ -192,12 +202,22 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // The activations come in as one bulk copy per row, row-major; rows >= m stay unwritten: their
-    // columns of the product are computed from whatever the shared memory holds and never stored.
-    if (tid == 0) {
-        const int rows = min(m, 8 * MT);
-        mbar_expect_tx(xbar, (unsigned)rows * (unsigned)k);
-        for (int r = 0; r < rows; ++r) bulk_load(sX + (size_t)r * pitch, xq + (size_t)r * k, (unsigned)k, xbar);
+    // The activations come in row-major by bulk copies; rows >= m stay unwritten: their columns of the
+    // product are computed from whatever the shared memory holds and never stored.  Up to 8 rows: one
+    // copy per row and one barrier (few large copies are the cheapest).  16 rows are 64 KB at k = 4096,
+    // wanted by every SM at once: one copy per row and k slice, tracked per slice, lets a slice's warps
+    // start on their part while the rest is still arriving.
+    constexpr bool SLICED = MT == 2;
+    if (!SLICED && tid == 0) {
+        mbar_expect_tx(&xbars[0], (unsigned)min(m, 8) * (unsigned)k);
+        for (int r = 0; r < min(m, 8); ++r) bulk_load(sX + (size_t)r * pitch, xq + (size_t)r * k, (unsigned)k, &xbars[0]);
+    }
+    if (SLICED && tl == 0 && lane == 0) {
+        const int rows = min(m, 16);
+        const unsigned bytes = (unsigned)nu * 128u;
+        mbar_expect_tx(&xbars[ks], (unsigned)rows * bytes);
+        for (int r = 0; r < rows; ++r)
+            bulk_load(sX + (size_t)r * pitch + (size_t)sb0 * 128, xq + (size_t)r * k + (size_t)sb0 * 128, bytes, &xbars[ks]);
     }
     float xs_reg[MT][2];  // x_scale of the activation rows this lane stores at the end
 #pragma unroll
@@ -227,7 +247,7 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-    bool timed_out = nu > 0 && !mbar_wait(xbar, 0);
+    bool timed_out = nu > 0 && !mbar_wait(&xbars[SLICED ? ks : 0], 0);
 
     // Chunks of UPC units walk the ring; slot and phase advance without divisions.
     int slot = 0;
@@ -482,7 +502,7 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     if (ksplit > nsb) ksplit = nsb;
     const int warps = tpc * ksplit;
     const int grid = (tiles + tpc - 1) / tpc;
-    const size_t fixed = (size_t)8 * MT * (k + 16) + ((size_t)warps * 8 + 1) * sizeof(uint64_t);
+    const size_t fixed = (size_t)8 * MT * (k + 16) + ((size_t)warps * 8 + MAX_WARPS) * sizeof(uint64_t);
     if (fixed + (size_t)warps * 2 * UNIT_BYTES > smem_cap)  // activations of a very long k leave no room for the rings
         return launch_tile<MT, DUMP, BITS>(y, xq, x_scale, wq, m, n, k, partials, st);
     const int per_warp = (nsb + ksplit - 1) / ksplit;
@@ -504,7 +524,7 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, xq, x_scale, (const unsigned char *)wq, m, n, k, tiles, tpc,
-                                     ksplit, depth, partials));
+                                     ksplit, nsb / ksplit, nsb % ksplit, depth, partials));
     return XN_OK;
 }
 
