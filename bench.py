@@ -357,7 +357,7 @@ def main() -> None:
             "decode_step": decode,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "traffic": 28878848,
+                         "peak_kind": f"of {peak_kind}", "traffic": 28875776,
                          "traffic_source": "dram__bytes_read+write per launch, ncu capture in profiles/linear_q4_kernel_int4_decode_gemv.md",
                          "kernel": "linear_q4_kernel",
                          "algorithmic_bytes_per_launch": alg, "us_per_launch": launch_s * 1e6},
