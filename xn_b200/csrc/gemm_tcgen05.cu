@@ -182,6 +182,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
+    // Programmatic dependent launch: barrier set-up and the tensor-memory allocation above overlap the
+    // tail of the previous kernel in the stream; operands and outputs are touched only after this wait.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -326,7 +330,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------
-// Skinny form for 16 < M <= 128 (weights >> activations, HBM-bound): the operands swap roles.  The
+// Skinny form for 8 < M <= 64 (weights >> activations, HBM-bound): the operands swap roles.  The
 // 128 TMEM lanes carry 128 output channels (a 16 KB weight tile per 128-byte k stage) and the MMA's N
 // dimension carries the M activation rows (one or two e4m3 pieces of MB rows each), so almost all
 // bytes in flight are weight bytes and a deep ring (up to 8 stages) keeps ~100 KB of them in flight
@@ -341,6 +345,7 @@ struct SkinnyArgs {
     int MB;      // MMA N dimension: M rounded up to 16
     int nstage;
     int np;      // pieces (1 or 2)
+    int uq, ur;  // stage units per CTA: total / grid and total % grid
 };
 
 // Work is cut at k-stage granularity ("stream-K"): total = tiles * num_kb stage units, CTA c owns the
@@ -348,7 +353,14 @@ struct SkinnyArgs {
 // that is covered by several CTAs is finished by whichever of them arrives last (per lane quarter):
 // every contributor stores its f32 partial to scratch, and the finisher adds all partials in k order
 // -- a fixed order, so the result does not depend on which CTA happens to be last.
-__device__ __forceinline__ long long unit_begin(int c, int G, long long total) { return (long long)c * total / G; }
+// (32-bit arithmetic only: a 64-bit division is ~100 dependent instructions, and the epilogue warps sit on
+// the critical path at the end of the kernel.)  uq = total / G, ur = total % G come from the host: the first ur
+// CTAs own uq + 1 units, the others uq.
+__device__ __forceinline__ int unit_begin(int c, int uq, int ur) { return c * uq + min(c, ur); }
+__device__ __forceinline__ int unit_owner(int u, int uq, int ur) {  // the CTA whose range holds unit u
+    const int big = ur * (uq + 1);
+    return u < big ? (int)((unsigned)u / (unsigned)(uq + 1)) : ur + (int)((unsigned)(u - big) / (unsigned)uq);
+}
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x0,
@@ -357,8 +369,12 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int X_BYTES = args.MB * BKB;
     const int STAGE_BYTES = W_BYTES + args.np * X_BYTES;
     const int NSTAGE = args.nstage;
-    const uint32_t IDESC = instr_desc(0, 0, args.MB);
-    const int TMEM_COLS = 2 * args.MB <= 32 ? 32 : (2 * args.MB <= 64 ? 64 : (2 * args.MB <= 128 ? 128 : (2 * args.MB <= 256 ? 256 : 512)));
+    // One MMA per k step covers both pieces: they sit back to back in the stage, so they form one
+    // K-major operand of np * MB rows; D columns [0, MB) are the hi products, [MB, 2 MB) the lo products
+    // (an MMA instruction costs about 130 cycles here however small N is: fewer, wider MMAs).
+    const int NB = args.np * args.MB;  // MMA N dimension = TMEM columns of one accumulator buffer
+    const uint32_t IDESC = instr_desc(0, 0, NB);
+    const int TMEM_COLS = 2 * NB <= 32 ? 32 : (2 * NB <= 64 ? 64 : (2 * NB <= 128 ? 128 : (2 * NB <= 256 ? 256 : 512)));
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -366,11 +382,9 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = (args.N + BM - 1) / BM;
     const int num_kb = (args.K + BKB - 1) / BKB;
-    const int G = gridDim.x;
-    const long long total = (long long)num_tiles * num_kb;
-    const long long u0 = unit_begin(blockIdx.x, G, total), u1 = unit_begin(blockIdx.x + 1, G, total);
+    const int uq = args.uq, ur = args.ur;
+    const int u0 = unit_begin(blockIdx.x, uq, ur), u1 = unit_begin(blockIdx.x + 1, uq, ur);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -388,14 +402,17 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
+    // Programmatic dependent launch: everything above overlapped the previous kernel's tail.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            for (long long u = u0; u < u1 && ok;) {
-                const int tile = (int)(u / num_kb), kb0 = (int)(u % num_kb);
-                const int kb1 = (int)min((long long)num_kb, kb0 + (u1 - u));
+            for (int u = u0; u < u1 && ok;) {
+                const int tile = (int)((unsigned)u / (unsigned)num_kb), kb0 = u - tile * num_kb;
+                const int kb1 = min(num_kb, kb0 + (u1 - u));
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
@@ -413,26 +430,25 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         if (lane == 0) {
             int it = 0, t_local = 0;
             bool ok = true;
-            for (long long u = u0; u < u1 && ok; ++t_local) {
-                const int kb0 = (int)(u % num_kb);
-                const int kb1 = (int)min((long long)num_kb, kb0 + (u1 - u));
+            for (int u = u0; u < u1 && ok; ++t_local) {
+                const int kb0 = u - (int)((unsigned)u / (unsigned)num_kb) * num_kb;
+                const int kb1 = min(num_kb, kb0 + (u1 - u));
                 const int acc = t_local & 1;
                 const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * args.MB);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NB);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
                     if (!mbar_wait(&full[s], ph)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-                    const uint64_t dw = smem_desc(st), dx0 = smem_desc(st + W_BYTES), dx1 = smem_desc(st + W_BYTES + X_BYTES);
+                    const uint64_t dw = smem_desc(st), dx = smem_desc(st + W_BYTES);
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
-                        umma<true>(d_tmem, dw + adv, dx0 + adv, IDESC, (kb > kb0) || ks != 0);
-                        if (args.np == 2) umma<true>(d_tmem, dw + adv, dx1 + adv, IDESC, 1u);
+                        umma<true>(d_tmem, dw + adv, dx + adv, IDESC, (kb > kb0) || ks != 0);
                     }
                     umma_commit(&empty[s]);
                 }
@@ -445,9 +461,9 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         int t_local = 0;
         bool ok = true;
         const size_t slot_elems = (size_t)args.MB * BM;
-        for (long long u = u0; u < u1 && ok; ++t_local) {
-            const int tile = (int)(u / num_kb), kb0 = (int)(u % num_kb);
-            const int kb1 = (int)min((long long)num_kb, kb0 + (u1 - u));
+        for (int u = u0; u < u1 && ok; ++t_local) {
+            const int tile = (int)((unsigned)u / (unsigned)num_kb), kb0 = u - tile * num_kb;
+            const int kb1 = min(num_kb, kb0 + (u1 - u));
             const bool whole = kb0 == 0 && kb1 == num_kb;
             const int acc = t_local & 1;
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
@@ -465,8 +481,20 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
                       "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                    : "r"(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * args.MB + c)));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    : "r"(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * NB + c)));
+                if (args.np == 2) {
+                    uint32_t w[16];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]),
+                          "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15])
+                        : "r"(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * NB + args.MB + c)));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+                } else {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                }
                 if (whole) {
                     if (ch < args.N) {
 #pragma unroll
@@ -489,12 +517,8 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
             if (!whole) {
                 // contributors of this tile: the CTAs whose unit ranges intersect [tile*num_kb, (tile+1)*num_kb)
-                const long long t0 = (long long)tile * num_kb, t1 = t0 + num_kb;
-                int c_first = (int)((t0 * G) / total);
-                while (c_first > 0 && unit_begin(c_first, G, total) > t0) --c_first;
-                while (unit_begin(c_first + 1, G, total) <= t0) ++c_first;
-                int c_last = c_first;
-                while (c_last + 1 < G && unit_begin(c_last + 1, G, total) < t1) ++c_last;
+                const int t0 = tile * num_kb, t1 = t0 + num_kb;
+                const int c_first = unit_owner(t0, uq, ur), c_last = unit_owner(t1 - 1, uq, ur);
                 const unsigned ncontrib = (unsigned)(c_last - c_first + 1);
                 __threadfence();
                 __syncwarp();
@@ -505,22 +529,30 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     __threadfence();
                     if (lane == 0) args.counters[(size_t)tile * 4 + q] = 0;  // ready for the next launch
                     if (ch < args.N) {
-                        // 32 activation rows at a time: 32 independent loads in flight per contributor
-                        for (int m0 = 0; m0 < args.M; m0 += 32) {
-                            float sum[32];
+                        // 16 activation rows at a time, four contributors' loads in flight together; the
+                        // additions run in contributor (= k) order whatever the arrival order was
+                        for (int m0 = 0; m0 < args.M; m0 += 16) {
+                            float sum[16];
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) sum[j] = 0.0f;
-                            for (int cc = c_first; cc <= c_last; ++cc) {
-                                const int slot = 2 * cc + (unit_begin(cc, G, total) >= t0 ? 0 : 1);
-                                const float *src = args.partials + (size_t)slot * slot_elems + (size_t)m0 * BM + q * 32 + lane;
-                                float tv[32];
+                            for (int j = 0; j < 16; ++j) sum[j] = 0.0f;
+                            for (int cc0 = c_first; cc0 <= c_last; cc0 += 4) {
+                                float tv[4][16];
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) tv[j] = (m0 + j < args.MB) ? __ldcg(src + (size_t)j * BM) : 0.0f;
+                                for (int d = 0; d < 4; ++d) {
+                                    const int cc = cc0 + d;
+                                    const bool on = cc <= c_last;
+                                    const int slot = on ? 2 * cc + (unit_begin(cc, uq, ur) >= t0 ? 0 : 1) : 0;
+                                    const float *src = args.partials + (size_t)slot * slot_elems + (size_t)m0 * BM + q * 32 + lane;
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) sum[j] += tv[j];
+                                    for (int j = 0; j < 16; ++j) tv[d][j] = (on && m0 + j < args.MB) ? __ldcg(src + (size_t)j * BM) : 0.0f;
+                                }
+#pragma unroll
+                                for (int d = 0; d < 4; ++d)
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j) sum[j] += tv[d][j];
                             }
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
+                            for (int j = 0; j < 16; ++j)
                                 if (m0 + j < args.M)
                                     args.y[(size_t)(m0 + j) * args.N + ch] =
                                         __float2bfloat16_rn(ws * (__ldg(args.x_scale + m0 + j) * sum[j]));
@@ -617,8 +649,17 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     const long long tiles = (long long)((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) * args.batch;
     const int sms = sm_count();
     const int grid = (int)(tiles < sms ? tiles : sms);
-    kern<<<grid, NTHREADS, smem, st>>>(ma0, ma1, mb, args2);
-    XN_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ma0, ma1, mb, args2));
     return XN_OK;
 }
 
@@ -686,9 +727,13 @@ int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, 
     // at least 4 k stages per CTA, so that a split never degenerates into single-stage crumbs
     long long grid = total / 4 < 1 ? 1 : total / 4;
     if (grid > sms) grid = sms;
-    // Whole tiles (no fix-up pass) when they already fill most of the machine; otherwise split at k-stage
-    // granularity so that every SM streams its share of the weights.
-    if (tiles <= sms && tiles * 100 >= sms * 64) grid = tiles;
+    // Whole tiles (no fix-up pass) only when they fill at least 90 % of the machine; otherwise split at
+    // k-stage granularity so that every SM streams its share of the weights and issues its share of the MMAs
+    // (an MMA costs ~130 cycles whatever its N, so the MMA count per CTA is what bounds a skinny problem).
+    if (tiles <= sms && tiles * 100 >= sms * 90) grid = tiles;
+    XN_REQUIRE(total < (1ll << 30), "linear_fp8: problem too large for the skinny kernel's 32-bit unit index");
+    a.uq = (int)(total / grid);
+    a.ur = (int)(total % grid);
     SkinnyScratch sc;
     int rc = skinny_scratch((size_t)2 * grid * a.MB * BM * sizeof(float), (size_t)tiles * 4, &sc);
     if (rc) return rc;
@@ -703,8 +748,17 @@ int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, 
     if (rc) return rc;
     const size_t smem = (size_t)a.nstage * stage + 1024;
     XN_ENSURE_SMEM(gemm_tcgen05_skinny_kernel, smem);
-    gemm_tcgen05_skinny_kernel<<<(unsigned)grid, NTHREADS, smem, st>>>(mw, mx0, mx1, a);
-    XN_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_skinny_kernel, mw, mx0, mx1, a));
     return XN_OK;
 }
 

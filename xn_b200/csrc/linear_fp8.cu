@@ -30,9 +30,10 @@ extern "C" int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const 
     XN_REQUIRE(aligned(wq, 16) && aligned(x_hi, 16) && (!x_lo || aligned(x_lo, 16)),
                "linear_fp8: weights and activation pieces must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    // Decode-sized batches stream the weights once through the GEMV kernel; anything larger goes to
-    // the tensor-memory GEMM (which pads the last row tile).
-    static const size_t gemv_max_m = [] { const char *e = getenv("XN_FP8_GEMV_MAX_M"); return e ? (size_t)atoi(e) : (size_t)16; }();
+    // Up to 8 rows (one MMA column group) stream the weights once through the GEMV kernel; anything larger
+    // goes to the tensor-memory kernels (skinny form up to 64 rows, tiled GEMM beyond), which were measured
+    // faster from 9 rows on for every transformer shape.
+    static const size_t gemv_max_m = [] { const char *e = getenv("XN_FP8_GEMV_MAX_M"); return e ? (size_t)atoi(e) : (size_t)8; }();
     if (m > gemv_max_m) return launch_linear_fp8_gemm(y_bf16, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
     for (size_t i0 = 0; i0 < m; i0 += 32) {
         const int mc = (int)((m - i0) < 32 ? (m - i0) : 32);
