@@ -168,196 +168,6 @@ linear_fp8_gemv_kernel(__nv_bfloat16 *__restrict__ y, const uint8_t *__restrict_
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Up to 8 activation rows: f16 tensor-core form.  On this architecture the e4m3 form of mma.sync is
-// not a native instruction: the compiler expands it into conversions of both operands plus f16 MMAs
-// (measured: 128 instructions per 64-byte k step, the kernel issue-bound).  Here the conversion is
-// explicit and done once: the weights go e4m3 -> f16 in registers (exact; one cvt per pair), the
-// activation row is staged in shared memory as f16(hi + lo) (hi only for W8A8), which carries
-// 11 significant bits against the 8 of the bf16 activation it came from, and one m16n8k16 f16 MMA
-// per 16 k values does the work of the former two e4m3 MMAs.  Products are exact in f32.
-// A lane's 16 weight bytes of a row feed four MMAs (bytes 4i..4i+3 -> MMA i: k slots 2t, 2t+1, 2t+8,
-// 2t+9), and the matching 16 f16 activations are 32 contiguous bytes of the staged row.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned cvt_e4m3x2_f16x2(unsigned short v) {
-    unsigned d;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(d) : "h"(v));
-    return d;
-}
-__device__ __forceinline__ void mma_f16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
-                                        unsigned b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned hadd2_u(unsigned a, unsigned b) {
-    __half2 r = __hadd2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
-    return *reinterpret_cast<unsigned *>(&r);
-}
-
-// staged activation row pitch in bytes: 2 bytes per k plus 16, so that the 8 lanes of a 128-bit
-// shared-memory access phase (two rows x four 32-byte segments) fall in distinct 16-byte bank groups
-__host__ __device__ inline int xh_row_pitch(int k) { return (k + 63) / 64 * 128 + 16; }
-
-constexpr int H_WARPS = 24;
-constexpr int H_DEPTH = 4;
-
-template <bool LO>
-__global__ void __launch_bounds__(H_WARPS * 32, 1)
-linear_fp8_gemv_f16_kernel(__nv_bfloat16 *__restrict__ y, const uint8_t *__restrict__ x_hi,
-                           const uint8_t *__restrict__ x_lo, const float *__restrict__ x_scale,
-                           const uint8_t *__restrict__ wq, const float *__restrict__ w_scale, int m, size_t n,
-                           int k, int tiles, int tpc, int ksplit, int ssplit, int srem) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    const int RS = xh_row_pitch(k);
-    unsigned char *sX = smem;                                       // 8 rows of f16
-    float *red = reinterpret_cast<float *>(smem + (size_t)8 * RS);  // k-split partial sums
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int tl = (int)((unsigned)warp / (unsigned)ksplit), ks = warp - tl * ksplit;
-    const int tile = blockIdx.x * tpc + tl;
-    const bool valid = tile < tiles;
-    const size_t r0 = valid ? min((size_t)tile * 16 + g, n - 1) : 0, r1 = valid ? min((size_t)tile * 16 + g + 8, n - 1) : 0;
-    // 64-byte k steps of this warp: slice ks of ksplit (the first srem slices have one step more)
-    const int st0 = ks * ssplit + min(ks, srem);
-    const int st1 = valid ? st0 + ssplit + (ks < srem ? 1 : 0) : st0;
-
-    const uint8_t *wp0 = wq + r0 * k + 16 * t;
-    const uint8_t *wp1 = wq + r1 * k + 16 * t;
-    uint4 w0[H_DEPTH], w1[H_DEPTH];
-    auto load = [&](int i, int st) {  // step st -> register slot i
-        if (st < st1 && st * 64 + 16 * t < k) {
-            w0[i] = ldg_stream(wp0 + (size_t)st * 64);
-            w1[i] = ldg_stream(wp1 + (size_t)st * 64);
-        } else {
-            w0[i] = make_uint4(0, 0, 0, 0);
-            w1[i] = make_uint4(0, 0, 0, 0);
-        }
-    };
-#pragma unroll
-    for (int i = 0; i < H_DEPTH; ++i) load(i, st0 + i);
-
-    // Everything so far read only the weights; the activations may come from the previous kernel.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    float xs_reg[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) xs_reg[e] = 2 * t + e < m ? __ldg(x_scale + 2 * t + e) : 0.0f;
-    const float ws0 = valid ? __ldg(w_scale + r0) : 0.0f, ws1 = valid ? __ldg(w_scale + r1) : 0.0f;
-
-    // stage rows [0, 8) as f16(hi + lo), zero outside [0, m) x [0, k): 16 k values per item
-    const int chunks = (k + 63) / 64 * 4;
-    for (int idx = tid; idx < 8 * chunks; idx += blockDim.x) {
-        const int row = (int)((unsigned)idx / (unsigned)chunks), c = idx - row * chunks;
-        uint4 o0 = make_uint4(0, 0, 0, 0), o1 = o0;
-        if (row < m && c * 16 < k) {
-            const size_t src = (size_t)row * k + (size_t)c * 16;
-            const uint4 h = __ldg(reinterpret_cast<const uint4 *>(x_hi + src));
-            const unsigned hw[4] = {h.x, h.y, h.z, h.w};
-            unsigned f[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                f[2 * i] = cvt_e4m3x2_f16x2((unsigned short)(hw[i] & 0xffffu));
-                f[2 * i + 1] = cvt_e4m3x2_f16x2((unsigned short)(hw[i] >> 16));
-            }
-            if (LO) {
-                const uint4 l = __ldg(reinterpret_cast<const uint4 *>(x_lo + src));
-                const unsigned lw[4] = {l.x, l.y, l.z, l.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    f[2 * i] = hadd2_u(f[2 * i], cvt_e4m3x2_f16x2((unsigned short)(lw[i] & 0xffffu)));
-                    f[2 * i + 1] = hadd2_u(f[2 * i + 1], cvt_e4m3x2_f16x2((unsigned short)(lw[i] >> 16)));
-                }
-            }
-            o0 = make_uint4(f[0], f[1], f[2], f[3]);
-            o1 = make_uint4(f[4], f[5], f[6], f[7]);
-        }
-        uint4 *dst = reinterpret_cast<uint4 *>(sX + (size_t)row * RS + (size_t)c * 32);
-        dst[0] = o0;
-        dst[1] = o1;
-    }
-    __syncthreads();
-
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    const unsigned char *xrow = sX + (size_t)g * RS + 32 * t;
-    for (int st = st0; st < st1; st += H_DEPTH) {
-#pragma unroll
-        for (int i = 0; i < H_DEPTH; ++i) {
-            if (st + i < st1) {
-                const uint4 b01 = *reinterpret_cast<const uint4 *>(xrow + (size_t)(st + i) * 128);
-                const uint4 b23 = *reinterpret_cast<const uint4 *>(xrow + (size_t)(st + i) * 128 + 16);
-                const unsigned wa[4] = {w0[i].x, w0[i].y, w0[i].z, w0[i].w};
-                const unsigned wb[4] = {w1[i].x, w1[i].y, w1[i].z, w1[i].w};
-                const unsigned bb[8] = {b01.x, b01.y, b01.z, b01.w, b23.x, b23.y, b23.z, b23.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const unsigned a0 = cvt_e4m3x2_f16x2((unsigned short)(wa[q] & 0xffffu));
-                    const unsigned a2 = cvt_e4m3x2_f16x2((unsigned short)(wa[q] >> 16));
-                    const unsigned a1 = cvt_e4m3x2_f16x2((unsigned short)(wb[q] & 0xffffu));
-                    const unsigned a3 = cvt_e4m3x2_f16x2((unsigned short)(wb[q] >> 16));
-                    mma_f16(acc, a0, a1, a2, a3, bb[2 * q], bb[2 * q + 1]);
-                }
-            }
-            load(i, st + i + H_DEPTH);
-        }
-    }
-
-    // fixed-order reduction over the ksplit warps of a tile, then the scaled bf16 store
-    if (ksplit > 1) {
-        if (ks > 0)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) red[((size_t)warp * 4 + i) * 32 + lane] = acc[i];
-        __syncthreads();
-        if (ks == 0)
-            for (int o = 1; o < ksplit; ++o)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[i] += red[((size_t)(warp + o) * 4 + i) * 32 + lane];
-    }
-    if (ks == 0 && valid) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const size_t row_n = (size_t)tile * 16 + g + 8 * (i >> 1);
-            const int row_m = 2 * t + (i & 1);
-            if (row_n < n && row_m < m)
-                y[(size_t)row_m * n + row_n] = __float2bfloat16_rn((i >> 1 ? ws1 : ws0) * (xs_reg[i & 1] * acc[i]));
-        }
-    }
-}
-
-// Returns XN_ERR_UNSUPPORTED-free "not applicable" as -1 when k does not fit the shared-memory budget.
-template <bool LO>
-int launch_f16(__nv_bfloat16 *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
-               const float *w_scale, int m, size_t n, int k, cudaStream_t st) {
-    const int tiles = (int)((n + 15) / 16);
-    const int sms = sm_count();
-    int tpc = (tiles + sms - 1) / sms;
-    if (tpc > H_WARPS) tpc = H_WARPS;
-    int ksplit = H_WARPS / tpc;
-    const int nst = (k + 63) / 64;
-    if (ksplit > nst / H_DEPTH) ksplit = nst / H_DEPTH;
-    if (ksplit < 1) ksplit = 1;
-    const int warps = tpc * ksplit;
-    const int grid = (tiles + tpc - 1) / tpc;
-    const size_t smem = (size_t)8 * xh_row_pitch(k) + (size_t)warps * 4 * 32 * sizeof(float);
-    if (smem > (size_t)SMEM_BUDGET) return -1;
-    auto kern = linear_fp8_gemv_f16_kernel<LO>;
-    XN_ENSURE_SMEM(kern, smem);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)warps * 32);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, tiles, tpc, ksplit,
-                                     nst / ksplit, nst % ksplit));
-    return XN_OK;
-}
-
 template <int MT, bool LO>
 int launch(__nv_bfloat16 *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
            const float *w_scale, int m, size_t n, int k, cudaStream_t st) {
@@ -399,12 +209,6 @@ int launch(__nv_bfloat16 *y, const uint8_t *x_hi, const uint8_t *x_lo, const flo
 int launch_linear_fp8_gemv(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
                            const uint8_t *wq, const float *w_scale, int m, size_t n, int k, cudaStream_t st) {
     __nv_bfloat16 *yy = (__nv_bfloat16 *)y;
-    static const int f16_form = [] { const char *e = getenv("XN_FP8_GEMV_F16"); return e ? atoi(e) : 1; }();
-    if (m <= 8 && f16_form) {
-        const int rc = x_lo ? launch_f16<true>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st)
-                            : launch_f16<false>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
-        if (rc >= 0) return rc;  // -1: k too long for the staged row, the chunked e4m3 form below takes it
-    }
     if (m <= 8)
         return x_lo ? launch<1, true>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st)
                     : launch<1, false>(yy, x_hi, x_lo, x_scale, wq, w_scale, m, n, k, st);
