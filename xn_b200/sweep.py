@@ -158,10 +158,61 @@ def sweep_f32(out, dev, pk):
     print(json.dumps(row), flush=True)
 
 
+def write_md(rows, path):
+    """The sweep as markdown tables (the form kept under profiles/)."""
+    pk = rows[0]["peaks"]
+    L = ["# Shape sweeps (CUDA-event timing, graph replay, operands rotated over >= 600 MB of distinct weight copies)", "",
+         "Command: `python -m xn_b200.sweep --what all --json gpurun_out/sweep_all.json --md gpurun_out/sweep_all.md` on one B200"
+         " (committed files only).",
+         "Roofline per point = max(algorithmic bytes / measured HBM GB/s, 2MNK / peak), peak = %s cuBLAS bf16 burst" % pk["kind"],
+         "(%.0f TFLOP/s) for the W8A16 and 16-bit rows and twice that for W8A8; HBM = %.0f GB/s; `frac` = roofline time / measured time."
+         % (pk["bf16_tflops"], pk["hbm_gbs"]),
+         "`cuBLAS bf16` = the reference's GPU path for an unquantized weight of the same shape (torch.matmul -> cublasGemmEx,"
+         " f32 accumulate).", ""]
+    fp8 = [r for r in rows if r.get("config") == "fp8_linear"]
+    if fp8:
+        L += ["## fp8-e4m3 transformer linears (bf16 activations in, bf16 out; matmul only, activation split listed separately)", "",
+              "| shape (N,K) | M | W8A16 µs | TFLOP/s | GB/s | frac | W8A8 µs | TFLOP/s | frac | split µs | cuBLAS bf16 µs |",
+              "|---|---|---|---|---|---|---|---|---|---|---|"]
+        for r in fp8:
+            a16, a8 = r["w8a16"], r["w8a8"]
+            L.append("| %s (%d,%d) | %d | %.1f | %.1f | %.0f | %.2f | %.1f | %.1f | %.2f | %.1f | %.1f |" % (
+                r["name"], r["n"], r["k"], r["m"], a16["us_matmul"], a16["tflops"], a16["gbs"], a16["frac_of_roofline"],
+                a8["us_matmul"], a8["tflops"], a8["frac_of_roofline"], max(0.0, a16["us_full"] - a16["us_matmul"]),
+                r["cublas_bf16_us"]))
+        L.append("")
+    dense = [r for r in rows if r.get("config") == "dense_16bit"]
+    if dense:
+        L += ["## 16-bit dense matmul_t on the tcgen05 kernel", "",
+              "| dtype | M x N x K | µs | TFLOP/s | cuBLAS µs | cuBLAS TFLOP/s | frac |", "|---|---|---|---|---|---|---|"]
+        for r in dense:
+            L.append("| %s | %dx%dx%d | %.1f | %.0f | %.1f | %.0f | %.2f |" % (
+                r["dtype"].replace("torch.", ""), r["m"], r["n"], r["k"], r["us"], r["tflops"], r["cublas_us"],
+                r["cublas_tflops"], r["frac_of_roofline"]))
+        L.append("")
+    grp = [r for r in rows if r.get("config") == "grouped_codebooks"]
+    if grp:
+        L += ["## Grouped per-codebook matmul (%d groups, x [%d,%d,K] viewed [%d,%d,K], W [%d,N,K] bf16, one launch)" % (
+                  grp[0]["groups"], grp[0]["b"], grp[0]["groups"], grp[0]["groups"], grp[0]["b"], grp[0]["groups"]), "",
+              "| stage | N | K | µs | GB/s | frac of HBM | cuBLAS bmm µs |", "|---|---|---|---|---|---|---|"]
+        for r in grp:
+            L.append("| %s | %d | %d | %.1f | %.0f | %.2f | %.1f |" % (r["name"], r["n"], r["k"], r["us"], r["gbs"],
+                                                                     r["frac_of_hbm"], r["cublas_us"]))
+        L.append("")
+    for r in rows:
+        if r.get("config") == "f32_linear":
+            L += ["## f32 linear (x [%d,%d], W [%d,%d], exact f32 products)" % (r["m"], r["k"], r["n"], r["k"]), "",
+                  "%.1f µs, %.0f GB/s (%.2f of %s HBM); cuBLAS SGEMM without TF32 (the reference's default): %.1f µs."
+                  % (r["us"], r["gbs"], r["frac_of_hbm"], pk["kind"], r["cublas_us"]), ""]
+    with open(path, "w") as f:
+        f.write("\n".join(L))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="all")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--md", default=None, help="also write the tables as markdown")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
@@ -174,6 +225,8 @@ def main():
     if a.json:
         with open(a.json, "w") as f:
             json.dump(out, f, indent=1)
+    if a.md:
+        write_md(out, a.md)
 
 
 if __name__ == "__main__":
