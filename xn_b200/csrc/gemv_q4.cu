@@ -227,13 +227,20 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
             const int row_m = 8 * mt + 2 * t + e;
             xs_reg[mt][e] = row_m < m ? __ldg(x_scale + row_m) : 0.0f;
         }
+    // The rest of the first ring-full.  With few activation rows it goes out at once.  From 6 rows on the
+    // activation copies (24+ KB per SM, wanted before any MMA can start) would share the SM's copy
+    // bandwidth with 100 KB of weights that are not needed yet: there the ring is filled only after the
+    // activations have landed (measured: 8.6 -> 7.8 us at 16 rows, 7.5 -> 6.8 us at 8; slower below 6).
+    // What is not in the ring yet is pulled into L2 right away either way, so that later copies into the
+    // ring are L2 hits instead of a second round trip to HBM.
+    const bool defer_ring = m >= 6;
     if (lane == 0) {
-        for (int c = 1; c < depth && c < nchunk; ++c) issue(c, c);  // the rest of the first ring-full
-        // What does not fit in the ring yet is pulled into L2 now, so that the refills of the
-        // ring are L2 hits instead of a second round trip to HBM.
-        if (nchunk > depth) {
-            const unsigned rest = (unsigned)(nu - depth * UPC) * UNIT_BYTES;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wsrc + (size_t)depth * slot_bytes), "r"(rest)
+        const int c1 = defer_ring ? 1 : depth;
+        if (!defer_ring)
+            for (int c = 1; c < depth && c < nchunk; ++c) issue(c, c);
+        if (nchunk > c1) {
+            const unsigned rest = (unsigned)(nu - c1 * UPC) * UNIT_BYTES;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wsrc + (size_t)c1 * slot_bytes), "r"(rest)
                          : "memory");
         }
     }
@@ -248,6 +255,8 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
     bool timed_out = nu > 0 && !mbar_wait(&xbars[SLICED ? ks : 0], 0);
+    if (defer_ring && lane == 0)
+        for (int c = 1; c < depth && c < nchunk; ++c) issue(c, c);
 
     // Chunks of UPC units walk the ring; slot and phase advance without divisions.
     int slot = 0;
