@@ -114,12 +114,19 @@ class Linear:
 # ---------------------------------------------------------------------------------------------
 # Quantized linears (no counterpart in the reference): same forward(x) signature as Linear.
 # ---------------------------------------------------------------------------------------------
-def quantize_rows_i8(x: torch.Tensor):
+def quantize_rows_i8(x: torch.Tensor, out: tuple[torch.Tensor, torch.Tensor] | None = None):
+    """Per-row symmetric int8 quantization; `out` = (xq int8 [m,k], x_scale f32 [m]) reuses buffers."""
     _require_cuda(x)
     x = x.contiguous()
     m, k = x.shape
-    xq = torch.empty(m, k, dtype=torch.int8, device=x.device)
-    xs = torch.empty(m, dtype=torch.float32, device=x.device)
+    if out is not None:
+        xq, xs = out
+        if xq.shape != (m, k) or xq.dtype != torch.int8 or xs.shape != (m,) or xs.dtype != torch.float32:
+            raise ValueError("quantize_rows_i8: out must be (int8 [m,k], float32 [m])")
+        _require_cuda(xq, xs)
+    else:
+        xq = torch.empty(m, k, dtype=torch.int8, device=x.device)
+        xs = torch.empty(m, dtype=torch.float32, device=x.device)
     check(lib().xn_mm_quantize_rows_i8(xq.data_ptr(), xs.data_ptr(), x.data_ptr(), _dtype_code(x), m, k, _stream()))
     return xq, xs
 
