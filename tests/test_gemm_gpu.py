@@ -105,6 +105,24 @@ def test_config1_f32_linear_full_size(xn, oracle, cuda):
     assert oracle.rel_err(y, truth) < 1e-4
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 256, 32), (3, 1000, 4096), (8, 4100, 1024), (9, 272, 8192), (16, 2048, 11264)])
+def test_f32_decode_linear_split_tf32_path(xn, oracle, cuda, m, n, k):
+    """f32 matmul_t with m <= 16, n >= 256, k % 32 == 0 runs on the tensor cores as three tf32 MMAs per
+    product (hi/lo split).  The bound of the path is 1e-4; the split is expected to stay well inside it
+    (about 1e-6 of the output's rms, i.e. 1e-5 in this metric).  Shapes cover both column groups, a ragged last tile, k chunking (k = 8192, 11264) and an
+    activation view with a row pitch."""
+    rng = np.random.default_rng(7 * m + n)
+    xfull = rng.standard_normal((m, k + 32)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.03).astype(np.float32)
+    xv = torch.from_numpy(xfull).to(cuda)[:, :k]  # rows k + 32 apart
+    y = xn.matmul_t(xv, torch.from_numpy(w).to(cuda)).cpu().numpy()
+    x = np.ascontiguousarray(xfull[:, :k])
+    truth = oracle.gemm_f64(0, x.reshape(-1), 0, w.reshape(-1), 0, m, n, k, 1, 0, 0, (1, k), (k, 1))
+    err = oracle.rel_err(y, truth)
+    assert err < 1e-4
+    assert err < 3e-5, err  # what the three-term split actually delivers
+
+
 @pytest.mark.parametrize("dt,m,n,k", [(2, 64, 256, 512), (1, 33, 130, 200), (0, 130, 70, 300), (2, 1, 512, 1024),
                                       (2, 16, 384, 2048)])
 def test_seeded_linear_shapes(xn, oracle, cuda, dt, m, n, k):

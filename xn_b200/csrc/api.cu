@@ -89,9 +89,16 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
     {
         const size_t v = 16 / es;
         if (m <= 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % v == 0 && lhs_rs % v == 0 && rhs_cs % v == 0 &&
-            (lhs_b == 1 || (lhs_b_stride % v == 0 && rhs_b_stride % v == 0)) && aligned(l, 16) && aligned(r, 16))
+            (lhs_b == 1 || (lhs_b_stride % v == 0 && rhs_b_stride % v == 0)) && aligned(l, 16) && aligned(r, 16)) {
+            // f32, one batch, k a multiple of 32, a weight worth streaming: the tensor-core 3xTF32 form
+            // (products to ~1e-6 relative; XN_MM_F32_EXACT=1 keeps the exact-product FFMA kernel)
+            static const bool exact = [] { const char *e = getenv("XN_MM_F32_EXACT"); return e && atoi(e) != 0; }();
+            if (dtype == XN_F32 && !exact && lhs_b == 1 && k % 32 == 0 && n >= 256)
+                return launch_gemv_f32x3((float *)dst, (const float *)l, (const float *)r, m, n, k, dst_rs, lhs_rs, rhs_cs,
+                                         (cudaStream_t)stream);
             return launch_gemv_dense(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_rs, lhs_rs, rhs_cs,
                                      (cudaStream_t)stream);
+        }
     }
     // Linear::forward's form with 16-bit elements -- both operands k-contiguous, rows of dst
     // contiguous -- goes to the tcgen05 kernel when TMA can address it (16-byte pitches and bases).

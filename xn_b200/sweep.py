@@ -201,7 +201,7 @@ def write_md(rows, path):
         L.append("")
     for r in rows:
         if r.get("config") == "f32_linear":
-            L += ["## f32 linear (x [%d,%d], W [%d,%d], exact f32 products)" % (r["m"], r["k"], r["n"], r["k"]), "",
+            L += ["## f32 linear (x [%d,%d], W [%d,%d]; 3xTF32 tensor-core form unless XN_MM_F32_EXACT=1)" % (r["m"], r["k"], r["n"], r["k"]), "",
                   "%.1f µs, %.0f GB/s (%.2f of %s HBM); cuBLAS SGEMM without TF32 (the reference's default): %.1f µs."
                   % (r["us"], r["gbs"], r["frac_of_hbm"], pk["kind"], r["cublas_us"]), ""]
     with open(path, "w") as f:
