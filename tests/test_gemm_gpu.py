@@ -105,6 +105,23 @@ def test_config1_f32_linear_full_size(xn, oracle, cuda):
     assert oracle.rel_err(y, truth) < 1e-4
 
 
+@pytest.mark.parametrize("dt", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 8), (5, 1000, 4096), (8, 4100, 1032), (9, 272, 8192), (16, 2048, 11264),
+                                   (17, 80, 520), (32, 1030, 12288)])
+def test_16bit_decode_linear_tensor_core_gemv(xn, oracle, cuda, dt, m, n, k):
+    """f16 / bf16 matmul_t with m <= 32 runs on the weight-streaming mma.sync kernel: 1, 2 and 4 column
+    groups, ragged last tile, k that is not a multiple of the 32-element step, k chunking (long k with
+    many rows) and an activation view with a row pitch."""
+    rng = np.random.default_rng(11 * m + n + dt)
+    xfull = oracle.from_f32(dt, rng.standard_normal((m, k + 16)).astype(np.float32))
+    w = oracle.from_f32(dt, (rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+    xv = _to_dev(dt, xfull, cuda)[:, :k]  # rows k + 16 apart
+    y = xn.matmul_t(xv, _to_dev(dt, w, cuda))
+    x = np.ascontiguousarray(xfull[:, :k])
+    truth = oracle.gemm_f64(dt, x.reshape(-1), 0, w.reshape(-1), 0, m, n, k, 1, 0, 0, (1, k), (k, 1))
+    assert oracle.rel_err(oracle.to_f32(dt, _to_host(dt, y).reshape(-1)), truth) < TOL[dt]
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 256, 32), (3, 1000, 4096), (8, 4100, 1024), (9, 272, 8192), (16, 2048, 11264)])
 def test_f32_decode_linear_split_tf32_path(xn, oracle, cuda, m, n, k):
     """f32 matmul_t with m <= 16, n >= 256, k % 32 == 0 runs on the tensor cores as three tf32 MMAs per
