@@ -107,10 +107,10 @@ def test_config1_f32_linear_full_size(xn, oracle, cuda):
 
 @pytest.mark.parametrize("dt", [1, 2])
 @pytest.mark.parametrize("m,n,k", [(1, 64, 8), (5, 1000, 4096), (8, 4100, 1032), (9, 272, 8192), (16, 2048, 11264),
-                                   (17, 80, 520), (32, 1030, 12288)])
+                                   (17, 80, 520), (32, 1030, 12288), (33, 200, 4096), (64, 528, 6144)])
 def test_16bit_decode_linear_tensor_core_gemv(xn, oracle, cuda, dt, m, n, k):
-    """f16 / bf16 matmul_t with m <= 32 runs on the weight-streaming mma.sync kernel: 1, 2 and 4 column
-    groups, ragged last tile, k that is not a multiple of the 32-element step, k chunking (long k with
+    """f16 / bf16 matmul_t with m <= 16 runs on the weight-streaming mma.sync kernel (1 or 2 column groups),
+    more rows on the tcgen05 kernel: ragged last tile, k that is not a multiple of the 32-element step, k chunking (long k with
     many rows) and an activation view with a row pitch."""
     rng = np.random.default_rng(11 * m + n + dt)
     xfull = oracle.from_f32(dt, rng.standard_normal((m, k + 16)).astype(np.float32))

@@ -84,9 +84,11 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                "gemm: unsupported dst strides (%zu, %zu) for m:%zu n:%zu", dst_cs, dst_rs, m, n);
     const char *l = static_cast<const char *>(lhs) + lhs_off * es;
     const char *r = static_cast<const char *>(rhs) + rhs_off * es;
-    // Decode-sized matmul_t with 16-bit elements (m <= 32, one batch, both operands k-contiguous, a weight worth
-    // streaming): the tensor-core weight-streaming kernel.
-    if (dtype != XN_F32 && m <= 32 && lhs_b == 1 && n >= 64 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
+    // Decode-sized matmul_t with 16-bit elements (m <= 16, one batch, both operands k-contiguous, a weight worth
+    // streaming): the tensor-core weight-streaming kernel.  (Its mma.sync instructions issue at about one per 32
+    // cycles per SM sub-partition on this architecture -- 1/16 of the tcgen05 rate -- so beyond two column groups
+    // it is bound by them and the tcgen05 kernel below is faster.)
+    if (dtype != XN_F32 && m <= 16 && lhs_b == 1 && n >= 64 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
         lhs_rs % 8 == 0 && rhs_cs % 8 == 0 && aligned(l, 16) && aligned(r, 16) && k <= 0x7fffffff)
         return launch_gemv_h16(dtype, dst, l, r, m, n, k, dst_rs, lhs_rs, rhs_cs, (cudaStream_t)stream);
     // Decode-sized matmul_t (m <= 16, both operands k-contiguous): the weight-streaming kernel with exact f32

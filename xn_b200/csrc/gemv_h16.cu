@@ -1,10 +1,11 @@
-// 16-bit (bf16 / f16) decode-sized matmul_t (lhs [m,k], rhs [n,k] both k-contiguous, m <= 32) on the
+// 16-bit (bf16 / f16) decode-sized matmul_t (lhs [m,k], rhs [n,k] both k-contiguous, m <= 16) on the
 // tensor cores: the decode-time Linear::forward of an unquantized model, which the reference sends to
 // cublasGemmStridedBatchedEx with f32 accumulation (xn-core/src/cuda_backend.rs:2151-2257).
 //
 // HBM-bound by the weights.  Output rows ride the 16-row dimension of mma.sync.m16n8k16 (a native
-// tensor instruction on sm_100a for both 16-bit types), the activation rows its 8 columns (1, 2 or 4
-// column groups).  A lane's 128-bit load of a weight row (8 consecutive k) feeds two MMAs through a
+// tensor instruction on sm_100a for both 16-bit types), the activation rows its 8 columns (1 or 2 column
+// groups; the instruction issues at about one per 32 cycles per SM sub-partition here, so with 4 groups the
+// kernel would be bound by it: 35 us at m = 32 on [12288, 4096] against 18 us at m <= 8).  A lane's 128-bit load of a weight row (8 consecutive k) feeds two MMAs through a
 // fixed k permutation that the activation fragment follows, so a 64-byte k step costs two loads and,
 // per column group, one 128-bit shared-memory read and two MMAs: about a dozen instructions per KB of
 // weights (the FFMA kernel this replaces for these shapes needed one FMA per weight element and
@@ -187,13 +188,12 @@ int launch_t(void *dst, const void *lhs, const void *rhs, size_t m, size_t n, si
     T *y = (T *)dst;
     const T *x = (const T *)lhs, *w = (const T *)rhs;
     if (m <= 8) return launch<T, 1>(y, x, w, (int)m, n, (int)k, dst_rs, lhs_rs, rhs_cs, st);
-    if (m <= 16) return launch<T, 2>(y, x, w, (int)m, n, (int)k, dst_rs, lhs_rs, rhs_cs, st);
-    return launch<T, 4>(y, x, w, (int)m, n, (int)k, dst_rs, lhs_rs, rhs_cs, st);
+    return launch<T, 2>(y, x, w, (int)m, n, (int)k, dst_rs, lhs_rs, rhs_cs, st);
 }
 
 }  // namespace
 
-// Caller guarantees: f16 or bf16, m <= 32, one batch, k a multiple of 8, lhs/rhs k-contiguous with pitches that
+// Caller guarantees: f16 or bf16, m <= 16, one batch, k a multiple of 8, lhs/rhs k-contiguous with pitches that
 // are multiples of 8 elements, 16-byte aligned bases, dst rows contiguous.
 int launch_gemv_h16(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k, size_t dst_rs,
                     size_t lhs_rs, size_t rhs_cs, cudaStream_t st) {
