@@ -337,8 +337,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 // per SM.  D[n, m] is written transposed: lane = output channel, column = activation row.
 // ---------------------------------------------------------------------------------------------
 struct SkinnyArgs {
-    __nv_bfloat16 *y;
-    const float *x_scale, *w_scale;
+    void *y;     // [M, ldy] bf16 (fp8 and bf16 operands) or f16
+    int ldy;
+    const float *x_scale, *w_scale;  // fp8 operands only
     float *partials;     // scratch: [2 * grid][MB][128] f32 partial accumulators of split tiles
     unsigned *counters;  // scratch: [tiles][4] arrival counts per (tile, lane quarter); zero between launches
     int M, N, K;
@@ -362,6 +363,8 @@ __device__ __forceinline__ int unit_owner(int u, int uq, int ur) {  // the CTA w
     return u < big ? (int)((unsigned)u / (unsigned)(uq + 1)) : ur + (int)((unsigned)(u - big) / (unsigned)uq);
 }
 
+// KIND: 0 = fp8 pieces -> bf16 out (scaled), 1 = bf16 -> bf16, 2 = f16 -> f16 (one piece, no scales)
+template <int KIND>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x0,
                            const __grid_constant__ CUtensorMap map_x1, const SkinnyArgs args) {
@@ -373,7 +376,8 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     // K-major operand of np * MB rows; D columns [0, MB) are the hi products, [MB, 2 MB) the lo products
     // (an MMA instruction costs about 130 cycles here however small N is: fewer, wider MMAs).
     const int NB = args.np * args.MB;  // MMA N dimension = TMEM columns of one accumulator buffer
-    const uint32_t IDESC = instr_desc(0, 0, NB);
+    constexpr bool F8 = KIND == 0;
+    const uint32_t IDESC = KIND == 1 ? instr_desc(1, 1, NB) : instr_desc(0, 0, NB);
     const int TMEM_COLS = 2 * NB <= 32 ? 32 : (2 * NB <= 64 ? 64 : (2 * NB <= 128 ? 128 : (2 * NB <= 256 ? 256 : 512)));
 
     extern __shared__ unsigned char smem_raw[];
@@ -382,7 +386,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (args.K + BKB - 1) / BKB;
+    const int num_kb = (args.K + (KIND == 0 ? BKB : BKB / 2) - 1) / (KIND == 0 ? BKB : BKB / 2);
     const int uq = args.uq, ur = args.ur;
     const int u0 = unit_begin(blockIdx.x, uq, ur), u1 = unit_begin(blockIdx.x + 1, uq, ur);
 
@@ -419,9 +423,10 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(st, &map_w, kb * BKB, tile * BM, &full[s]);
-                    tma_load_2d(st + W_BYTES, &map_x0, kb * BKB, 0, &full[s]);
-                    if (args.np == 2) tma_load_2d(st + W_BYTES + X_BYTES, &map_x1, kb * BKB, 0, &full[s]);
+                    constexpr int BK = F8 ? BKB : BKB / 2;  // k elements per stage
+                    tma_load_2d(st, &map_w, kb * BK, tile * BM, &full[s]);
+                    tma_load_2d(st + W_BYTES, &map_x0, kb * BK, 0, &full[s]);
+                    if (args.np == 2) tma_load_2d(st + W_BYTES + X_BYTES, &map_x1, kb * BK, 0, &full[s]);
                 }
                 u += kb1 - kb0;
             }
@@ -448,7 +453,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
-                        umma<true>(d_tmem, dw + adv, dx + adv, IDESC, (kb > kb0) || ks != 0);
+                        umma<F8>(d_tmem, dw + adv, dx + adv, IDESC, (kb > kb0) || ks != 0);
                     }
                     umma_commit(&empty[s]);
                 }
@@ -470,7 +475,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             if (!mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int ch = tile * BM + q * 32 + lane;  // output channel of this lane
-            const float ws = ch < args.N ? __ldg(args.w_scale + ch) : 0.0f;
+            const float ws = !F8 ? 1.0f : (ch < args.N ? __ldg(args.w_scale + ch) : 0.0f);
             // a split tile's segment is this CTA's first one iff its range starts inside that tile
             const int my_slot = 2 * blockIdx.x + ((u == u0) ? 0 : 1);
             float *mine = args.partials + (size_t)my_slot * slot_elems + q * 32 + lane;
@@ -500,9 +505,11 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int mrow = c + j;
-                            if (mrow < args.M)  // 32 lanes = 32 consecutive channels of one activation row
-                                args.y[(size_t)mrow * args.N + ch] =
-                                    __float2bfloat16_rn(ws * (__ldg(args.x_scale + mrow) * __uint_as_float(v[j])));
+                            if (mrow < args.M) {  // 32 lanes = 32 consecutive channels of one activation row
+                                const float val = F8 ? ws * (__ldg(args.x_scale + mrow) * __uint_as_float(v[j])) : __uint_as_float(v[j]);
+                                if (KIND == 2) reinterpret_cast<__half *>(args.y)[(size_t)mrow * args.ldy + ch] = __float2half_rn(val);
+                                else reinterpret_cast<__nv_bfloat16 *>(args.y)[(size_t)mrow * args.ldy + ch] = __float2bfloat16_rn(val);
+                            }
                         }
                     }
                 } else {
@@ -553,9 +560,11 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                             }
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (m0 + j < args.M)
-                                    args.y[(size_t)(m0 + j) * args.N + ch] =
-                                        __float2bfloat16_rn(ws * (__ldg(args.x_scale + m0 + j) * sum[j]));
+                                if (m0 + j < args.M) {
+                                    const float val = F8 ? ws * (__ldg(args.x_scale + m0 + j) * sum[j]) : sum[j];
+                                    if (KIND == 2) reinterpret_cast<__half *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2half_rn(val);
+                                    else reinterpret_cast<__nv_bfloat16 *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2bfloat16_rn(val);
+                                }
                         }
                     }
                 }
@@ -710,18 +719,22 @@ int skinny_scratch(size_t partial_bytes, size_t ncounters, SkinnyScratch *out) {
     return XN_OK;
 }
 
-// Skinny path: 16 < m <= 128.
-int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
-                             const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
+// Skinny path, m <= 64.  KIND 0: e4m3 pieces x0 (hi) and optional x1 (lo) with scales; KIND 1 / 2: bf16 / f16
+// operands (x1, scales unused).  Strides in elements.
+template <int KIND>
+int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ldx, const float *x_scale, const void *w,
+                  size_t ldw, const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
+    constexpr int ELEM = KIND == 0 ? 1 : 2;
+    constexpr int BK = BKB / ELEM;  // k elements per stage
     SkinnyArgs a{};
-    a.y = (__nv_bfloat16 *)y; a.x_scale = x_scale; a.w_scale = w_scale;
+    a.y = y; a.ldy = (int)ldy; a.x_scale = x_scale; a.w_scale = w_scale;
     a.M = (int)m; a.N = (int)n; a.K = (int)k;
     a.MB = (int)((m + 15) / 16 * 16);
-    a.np = x_lo ? 2 : 1;
+    a.np = x1 ? 2 : 1;
     const int stage = BM * BKB + a.np * a.MB * BKB;
     a.nstage = (196 * 1024) / stage > 8 ? 8 : (196 * 1024) / stage;
     const int tiles = (int)((n + BM - 1) / BM);
-    const int num_kb = (int)((k + BKB - 1) / BKB);
+    const int num_kb = (int)((k + BK - 1) / BK);
     const int sms = sm_count();
     const long long total = (long long)tiles * num_kb;
     // at least 4 k stages per CTA, so that a split never degenerates into single-stage crumbs
@@ -731,7 +744,7 @@ int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, 
     // k-stage granularity so that every SM streams its share of the weights and issues its share of the MMAs
     // (an MMA costs ~130 cycles whatever its N, so the MMA count per CTA is what bounds a skinny problem).
     if (tiles <= sms && tiles * 100 >= sms * 90) grid = tiles;
-    XN_REQUIRE(total < (1ll << 30), "linear_fp8: problem too large for the skinny kernel's 32-bit unit index");
+    XN_REQUIRE(total < (1ll << 30), "skinny matmul: problem too large for the kernel's 32-bit unit index");
     a.uq = (int)(total / grid);
     a.ur = (int)(total % grid);
     SkinnyScratch sc;
@@ -740,14 +753,15 @@ int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, 
     a.partials = sc.partials;
     a.counters = sc.counters;
     CUtensorMap mw, mx0, mx1;
-    rc = make_map(&mw, wq, 1, n, k, k, BM);
+    rc = make_map(&mw, w, ELEM, n, k, ldw, BM);
     if (rc) return rc;
-    rc = make_map(&mx0, x_hi, 1, m, k, k, a.MB);
+    rc = make_map(&mx0, x0, ELEM, m, k, ldx, a.MB);
     if (rc) return rc;
-    rc = make_map(&mx1, x_lo ? x_lo : x_hi, 1, m, k, k, a.MB);
+    rc = make_map(&mx1, x1 ? x1 : x0, ELEM, m, k, ldx, a.MB);
     if (rc) return rc;
     const size_t smem = (size_t)a.nstage * stage + 1024;
-    XN_ENSURE_SMEM(gemm_tcgen05_skinny_kernel, smem);
+    auto kern = gemm_tcgen05_skinny_kernel<KIND>;
+    XN_ENSURE_SMEM(kern, smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(NTHREADS);
@@ -758,8 +772,13 @@ int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_skinny_kernel, mw, mx0, mx1, a));
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, mw, mx0, mx1, a));
     return XN_OK;
+}
+
+int launch_linear_fp8_skinny(void *y, const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
+                             const float *w_scale, size_t m, size_t n, size_t k, cudaStream_t st) {
+    return launch_skinny<0>(y, n, x_hi, x_lo, k, x_scale, wq, k, w_scale, m, n, k, st);
 }
 
 // y bf16 [m,n] = x_scale[m] * w_scale[n] * (x_hi (+ x_lo)) * wq^T, all operands row-major e4m3.
@@ -789,6 +808,14 @@ int launch_linear_fp8_gemm_scatter(void *const *y_dsts, int ndst, size_t ldy, si
 // rhs [b][n,k]^T (row stride ldb, batch stride rhs_bs); dt BF16 or F16; one launch for all batches.
 int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
                          size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st) {
+    // Up to 64 rows, one batch: the skinny form (weights on the tensor-memory lanes, work split at k-stage
+    // granularity over all SMs) -- a tiled launch would have too few tiles and too many MMAs per CTA.
+    static const size_t skinny_max = [] { const char *e = getenv("XN_MM_SKINNY16_MAX_M"); return e ? (size_t)atoi(e) : (size_t)64; }();
+    // (measured on the transformer shapes: always better up to 32 rows; from 33 to 64 only when the tiled kernel
+    // would have fewer 64-column tiles than there are SMs)
+    if (batch == 1 && m <= skinny_max && (m <= 32 || (m <= 64 && (n + 63) / 64 < (size_t)sm_count())))
+        return dt == XN_BF16 ? launch_skinny<1>(dst, ldd, lhs, nullptr, lda, nullptr, rhs, ldb, nullptr, m, n, k, st)
+                             : launch_skinny<2>(dst, ldd, lhs, nullptr, lda, nullptr, rhs, ldb, nullptr, m, n, k, st);
     GemmArgs a{};
     a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
