@@ -13,6 +13,7 @@ import argparse
 import json
 import os
 import sys
+import time
 
 import torch
 
@@ -46,6 +47,11 @@ def time_graph(fns, reps_per_fn=1, iters=5):
     torch.cuda.synchronize()
     for _ in range(3):
         g.replay()
+    torch.cuda.synchronize()
+    # let the part settle after the previous point: a bandwidth-bound point timed right behind a
+    # power-capped GEMM reads 15-20 % slow (for this library and for cuBLAS alike)
+    time.sleep(0.4)
+    g.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -104,7 +110,10 @@ def sweep_fp8(out, dev, pk):
 
 def sweep_dense(out, dev, pk):
     for dt in (torch.bfloat16, torch.float16):
-        for m, n, k in ((4096, 4096, 4096), (8192, 8192, 8192), (1024, 12288, 4096), (256, 12288, 4096), (64, 12288, 4096)):
+        shapes = [(4096, 4096, 4096), (8192, 8192, 8192), (1024, 12288, 4096), (256, 12288, 4096), (64, 12288, 4096)]
+        if dt == torch.bfloat16:  # the reference's decode path: unquantized bf16 weights, decode-sized m
+            shapes += [(m, n, k) for (n, k) in ((12288, 4096), (4096, 4096), (22528, 4096), (4096, 11264)) for m in (1, 16, 32)]
+        for m, n, k in shapes:
             R = replicas_for(2 * n * k, hi=8)
             ws = [(torch.randn(n, k, device=dev) * 0.05).to(dt) for _ in range(R)]
             x = torch.randn(m, k, device=dev).to(dt)
@@ -183,7 +192,7 @@ def write_md(rows, path):
         L.append("")
     dense = [r for r in rows if r.get("config") == "dense_16bit"]
     if dense:
-        L += ["## 16-bit dense matmul_t on the tcgen05 kernel", "",
+        L += ["## 16-bit dense matmul_t (tcgen05 tiled kernel; skinny tcgen05 form for 17-64 rows; mma.sync GEMV up to 16 rows)", "",
               "| dtype | M x N x K | µs | TFLOP/s | cuBLAS µs | cuBLAS TFLOP/s | frac |", "|---|---|---|---|---|---|---|"]
         for r in dense:
             L.append("| %s | %dx%dx%d | %.1f | %.0f | %.1f | %.0f | %.2f |" % (
