@@ -88,14 +88,21 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
     // streaming): the tensor-core weight-streaming kernel.  (Its mma.sync instructions issue at about one per 32
     // cycles per SM sub-partition on this architecture -- 1/16 of the tcgen05 rate -- so beyond two column groups
     // it is bound by them and the tcgen05 kernel below is faster.)
-    if (dtype != XN_F32 && m <= 16 && lhs_b == 1 && n >= 64 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
+    const bool h16_fits = dtype != XN_F32 && m <= 16 && k <= 0x7fffffff && gemv_h16_single_chunk(m, k);
+    // what the tcgen05 kernels need: both operands k-contiguous, dst rows contiguous, 16-byte pitches and bases
+    const bool tn16_ok = dtype != XN_F32 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 && lhs_rs % 8 == 0 &&
+                         rhs_cs % 8 == 0 && aligned(l, 16) && aligned(r, 16) && m <= 0x7fffffff && n <= 0x7fffffff &&
+                         k <= 0x7fffffff && dst_rs <= 0x7fffffff;
+    // up to 16 rows with k too long for the weight-streaming kernel's staged activations: tensor-memory skinny form
+    const bool long_k_skinny = tn16_ok && m <= 16 && !h16_fits && n >= 256 && lhs_b == 1;
+    if (h16_fits && lhs_b == 1 && n >= 64 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
         lhs_rs % 8 == 0 && rhs_cs % 8 == 0 && aligned(l, 16) && aligned(r, 16) && k <= 0x7fffffff)
         return launch_gemv_h16(dtype, dst, l, r, m, n, k, dst_rs, lhs_rs, rhs_cs, (cudaStream_t)stream);
     // Decode-sized matmul_t (m <= 16, both operands k-contiguous): the weight-streaming kernel with exact f32
     // products, for all three element types and any batch count.
     {
         const size_t v = 16 / es;
-        if (m <= 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % v == 0 && lhs_rs % v == 0 && rhs_cs % v == 0 &&
+        if (m <= 16 && !long_k_skinny && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % v == 0 && lhs_rs % v == 0 && rhs_cs % v == 0 &&
             (lhs_b == 1 || (lhs_b_stride % v == 0 && rhs_b_stride % v == 0)) && aligned(l, 16) && aligned(r, 16)) {
             // f32, one batch, k a multiple of 32, a weight worth streaming: the tensor-core 3xTF32 form
             // (products to ~1e-6 relative; XN_MM_F32_EXACT=1 keeps the exact-product FFMA kernel)
@@ -110,9 +117,7 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
     // Linear::forward's form with 16-bit elements -- both operands k-contiguous, rows of dst
     // contiguous -- goes to the tcgen05 kernel when TMA can address it (16-byte pitches and bases).
     // The strided-batched / grouped form (lhs_b > 1 with per-batch weights) is one launch as well.
-    if (dtype != XN_F32 && m > 16 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 && k % 8 == 0 &&
-        lhs_rs % 8 == 0 && rhs_cs % 8 == 0 && aligned(l, 16) && aligned(r, 16) && m <= 0x7fffffff &&
-        n <= 0x7fffffff && k <= 0x7fffffff && dst_rs <= 0x7fffffff &&
+    if (tn16_ok && (m > 16 || long_k_skinny) &&
         (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 && rhs_b_stride != 0 &&
                         lhs_b_stride != 0)))
         return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,

@@ -96,6 +96,7 @@ int launch_gemm_generic(xn_dtype dt, void *dst, const void *lhs, const void *rhs
                         size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs, size_t rhs_cs,
                         size_t rhs_rs, cudaStream_t st);
 
+bool gemv_h16_single_chunk(size_t m, size_t k);
 int launch_gemv_h16(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k, size_t dst_rs,
                     size_t lhs_rs, size_t rhs_cs, cudaStream_t st);
 int launch_gemv_f32x3(float *dst, const float *lhs, const float *rhs, size_t m, size_t n, size_t k, size_t dst_rs,

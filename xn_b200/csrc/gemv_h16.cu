@@ -193,6 +193,13 @@ int launch_t(void *dst, const void *lhs, const void *rhs, size_t m, size_t n, si
 
 }  // namespace
 
+// True when the staged activations of an m x k problem fit in shared memory at once (no k chunking): the
+// case this kernel is good at.  Chunked, it loses to the tcgen05 skinny kernel.
+bool gemv_h16_single_chunk(size_t m, size_t k) {
+    const size_t mt = m <= 8 ? 1 : 2;
+    return mt * 8 * (size_t)h_pitch((int)((k + 255) / 256 * 256)) <= (size_t)H_SMEM - H_WARPS * mt * 4 * 32 * 4;
+}
+
 // Caller guarantees: f16 or bf16, m <= 16, one batch, k a multiple of 8, lhs/rhs k-contiguous with pitches that
 // are multiples of 8 elements, 16-byte aligned bases, dst rows contiguous.
 int launch_gemv_h16(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k, size_t dst_rs,
