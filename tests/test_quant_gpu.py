@@ -235,3 +235,29 @@ def test_linear_q8_block_int8_weights(xn, oracle, cuda, m, n, k):
     assert np.array_equal(part.cpu().numpy(), want_p)
     assert torch.equal(y, y2)
     assert oracle.rel_err(y.cpu().numpy(), want_y) < 1e-4
+
+
+def test_quantized_checkpoint_feeds_the_kernels_unchanged(xn, oracle, cuda, tmp_path):
+    """Weights quantized on the host, written to a quantized safetensors file, read back and uploaded as
+    stored give bit-identical packed bytes to the device quantizers, and the linears run from them."""
+    import os
+
+    from xn_b200 import checkpoint as ck
+
+    rng = np.random.default_rng(21)
+    w4 = (rng.standard_normal((304, 512)) * 0.02).astype(np.float32)
+    w8 = (rng.standard_normal((200, 384)) * 0.05).astype(np.float32)
+    path = os.path.join(tmp_path, "m.safetensors")
+    ck.save_quantized(path, {"a": w4, "b": w8}, {"a": "q4", "b": "fp8"})
+    linears, _ = ck.load_quantized(path)
+    la = ck.linear_from_entry(linears["a"], cuda)
+    lb = ck.linear_from_entry(linears["b"], cuda)
+    assert torch.equal(la.wq.cpu(), xn.quantize_weights_q4(torch.from_numpy(w4).to(cuda)).cpu())
+    dq, ds = xn.quantize_weights_fp8(torch.from_numpy(w8).to(cuda))
+    assert torch.equal(lb.wq.cpu(), dq.cpu()) and torch.equal(lb.ws.cpu(), ds.cpu())
+    x = rng.standard_normal((5, 512)).astype(np.float32)
+    y = la(torch.from_numpy(x).to(cuda)).cpu().numpy()
+    xq, xs = oracle.quantize_rows_i8(x)
+    q, s = oracle.quantize_q4(w4)
+    ref, _ = oracle.linear_q(xq, xs, q, s)
+    assert oracle.rel_err(y, ref) < 1e-4

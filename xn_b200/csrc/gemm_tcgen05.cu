@@ -45,6 +45,9 @@ __device__ __forceinline__ void mbar_init(uint64_t *b, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *b, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx_only(uint64_t *b, unsigned bytes) {  // no arrival
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t *b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
@@ -389,6 +392,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int num_kb = (args.K + (KIND == 0 ? BKB : BKB / 2) - 1) / (KIND == 0 ? BKB : BKB / 2);
     const int uq = args.uq, ur = args.ur;
     const int u0 = unit_begin(blockIdx.x, uq, ur), u1 = unit_begin(blockIdx.x + 1, uq, ur);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -406,12 +410,24 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
-    // Programmatic dependent launch: everything above overlapped the previous kernel's tail.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    // Programmatic dependent launch.  The kernel is small enough (shared memory, registers, tensor-memory
+    // columns) for two of them to share an SM, so the next launch's CTAs set up, allocate and -- since
+    // weights do not depend on the previous kernel -- fetch the weight halves of their first ring-full while
+    // this one is still running.  Activations, scales, the output and the split-tile scratch belong to the
+    // stream order: the producer waits before its first activation load, the epilogue warps before their
+    // first global access; the MMA warp only reads shared memory.
     if (warp == 0) {
         if (lane == 0) {
+            constexpr int BK = F8 ? BKB : BKB / 2;  // k elements per stage
+            const int pre = min(NSTAGE, u1 - u0);
+            for (int it = 0; it < pre; ++it) {
+                const int u = u0 + it;
+                const int tile = (int)((unsigned)u / (unsigned)num_kb), kb = u - tile * num_kb;
+                mbar_expect_tx_only(&full[it], (unsigned)W_BYTES);
+                tma_load_2d(smem + (size_t)it * STAGE_BYTES, &map_w, kb * BK, tile * BM, &full[it]);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int it = 0;
             bool ok = true;
             for (int u = u0; u < u1 && ok;) {
@@ -420,11 +436,14 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
-                    if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
-                    constexpr int BK = F8 ? BKB : BKB / 2;  // k elements per stage
-                    tma_load_2d(st, &map_w, kb * BK, tile * BM, &full[s]);
+                    if (it < pre) {  // the weights of this stage are already on their way
+                        mbar_expect_tx(&full[s], (unsigned)(args.np * X_BYTES));
+                    } else {
+                        if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
+                        mbar_expect_tx(&full[s], STAGE_BYTES);
+                        tma_load_2d(st, &map_w, kb * BK, tile * BM, &full[s]);
+                    }
                     tma_load_2d(st + W_BYTES, &map_x0, kb * BK, 0, &full[s]);
                     if (args.np == 2) tma_load_2d(st + W_BYTES + X_BYTES, &map_x1, kb * BK, 0, &full[s]);
                 }
@@ -466,6 +485,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         int t_local = 0;
         bool ok = true;
         const size_t slot_elems = (size_t)args.MB * BM;
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int u = u0; u < u1 && ok; ++t_local) {
             const int tile = (int)((unsigned)u / (unsigned)num_kb), kb0 = u - tile * num_kb;
             const int kb1 = min(num_kb, kb0 + (u1 - u));
@@ -732,7 +752,10 @@ int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ld
     a.MB = (int)((m + 15) / 16 * 16);
     a.np = x1 ? 2 : 1;
     const int stage = BM * BKB + a.np * a.MB * BKB;
-    a.nstage = (196 * 1024) / stage > 8 ? 8 : (196 * 1024) / stage;
+    // a ring of about 100 KB: two CTAs (this launch's and the next one's, see the kernel) fit an SM, and the
+    // kernel is not bound by bytes in flight (3 to 8 stages measured the same)
+    a.nstage = (100 * 1024) / stage > 8 ? 8 : (100 * 1024) / stage;
+    if (a.nstage < 2) a.nstage = 2;
     const int tiles = (int)((n + BM - 1) / BM);
     const int num_kb = (int)((k + BK - 1) / BK);
     const int sms = sm_count();
