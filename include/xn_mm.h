@@ -196,6 +196,17 @@ int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, cons
 int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t q_batch_stride, const void *k_cache_bf16,
                            const void *v_cache_bf16, const float *mask_or_null, size_t batch, size_t heads,
                            size_t context, size_t head_dim, float scale, void *stream);
+/* The same attention with the context cut into slices handled by different CTAs and merged by a
+ * log-sum-exp combine: with few streams one CTA per (stream, head) leaves most of the GPU idle (8 streams
+ * x 32 heads = 256 CTAs of 128 threads on 148 SMs).  The number of slices is chosen inside (1 when
+ * batch * heads already fills the machine: then this is xn_mm_decode_attention).  `workspace` holds the
+ * slices' partial results: xn_mm_decode_attention_workspace_bytes(batch, heads, context) bytes of device
+ * memory (may be 0), owned by the caller and reusable by every call on the same stream. */
+size_t xn_mm_decode_attention_workspace_bytes(size_t batch, size_t heads, size_t context);
+int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, size_t q_batch_stride, const void *k_cache_bf16,
+                                 const void *v_cache_bf16, const float *mask_or_null, size_t batch, size_t heads,
+                                 size_t context, size_t head_dim, float scale, void *workspace, size_t workspace_bytes,
+                                 void *stream);
 
 /* Allocation-free form of xn_mm_linear_fp8.  It has no counterpart in the reference.  For hosts
  * that must not (or cannot) allocate device memory at call time -- a serving loop whose device

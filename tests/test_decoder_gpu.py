@@ -157,3 +157,49 @@ def test_decode_attention_full_width_slice(xn, oracle, cuda):
     sc = torch.einsum("bhd,bhcd->bhc", q, k.double()) / math.sqrt(hd)
     ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(sc, -1), v.double()).reshape(B, H * hd).cpu().numpy()
     assert oracle.rel_err(out.float().cpu().numpy(), ref) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,ctx,masked", [(1, 3000, False), (2, 777, True), (8, 4096, True), (40, 512, False)])
+def test_decode_attention_split_context_matches_single_pass(xn, oracle, cuda, B, ctx, masked):
+    """The context-split form (slices merged by log-sum-exp) against the one-pass kernel and against f64:
+    few streams (several slices), a ragged context, masked slices (a fully masked slice must drop out), and a
+    batch large enough for the split to switch itself off."""
+    H, hd = 4, 128
+    g = torch.Generator().manual_seed(B * 1000 + ctx)
+    q = torch.randn(B, H, hd, generator=g).bfloat16().to(cuda)
+    k = torch.randn(B, H, ctx, hd, generator=g).bfloat16().to(cuda)
+    v = torch.randn(B, H, ctx, hd, generator=g).bfloat16().to(cuda)
+    mask = None
+    if masked:
+        mask = torch.zeros(B, ctx)
+        mask[:, ctx // 3: ctx // 3 + ctx // 2] = float("-inf")   # covers whole slices
+        mask = mask.to(cuda)
+    L = xn.lib()
+    ws_bytes = int(L.xn_mm_decode_attention_workspace_bytes(B, H, ctx))
+    if B <= 8:
+        assert ws_bytes > 0
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=cuda)
+    out_s = torch.empty(B, H, hd, dtype=torch.bfloat16, device=cuda)
+    out_1 = torch.empty_like(out_s)
+    scale = 1.0 / np.sqrt(hd)
+    mp = mask.data_ptr() if mask is not None else None
+    xn._lib.check(L.xn_mm_decode_attention_split(out_s.data_ptr(), q.data_ptr(), H * hd, k.data_ptr(), v.data_ptr(), mp, B, H,
+                                                 ctx, hd, scale, ws.data_ptr(), ws_bytes, None))
+    xn._lib.check(L.xn_mm_decode_attention(out_1.data_ptr(), q.data_ptr(), H * hd, k.data_ptr(), v.data_ptr(), mp, B, H, ctx,
+                                           hd, scale, None))
+    torch.cuda.synchronize()
+    a, b = out_s.float().cpu().numpy(), out_1.float().cpu().numpy()
+    assert np.max(np.abs(a - b)) <= 2e-2 * max(1e-3, float(np.max(np.abs(b))))  # both round to bf16 once
+    # f64 reference
+    qd, kd, vd = q.double().cpu(), k.double().cpu(), v.double().cpu()
+    s = torch.einsum("bhd,bhcd->bhc", qd, kd) * scale
+    if mask is not None:
+        s = s + mask.double().cpu()[:, None, :]
+    ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(s, dim=-1), vd).numpy()
+    assert oracle.rel_err(a.reshape(-1), ref.reshape(-1)) < 1e-2
+    # too small a workspace is refused, not overrun
+    if ws_bytes:
+        rc = L.xn_mm_decode_attention_split(out_s.data_ptr(), q.data_ptr(), H * hd, k.data_ptr(), v.data_ptr(), mp, B, H, ctx,
+                                            hd, scale, ws.data_ptr(), ws_bytes - 4, None)
+        assert rc == 4

@@ -176,8 +176,12 @@ __global__ void __launch_bounds__(128)
 decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ q,
                         const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
                         const float *__restrict__ mask, size_t heads, size_t context, size_t q_batch_stride,
-                        float scale) {
+                        float scale, size_t rows_per_split, float *__restrict__ partial) {
+    // blockIdx.y = slice of the context (rows [row_lo, row_hi)); with one slice the result goes straight to `out`,
+    // otherwise the slice's running maximum, sum and unnormalised output go to `partial` for the combine kernel
     const size_t bh = blockIdx.x, b = bh / heads;
+    const size_t row_lo = (size_t)blockIdx.y * rows_per_split;
+    const size_t row_hi = row_lo + rows_per_split < context ? row_lo + rows_per_split : context;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half = lane >> 4, l16 = lane & 15;
     const int group = warp * 2 + half;  // 8 half-warps stride over the rows
@@ -192,14 +196,14 @@ decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__
     const float *mrow = mask ? mask + b * context : nullptr;
     float m_run = -INFINITY, l_run = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     constexpr int U = 4;
-    for (size_t base = 0; base < context; base += 8 * U) {  // uniform trip count across the CTA
+    for (size_t base = row_lo; base < row_hi; base += 8 * U) {  // uniform trip count across the CTA
         const size_t r0 = base + group;
         uint4 kr[U], vr[U];
         float s[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const size_t r = r0 + 8 * u;
-            if (r < context) {
+            if (r < row_hi) {
                 kr[u] = ldg_stream(kb + r * HD + l16 * 8);
                 vr[u] = ldg_stream(vb + r * HD + l16 * 8);
             } else {
@@ -216,7 +220,7 @@ decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);  // within the half-warp
             const size_t r = r0 + 8 * u;
-            if (r >= context) d = -INFINITY;
+            if (r >= row_hi) d = -INFINITY;
             else if (mrow) d += mrow[r];
             s[u] = d;
         }
@@ -255,8 +259,33 @@ decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__
             l += w * sm_l[gI];
             o += w * sm_acc[gI][threadIdx.x];
         }
-        out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
+        if (gridDim.y == 1) {
+            out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
+        } else {
+            float *p = partial + (bh * gridDim.y + blockIdx.y) * (HD + 2);
+            p[2 + threadIdx.x] = o;
+            if (threadIdx.x == 0) { p[0] = mx; p[1] = l; }
+        }
     }
+}
+
+// Log-sum-exp merge of the context slices of one (stream, head): out = sum_s w_s o_s / sum_s w_s l_s,
+// w_s = exp(m_s - max_s m_s).  One CTA of 128 threads per (stream, head).
+__global__ void __launch_bounds__(HD)
+decode_attention_combine_kernel(__nv_bfloat16 *__restrict__ out, const float *__restrict__ partial, int splits) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t bh = blockIdx.x;
+    const float *p = partial + bh * splits * (HD + 2);
+    float mx = -INFINITY;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p[(size_t)s * (HD + 2)]);
+    float l = 0.0f, o = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = p[(size_t)s * (HD + 2)];
+        const float w = m == -INFINITY ? 0.0f : __expf(m - mx);
+        l += w * p[(size_t)s * (HD + 2) + 1];
+        o += w * p[(size_t)s * (HD + 2) + 2 + threadIdx.x];
+    }
+    out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
 }
 
 }  // namespace
@@ -351,10 +380,20 @@ extern "C" int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, siz
     return XN_OK;
 }
 
-extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t q_batch_stride,
-                                      const void *k_cache_bf16, const void *v_cache_bf16, const float *mask_or_null,
-                                      size_t batch, size_t heads, size_t context, size_t head_dim, float scale,
-                                      void *stream) {
+namespace {
+// Slices of the context per (stream, head): enough CTAs to keep every SM busy with several of them
+// (one slice already does that from about 24 streams x 32 heads on), each slice at least 256 rows.
+int attention_splits(size_t batch, size_t heads, size_t context) {
+    const size_t want = (size_t)sm_count() * 6;
+    size_t s = (want + batch * heads - 1) / (batch * heads);
+    if (s > context / 256) s = context / 256;
+    if (s > 16) s = 16;
+    return s < 1 ? 1 : (int)s;
+}
+
+int decode_attention_impl(void *out_bf16, const void *q_bf16, size_t q_batch_stride, const void *k_cache_bf16,
+                          const void *v_cache_bf16, const float *mask_or_null, size_t batch, size_t heads, size_t context,
+                          size_t head_dim, float scale, void *workspace, size_t workspace_bytes, bool use_ws, void *stream) {
     XN_REQUIRE(head_dim == 128, "decode_attention: head_dim %zu is not supported (128 only)", head_dim);
     if (batch == 0 || heads == 0) return XN_OK;
     XN_REQUIRE(context > 0, "decode_attention: empty context");
@@ -362,9 +401,56 @@ extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t
     XN_REQUIRE(aligned(q_bf16, 16) && aligned(k_cache_bf16, 16) && aligned(v_cache_bf16, 16) && q_batch_stride % 8 == 0,
                "decode_attention: q and the caches must be 16-byte aligned (q_batch_stride a multiple of 8)");
     XN_REQUIRE(batch * heads <= 0x7fffffffull, "decode_attention: too many (stream, head) pairs");
-    decode_attention_kernel<<<(unsigned)(batch * heads), 128, 0, (cudaStream_t)stream>>>(
+    int splits = use_ws ? attention_splits(batch, heads, context) : 1;
+    if (splits > 1) {
+        const size_t need = batch * heads * splits * (HD + 2) * sizeof(float);
+        if (workspace_bytes < need || !workspace)
+            return fail(XN_ERR_WORKSPACE, "decode_attention_split: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        XN_REQUIRE(aligned(workspace, 4), "decode_attention_split: workspace must be 4-byte aligned");
+    }
+    const size_t rows_per_split = ((context + splits - 1) / splits + 31) / 32 * 32;
+    splits = (int)((context + rows_per_split - 1) / rows_per_split);
+    cudaStream_t st = (cudaStream_t)stream;
+    decode_attention_kernel<<<dim3((unsigned)(batch * heads), (unsigned)splits), 128, 0, st>>>(
         (__nv_bfloat16 *)out_bf16, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_cache_bf16,
-        (const __nv_bfloat16 *)v_cache_bf16, mask_or_null, heads, context, q_batch_stride, scale);
+        (const __nv_bfloat16 *)v_cache_bf16, mask_or_null, heads, context, q_batch_stride, scale, rows_per_split,
+        (float *)workspace);
     XN_CHECK_CUDA(cudaGetLastError());
+    if (splits > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(batch * heads));
+        cfg.blockDim = dim3(HD);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_combine_kernel, (__nv_bfloat16 *)out_bf16,
+                                         (const float *)workspace, splits));
+    }
     return XN_OK;
+}
+}  // namespace
+
+extern "C" size_t xn_mm_decode_attention_workspace_bytes(size_t batch, size_t heads, size_t context) {
+    if (batch == 0 || heads == 0 || context == 0) return 0;
+    const int splits = attention_splits(batch, heads, context);
+    return splits > 1 ? batch * heads * splits * (HD + 2) * sizeof(float) : 0;
+}
+
+extern "C" int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, size_t q_batch_stride,
+                                            const void *k_cache_bf16, const void *v_cache_bf16, const float *mask_or_null,
+                                            size_t batch, size_t heads, size_t context, size_t head_dim, float scale,
+                                            void *workspace, size_t workspace_bytes, void *stream) {
+    return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
+                                 context, head_dim, scale, workspace, workspace_bytes, true, stream);
+}
+
+extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t q_batch_stride,
+                                      const void *k_cache_bf16, const void *v_cache_bf16, const float *mask_or_null,
+                                      size_t batch, size_t heads, size_t context, size_t head_dim, float scale,
+                                      void *stream) {
+    return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
+                                 context, head_dim, scale, nullptr, 0, false, stream);
 }

@@ -59,6 +59,9 @@ class DecoderStack:
         self.xs = torch.empty(B, dtype=torch.float32, device=device)
         self.qkv = torch.empty(B, 3 * d, **bf)
         self.attn = torch.empty(B, d, **bf)
+        # partial results of the context slices of the attention (empty when one slice per head fills the GPU)
+        self.attn_ws_bytes = int(lib().xn_mm_decode_attention_workspace_bytes(B, n_heads, context))
+        self.attn_ws = torch.empty(self.attn_ws_bytes, dtype=torch.uint8, device=device) if self.attn_ws_bytes else None
         self.proj = torch.empty(B, d, **bf)
         self.h = torch.empty(B, 2 * hid, **bf)
         self.x_mid = torch.empty(B, d, **bf)
@@ -91,9 +94,10 @@ class DecoderStack:
             q, kn, vn = self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * d, self.qkv.data_ptr() + 4 * d
             check(L.xn_mm_kv_append(BF16, lay["k"].data_ptr(), kn, 3 * d, self.pos.data_ptr(), B, H, ctx, 128, s))
             check(L.xn_mm_kv_append(BF16, lay["v"].data_ptr(), vn, 3 * d, self.pos.data_ptr(), B, H, ctx, 128, s))
-            check(L.xn_mm_decode_attention(self.attn.data_ptr(), q, 3 * d, lay["k"].data_ptr(), lay["v"].data_ptr(),
-                                           self.mask.data_ptr() if self.mask is not None else None, B, H, ctx, 128,
-                                           1.0 / math.sqrt(128.0), s))
+            check(L.xn_mm_decode_attention_split(self.attn.data_ptr(), q, 3 * d, lay["k"].data_ptr(), lay["v"].data_ptr(),
+                                                 self.mask.data_ptr() if self.mask is not None else None, B, H, ctx, 128,
+                                                 1.0 / math.sqrt(128.0), self.attn_ws.data_ptr() if self.attn_ws is not None else None,
+                                                 self.attn_ws_bytes, s))
             check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn.data_ptr(), BF16,
                                           B, d, s))
             self._linear(self.proj, lay["out_proj"], B, d, d)
