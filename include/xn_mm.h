@@ -217,7 +217,9 @@ int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, size_t q_ba
  * m*k <= xn_mm_linear_fp8_noalloc_max_elems() (262144); larger calls return XN_ERR_UNSUPPORTED.
  * All calls on a device share that array: calls that overlap on the GPU race, so keep them in one
  * stream order.  The first call on a device resolves the array's device address and should be made
- * outside any stream capture.  Results are identical to xn_mm_linear_fp8. */
+ * outside any stream capture.  It runs only kernels that need no scratch of their own (the
+ * weight-streaming kernel up to 32 rows, the tiled tensor-memory kernel beyond), so from 9 rows on its
+ * results can differ from xn_mm_linear_fp8 in the last bf16 bit (another summation order). */
 size_t xn_mm_linear_fp8_noalloc_max_elems(void);
 int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
                              size_t m, size_t n, size_t k, int variant, void *stream);

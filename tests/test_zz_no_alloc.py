@@ -33,16 +33,23 @@ def _pair(xn, cuda, m, n, k, variant, seed):
     return got, want
 
 
+def _same(got, want):
+    """Same result up to the last bf16 bit: the two entry points may run different kernels (the allocation-free
+    one avoids the kernel whose split-tile scratch is library-allocated), i.e. sum in a different order."""
+    g, w = got.float(), want.float()
+    return bool(not torch.isnan(g).any()) and float((g - w).abs().max()) <= 2.0 ** -7 * float(w.abs().max())
+
+
 def test_noalloc_matches_workspace_entry_point_on_two_calls_in_a_row(xn, cuda):
     # first call: a large decode batch that fills most of the built-in scratch
     got, want = _pair(xn, cuda, 16, 512, 8192, 0, seed=0)
-    assert not torch.isnan(got.float()).any() and torch.equal(got, want)
+    assert _same(got, want)
     # second call right after it: smaller, different data, other variant -- must not see stale pieces
     got, want = _pair(xn, cuda, 3, 328, 1040, 1, seed=1)
-    assert not torch.isnan(got.float()).any() and torch.equal(got, want)
-    # and a batch that takes the tensor-memory GEMM path (m > 16)
+    assert torch.equal(got, want)  # same kernel on both sides at 3 rows
+    # and a batch that takes the tiled tensor-memory path (m > 32)
     got, want = _pair(xn, cuda, 64, 256, 4096, 0, seed=2)
-    assert torch.equal(got, want)
+    assert _same(got, want)
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch(xn, cuda):

@@ -151,5 +151,15 @@ extern "C" int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const 
     float *xs = reinterpret_cast<float *>(base + NOALLOC_SCALE_OFFSET);
     rc = xn_mm_split_rows_e4m3(hi, variant == 0 ? lo : nullptr, xs, x_bf16, XN_BF16, m, k, stream);
     if (rc) return rc;
-    return xn_mm_linear_fp8_pieces(y_bf16, hi, variant == 0 ? lo : nullptr, xs, wq, w_scale, m, n, k, stream);
+    // Only kernels that need no scratch of their own: the weight-streaming GEMV up to 32 rows, the tiled
+    // tensor-memory kernel beyond.  (xn_mm_linear_fp8_pieces would pick the skinny kernel from 9 rows on, whose
+    // split-tile hand-over lives in a library-owned buffer that is allocated on first use.)
+    XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_noalloc: k=%zu must be a positive multiple of 16", k);
+    XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull, "linear_fp8_noalloc: dimension too large");
+    XN_REQUIRE(y_bf16 && wq && w_scale, "linear_fp8_noalloc: null pointer");
+    XN_REQUIRE(aligned(wq, 16), "linear_fp8_noalloc: weights must be 16-byte aligned");
+    const uint8_t *lo_or_null = variant == 0 ? lo : nullptr;
+    if (m <= 32) return launch_linear_fp8_gemv(y_bf16, hi, lo_or_null, xs, wq, w_scale, (int)m, n, (int)k, (cudaStream_t)stream);
+    void *dst[1] = {y_bf16};
+    return launch_linear_fp8_gemm_scatter(dst, 1, n, 0, hi, lo_or_null, xs, wq, w_scale, m, n, k, (cudaStream_t)stream);
 }
