@@ -14,6 +14,14 @@
  * no entry point traps on the device.  Entry points may be called from many
  * host threads at once (the reference's Backend is Send + Sync,
  * xn-core/src/backend.rs:4).
+ *
+ * Library-owned device memory: one kernel (the skinny tensor-memory form, used by xn_mm_gemm for
+ * 16-bit operands with 17..64 rows, or fewer rows and a very long k, and by the fp8 linears for 9..64
+ * rows) hands split tiles over through a per-device buffer that the library allocates when first needed
+ * and grows when a larger problem arrives (a few MB; cudaMalloc, i.e. not allowed during stream capture:
+ * run each shape once before capturing it, as a decode loop does anyway).  Calls that use it must be
+ * stream-ordered with respect to each other on a device, which is how xn drives a device (one stream per
+ * Device).  Nothing else allocates; xn_mm_linear_fp8_noalloc avoids that kernel altogether.
  */
 #ifndef XN_MM_H
 #define XN_MM_H
