@@ -17,11 +17,13 @@
  *
  * Library-owned device memory: one kernel (the skinny tensor-memory form, used by xn_mm_gemm for
  * 16-bit operands with 17..64 rows, or fewer rows and a very long k, and by the fp8 linears for 9..64
- * rows) hands split tiles over through a per-device buffer that the library allocates when first needed
- * and grows when a larger problem arrives (a few MB; cudaMalloc, i.e. not allowed during stream capture:
- * run each shape once before capturing it, as a decode loop does anyway).  Calls that use it must be
- * stream-ordered with respect to each other on a device, which is how xn drives a device (one stream per
- * Device).  Nothing else allocates; xn_mm_linear_fp8_noalloc avoids that kernel altogether.
+ * rows) hands split tiles over through a buffer per (device, stream) that the library allocates when a
+ * stream first needs it and grows when a larger problem arrives (a few MB; cudaMalloc, i.e. not allowed
+ * during stream capture: run each shape once before capturing it, as a decode loop does anyway; a stream
+ * under capture borrows the buffer of the stream that ran those shapes, so keep the graph's replays ordered
+ * with that stream's own calls).  Calls on different streams use different buffers and may overlap.
+ * Nothing else allocates;
+ * xn_mm_linear_fp8_noalloc avoids that kernel altogether.
  */
 #ifndef XN_MM_H
 #define XN_MM_H
@@ -196,6 +198,12 @@ int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void
                               const void *alpha, xn_dtype dtype, size_t rows, size_t cols, float eps, void *stream);
 int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const void *src, xn_dtype dtype,
                               size_t rows, size_t hidden, void *stream);
+/* Residual add fused into the next norm: sum_out = a + b (rounded like xn_mm_add; sum_out may alias a or b),
+ * then the pieces of rms_norm(sum_out) as above -- identical to xn_mm_add followed by
+ * xn_mm_rms_norm_split_e4m3, in one launch and one pass less over the row. */
+int xn_mm_add_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *sum_out, const void *a,
+                                  const void *b, const void *alpha, xn_dtype dtype, size_t rows, size_t cols, float eps,
+                                  void *stream);
 /* Single-token attention in one pass over the cache: replaces q.matmul_t(k) -> scale -> +mask ->
  * softmax -> matmul(v) (xn-moshi/src/batched_transformer.rs:174-190) for T = 1.  q: (batch, heads,
  * 128) bf16 with a batch stride of q_batch_stride elements; out: contiguous (batch, heads, 128) bf16;

@@ -203,3 +203,31 @@ def test_decode_attention_split_context_matches_single_pass(xn, oracle, cuda, B,
         rc = L.xn_mm_decode_attention_split(out_s.data_ptr(), q.data_ptr(), H * hd, k.data_ptr(), v.data_ptr(), mp, B, H, ctx,
                                             hd, scale, ws.data_ptr(), ws_bytes - 4, None)
         assert rc == 4
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+def test_add_rms_norm_split_equals_the_two_separate_ops(xn, cuda, variant):
+    """The fused residual add + norm + e4m3 split gives bit for bit what xn_mm_add followed by
+    xn_mm_rms_norm_split_e4m3 gives (pieces, row scales and the residual sum), also when the sum overwrites
+    one of its inputs."""
+    L = xn.lib()
+    rows, cols = 5, 4096
+    g = torch.Generator(device=cuda).manual_seed(3)
+    a = torch.randn(rows, cols, generator=g, device=cuda).bfloat16()
+    b = (torch.randn(rows, cols, generator=g, device=cuda) * 0.3).bfloat16()
+    alpha = (1 + 0.1 * torch.randn(cols, generator=g, device=cuda)).bfloat16()
+    u8 = dict(dtype=torch.uint8, device=cuda)
+    s0 = torch.empty_like(a)
+    hi0, lo0, xs0 = torch.empty(rows, cols, **u8), torch.empty(rows, cols, **u8), torch.empty(rows, device=cuda)
+    xn._lib.check(L.xn_mm_add(2, s0.data_ptr(), a.data_ptr(), b.data_ptr(), rows * cols, None))
+    xn._lib.check(L.xn_mm_rms_norm_split_e4m3(hi0.data_ptr(), lo0.data_ptr() if variant == 0 else None, xs0.data_ptr(), None,
+                                              s0.data_ptr(), alpha.data_ptr(), 2, rows, cols, 1e-5, None))
+    hi1, lo1, xs1 = torch.empty(rows, cols, **u8), torch.empty(rows, cols, **u8), torch.empty(rows, device=cuda)
+    s1 = a.clone()  # the sum overwrites its first input
+    xn._lib.check(L.xn_mm_add_rms_norm_split_e4m3(hi1.data_ptr(), lo1.data_ptr() if variant == 0 else None, xs1.data_ptr(),
+                                                  s1.data_ptr(), s1.data_ptr(), b.data_ptr(), alpha.data_ptr(), 2, rows,
+                                                  cols, 1e-5, None))
+    torch.cuda.synchronize()
+    assert torch.equal(s0, s1) and torch.equal(hi0, hi1) and torch.equal(xs0, xs1)
+    if variant == 0:
+        assert torch.equal(lo0, lo1)

@@ -242,3 +242,35 @@ def test_gemm_is_reentrant_from_many_host_threads(xn, oracle, cuda):
     for t in ts:
         t.join()
     assert not errs, errs
+
+
+def test_skinny_kernel_on_concurrent_streams(xn, oracle, cuda):
+    """The skinny tensor-memory kernel hands split tiles over through library-owned scratch, one buffer per
+    (device, stream): threads on different streams must not disturb each other."""
+    import threading
+    m, n, k = 32, 640, 4096  # 5 row tiles x 64 k stages over all SMs: every tile is split
+    g = torch.Generator(device=cuda).manual_seed(5)
+    w = (torch.randn(n, k, generator=g, device=cuda) * 0.05).bfloat16()
+    xs = [torch.randn(m, k, generator=g, device=cuda).bfloat16() for _ in range(8)]
+    refs = [(x.double() @ w.double().T).cpu().numpy() for x in xs]
+    errs = []
+
+    def work(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(20):
+                    y = xn.matmul_t(xs[i], w)
+                st.synchronize()
+            if oracle.rel_err(y.float().cpu().numpy().reshape(-1), refs[i].reshape(-1)) >= 1e-2:
+                errs.append((i, "mismatch"))
+        except Exception as e:  # noqa: BLE001
+            errs.append((i, repr(e)))
+
+    torch.cuda.synchronize()
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(8)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs

@@ -711,18 +711,49 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
 
 }  // namespace
 
-// Per-device scratch of the skinny path (partial accumulators + arrival counters).  One buffer per
-// device, grown on demand; calls that use it must be stream-ordered with respect to each other on a
-// device, which is how xn drives a device (one stream per Device, xn-core/src/cuda_backend.rs:52).
+// Scratch of the skinny path (partial accumulators + arrival counters): one buffer per (device, stream),
+// allocated when a stream first needs it and grown on demand.  Calls on one stream are ordered, so they can
+// share; calls on different streams get different buffers and may overlap.  (xn drives a device through one
+// stream, xn-core/src/cuda_backend.rs:52: one buffer per GPU in practice.)  A stream that is being captured
+// cannot allocate: it borrows the largest buffer of its device -- the one of the stream that ran the same
+// shapes before the capture, which is how a CUDA graph is normally warmed up -- and is refused with a clear
+// message when no buffer is large enough.
 struct SkinnyScratch { float *partials = nullptr; size_t partial_bytes = 0; unsigned *counters = nullptr; size_t ncounters = 0; };
-int skinny_scratch(size_t partial_bytes, size_t ncounters, SkinnyScratch *out) {
-    static SkinnyScratch table[64];
+int skinny_scratch(cudaStream_t st, size_t partial_bytes, size_t ncounters, SkinnyScratch *out) {
+    struct Entry { int dev; cudaStream_t st; SkinnyScratch s; };
+    static Entry table[256];
+    static int used = 0;
     static std::mutex mu;
     int dev = 0;
     XN_CHECK_CUDA(cudaGetDevice(&dev));
-    XN_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    XN_CHECK_CUDA(cudaStreamIsCapturing(st, &cap));
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
     std::lock_guard<std::mutex> lock(mu);
-    SkinnyScratch &s = table[dev];
+    Entry *e = nullptr;
+    for (int i = 0; i < used; ++i)
+        if (table[i].dev == dev && table[i].st == st) { e = &table[i]; break; }
+    if (capturing) {
+        if (!e || e->s.partial_bytes < partial_bytes || e->s.ncounters < ncounters) {
+            e = nullptr;
+            for (int i = 0; i < used; ++i)
+                if (table[i].dev == dev && table[i].s.partial_bytes >= partial_bytes && table[i].s.ncounters >= ncounters &&
+                    (!e || table[i].s.partial_bytes > e->s.partial_bytes))
+                    e = &table[i];
+        }
+        if (!e)
+            return fail(XN_ERR_UNSUPPORTED,
+                        "skinny matmul: this shape needs %zu bytes of library scratch and the stream is being captured; "
+                        "run the call once outside stream capture first", partial_bytes);
+        *out = e->s;
+        return XN_OK;
+    }
+    if (!e) {
+        if (used == 256) return fail(XN_ERR_UNSUPPORTED, "skinny matmul: more than 256 (device, stream) pairs in use");
+        e = &table[used++];
+        e->dev = dev; e->st = st; e->s = SkinnyScratch();
+    }
+    SkinnyScratch &s = e->s;
     if (s.partial_bytes < partial_bytes) {
         if (s.partials) { XN_CHECK_CUDA(cudaDeviceSynchronize()); XN_CHECK_CUDA(cudaFree(s.partials)); s.partials = nullptr; s.partial_bytes = 0; }
         XN_CHECK_CUDA(cudaMalloc(&s.partials, partial_bytes));
@@ -771,7 +802,7 @@ int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ld
     a.uq = (int)(total / grid);
     a.ur = (int)(total % grid);
     SkinnyScratch sc;
-    int rc = skinny_scratch((size_t)2 * grid * a.MB * BM * sizeof(float), (size_t)tiles * 4, &sc);
+    int rc = skinny_scratch(st, (size_t)2 * grid * a.MB * BM * sizeof(float), (size_t)tiles * 4, &sc);
     if (rc) return rc;
     a.partials = sc.partials;
     a.counters = sc.counters;

@@ -64,16 +64,26 @@ __device__ __forceinline__ float pow2_scale(float amax) {
 }
 
 // y = x / sqrt(mean(x^2) + eps) * alpha, rounded to T.  Optionally also the e4m3 pieces of y.
+// With `res` the input is the residual sum x = T(src + res), which is also written to `sum_out` (the row then
+// comes from sum_out in the later passes: every thread re-reads only what it wrote itself).
 template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(NT)
 rms_norm_kernel(T *__restrict__ dst, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo, float *__restrict__ scale,
-                const T *__restrict__ src, const T *__restrict__ alpha, size_t cols, float eps) {
+                const T *__restrict__ src, const T *__restrict__ alpha, size_t cols, float eps,
+                const T *__restrict__ res = nullptr, T *sum_out = nullptr) {
     __shared__ float red[32];
     const size_t row = blockIdx.x;
-    const T *x = src + row * cols;
+    const T *x = res ? sum_out + row * cols : src + row * cols;
     float s2 = 0.0f;
     for (size_t c = threadIdx.x; c < cols; c += NT) {
-        const float v = to_f32(x[c]);
+        float v;
+        if (res) {
+            const T sum = from_f32<T>(to_f32(src[row * cols + c]) + to_f32(res[row * cols + c]));
+            sum_out[row * cols + c] = sum;
+            v = to_f32(sum);
+        } else {
+            v = to_f32(x[c]);
+        }
         s2 += v * v;
     }
     s2 = block_sum(s2, red);
@@ -172,6 +182,9 @@ __global__ void kv_append_kernel(T *__restrict__ cache, const T *__restrict__ sr
 // (stream, head); a half-warp owns a key/value row (16 lanes x 16 bytes = 128 bf16), so a warp
 // handles two rows per step; online softmax per half-warp, merged at the end.  f32 throughout.
 constexpr int HD = 128;
+// SLICED = false is the one-pass form (whole context, result straight to `out`); it is a separate
+// instantiation because the sliced form's extra bounds cost the one-pass case 6 % when they are run-time values.
+template <bool SLICED>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ q,
                         const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
@@ -180,8 +193,8 @@ decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__
     // blockIdx.y = slice of the context (rows [row_lo, row_hi)); with one slice the result goes straight to `out`,
     // otherwise the slice's running maximum, sum and unnormalised output go to `partial` for the combine kernel
     const size_t bh = blockIdx.x, b = bh / heads;
-    const size_t row_lo = (size_t)blockIdx.y * rows_per_split;
-    const size_t row_hi = row_lo + rows_per_split < context ? row_lo + rows_per_split : context;
+    const size_t row_lo = SLICED ? (size_t)blockIdx.y * rows_per_split : 0;
+    const size_t row_hi = SLICED ? (row_lo + rows_per_split < context ? row_lo + rows_per_split : context) : context;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half = lane >> 4, l16 = lane & 15;
     const int group = warp * 2 + half;  // 8 half-warps stride over the rows
@@ -259,7 +272,7 @@ decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__
             l += w * sm_l[gI];
             o += w * sm_acc[gI][threadIdx.x];
         }
-        if (gridDim.y == 1) {
+        if (!SLICED) {
             out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
         } else {
             float *p = partial + (bh * gridDim.y + blockIdx.y) * (HD + 2);
@@ -314,6 +327,20 @@ extern "C" int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_
     XN_REQUIRE(rows <= 0x7fffffffull, "rms_norm_split: too many rows");
     XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
                                     (T *)dst_or_null, x_hi, x_lo, x_scale, (const T *)src, (const T *)alpha, cols, eps));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_add_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *sum_out, const void *a,
+                                             const void *b, const void *alpha, xn_dtype dtype, size_t rows, size_t cols,
+                                             float eps, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "add_rms_norm_split: unknown dtype %d", (int)dtype);
+    if (rows == 0 || cols == 0) return XN_OK;
+    XN_REQUIRE(x_hi && x_scale && sum_out && a && b && alpha, "add_rms_norm_split: null pointer");
+    XN_REQUIRE(rows <= 0x7fffffffull, "add_rms_norm_split: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                                    (T *)nullptr, x_hi, x_lo, x_scale, (const T *)a, (const T *)alpha, cols, eps,
+                                    (const T *)b, (T *)sum_out));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -411,10 +438,15 @@ int decode_attention_impl(void *out_bf16, const void *q_bf16, size_t q_batch_str
     const size_t rows_per_split = ((context + splits - 1) / splits + 31) / 32 * 32;
     splits = (int)((context + rows_per_split - 1) / rows_per_split);
     cudaStream_t st = (cudaStream_t)stream;
-    decode_attention_kernel<<<dim3((unsigned)(batch * heads), (unsigned)splits), 128, 0, st>>>(
-        (__nv_bfloat16 *)out_bf16, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_cache_bf16,
-        (const __nv_bfloat16 *)v_cache_bf16, mask_or_null, heads, context, q_batch_stride, scale, rows_per_split,
-        (float *)workspace);
+    if (splits > 1)
+        decode_attention_kernel<true><<<dim3((unsigned)(batch * heads), (unsigned)splits), 128, 0, st>>>(
+            (__nv_bfloat16 *)out_bf16, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_cache_bf16,
+            (const __nv_bfloat16 *)v_cache_bf16, mask_or_null, heads, context, q_batch_stride, scale, rows_per_split,
+            (float *)workspace);
+    else
+        decode_attention_kernel<false><<<(unsigned)(batch * heads), 128, 0, st>>>(
+            (__nv_bfloat16 *)out_bf16, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_cache_bf16,
+            (const __nv_bfloat16 *)v_cache_bf16, mask_or_null, heads, context, q_batch_stride, scale, context, nullptr);
     XN_CHECK_CUDA(cudaGetLastError());
     if (splits > 1) {
         cudaLaunchConfig_t cfg = {};

@@ -87,9 +87,10 @@ class DecoderStack:
         L, B, d, H, hid, ctx = lib(), self.B, self.d, self.H, self.hid, self.ctx
         s = self._s()
         cur = x
-        for lay in self.layers:
-            check(L.xn_mm_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), None, cur.data_ptr(),
-                                              lay["norm1"].data_ptr(), BF16, B, d, self.eps, s))
+        for li, lay in enumerate(self.layers):
+            if li == 0:  # later layers get their pieces from the fused add + norm that ends the previous layer
+                check(L.xn_mm_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), None, cur.data_ptr(),
+                                                  lay["norm1"].data_ptr(), BF16, B, d, self.eps, s))
             self._linear(self.qkv, lay["in_proj"], B, 3 * d, d)
             q, kn, vn = self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * d, self.qkv.data_ptr() + 4 * d
             check(L.xn_mm_kv_append(BF16, lay["k"].data_ptr(), kn, 3 * d, self.pos.data_ptr(), B, H, ctx, 128, s))
@@ -101,14 +102,19 @@ class DecoderStack:
             check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn.data_ptr(), BF16,
                                           B, d, s))
             self._linear(self.proj, lay["out_proj"], B, d, d)
-            check(L.xn_mm_add(BF16, self.x_mid.data_ptr(), cur.data_ptr(), self.proj.data_ptr(), B * d, s))
-            check(L.xn_mm_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), None,
-                                              self.x_mid.data_ptr(), lay["norm2"].data_ptr(), BF16, B, d, self.eps, s))
+            check(L.xn_mm_add_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.x_mid.data_ptr(),
+                                                  cur.data_ptr(), self.proj.data_ptr(), lay["norm2"].data_ptr(), BF16, B, d,
+                                                  self.eps, s))
             self._linear(self.h, lay["linear_in"], B, 2 * hid, d)
             check(L.xn_mm_silu_mul_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.h.data_ptr(), BF16,
                                               B, hid, s))
             self._linear(self.proj, lay["linear_out"], B, d, hid)
-            check(L.xn_mm_add(BF16, self.x_out.data_ptr(), self.x_mid.data_ptr(), self.proj.data_ptr(), B * d, s))
+            if li + 1 < len(self.layers):  # x_out = x_mid + proj, pieces of the next layer's norm1(x_out)
+                check(L.xn_mm_add_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(),
+                                                      self.x_out.data_ptr(), self.x_mid.data_ptr(), self.proj.data_ptr(),
+                                                      self.layers[li + 1]["norm1"].data_ptr(), BF16, B, d, self.eps, s))
+            else:
+                check(L.xn_mm_add(BF16, self.x_out.data_ptr(), self.x_mid.data_ptr(), self.proj.data_ptr(), B * d, s))
             cur = self.x_out
         return self.x_out
 
@@ -119,4 +125,6 @@ class DecoderStack:
         return {"weights": w, "kv": kv, "total": w + kv}
 
     def launches_per_step(self) -> int:
-        return self.L * 13
+        # per layer: in_proj, 2 kv appends, attention (+ its combine when the context is split), split, out_proj,
+        # add+norm, linear_in, silu*mul, linear_out, add+norm (plain add after the last layer); one norm up front
+        return self.L * (11 + (1 if self.attn_ws_bytes else 0)) + 1
