@@ -259,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             // Column groups of GC: the warp's 32 x GC slab goes through shared memory (16-byte chunks
             // XOR-swizzled by row) so that global stores are whole row segments of GC*2 bytes instead of
             // 16 bytes per row -- this matters most when the destination is a peer GPU.
-            constexpr int GC = BN < 128 ? BN : 128;     // columns per group
+            constexpr int GC = BN % 128 == 0 ? 128 : (BN % 64 == 0 ? 64 : 32);  // columns per group (divides BN)
             constexpr int CPR = GC / 8;                 // 16-byte chunks per slab row
             constexpr int RPI = 32 / CPR;               // rows written per store instruction
             unsigned char *slab = epi_smem + (size_t)(warp - 2) * 32 * 256;
@@ -695,18 +695,31 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
 template <int KIND, int NA>
 int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
                 cudaStream_t st, const BatchGeom &bg = BatchGeom()) {
-    // Wide tiles when there are enough of them to fill the machine, narrower ones otherwise.
+    // Tile width.  A CTA's time per k stage follows the bytes it pulls through L2 (NA activation tiles of 128
+    // rows + BN weight rows; an MMA costs the same ~130 cycles for any BN <= 256), and the launch lasts as many
+    // stages as the busiest SM gets: waves x bytes per stage, minimised over the widths the kernel is
+    // instantiated for.  Ties go to the wider tile (fewer re-reads of the activation tile).
     const int sms = sm_count();
     static const int force_bn = [] { const char *e = getenv("XN_GEMM_BN"); return e ? atoi(e) : 0; }();
-    if (force_bn == 256) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
-    if (force_bn == 128) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
-    if (force_bn == 64) return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
     const long long m_tiles = (long long)((args.M + BM - 1) / BM) * args.batch;
-    // (measured on the transformer shapes: the widest tile that still gives ~0.55 tiles per SM wins, because
-    // every extra column tile re-reads the activation tile from L2)
-    if (m_tiles * ((args.N + 255) / 256) * 100 >= sms * 55) return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
-    if (m_tiles * ((args.N + 127) / 128) * 100 >= sms * 55) return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
-    return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn = 256; bn >= 64; bn -= 32) {
+        const long long tiles = m_tiles * ((args.N + bn - 1) / bn);
+        const long long waves = (tiles + sms - 1) / sms;
+        const long long cost = waves * (NA * BM + bn);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    if (force_bn >= 64 && force_bn <= 256 && force_bn % 32 == 0) best = force_bn;
+    switch (best) {
+        case 256: return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        case 224: return launch_cfg<KIND, 224, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        case 192: return launch_cfg<KIND, 192, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        case 160: return launch_cfg<KIND, 160, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        case 128: return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        case 96: return launch_cfg<KIND, 96, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        default: return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
+    }
 }
 
 }  // namespace
