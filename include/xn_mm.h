@@ -240,6 +240,41 @@ size_t xn_mm_linear_fp8_noalloc_max_elems(void);
 int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
                              size_t m, size_t n, size_t k, int variant, void *stream);
 
+/* --------------------------------------------------------------------------------------------
+ * Convolutions as implicit GEMMs.  Argument lists of Backend::conv1d / Backend::conv_transpose1d
+ * (xn-core/src/backend.rs:275-316) plus an optional bias the reference adds as a separate
+ * broadcast_add (xn-core/src/ops.rs:253-300, 305-350); replaces the im2col -> gemm -> transpose and
+ * transpose -> gemm -> col2im lowerings of xn-core/src/cuda_backend.rs:1376-1488, 1490-1561,
+ * 1783-1856 and their direct fallbacks, for every groups / padding / dilation value.
+ *   src    (batch, in_channels, length), contiguous
+ *   kernel conv1d: (out_channels, in_channels/groups, kernel_size)
+ *          conv_transpose1d: (in_channels, out_channels/groups, kernel_size)
+ *   bias   (out_channels) or NULL
+ *   dst    (batch, out_channels, out_length), contiguous; out_length must be
+ *          (length + 2*padding - dilation*(kernel_size-1) - 1)/stride + 1, respectively
+ *          (length-1)*stride + kernel_size + output_padding - 2*padding, as the reference computes it
+ * Accumulation is f32 with one rounding to dtype (f32 operands: products to about 1e-6 relative,
+ * exact on small integers).
+ * workspace: f16 / bf16 calls with groups == 1, dilation == 1 and in_channels a multiple of 8 run on the
+ * tensor-memory GEMM kernel over a channels-last copy of the input and repacked taps, which live in
+ * caller-owned device scratch of xn_mm_conv*_workspace_bytes(...) bytes (256-byte aligned, reusable by
+ * every call on the same stream; XN_ERR_WORKSPACE when absent or too small).  Every other call needs no
+ * scratch: the size function returns 0 and workspace may be NULL.
+ * ------------------------------------------------------------------------------------------ */
+size_t xn_mm_conv1d_workspace_bytes(xn_dtype dtype, size_t batch, size_t in_channels, size_t out_channels, size_t length,
+                                    size_t kernel_size, size_t stride, size_t padding, size_t dilation, size_t groups);
+int xn_mm_conv1d(xn_dtype dtype, void *dst, const void *src, const void *kernel, const void *bias_or_null,
+                 size_t batch, size_t in_channels, size_t out_channels, size_t length, size_t out_length,
+                 size_t kernel_size, size_t stride, size_t padding, size_t dilation, size_t groups, void *workspace,
+                 size_t workspace_bytes, void *stream);
+size_t xn_mm_conv_transpose1d_workspace_bytes(xn_dtype dtype, size_t batch, size_t in_channels, size_t out_channels,
+                                              size_t length, size_t kernel_size, size_t stride, size_t padding,
+                                              size_t output_padding, size_t groups);
+int xn_mm_conv_transpose1d(xn_dtype dtype, void *dst, const void *src, const void *kernel, const void *bias_or_null,
+                           size_t batch, size_t in_channels, size_t out_channels, size_t length, size_t out_length,
+                           size_t kernel_size, size_t stride, size_t padding, size_t output_padding, size_t groups,
+                           void *workspace, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

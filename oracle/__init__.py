@@ -272,6 +272,29 @@ def silu_mul(dtype, src):
     return dst
 
 
+def conv1d(dtype, src, kernel, stride=1, padding=0, dilation=1, groups=1):
+    """Backend::conv1d of the CPU backend; src (b, c_in, l), kernel (c_out, c_in/groups, ks) in storage form."""
+    b, cin, length = src.shape
+    cout, _, ks = kernel.shape
+    lo = (length + 2 * padding - dilation * (ks - 1) - 1) // stride + 1
+    dst = np.zeros((b, cout, lo), dtype=src.dtype)
+    lib().xo_conv1d(C.c_int(dtype), _p(dst), _p(np.ascontiguousarray(src)), _p(np.ascontiguousarray(kernel)),
+                    *_sz(b, cin, cout, length, lo, ks, stride, padding, dilation, groups))
+    return dst
+
+
+def conv_transpose1d(dtype, src, kernel, stride=1, padding=0, output_padding=0, groups=1):
+    """Backend::conv_transpose1d of the CPU backend; kernel (c_in, c_out/groups, ks)."""
+    b, cin, length = src.shape
+    _, cog, ks = kernel.shape
+    cout = cog * groups
+    lo = (length - 1) * stride + ks + output_padding - 2 * padding
+    dst = np.zeros((b, cout, lo), dtype=src.dtype)
+    lib().xo_conv_transpose1d(C.c_int(dtype), _p(dst), _p(np.ascontiguousarray(src)), _p(np.ascontiguousarray(kernel)),
+                              *_sz(b, cin, cout, length, lo, ks, stride, padding, output_padding, groups))
+    return dst
+
+
 def linear_f32_fast(x, w):
     m, k = x.shape
     n = w.shape[0]

@@ -525,3 +525,119 @@ int xo_num_threads(void) {
     return 1;
 #endif
 }
+
+/* ------------------------------------------------------------------------- */
+/* Convolutions, as Backend::conv1d / conv_transpose1d of the CPU backend      */
+/* run them (xn-core/src/cpu_backend.rs:959-1136): groups == 1 goes through    */
+/* im2col + gemm + transpose (:959-1030), respectively transpose + gemm +      */
+/* col2im when padding and output_padding are 0 (:1072-1115, col2im :1319-     */
+/* 1350); everything else takes the direct loops (:1233-1310, :1354-1430),     */
+/* which accumulate in the ELEMENT type: every product and every sum is        */
+/* rounded to f16 / bf16 there.                                                */
+/* ------------------------------------------------------------------------- */
+static inline float round_elem(int dtype, float v) {
+    if (dtype == XO_F32) return v;
+    uint16_t t;
+    store_elem(dtype, &t, 0, v);
+    return load_elem(dtype, &t, 0);
+}
+static inline size_t elem_size(int dtype) { return dtype == XO_F32 ? 4 : 2; }
+
+void xo_conv1d(int dtype, void *dst, const void *src, const void *kernel, size_t batch,
+               size_t in_channels, size_t out_channels, size_t length, size_t out_length,
+               size_t kernel_size, size_t stride, size_t padding, size_t dilation, size_t groups) {
+    size_t es = elem_size(dtype);
+    if (groups == 1) {
+        size_t k = in_channels * kernel_size;
+        void *col = calloc(batch * out_length * k + 1, es);
+        void *res = calloc(batch * out_length * out_channels + 1, es);
+        for (size_t b = 0; b < batch; ++b)
+            for (size_t l = 0; l < out_length; ++l)
+                for (size_t c = 0; c < in_channels; ++c)
+                    for (size_t kk = 0; kk < kernel_size; ++kk) {
+                        size_t sl = l * stride + kk * dilation;
+                        if (sl < padding || sl >= length + padding) continue;
+                        store_elem(dtype, col, (b * out_length + l) * k + c * kernel_size + kk,
+                                   load_elem(dtype, src, (b * in_channels + c) * length + sl - padding));
+                    }
+        xo_gemm(dtype, res, col, 0, kernel, 0, out_length, out_channels, k, batch, out_length * k, 0,
+                1, out_channels, 1, k, k, 1, 0);
+        for (size_t b = 0; b < batch; ++b)
+            for (size_t l = 0; l < out_length; ++l)
+                for (size_t c = 0; c < out_channels; ++c)
+                    store_elem(dtype, dst, (b * out_channels + c) * out_length + l,
+                               load_elem(dtype, res, (b * out_length + l) * out_channels + c));
+        free(col);
+        free(res);
+        return;
+    }
+    size_t cig = in_channels / groups, cog = out_channels / groups;
+    for (size_t i = 0; i < batch * out_channels * out_length; ++i) store_elem(dtype, dst, i, 0.0f);
+    for (size_t kk = 0; kk < kernel_size; ++kk)
+        for (size_t oc = 0; oc < out_channels; ++oc) {
+            size_t c0 = (oc / cog) * cig;
+            for (size_t b = 0; b < batch; ++b)
+                for (size_t ol = 0; ol < out_length; ++ol) {
+                    size_t sl = ol * stride + kk * dilation;
+                    if (sl < padding || sl >= padding + length) continue;
+                    sl -= padding;
+                    float d = 0.0f;
+                    for (size_t ic = 0; ic < cig; ++ic) {
+                        float p = round_elem(dtype, load_elem(dtype, src, (b * in_channels + c0 + ic) * length + sl) *
+                                                        load_elem(dtype, kernel, (oc * cig + ic) * kernel_size + kk));
+                        d = round_elem(dtype, d + p);
+                    }
+                    size_t di = (b * out_channels + oc) * out_length + ol;
+                    store_elem(dtype, dst, di, load_elem(dtype, dst, di) + d);
+                }
+        }
+}
+
+void xo_conv_transpose1d(int dtype, void *dst, const void *src, const void *kernel, size_t batch,
+                         size_t in_channels, size_t out_channels, size_t length, size_t out_length,
+                         size_t kernel_size, size_t stride, size_t padding, size_t output_padding,
+                         size_t groups) {
+    size_t es = elem_size(dtype);
+    for (size_t i = 0; i < batch * out_channels * out_length; ++i) store_elem(dtype, dst, i, 0.0f);
+    if (groups == 1 && padding == 0 && output_padding == 0) {
+        size_t n = out_channels * kernel_size;
+        void *srct = calloc(batch * length * in_channels + 1, es);
+        void *col = calloc(batch * length * n + 1, es);
+        for (size_t b = 0; b < batch; ++b)
+            for (size_t l = 0; l < length; ++l)
+                for (size_t c = 0; c < in_channels; ++c)
+                    store_elem(dtype, srct, (b * length + l) * in_channels + c,
+                               load_elem(dtype, src, (b * in_channels + c) * length + l));
+        xo_gemm(dtype, col, srct, 0, kernel, 0, length, n, in_channels, batch, length * in_channels, 0,
+                1, n, 1, in_channels, 1, n, 0);
+        for (size_t l = 0; l < length; ++l)
+            for (size_t kk = 0; kk < kernel_size; ++kk)
+                for (size_t b = 0; b < batch; ++b)
+                    for (size_t c = 0; c < out_channels; ++c) {
+                        size_t di = (b * out_channels + c) * out_length + l * stride + kk;
+                        store_elem(dtype, dst, di, load_elem(dtype, dst, di) +
+                                   load_elem(dtype, col, ((b * length + l) * out_channels + c) * kernel_size + kk));
+                    }
+        free(srct);
+        free(col);
+        return;
+    }
+    size_t cig = in_channels / groups, cog = out_channels / groups;
+    for (size_t kk = 0; kk < kernel_size; ++kk)
+        for (size_t oc = 0; oc < out_channels; ++oc) {
+            size_t g = oc / cog, ocg = oc % cog, c0 = g * cig;
+            for (size_t b = 0; b < batch; ++b)
+                for (size_t il = 0; il < length; ++il) {
+                    size_t raw = il * stride + kk;
+                    if (raw < padding || raw >= out_length + padding) continue;
+                    float d = 0.0f;
+                    for (size_t ic = 0; ic < cig; ++ic) {
+                        float p = round_elem(dtype, load_elem(dtype, src, (b * in_channels + c0 + ic) * length + il) *
+                                                        load_elem(dtype, kernel, ((c0 + ic) * cog + ocg) * kernel_size + kk));
+                        d = round_elem(dtype, d + p);
+                    }
+                    size_t di = (b * out_channels + oc) * out_length + raw - padding;
+                    store_elem(dtype, dst, di, load_elem(dtype, dst, di) + d);
+                }
+        }
+}

@@ -126,6 +126,35 @@ def run_conv_transpose1d_case(be, case):
     assert np.array_equal(out.reshape(-1), np.array(case["expected"], np.float32)), (case["name"], out)
 
 
+def conv1d_f64(x, w, stride, padding, dilation, groups):
+    """The definition of conv1d evaluated in float64 (independent of the oracle's lowering)."""
+    b, cin, length = x.shape
+    cout, cig, ks = w.shape
+    lo = (length + 2 * padding - dilation * (ks - 1) - 1) // stride + 1
+    xp = np.zeros((b, cin, length + 2 * padding + stride))
+    xp[:, :, padding:padding + length] = x
+    out = np.zeros((b, cout, lo))
+    cog = cout // groups
+    for g in range(groups):
+        for kk in range(ks):
+            sl = xp[:, g * cig:(g + 1) * cig, kk * dilation: kk * dilation + (lo - 1) * stride + 1: stride]
+            out[:, g * cog:(g + 1) * cog] += np.einsum("bcl,oc->bol", sl, w[g * cog:(g + 1) * cog, :, kk].astype(np.float64))
+    return out
+
+
+def conv_transpose1d_f64(x, w, stride, padding, output_padding, groups):
+    b, cin, length = x.shape
+    _, cog, ks = w.shape
+    cig = cin // groups
+    full = np.zeros((b, cog * groups, (length - 1) * stride + ks + output_padding + padding))
+    for g in range(groups):
+        for kk in range(ks):
+            full[:, g * cog:(g + 1) * cog, kk: kk + (length - 1) * stride + 1: stride] += np.einsum(
+                "bcl,co->bol", x[:, g * cig:(g + 1) * cig].astype(np.float64), w[g * cig:(g + 1) * cig, :, kk].astype(np.float64))
+    lo = (length - 1) * stride + ks + output_padding - 2 * padding
+    return full[:, :, padding:padding + lo]
+
+
 def run_all(be):
     g = load()
     for c in g["matmul"]:

@@ -149,3 +149,39 @@ def test_row_ops(oracle):
     assert np.allclose(oracle.softmax(oracle.F32, x.numpy()), torch.softmax(x, -1).numpy(), rtol=1e-5, atol=1e-7)
     y = oracle.silu_mul(oracle.F32, x.numpy())
     assert np.allclose(y, (torch.nn.functional.silu(x[:, :32]) * x[:, 32:]).numpy(), rtol=1e-5, atol=1e-6)
+
+
+def test_oracle_conv_entry_points_on_reference_kats(oracle):
+    """xn-core/tests/tensor_tests.rs:467-613 through xo_conv1d / xo_conv_transpose1d, exact."""
+    g = kats.load()
+    for c in g["conv1d"]:
+        x = np.array(c["input"], np.float32).reshape(c["input_dims"])
+        k = np.array(c["kernel"], np.float32).reshape(c["kernel_dims"])
+        out = oracle.conv1d(oracle.F32, x, k, c["stride"], c["padding"])
+        if c["bias"] is not None:
+            out = out + np.array(c["bias"], np.float32).reshape(1, -1, 1)
+        assert list(out.shape) == c["expected_dims"] and out.reshape(-1).tolist() == c["expected"], c["name"]
+    for c in g["conv_transpose1d"]:
+        x = np.array(c["input"], np.float32).reshape(c["input_dims"])
+        k = np.array(c["kernel"], np.float32).reshape(c["kernel_dims"])
+        out = oracle.conv_transpose1d(oracle.F32, x, k, c["stride"])
+        if c["bias"] is not None:
+            out = out + np.array(c["bias"], np.float32).reshape(1, -1, 1)
+        assert list(out.shape) == c["expected_dims"] and out.reshape(-1).tolist() == c["expected"], c["name"]
+
+
+def test_oracle_conv_lowerings_agree_with_the_definition(oracle):
+    """im2col / col2im lowerings (groups == 1) and the direct loops (groups, padding) against float64."""
+    rng = np.random.default_rng(5)
+    for b, cin, cout, length, ks, stride, pad, dil, groups in [(2, 8, 6, 17, 3, 1, 1, 1, 1), (1, 6, 4, 20, 4, 2, 3, 2, 2),
+                                                              (2, 4, 4, 9, 3, 1, 0, 1, 4), (1, 5, 7, 30, 8, 4, 2, 1, 1)]:
+        x = rng.standard_normal((b, cin, length)).astype(np.float32)
+        w = rng.standard_normal((cout, cin // groups, ks)).astype(np.float32)
+        got = oracle.conv1d(oracle.F32, x, w, stride, pad, dil, groups)
+        assert oracle.rel_err(got, kats.conv1d_f64(x, w, stride, pad, dil, groups)) < 1e-5
+    for b, cin, cog, length, ks, stride, pad, opad, groups in [(2, 8, 6, 7, 4, 2, 0, 0, 1), (1, 6, 2, 5, 5, 3, 1, 1, 2),
+                                                               (2, 4, 3, 6, 8, 4, 2, 0, 1), (1, 4, 3, 5, 2, 4, 0, 0, 1)]:
+        x = rng.standard_normal((b, cin, length)).astype(np.float32)
+        w = rng.standard_normal((cin, cog, ks)).astype(np.float32)
+        got = oracle.conv_transpose1d(oracle.F32, x, w, stride, pad, opad, groups)
+        assert oracle.rel_err(got, kats.conv_transpose1d_f64(x, w, stride, pad, opad, groups)) < 1e-5

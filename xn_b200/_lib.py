@@ -46,6 +46,10 @@ SIGNATURES = {
     "xn_mm_linear_fp8_pieces_scatter": (_i, [_p, _sz, _sz, _sz, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "xn_mm_linear_fp8_workspace_bytes": (_sz, [_sz, _sz]),
     "xn_mm_linear_fp8": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p, _sz, _p]),
+    "xn_mm_conv1d_workspace_bytes": (_sz, [_i] + [_sz] * 9),
+    "xn_mm_conv1d": (_i, [_i, _p, _p, _p, _p] + [_sz] * 10 + [_p, _sz, _p]),
+    "xn_mm_conv_transpose1d_workspace_bytes": (_sz, [_i] + [_sz] * 9),
+    "xn_mm_conv_transpose1d": (_i, [_i, _p, _p, _p, _p] + [_sz] * 10 + [_p, _sz, _p]),
     "xn_mm_rms_norm": (_i, [_i, _p, _p, _p, _sz, _sz, C.c_float, _p]),
     "xn_mm_softmax": (_i, [_i, _p, _p, _sz, _sz, _p]),
     "xn_mm_silu_mul": (_i, [_i, _p, _p, _sz, _sz, _p]),

@@ -142,6 +142,8 @@ struct GemmArgs {
     int batch;            // strided-batched / grouped form: `batch` independent problems in one launch
     long long y_batch_stride;  // elements between consecutive outputs (m * n in Backend::gemm)
     int a_batch_inner, b_batch_inner;  // the tensor map's dimension order is (k, batch, rows) instead of (k, rows, batch)
+    int a_bcast;          // every batch entry multiplies the same A matrix (the A map then holds one matrix)
+    const void *row_bias; // optional, 16-bit kinds only: added to every element of output row i (element type of y)
 };
 
 // KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16
@@ -204,7 +206,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    const int ay = args.a_batch_inner ? g : m_blk * BM, az = args.a_batch_inner ? m_blk * BM : g;
+                    const int ga = args.a_bcast ? 0 : g;
+                    const int ay = args.a_batch_inner ? ga : m_blk * BM, az = args.a_batch_inner ? m_blk * BM : ga;
                     const int by = args.b_batch_inner ? g : n_blk * BN, bz = args.b_batch_inner ? n_blk * BN : g;
                     tma_load_3d(st, &map_a0, kb * BK, ay, az, &full[s]);
                     if (NA == 2) tma_load_3d(st + A_BYTES, &map_a1, kb * BK, ay, az, &full[s]);
@@ -256,6 +259,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             const int row = m_blk * BM + q * 32 + lane;
             float xs = 1.0f;
             if (F8 && row < args.M) xs = __ldg(args.x_scale + row);
+            float rb = 0.0f;
+            if (!F8 && args.row_bias && row < args.M)
+                rb = KIND == 2 ? __half2float(reinterpret_cast<const __half *>(args.row_bias)[row])
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(args.row_bias)[row]);
             // Column groups of GC: the warp's 32 x GC slab goes through shared memory (16-byte chunks
             // XOR-swizzled by row) so that global stores are whole row segments of GC*2 bytes instead of
             // 16 bytes per row -- this matters most when the destination is a peer GPU.
@@ -278,6 +285,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                             const int c0 = min(col0 + 2 * j, args.N - 1), c1 = min(col0 + 2 * j + 1, args.N - 1);
                             f0 = __ldg(args.w_scale + c0) * (xs * f0);
                             f1 = __ldg(args.w_scale + c1) * (xs * f1);
+                        } else {
+                            f0 += rb;
+                            f1 += rb;
                         }
                         if (KIND == 2) {
                             __half2 h = __floats2half2_rn(f0, f1);
@@ -666,9 +676,10 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
     CUtensorMap ma0, ma1, mb;
     GemmArgs args2 = args;
-    int rc = make_map3(&ma0, a0, ELEM, args.M, args.K, lda, BM, bg.batch, bg.a_stride, &args2.a_batch_inner);
+    const size_t a_batch = args.a_bcast ? 1 : bg.batch;
+    int rc = make_map3(&ma0, a0, ELEM, args.M, args.K, lda, BM, a_batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
-    rc = make_map3(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM, bg.batch, bg.a_stride, &args2.a_batch_inner);
+    rc = make_map3(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM, a_batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
     rc = make_map3(&mb, b, ELEM, args.N, args.K, ldb, BN, bg.batch, bg.b_stride, &args2.b_batch_inner);
     if (rc) return rc;
@@ -888,6 +899,22 @@ int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rh
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
     BatchGeom bg;
     bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;
+    return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
+                         : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
+}
+
+// The same product with one lhs shared by every batch entry and an optional per-row bias: the form the
+// convolutions use (lhs = packed kernel taps, rhs = overlapping rows of the channels-last input, dst rows =
+// output channels).  Always the tiled kernel.  dst batch stride dst_bs elements.
+int launch_gemm_tn_16bit_shared_lhs(xn_dtype dt, void *dst, const void *lhs, const void *rhs, const void *row_bias, size_t m,
+                                    size_t n, size_t k, size_t lda, size_t ldb, size_t ldd, size_t batch, size_t rhs_bs,
+                                    size_t dst_bs, cudaStream_t st) {
+    GemmArgs a{};
+    a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)dst_bs;
+    a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    a.a_bcast = 1; a.row_bias = row_bias;
+    BatchGeom bg;
+    bg.batch = batch; bg.a_stride = 0; bg.b_stride = rhs_bs;
     return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
                          : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
 }

@@ -248,6 +248,88 @@ class LinearFp8:
 
 
 # ---------------------------------------------------------------------------------------------
+# Convolutions: Tensor::conv1d / Tensor::conv_transpose1d (xn-core/src/ops.rs:253-300, 305-350),
+# same arguments, same shape rules and error texts; one launch each, bias fused.
+# ---------------------------------------------------------------------------------------------
+_CONV_WS: dict = {}
+
+
+def _conv_workspace(device, nbytes: int):
+    """Scratch of the tensor-memory conv path: one buffer per (device, stream), grown on demand."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _CONV_WS.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _CONV_WS[key] = buf
+    return buf
+
+
+def _check_bias(bias, out_channels):
+    if bias is not None and list(bias.shape) != [out_channels]:
+        raise XnError(1, f"bias shape mismatch: expected [{out_channels}], got {list(bias.shape)}")
+
+
+def conv1d(x: torch.Tensor, kernel: torch.Tensor, bias: torch.Tensor | None = None, stride: int = 1,
+           padding: int = 0, dilation: int = 1, groups: int = 1) -> torch.Tensor:
+    _require_cuda(x, kernel)
+    if x.dim() != 3 or kernel.dim() != 3:
+        raise XnError(1, f"conv1d expects rank-3 input and kernel, got {list(x.shape)} and {list(kernel.shape)}")
+    batch, in_channels, length = x.shape
+    out_channels, kernel_in_channels, kernel_size = kernel.shape
+    if groups < 1 or in_channels % groups:
+        raise XnError(1, f"in_channels ({in_channels}) must be divisible by groups ({groups})")
+    if out_channels % groups:
+        raise XnError(1, f"out_channels ({out_channels}) must be divisible by groups ({groups})")
+    if kernel_in_channels != in_channels // groups:
+        raise XnError(1, f"kernel in_channels/groups mismatch: expected {in_channels // groups}, got {kernel_in_channels}")
+    _check_bias(bias, out_channels)
+    span = dilation * (kernel_size - 1) + 1
+    if length + 2 * padding < span:
+        raise XnError(1, f"kernel span {span} exceeds the padded length {length + 2 * padding}")
+    out_length = (length + 2 * padding - span) // stride + 1
+    x, kernel = x.contiguous(), kernel.contiguous()
+    out = torch.empty(batch, out_channels, out_length, dtype=x.dtype, device=x.device)
+    ws_bytes = lib().xn_mm_conv1d_workspace_bytes(_dtype_code(x), batch, in_channels, out_channels, length, kernel_size,
+                                                  stride, padding, dilation, groups)
+    ws = _conv_workspace(x.device, ws_bytes)
+    check(lib().xn_mm_conv1d(_dtype_code(x), out.data_ptr(), x.data_ptr(), kernel.data_ptr(),
+                             bias.contiguous().data_ptr() if bias is not None else None, batch, in_channels,
+                             out_channels, length, out_length, kernel_size, stride, padding, dilation, groups,
+                             ws.data_ptr() if ws is not None else None, ws_bytes, _stream()))
+    return out
+
+
+def conv_transpose1d(x: torch.Tensor, kernel: torch.Tensor, bias: torch.Tensor | None = None, stride: int = 1,
+                     padding: int = 0, output_padding: int = 0, groups: int = 1) -> torch.Tensor:
+    _require_cuda(x, kernel)
+    if x.dim() != 3 or kernel.dim() != 3:
+        raise XnError(1, f"conv_transpose1d expects rank-3 input and kernel, got {list(x.shape)} and {list(kernel.shape)}")
+    batch, in_channels, length = x.shape
+    k_in_channels, out_channels_per_group, kernel_size = kernel.shape
+    out_channels = out_channels_per_group * groups
+    if groups < 1 or in_channels % groups:
+        raise XnError(1, f"in_channels ({in_channels}) must be divisible by groups ({groups})")
+    if k_in_channels != in_channels:
+        raise XnError(1, f"kernel in_channels mismatch: expected {in_channels}, got {k_in_channels}")
+    _check_bias(bias, out_channels)
+    out_length = (length - 1) * stride + kernel_size + output_padding - 2 * padding
+    if out_length < 0:
+        raise XnError(1, f"padding {padding} leaves no output")
+    x, kernel = x.contiguous(), kernel.contiguous()
+    out = torch.empty(batch, out_channels, out_length, dtype=x.dtype, device=x.device)
+    ws_bytes = lib().xn_mm_conv_transpose1d_workspace_bytes(_dtype_code(x), batch, in_channels, out_channels, length,
+                                                            kernel_size, stride, padding, output_padding, groups)
+    ws = _conv_workspace(x.device, ws_bytes)
+    check(lib().xn_mm_conv_transpose1d(_dtype_code(x), out.data_ptr(), x.data_ptr(), kernel.data_ptr(),
+                                       bias.contiguous().data_ptr() if bias is not None else None, batch, in_channels,
+                                       out_channels, length, out_length, kernel_size, stride, padding, output_padding,
+                                       groups, ws.data_ptr() if ws is not None else None, ws_bytes, _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
 # Row operations of a decoder step (xn_mm_rms_norm & co.): thin wrappers used by decoder.py and tests.
 # ---------------------------------------------------------------------------------------------
 def rms_norm(x: torch.Tensor, alpha: torch.Tensor, eps: float) -> torch.Tensor:
