@@ -109,5 +109,10 @@ int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rh
 int launch_gemm_tn_16bit_shared_lhs(xn_dtype dt, void *dst, const void *lhs, const void *rhs, const void *row_bias, size_t m,
                                     size_t n, size_t k, size_t lda, size_t ldb, size_t ldd, size_t batch, size_t rhs_bs,
                                     size_t dst_bs, cudaStream_t st);
+int launch_gemm_tn_tf32_shared_lhs(float *dst, const float *lhs, const float *rhs, const float *row_bias, size_t m, size_t n,
+                                   size_t k, size_t lda, size_t ldb, size_t ldd, size_t batch, size_t rhs_bs, size_t dst_bs,
+                                   cudaStream_t st);
+int launch_gemm_tn_tf32_splitk(float *partials, const float *lhs, const float *rhs, size_t m, size_t n, size_t kchunk,
+                               size_t splits, size_t lda, size_t ldb, cudaStream_t st);
 
 }  // namespace xn

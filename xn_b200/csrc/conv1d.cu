@@ -306,6 +306,23 @@ conv_direct_kernel(T *__restrict__ dst, const T *__restrict__ src, const T *__re
 // extra rows of the same GEMM (rows = (phase, out channel), columns = position / stride) and a last pass
 // interleaves the phases into the output.
 // ---------------------------------------------------------------------------------------------------
+// Packed rows.  16-bit types: `cin` channels.  f32: three pieces of `cin` words on the tf32 grid each, the input
+// as (hi | hi | lo) and the taps as (hi | lo | hi), so that one kind::tf32 dot product over the tripled row is
+// x_hi*w_hi + x_hi*w_lo + x_lo*w_hi: f32 products to ~2^-21 relative on MMAs that read 11-bit mantissas.
+template <typename T> __host__ __device__ constexpr int pack_mult() { return sizeof(T) == 4 ? 3 : 1; }
+__device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
+template <typename T, bool IS_TAP>
+__device__ __forceinline__ void pack_store(T *row, int cin, int c, T v) {
+    if constexpr (sizeof(T) == 4) {
+        const float hi = tf32_round(v), lo = tf32_round(v - hi);
+        row[c] = hi;
+        row[cin + c] = IS_TAP ? lo : hi;
+        row[2 * cin + c] = IS_TAP ? hi : lo;
+    } else {
+        row[c] = v;
+    }
+}
+
 // xt[b][lead + l][c] = x[b][c][l]; rows outside [lead, lead + length) are zero.  32 x 32 tiles through
 // shared memory so that both the reads (along l) and the writes (along c) are coalesced.
 template <typename T>
@@ -315,7 +332,7 @@ conv_pack_input_kernel(T *__restrict__ xt, const T *__restrict__ x, int cin, int
     const int b = blockIdx.z, r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const T *xb = x + (size_t)b * cin * length;
-    T *xtb = xt + (size_t)b * rows * cin;
+    T *xtb = xt + (size_t)b * rows * cin * pack_mult<T>();
     for (int i = ty; i < 32; i += 8) {
         const int c = c0 + i, l = r0 + tx - lead;
         T v = from_f32<T>(0.f);
@@ -325,7 +342,7 @@ conv_pack_input_kernel(T *__restrict__ xt, const T *__restrict__ x, int cin, int
     __syncthreads();
     for (int i = ty; i < 32; i += 8) {
         const int r = r0 + i, c = c0 + tx;
-        if (r < rows && c < cin) xtb[(size_t)r * cin + c] = tile[tx][i];
+        if (r < rows && c < cin) pack_store<T, false>(xtb + (size_t)r * cin * pack_mult<T>(), cin, c, tile[tx][i]);
     }
 }
 
@@ -338,7 +355,7 @@ conv_pack_taps_kernel(T *__restrict__ wp, const T *__restrict__ w, int cin, int 
         const size_t t = i / cin;
         const int kk = (int)(t % ksize);
         const size_t co = t / ksize;
-        wp[i] = w[(co * cin + ci) * ksize + kk];
+        pack_store<T, true>(wp + t * cin * pack_mult<T>(), cin, ci, w[(co * cin + ci) * ksize + kk]);
     }
 }
 
@@ -350,12 +367,80 @@ conv_pack_taps_tr_kernel(T *__restrict__ wp, const T *__restrict__ w, int cin, i
                          size_t total) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int ci = (int)(i % cin);
-        size_t t = i / cin;
+        const size_t row = i / cin;
+        size_t t = row;
         const int j = (int)(t % taps);
         t /= taps;
         const int co = (int)(t % cout), r = (int)(t / cout);
         const int kk = r + stride * (taps - 1 - j);
-        wp[i] = kk < ksize ? w[((size_t)ci * cout + co) * ksize + kk] : from_f32<T>(0.f);
+        pack_store<T, true>(wp + row * cin * pack_mult<T>(), cin, ci,
+                            kk < ksize ? w[((size_t)ci * cout + co) * ksize + kk] : from_f32<T>(0.f));
+    }
+}
+
+// The same two repackings through shared memory, one block per (out channel, 64 input channels): the taps are
+// read in runs of kernel_size contiguous elements and written in runs of 64 contiguous channels, so every
+// sector moves once (the per-element kernels above touch a sector per element on one side and are kept for
+// kernel sizes whose tile does not fit).  TR = false: source (ci, kk) at w[(co * cin + ci) * ksize + kk],
+// destination rows co * ksize + kk.  TR = true: source at w[(ci * cout + co) * ksize + kk], destination rows
+// ((r * cout + co) * taps + j) holding tap kk = r + stride * (taps - 1 - j) or zeros.
+constexpr int PK_CC = 64;
+template <typename T, bool TR>
+__global__ void __launch_bounds__(256)
+conv_pack_taps_tiled_kernel(T *__restrict__ wp, const T *__restrict__ w, int cin, int cout, int ksize, int stride, int taps) {
+    extern __shared__ __align__(16) unsigned char pk_smem[];
+    T *tile = reinterpret_cast<T *>(pk_smem);   // [PK_CC][ksize + 1]
+    const int co = blockIdx.x, c0 = blockIdx.y * PK_CC, pitch = ksize + 1;
+    const size_t ci_stride = TR ? (size_t)cout * ksize : (size_t)ksize;
+    const T *base = TR ? w + (size_t)co * ksize : w + (size_t)co * cin * ksize;
+    for (int e = threadIdx.x; e < PK_CC * ksize; e += 256) {
+        const int ci = e / ksize, kk = e - ci * ksize;
+        T v = from_f32<T>(0.f);
+        if (c0 + ci < cin) v = base[(size_t)(c0 + ci) * ci_stride + kk];
+        tile[ci * pitch + kk] = v;
+    }
+    __syncthreads();
+    const int nslots = TR ? stride * taps : ksize;
+    const int ci = threadIdx.x & (PK_CC - 1);
+    if (c0 + ci >= cin) return;
+    for (int sl = threadIdx.x / PK_CC; sl < nslots; sl += 256 / PK_CC) {
+        size_t row;
+        int kk;
+        if (TR) {
+            const int r = sl / taps, j = sl - r * taps;
+            row = ((size_t)r * cout + co) * taps + j;
+            kk = r + stride * (taps - 1 - j);
+        } else {
+            row = (size_t)co * ksize + sl;
+            kk = sl;
+        }
+        pack_store<T, true>(wp + row * cin * pack_mult<T>(), cin, c0 + ci, kk < ksize ? tile[ci * pitch + kk] : from_f32<T>(0.f));
+    }
+}
+
+// Phase interleave through shared memory: one block per (batch entry, out channel, 128 values of q); rows of d
+// are read contiguously, the output run of 128 * stride positions is written contiguously.
+constexpr int IL_QT = 128;
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_interleave_tiled_kernel(T *__restrict__ out, const T *__restrict__ d, const T *__restrict__ bias, int cout, int out_length,
+                             int stride, int padding, int nq) {
+    extern __shared__ __align__(16) unsigned char il_smem[];
+    T *tile = reinterpret_cast<T *>(il_smem);
+    constexpr int PITCH = IL_QT + 4 / (int)sizeof(T);   // an odd number of 32-bit words: phases fall in distinct banks
+    const int q0 = blockIdx.x * IL_QT, co = blockIdx.y, b = blockIdx.z;
+    const T *db = d + ((size_t)b * stride * cout + co) * nq;
+    for (int i = threadIdx.x; i < stride * IL_QT; i += 256) {
+        const int r = i / IL_QT, q = i - r * IL_QT;
+        if (q0 + q < nq) tile[r * PITCH + q] = db[(size_t)r * cout * nq + q0 + q];
+    }
+    __syncthreads();
+    const float bv = bias ? to_f32(bias[co]) : 0.f;
+    T *ob = out + ((size_t)b * cout + co) * out_length;
+    for (int i = threadIdx.x; i < stride * IL_QT; i += 256) {
+        const int q = i / stride, r = i - q * stride;
+        const int lo = (q0 + q) * stride + r - padding;
+        if (q0 + q < nq && lo >= 0 && lo < out_length) ob[lo] = from_f32<T>(to_f32(tile[r * PITCH + q]) + bv);
     }
 }
 
@@ -377,29 +462,66 @@ conv_interleave_kernel(T *__restrict__ out, const T *__restrict__ d, const T *__
     }
 }
 
+// out[row][col] = sum over splits of part[s][row][col] (+ bias[row]), summed in split order
+__global__ void __launch_bounds__(256)
+conv_sum_partials_kernel(float *__restrict__ out, const float *__restrict__ part, const float *__restrict__ bias, int splits,
+                         size_t n, size_t total) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < splits; ++k) s += part[(size_t)k * total + i];
+        if (bias) s += bias[i / n];
+        out[i] = s;
+    }
+}
+
 inline size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 
 // Scratch of the tensor-memory path in bytes (0: the call uses the scratch-free kernels).
-struct ConvPlan { bool gemm; size_t xt_bytes, wp_bytes, d_bytes; int rows, taps, nq; };
+struct ConvPlan { bool gemm; size_t xt_bytes, wp_bytes, d_bytes, part_bytes; int rows, taps, nq, splits; };
+
+// f32, one batch entry, few output tiles, long k: cut k into equal chunks (multiples of the 32-word k stage)
+// so that about one CTA per SM has work; 1 = no split.
+inline int conv_splits(size_t m, size_t n, size_t k) {
+    if (k % 32) return 1;
+    const size_t tiles = ((m + 127) / 128) * ((n + 255) / 256), sms = (size_t)sm_count();
+    const size_t units = k / 32;
+    if (tiles == 0 || tiles * 2 > sms || units < 8) return 1;
+    size_t want = sms / tiles;
+    if (want > units / 4) want = units / 4;   // at least 4 k stages per chunk
+    if (want > 64) want = 64;
+    for (size_t s = want; s > 1; --s)
+        if (units % s == 0) return (int)s;
+    return 1;
+}
 template <bool TR>
 ConvPlan conv_plan(int dtype, const ConvArgs &a) {
     ConvPlan p{};
     static const bool off = [] { const char *e = getenv("XN_CONV_GEMM"); return e && atoi(e) == 0; }();
     const size_t cin = (size_t)a.cin_g, cout = (size_t)a.cout_g;
-    p.gemm = !off && dtype != XN_F32 && a.groups == 1 && a.dilation == 1 && cin % 8 == 0 && a.batch <= 65535;
+    const size_t es = dtype == XN_F32 ? 4 : 2, mult = dtype == XN_F32 ? 3 : 1;
+    p.gemm = !off && a.groups == 1 && a.dilation == 1 && (cin * mult * es) % 16 == 0 && a.batch <= 65535;
     if (!p.gemm) return p;
     if (!TR) {
         p.rows = a.length + 2 * a.padding;
         p.taps = a.ksize;
-        p.wp_bytes = round256(cout * a.ksize * cin * 2);
+        p.wp_bytes = round256(cout * a.ksize * cin * mult * es);
     } else {
         p.taps = (a.ksize + a.stride - 1) / a.stride;
         p.nq = (a.out_length - 1 + a.padding) / a.stride + 1;
         p.rows = p.nq + p.taps - 1;      // window of position q starts at input position q - (taps - 1)
-        p.wp_bytes = round256((size_t)a.stride * cout * p.taps * cin * 2);
-        p.d_bytes = round256((size_t)a.batch * a.stride * cout * p.nq * 2);
+        p.wp_bytes = round256((size_t)a.stride * cout * p.taps * cin * mult * es);
+        p.d_bytes = round256((size_t)a.batch * a.stride * cout * p.nq * es);
     }
-    p.xt_bytes = round256((size_t)a.batch * p.rows * cin * 2);
+    p.xt_bytes = round256((size_t)a.batch * p.rows * cin * mult * es);
+    p.splits = 1;
+    if (dtype == XN_F32 && a.batch == 1) {
+        const size_t m = TR ? (size_t)a.stride * cout : cout, n = TR ? (size_t)p.nq : (size_t)a.out_length;
+        p.splits = conv_splits(m, n, (size_t)p.taps * cin * mult);
+        if (p.splits > 1) {
+            p.part_bytes = round256((size_t)p.splits * m * n * 4);
+            if (!TR) p.d_bytes = 0;
+        }
+    }
     return p;
 }
 
@@ -415,23 +537,47 @@ int launch_conv_gemm(xn_dtype dt, T *dst, const T *src, const T *kernel, const T
     conv_pack_input_kernel<T><<<pg, 256, 0, st>>>(xt, src, cin, a.length, lead, p.rows);
     const size_t wtotal = TR ? (size_t)a.stride * cout * p.taps * cin : (size_t)cout * a.ksize * cin;
     const unsigned wgrid = (unsigned)((wtotal + 255) / 256 < 4096 ? (wtotal + 255) / 256 : 4096);
-    if (!TR)
+    const size_t pk_smem = (size_t)PK_CC * (a.ksize + 1) * sizeof(T);
+    if (pk_smem <= 40 * 1024 && cout <= 0x7fffffff / 2 && (cin + PK_CC - 1) / PK_CC <= 65535) {
+        dim3 wg((unsigned)cout, (unsigned)((cin + PK_CC - 1) / PK_CC));
+        conv_pack_taps_tiled_kernel<T, TR><<<wg, 256, pk_smem, st>>>(wp, kernel, cin, cout, a.ksize, a.stride, p.taps);
+    } else if (!TR) {
         conv_pack_taps_kernel<T><<<wgrid, 256, 0, st>>>(wp, kernel, cin, a.ksize, wtotal);
-    else
+    } else {
         conv_pack_taps_tr_kernel<T><<<wgrid, 256, 0, st>>>(wp, kernel, cin, cout, a.ksize, a.stride, p.taps, wtotal);
+    }
     XN_CHECK_CUDA(cudaGetLastError());
-    const size_t k = (size_t)p.taps * cin;
-    if (!TR)
-        return launch_gemm_tn_16bit_shared_lhs(dt, dst, wp, xt, bias, cout, a.out_length, k, k, (size_t)a.stride * cin,
-                                               a.out_length, a.batch, (size_t)p.rows * cin, (size_t)cout * a.out_length, st);
+    const size_t cpr = (size_t)cin * pack_mult<T>();   // packed row length
+    const size_t k = (size_t)p.taps * cpr;
+    auto gemm = [&](T *out, const T *row_bias, size_t m, size_t n, size_t ldb, size_t out_bs) -> int {
+        if constexpr (sizeof(T) == 4) {
+            if (p.splits > 1) {
+                float *part = reinterpret_cast<float *>(ws + p.xt_bytes + p.wp_bytes + p.d_bytes);
+                if (int rc = launch_gemm_tn_tf32_splitk(part, wp, xt, m, n, k / p.splits, p.splits, k, ldb, st)) return rc;
+                const size_t total = m * n;
+                const unsigned grid = (unsigned)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048);
+                conv_sum_partials_kernel<<<grid, 256, 0, st>>>(out, part, row_bias, p.splits, n, total);
+                XN_CHECK_CUDA(cudaGetLastError());
+                return XN_OK;
+            }
+            return launch_gemm_tn_tf32_shared_lhs(out, wp, xt, row_bias, m, n, k, k, ldb, n, a.batch, (size_t)p.rows * cpr, out_bs, st);
+        } else
+            return launch_gemm_tn_16bit_shared_lhs(dt, out, wp, xt, row_bias, m, n, k, k, ldb, n, a.batch, (size_t)p.rows * cpr,
+                                                   out_bs, st);
+    };
+    if (!TR) return gemm(dst, bias, cout, a.out_length, (size_t)a.stride * cpr, (size_t)cout * a.out_length);
     const size_t m = (size_t)a.stride * cout;
-    if (int rc = launch_gemm_tn_16bit_shared_lhs(dt, d, wp, xt, nullptr, m, p.nq, k, k, cin, p.nq, a.batch, (size_t)p.rows * cin,
-                                                 m * p.nq, st))
-        return rc;
+    if (int rc = gemm(d, nullptr, m, p.nq, cpr, m * p.nq)) return rc;
     const size_t total = (size_t)a.batch * cout * a.out_length;
     const size_t blocks = (total + 255) / 256;
     const unsigned grid = (unsigned)(blocks < (size_t)sm_count() * 32 ? blocks : (size_t)sm_count() * 32);
-    conv_interleave_kernel<T><<<grid, 256, 0, st>>>(dst, d, bias, cout, a.out_length, a.stride, a.padding, p.nq, total);
+    const size_t il_smem = (size_t)a.stride * (IL_QT + 4 / sizeof(T)) * sizeof(T);
+    if (il_smem <= 40 * 1024 && cout <= 65535) {
+        dim3 ig((unsigned)((p.nq + IL_QT - 1) / IL_QT), (unsigned)cout, (unsigned)a.batch);
+        conv_interleave_tiled_kernel<T><<<ig, 256, il_smem, st>>>(dst, d, bias, cout, a.out_length, a.stride, a.padding, p.nq);
+    } else {
+        conv_interleave_kernel<T><<<grid, 256, 0, st>>>(dst, d, bias, cout, a.out_length, a.stride, a.padding, p.nq, total);
+    }
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -443,10 +589,10 @@ int launch_conv(xn_dtype dt, T *dst, const T *src, const T *kernel, const T *bia
                 cudaStream_t st) {
     const size_t total = (size_t)a.batch * a.cout_g * a.groups * a.out_length;
     if (total == 0) return XN_OK;
-    if constexpr (sizeof(T) == 2) {
+    {
         const ConvPlan p = conv_plan<TR>(dt, a);
         if (p.gemm) {
-            const size_t need = p.xt_bytes + p.wp_bytes + p.d_bytes;
+            const size_t need = p.xt_bytes + p.wp_bytes + p.d_bytes + p.part_bytes;
             if (!ws || ws_bytes < need)
                 return fail(XN_ERR_WORKSPACE, "conv: workspace of %zu bytes, %zu needed (ask the _workspace_bytes function)",
                             ws ? ws_bytes : (size_t)0, need);
@@ -557,8 +703,11 @@ extern "C" size_t xn_mm_conv1d_workspace_bytes(xn_dtype dtype, size_t batch, siz
     ConvArgs a{};
     a.batch = (int)batch, a.groups = 1, a.cin_g = (int)in_channels, a.cout_g = (int)out_channels;
     a.length = (int)length, a.ksize = (int)kernel_size, a.stride = (int)stride, a.padding = (int)padding, a.dilation = (int)dilation;
+    const size_t span = dilation * (kernel_size - 1) + 1;
+    if (dilation < 1 || length + 2 * padding < span) return 0;
+    a.out_length = (int)((length + 2 * padding - span) / stride + 1);
     const ConvPlan p = conv_plan<false>(dtype, a);
-    return p.gemm ? p.xt_bytes + p.wp_bytes + p.d_bytes : 0;
+    return p.gemm ? p.xt_bytes + p.wp_bytes + p.d_bytes + p.part_bytes : 0;
 }
 
 extern "C" size_t xn_mm_conv_transpose1d_workspace_bytes(xn_dtype dtype, size_t batch, size_t in_channels,
@@ -573,5 +722,5 @@ extern "C" size_t xn_mm_conv_transpose1d_workspace_bytes(xn_dtype dtype, size_t 
     a.length = (int)length, a.out_length = (int)(full - 2 * padding), a.ksize = (int)kernel_size, a.stride = (int)stride;
     a.padding = (int)padding, a.dilation = 1;
     const ConvPlan p = conv_plan<true>(dtype, a);
-    return p.gemm ? p.xt_bytes + p.wp_bytes + p.d_bytes : 0;
+    return p.gemm ? p.xt_bytes + p.wp_bytes + p.d_bytes + p.part_bytes : 0;
 }

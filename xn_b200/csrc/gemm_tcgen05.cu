@@ -112,6 +112,13 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
             : "memory");
 }
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -146,17 +153,19 @@ struct GemmArgs {
     const void *row_bias; // optional, 16-bit kinds only: added to every element of output row i (element type of y)
 };
 
-// KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16
+// KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16, 3 = tf32 operands (f32 words already on
+// the tf32 grid) -> f32 out
 template <int KIND, int BN, int NA, int NSTAGE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                     const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
     constexpr bool F8 = KIND == 0;
-    constexpr int ELEM = F8 ? 1 : 2;
+    constexpr int ELEM = F8 ? 1 : (KIND == 3 ? 4 : 2);
     constexpr int BK = BKB / ELEM;  // K elements per stage
     constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB;
     constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES;
-    constexpr uint32_t IDESC = F8 ? instr_desc(0, 0, BN) : (KIND == 1 ? instr_desc(1, 1, BN) : instr_desc(0, 0, BN));
+    constexpr uint32_t IDESC = F8 ? instr_desc(0, 0, BN)
+                               : (KIND == 1 ? instr_desc(1, 1, BN) : (KIND == 3 ? instr_desc(2, 2, BN) : instr_desc(0, 0, BN)));
     constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
 
     extern __shared__ unsigned char smem_raw[];
@@ -236,8 +245,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
-                        umma<F8>(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
-                        if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + adv, IDESC, 1u);
+                        if constexpr (KIND == 3) {
+                            umma_tf32(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
+                        } else {
+                            umma<F8>(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
+                            if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + adv, IDESC, 1u);
+                        }
                     }
                     umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
                 }
@@ -261,13 +274,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             if (F8 && row < args.M) xs = __ldg(args.x_scale + row);
             float rb = 0.0f;
             if (!F8 && args.row_bias && row < args.M)
-                rb = KIND == 2 ? __half2float(reinterpret_cast<const __half *>(args.row_bias)[row])
-                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(args.row_bias)[row]);
+                rb = KIND == 3 ? reinterpret_cast<const float *>(args.row_bias)[row]
+                     : KIND == 2 ? __half2float(reinterpret_cast<const __half *>(args.row_bias)[row])
+                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(args.row_bias)[row]);
             // Column groups of GC: the warp's 32 x GC slab goes through shared memory (16-byte chunks
             // XOR-swizzled by row) so that global stores are whole row segments of GC*2 bytes instead of
             // 16 bytes per row -- this matters most when the destination is a peer GPU.
-            constexpr int GC = BN % 128 == 0 ? 128 : (BN % 64 == 0 ? 64 : 32);  // columns per group (divides BN)
-            constexpr int CPR = GC / 8;                 // 16-byte chunks per slab row
+            constexpr bool F32OUT = KIND == 3;
+            constexpr int OES = F32OUT ? 4 : 2;         // bytes per output element
+            constexpr int EPC = 16 / OES;               // output elements per 16-byte chunk
+            constexpr int GC = (BN % 128 == 0 && !F32OUT) ? 128 : (BN % 64 == 0 ? 64 : 32);  // columns per group (divides BN)
+            constexpr int CPR = GC / EPC;               // 16-byte chunks per slab row (a row is at most 256 bytes)
             constexpr int RPI = 32 / CPR;               // rows written per store instruction
             unsigned char *slab = epi_smem + (size_t)(warp - 2) * 32 * 256;
 #pragma unroll 1
@@ -277,6 +294,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + g0 + c * 32), v);
                     const int col0 = n_blk * BN + g0 + c * 32;
+                    if constexpr (F32OUT) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int chunk = (c * 8 + j) ^ (lane & (CPR - 1));
+                            *reinterpret_cast<uint4 *>(slab + lane * (GC * OES) + chunk * 16) =
+                                make_uint4(__float_as_uint(__uint_as_float(v[4 * j]) + rb), __float_as_uint(__uint_as_float(v[4 * j + 1]) + rb),
+                                           __float_as_uint(__uint_as_float(v[4 * j + 2]) + rb), __float_as_uint(__uint_as_float(v[4 * j + 3]) + rb));
+                        }
+                        continue;
+                    }
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -300,7 +327,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int chunk = (c * 4 + j) ^ (lane & (CPR - 1));
-                        *reinterpret_cast<uint4 *>(slab + lane * (GC * 2) + chunk * 16) =
+                        *reinterpret_cast<uint4 *>(slab + lane * (GC * OES) + chunk * 16) =
                             make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
                     }
                 }
@@ -309,11 +336,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 #pragma unroll 1
                 for (int r0 = 0; r0 < 32; r0 += RPI) {
                     const int r = r0 + sub;
-                    const uint4 val = *reinterpret_cast<const uint4 *>(slab + r * (GC * 2) + ((ch ^ (r & (CPR - 1))) * 16));
+                    const uint4 val = *reinterpret_cast<const uint4 *>(slab + r * (GC * OES) + ((ch ^ (r & (CPR - 1))) * 16));
                     const int grow = m_blk * BM + q * 32 + r;
-                    const int gcol = n_blk * BN + g0 + ch * 8;
+                    const int gcol = n_blk * BN + g0 + ch * EPC;
                     if (grow < args.M && gcol < args.N) {
                         for (int p = 0; p < args.ndst; ++p) {
+                            if constexpr (F32OUT) {
+                                uint32_t *dst = reinterpret_cast<uint32_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
+                                                (size_t)grow * args.ldy + args.col_offset + gcol;
+                                if (gcol + 4 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                    *reinterpret_cast<uint4 *>(dst) = val;
+                                } else {
+                                    const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                                    for (int j = 0; j < 4 && gcol + j < args.N; ++j) dst[j] = w4[j];
+                                }
+                                continue;
+                            }
                             uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
                                             (size_t)grow * args.ldy + args.col_offset + gcol;
                             if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
@@ -645,7 +683,8 @@ int make_map3(CUtensorMap *map, const void *base, int elem, size_t rows, size_t 
     cuuint64_t strides[2] = {(cuuint64_t)(inner ? batch_stride : ld) * elem, (cuuint64_t)(inner ? ld : batch_stride) * elem};
     cuuint32_t box[3] = {(cuuint32_t)(BKB / elem), (cuuint32_t)(inner ? 1 : box_rows), (cuuint32_t)(inner ? box_rows : 1)};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUtensorMapDataType dt = elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    CUtensorMapDataType dt = elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                       : (elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16);
     CUresult r = fn(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with code %d", (int)r);
@@ -671,7 +710,7 @@ struct BatchGeom { size_t batch = 1, a_stride = 0, b_stride = 0; };
 template <int KIND, int BN, int NA>
 int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
                cudaStream_t st, const BatchGeom &bg = BatchGeom()) {
-    constexpr int ELEM = KIND == 0 ? 1 : 2;
+    constexpr int ELEM = KIND == 0 ? 1 : (KIND == 3 ? 4 : 2);
     constexpr int STAGE_BYTES = NA * BM * BKB + BN * BKB;
     constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
     CUtensorMap ma0, ma1, mb;
@@ -917,6 +956,34 @@ int launch_gemm_tn_16bit_shared_lhs(xn_dtype dt, void *dst, const void *lhs, con
     bg.batch = batch; bg.a_stride = 0; bg.b_stride = rhs_bs;
     return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
                          : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
+}
+
+// f32 form of the same call on kind::tf32 MMAs.  Both operands must already be f32 words on the tf32 grid
+// (low 13 mantissa bits zero): the caller carries full f32 precision by splitting each operand into such
+// pieces along k (see conv1d.cu).  dst and row_bias are f32.
+int launch_gemm_tn_tf32_shared_lhs(float *dst, const float *lhs, const float *rhs, const float *row_bias, size_t m, size_t n,
+                                   size_t k, size_t lda, size_t ldb, size_t ldd, size_t batch, size_t rhs_bs, size_t dst_bs,
+                                   cudaStream_t st) {
+    GemmArgs a{};
+    a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)dst_bs;
+    a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    a.a_bcast = 1; a.row_bias = row_bias;
+    BatchGeom bg;
+    bg.batch = batch; bg.a_stride = 0; bg.b_stride = rhs_bs;
+    return launch_kind<3, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
+}
+
+// Split-k form for problems with too few output tiles to fill the GPU: the k axis is cut into `splits` equal
+// chunks of kchunk elements that ride the kernel's batch dimension (both tensor maps get a batch stride of
+// kchunk inside the rows), each writing its own [m, n] f32 partial; the caller sums them in a fixed order.
+int launch_gemm_tn_tf32_splitk(float *partials, const float *lhs, const float *rhs, size_t m, size_t n, size_t kchunk,
+                               size_t splits, size_t lda, size_t ldb, cudaStream_t st) {
+    GemmArgs a{};
+    a.y[0] = partials; a.ndst = 1; a.col_offset = 0; a.batch = (int)splits; a.y_batch_stride = (long long)(m * n);
+    a.M = (int)m; a.N = (int)n; a.K = (int)kchunk; a.ldy = (int)n;
+    BatchGeom bg;
+    bg.batch = splits; bg.a_stride = kchunk; bg.b_stride = kchunk;
+    return launch_kind<3, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
 }
 
 }  // namespace xn

@@ -2,7 +2,7 @@
 the f32 linear, and the 16-bit dense GEMM, each with its roofline and (where the reference has a
 GPU path) the same call through cuBLAS as xn issues it (torch.matmul -> cublasGemmEx, f32 accumulate).
 
-    python -m xn_b200.sweep [--what fp8|dense|grouped|f32|all] [--json out.json]
+    python -m xn_b200.sweep [--what fp8|dense|grouped|f32|conv|all] [--json out.json]
 
 Timing: CUDA events around a CUDA-graph replay of `reps` launches that rotate over enough distinct
 weight copies to exceed the L2 several times for the bandwidth-bound points.
@@ -167,12 +167,71 @@ def sweep_f32(out, dev, pk):
     print(json.dumps(row), flush=True)
 
 
-def write_md(rows, path):
+def sweep_conv(out, dev, pk):
+    """conv1d / conv_transpose1d at codec-encoder sizes.  Beside each point: the reference's own GPU lowering
+    built from the same library calls (im2col -> cuBLAS GEMM -> transpose, xn-core/src/cuda_backend.rs:1490-1561;
+    transpose -> cuBLAS GEMM -> col2im, :1783-1856) and cuDNN through torch."""
+    import torch.nn.functional as F
+    prev = (torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32)
+    torch.backends.cuda.matmul.allow_tf32 = False  # the reference keeps full-precision f32
+    torch.backends.cudnn.allow_tf32 = False
+    # batch, c_in, c_out, length, kernel, stride, padding
+    conv = [(8, 512, 512, 4096, 7, 1, 3), (8, 512, 1024, 4096, 16, 8, 4), (8, 64, 64, 32768, 7, 1, 3), (32, 512, 512, 256, 3, 1, 1),
+            (1, 512, 512, 64, 7, 1, 3)]
+    convt = [(8, 512, 256, 512, 16, 8), (8, 1024, 512, 256, 8, 4), (1, 512, 256, 16, 16, 8)]
+    for dt in (torch.bfloat16, torch.float32):
+        es = 2 if dt == torch.bfloat16 else 4
+        peak = pk["bf16_tflops"] if es == 2 else None
+        for b, ci, co, length, ks, st, pad in conv:
+            x = torch.randn(b, ci, length, device=dev, dtype=dt)
+            w = (torch.randn(co, ci, ks, device=dev) / (ci * ks) ** 0.5).to(dt)
+            bias = torch.randn(co, device=dev, dtype=dt)
+            lo = (length + 2 * pad - (ks - 1) - 1) // st + 1
+            t = time_graph([lambda: xn.ops.conv1d(x, w, bias, st, pad, 1, 1)], 4)
+
+            def lowered():
+                col = F.unfold(F.pad(x, (pad, pad)).unsqueeze(2), (1, ks), stride=(1, st)).transpose(1, 2).contiguous()
+                return (torch.matmul(col, w.reshape(co, -1).t()).transpose(1, 2).contiguous() + bias.view(1, -1, 1))
+            t_low = time_graph([lowered], 2)
+            t_dnn = time_graph([lambda: F.conv1d(x, w, bias, st, pad)], 4)
+            flops = 2.0 * b * co * ci * ks * lo
+            byts = es * (b * ci * length + co * ci * ks + b * co * lo)
+            roof = max(byts / (pk["hbm_gbs"] * 1e9), flops / (peak * 1e12) if peak else 0.0)
+            row = {"config": "conv1d", "dtype": str(dt), "b": b, "c_in": ci, "c_out": co, "length": length, "k": ks, "stride": st,
+                   "us": t * 1e6, "tflops": flops / t / 1e12, "gbs": byts / t / 1e9, "frac_of_roofline": roof / t,
+                   "lowered_us": t_low * 1e6, "cudnn_us": t_dnn * 1e6}
+            out.append(row)
+            print(json.dumps(row), flush=True)
+        for b, ci, co, length, ks, st in convt:
+            x = torch.randn(b, ci, length, device=dev, dtype=dt)
+            w = (torch.randn(ci, co, ks, device=dev) / ci ** 0.5).to(dt)
+            bias = torch.randn(co, device=dev, dtype=dt)
+            lo = (length - 1) * st + ks
+            t = time_graph([lambda: xn.ops.conv_transpose1d(x, w, bias, st, 0, 0, 1)], 4)
+
+            def lowered_t():
+                col = torch.matmul(x.transpose(1, 2).contiguous(), w.reshape(ci, co * ks))          # [b, l, co*ks]
+                return F.fold(col.transpose(1, 2), (1, lo), (1, ks), stride=(1, st)).squeeze(2) + bias.view(1, -1, 1)
+            t_low = time_graph([lowered_t], 2)
+            t_dnn = time_graph([lambda: F.conv_transpose1d(x, w, bias, st)], 4)
+            flops = 2.0 * b * co * ci * ks * length
+            byts = es * (b * ci * length + co * ci * ks + b * co * lo)
+            roof = max(byts / (pk["hbm_gbs"] * 1e9), flops / (peak * 1e12) if peak else 0.0)
+            row = {"config": "conv_transpose1d", "dtype": str(dt), "b": b, "c_in": ci, "c_out": co, "length": length, "k": ks,
+                   "stride": st, "us": t * 1e6, "tflops": flops / t / 1e12, "gbs": byts / t / 1e9, "frac_of_roofline": roof / t,
+                   "lowered_us": t_low * 1e6, "cudnn_us": t_dnn * 1e6}
+            out.append(row)
+            print(json.dumps(row), flush=True)
+    torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = prev
+
+
+def write_md(rows, path, what="all"):
     """The sweep as markdown tables (the form kept under profiles/)."""
     pk = rows[0]["peaks"]
+    tag = "sweep_" + what
     L = ["# Shape sweeps (CUDA-event timing, graph replay, operands rotated over >= 600 MB of distinct weight copies)", "",
-         "Command: `python -m xn_b200.sweep --what all --json gpurun_out/sweep_all.json --md gpurun_out/sweep_all.md` on one B200"
-         " (committed files only).",
+         "Command: `python -m xn_b200.sweep --what %s --json gpurun_out/%s.json --md gpurun_out/%s.md` on one B200"
+         " (committed files only)." % (what, tag, tag),
          "Roofline per point = max(algorithmic bytes / measured HBM GB/s, 2MNK / peak), peak = %s cuBLAS bf16 burst" % pk["kind"],
          "(%.0f TFLOP/s) for the W8A16 and 16-bit rows and twice that for W8A8; HBM = %.0f GB/s; `frac` = roofline time / measured time."
          % (pk["bf16_tflops"], pk["hbm_gbs"]),
@@ -213,6 +272,19 @@ def write_md(rows, path):
             L += ["## f32 linear (x [%d,%d], W [%d,%d]; 3xTF32 tensor-core form unless XN_MM_F32_EXACT=1)" % (r["m"], r["k"], r["n"], r["k"]), "",
                   "%.1f µs, %.0f GB/s (%.2f of %s HBM); cuBLAS SGEMM without TF32 (the reference's default): %.1f µs."
                   % (r["us"], r["gbs"], r["frac_of_hbm"], pk["kind"], r["cublas_us"]), ""]
+    cv = [r for r in rows if r.get("config") in ("conv1d", "conv_transpose1d")]
+    if cv:
+        L += ["## conv1d / conv_transpose1d (bias fused; tensor-memory GEMM over a channels-last view: bf16 on kind::f16, f32 as three tf32 pieces on kind::tf32)", "",
+              "`lowered` = the reference's GPU lowering from the same library calls (im2col / col2im around a cuBLAS GEMM, f32 without TF32);"
+              " `cuDNN` = torch's conv (TF32 off). frac: bf16 rows against max(HBM, tensor) roofline, f32 rows against HBM alone"
+              " (no measured f32-exact tensor peak exists; 3 tf32 MMAs per product).", "",
+              "| op | dtype | batch | C_in→C_out | length | kernel/stride | µs | TFLOP/s | frac | lowered µs | cuDNN µs |",
+              "|---|---|---|---|---|---|---|---|---|---|---|"]
+        for r in cv:
+            L.append("| %s | %s | %d | %d→%d | %d | %d/%d | %.1f | %.1f | %.2f | %.1f | %.1f |" % (
+                r["config"], r["dtype"].replace("torch.", ""), r["b"], r["c_in"], r["c_out"], r["length"], r["k"], r["stride"],
+                r["us"], r["tflops"], r["frac_of_roofline"], r["lowered_us"], r["cudnn_us"]))
+        L.append("")
     with open(path, "w") as f:
         f.write("\n".join(L))
 
@@ -228,14 +300,14 @@ def main():
     pk = peaks()
     out = [{"peaks": pk, "nominal": NOMINAL}]
     print(json.dumps(out[0]), flush=True)
-    for name, fn in (("fp8", sweep_fp8), ("dense", sweep_dense), ("grouped", sweep_grouped), ("f32", sweep_f32)):
+    for name, fn in (("fp8", sweep_fp8), ("dense", sweep_dense), ("grouped", sweep_grouped), ("f32", sweep_f32), ("conv", sweep_conv)):
         if a.what in ("all", name):
             fn(out, dev, pk)
     if a.json:
         with open(a.json, "w") as f:
             json.dump(out, f, indent=1)
     if a.md:
-        write_md(out, a.md)
+        write_md(out, a.md, a.what)
 
 
 if __name__ == "__main__":
