@@ -140,6 +140,30 @@ def test_f32_decode_linear_split_tf32_path(xn, oracle, cuda, m, n, k):
     assert err < 3e-5, err  # what the three-term split actually delivers
 
 
+@pytest.mark.parametrize("m,n,k,form", [(130, 70, 300, "t"), (300, 1000, 4096, "t"), (257, 264, 1028, "kn"),
+                                         (128, 64, 32, "t"), (512, 200, 2052, "views")])
+def test_f32_many_rows_tf32_piece_path(xn, oracle, cuda, m, n, k, form):
+    """f32 with at least 128 rows runs on the tensor-memory kernel as three tf32 pieces per operand, whatever
+    the operand strides (the repack normalises them); the accumulator is handed to f32 registers every 64
+    MMAs, so the result stays at f32-accumulation accuracy, far inside the 1e-4 bar."""
+    rng = np.random.default_rng(m + n + k)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.03).astype(np.float32)
+    xd, wd = torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda)
+    if form == "t":
+        y = xn.matmul_t(xd, wd)
+    elif form == "kn":
+        y = xn.matmul(xd, wd.t().contiguous())                      # rhs [k, n], n-contiguous
+    else:
+        xs = torch.zeros(m, k + 8, device=cuda)
+        xs[:, :k] = xd
+        y = xn.matmul(xs[:, :k], wd.t())                            # row-pitched lhs, transposed VIEW as rhs
+    truth = oracle.gemm_f64(0, x.reshape(-1), 0, w.reshape(-1), 0, m, n, k, 1, 0, 0, (1, k), (k, 1))
+    err = oracle.rel_err(y.cpu().numpy(), truth)
+    assert err < 1e-4
+    assert err < 5e-5, err
+
+
 @pytest.mark.parametrize("dt,m,n,k", [(2, 64, 256, 512), (1, 33, 130, 200), (0, 130, 70, 300), (2, 1, 512, 1024),
                                       (2, 16, 384, 2048)])
 def test_seeded_linear_shapes(xn, oracle, cuda, dt, m, n, k):

@@ -122,6 +122,11 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                         lhs_b_stride != 0)))
         return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
                                     (cudaStream_t)stream);
+    // f32 with many rows, one batch, row-major dst: three tf32 pieces per operand on the tensor-memory kernel
+    // (any operand strides; the repack normalises them).
+    if (dtype == XN_F32 && lhs_b == 1 && dst_cs == 1 && dst_rs <= 0x7fffffff && gemm_f32_tc_fits(m, n, k))
+        return launch_gemm_f32_tc(static_cast<float *>(dst), reinterpret_cast<const float *>(l), reinterpret_cast<const float *>(r),
+                                  m, n, k, dst_rs, lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
     return launch_gemm_generic(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
                                lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
 }

@@ -114,5 +114,12 @@ int launch_gemm_tn_tf32_shared_lhs(float *dst, const float *lhs, const float *rh
                                    cudaStream_t st);
 int launch_gemm_tn_tf32_splitk(float *partials, const float *lhs, const float *rhs, size_t m, size_t n, size_t kchunk,
                                size_t splits, size_t lda, size_t ldb, cudaStream_t st);
+int launch_gemm_tn_tf32(float *dst, const float *lhs, const float *rhs, size_t m, size_t n, size_t k, size_t ldd,
+                        cudaStream_t st);
+int library_scratch(cudaStream_t st, size_t bytes, void **out);
+// f32 matmul with many rows on the kind::tf32 tensor-memory kernel (three tf32 pieces per operand); any strides
+bool gemm_f32_tc_fits(size_t m, size_t n, size_t k);
+int launch_gemm_f32_tc(float *dst, const float *lhs, const float *rhs, size_t m, size_t n, size_t k, size_t dst_rs,
+                       size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, cudaStream_t st);
 
 }  // namespace xn

@@ -164,6 +164,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     constexpr int BK = BKB / ELEM;  // K elements per stage
     constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB;
     constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES;
+    // tcgen05 adds into its f32 accumulator with truncation: over n MMAs the result drifts by about n * 3e-8
+    // of the running sum (4e-5 at 1536 MMAs, measured).  The tf32 kind, whose callers expect f32 accuracy, therefore
+    // hands the accumulator to the epilogue every KCH k stages (64 MMAs); the epilogue warps keep the sum in
+    // registers, in round-to-nearest f32.
+    constexpr int KCH = KIND == 3 ? 16 : (1 << 30);
+    static_assert(KIND != 3 || BN <= 128, "the tf32 kind keeps BN accumulator registers per epilogue thread");
     constexpr uint32_t IDESC = F8 ? instr_desc(0, 0, BN)
                                : (KIND == 1 ? instr_desc(1, 1, BN) : (KIND == 3 ? instr_desc(2, 2, BN) : instr_desc(0, 0, BN)));
     constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
@@ -227,15 +233,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int it = 0, t_local = 0;
+            int it = 0, vt = 0;   // vt: accumulator hand-overs to the epilogue so far (one per tile, or per k chunk)
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
-                const int acc = t_local & 1;
-                const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
+            for (int kb0 = 0; (kb0 < num_kb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
+                const int acc = vt & 1;
+                const unsigned acc_ph = (unsigned)(vt >> 1) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kend = num_kb - kb0 < KCH ? num_kb : kb0 + KCH;
+                for (int kb = kb0; kb < kend; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
                     if (!mbar_wait(&full[s], ph)) { ok = false; break; }
@@ -246,7 +254,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
                         if constexpr (KIND == 3) {
-                            umma_tf32(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
+                            umma_tf32(d_tmem, da0 + adv, db + adv, IDESC, kb > kb0 || ks != 0);
                         } else {
                             umma<F8>(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
                             if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + adv, IDESC, 1u);
@@ -262,6 +270,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int t_local = 0;
         bool ok = true;
+        if constexpr (KIND == 3) {
+            constexpr int GC = BN % 64 == 0 ? 64 : 32, CPR = GC / 4, RPI = 32 / CPR;
+            unsigned char *slab = epi_smem + (size_t)(warp - 2) * 32 * 256;
+            int vt = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
+                const int m_blk = tin % num_m, n_blk = tin / num_m;
+                float racc[BN];
+#pragma unroll
+                for (int i = 0; i < BN; ++i) racc[i] = 0.f;
+                for (int kb0 = 0; (kb0 < num_kb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
+                    const int acc = vt & 1;
+                    if (!mbar_wait(&tmem_full[acc], (unsigned)(vt >> 1) & 1u)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < BN / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) racc[c * 32 + i] += __uint_as_float(v[i]);
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+                }
+                if (!ok) break;
+                const int row = m_blk * BM + q * 32 + lane;
+                const float rb = (args.row_bias && row < args.M) ? reinterpret_cast<const float *>(args.row_bias)[row] : 0.f;
+#pragma unroll
+                for (int g0 = 0; g0 < BN; g0 += GC) {
+#pragma unroll
+                    for (int j = 0; j < GC / 4; ++j) {
+                        const int chunk = j ^ (lane & (CPR - 1));
+                        *reinterpret_cast<float4 *>(slab + lane * (GC * 4) + chunk * 16) =
+                            make_float4(racc[g0 + 4 * j] + rb, racc[g0 + 4 * j + 1] + rb, racc[g0 + 4 * j + 2] + rb,
+                                        racc[g0 + 4 * j + 3] + rb);
+                    }
+                    __syncwarp();
+                    const int sub = lane / CPR, ch = lane % CPR;
+#pragma unroll 1
+                    for (int r0 = 0; r0 < 32; r0 += RPI) {
+                        const int r = r0 + sub;
+                        const uint4 val = *reinterpret_cast<const uint4 *>(slab + r * (GC * 4) + ((ch ^ (r & (CPR - 1))) * 16));
+                        const int grow = m_blk * BM + q * 32 + r;
+                        const int gcol = n_blk * BN + g0 + ch * 4;
+                        if (grow < args.M && gcol < args.N) {
+                            uint32_t *dst = reinterpret_cast<uint32_t *>(args.y[0]) + (size_t)g * args.y_batch_stride +
+                                            (size_t)grow * args.ldy + args.col_offset + gcol;
+                            if (gcol + 4 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                *reinterpret_cast<uint4 *>(dst) = val;
+                            } else {
+                                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                                for (int j = 0; j < 4 && gcol + j < args.N; ++j) dst[j] = w4[j];
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        } else
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
             const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
             const int m_blk = tin % num_m, n_blk = tin / num_m;
@@ -761,6 +829,21 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
     if (force_bn >= 64 && force_bn <= 256 && force_bn % 32 == 0) best = force_bn;
+    if constexpr (KIND == 3) {
+        // the tf32 kind is instantiated up to 128 columns (its epilogue holds a row of the tile in registers)
+        best = 128;
+        best_cost = -1;
+        for (int bn = 128; bn >= 64; bn -= 32) {
+            const long long tiles = m_tiles * ((args.N + bn - 1) / bn);
+            const long long cost = ((tiles + sms - 1) / sms) * (NA * BM + bn);
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+        }
+        switch (best) {
+            case 128: return launch_cfg<KIND, 128, NA>(a0, a1, b, lda, ldb, args, st, bg);
+            case 96: return launch_cfg<KIND, 96, NA>(a0, a1, b, lda, ldb, args, st, bg);
+            default: return launch_cfg<KIND, 64, NA>(a0, a1, b, lda, ldb, args, st, bg);
+        }
+    } else
     switch (best) {
         case 256: return launch_cfg<KIND, 256, NA>(a0, a1, b, lda, ldb, args, st, bg);
         case 224: return launch_cfg<KIND, 224, NA>(a0, a1, b, lda, ldb, args, st, bg);
@@ -830,6 +913,14 @@ int skinny_scratch(cudaStream_t st, size_t partial_bytes, size_t ncounters, Skin
         s.ncounters = ncounters;
     }
     *out = s;
+    return XN_OK;
+}
+
+// The same per-(device, stream) buffer for other internal users (the f32 matmul's packed operands).
+int library_scratch(cudaStream_t st, size_t bytes, void **out) {
+    SkinnyScratch s;
+    if (int rc = skinny_scratch(st, bytes, 0, &s)) return rc;
+    *out = s.partials;
     return XN_OK;
 }
 
@@ -976,6 +1067,15 @@ int launch_gemm_tn_tf32_shared_lhs(float *dst, const float *lhs, const float *rh
 // Split-k form for problems with too few output tiles to fill the GPU: the k axis is cut into `splits` equal
 // chunks of kchunk elements that ride the kernel's batch dimension (both tensor maps get a batch stride of
 // kchunk inside the rows), each writing its own [m, n] f32 partial; the caller sums them in a fixed order.
+// dst [m, n] f32 (row stride ldd) = lhs [m, k] * rhs [n, k]^T, both operands packed tf32 pieces (row stride = k).
+int launch_gemm_tn_tf32(float *dst, const float *lhs, const float *rhs, size_t m, size_t n, size_t k, size_t ldd,
+                        cudaStream_t st) {
+    GemmArgs a{};
+    a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = 1; a.y_batch_stride = 0;
+    a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    return launch_kind<3, 1>(lhs, nullptr, rhs, k, k, a, st);
+}
+
 int launch_gemm_tn_tf32_splitk(float *partials, const float *lhs, const float *rhs, size_t m, size_t n, size_t kchunk,
                                size_t splits, size_t lda, size_t ldb, cudaStream_t st) {
     GemmArgs a{};

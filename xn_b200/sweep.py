@@ -165,6 +165,19 @@ def sweep_f32(out, dev, pk):
            "frac_of_hbm": byts / t / 1e9 / pk["hbm_gbs"], "cublas_us": t_ref * 1e6}
     out.append(row)
     print(json.dumps(row), flush=True)
+    # many rows: three tf32 pieces per operand on the tensor-memory kernel, repack passes included
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for m, n, k in ((128, 11264, 4096), (1024, 4096, 4096), (4096, 4096, 4096), (4096, 11264, 4096)):
+        x = torch.randn(m, k, device=dev)
+        w = torch.randn(n, k, device=dev) * 0.02
+        y = torch.empty(m, n, device=dev)
+        t = time_graph([lambda: xn.matmul_(y, x, w, True)], 2)
+        t_ref = time_graph([lambda: torch.matmul(x, w.t(), out=y)], 2)
+        row = {"config": "f32_gemm", "m": m, "n": n, "k": k, "us": t * 1e6, "tflops": 2.0 * m * n * k / t / 1e12,
+               "cublas_us": t_ref * 1e6, "cublas_tflops": 2.0 * m * n * k / t_ref / 1e12}
+        out.append(row)
+        print(json.dumps(row), flush=True)
+    torch.backends.cuda.matmul.allow_tf32 = prev
 
 
 def sweep_conv(out, dev, pk):
@@ -272,6 +285,15 @@ def write_md(rows, path, what="all"):
             L += ["## f32 linear (x [%d,%d], W [%d,%d]; 3xTF32 tensor-core form unless XN_MM_F32_EXACT=1)" % (r["m"], r["k"], r["n"], r["k"]), "",
                   "%.1f µs, %.0f GB/s (%.2f of %s HBM); cuBLAS SGEMM without TF32 (the reference's default): %.1f µs."
                   % (r["us"], r["gbs"], r["frac_of_hbm"], pk["kind"], r["cublas_us"]), ""]
+    fg = [r for r in rows if r.get("config") == "f32_gemm"]
+    if fg:
+        L += ["## f32 matmul_t with many rows (three tf32 pieces per operand on kind::tf32, repack passes included;"
+              " accumulator promoted to f32 registers every 64 MMAs)", "",
+              "| M x N x K | µs | TFLOP/s | cuBLAS SGEMM (no TF32) µs | TFLOP/s |", "|---|---|---|---|---|"]
+        for r in fg:
+            L.append("| %dx%dx%d | %.1f | %.1f | %.1f | %.1f |" % (r["m"], r["n"], r["k"], r["us"], r["tflops"], r["cublas_us"],
+                                                                 r["cublas_tflops"]))
+        L.append("")
     cv = [r for r in rows if r.get("config") in ("conv1d", "conv_transpose1d")]
     if cv:
         L += ["## conv1d / conv_transpose1d (bias fused; tensor-memory GEMM over a channels-last view: bf16 on kind::f16, f32 as three tf32 pieces on kind::tf32)", "",
