@@ -190,6 +190,9 @@ int xn_mm_rms_norm(xn_dtype dtype, void *dst, const void *src, const void *alpha
 int xn_mm_softmax(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t cols, void *stream);
 int xn_mm_silu_mul(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t hidden, void *stream);
 int xn_mm_add(xn_dtype dtype, void *dst, const void *a, const void *b, size_t len, void *stream);
+/* dst[r][c] = src[r][c] + bias[c] (dst may alias src): the broadcast_add of Linear::forward's bias,
+ * xn-core/src/nn/linear.rs:61-64. */
+int xn_mm_add_bias(xn_dtype dtype, void *dst, const void *src, const void *bias, size_t rows, size_t cols, void *stream);
 int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_batch_stride, const int64_t *index,
                     size_t batch, size_t heads, size_t context, size_t head_dim, void *stream);
 

@@ -54,6 +54,7 @@ SIGNATURES = {
     "xn_mm_softmax": (_i, [_i, _p, _p, _sz, _sz, _p]),
     "xn_mm_silu_mul": (_i, [_i, _p, _p, _sz, _sz, _p]),
     "xn_mm_add": (_i, [_i, _p, _p, _p, _sz, _p]),
+    "xn_mm_add_bias": (_i, [_i, _p, _p, _p, _sz, _sz, _p]),
     "xn_mm_kv_append": (_i, [_i, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _p]),
     "xn_mm_rms_norm_split_e4m3": (_i, [_p, _p, _p, _p, _p, _p, _i, _sz, _sz, C.c_float, _p]),
     "xn_mm_silu_mul_split_e4m3": (_i, [_p, _p, _p, _p, _i, _sz, _sz, _p]),

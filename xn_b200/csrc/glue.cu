@@ -392,6 +392,29 @@ extern "C" int xn_mm_add(xn_dtype dtype, void *dst, const void *a, const void *b
     return XN_OK;
 }
 
+// dst[r][c] = src[r][c] + bias[c]: the broadcast_add that follows Linear::forward's matmul
+// (xn-core/src/nn/linear.rs:61-64); the sum is formed in f32 and rounded once to the element type, as the
+// reference's binary Add does for f16 / bf16.  dst may alias src.
+template <typename T>
+__global__ void __launch_bounds__(256) add_bias_kernel(T *dst, const T *src, const T *__restrict__ bias, size_t cols, size_t len) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < len; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = from_f32<T>(to_f32(src[i]) + to_f32(bias[i % cols]));
+}
+
+extern "C" int xn_mm_add_bias(xn_dtype dtype, void *dst, const void *src, const void *bias, size_t rows, size_t cols,
+                              void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "add_bias: unknown dtype %d", (int)dtype);
+    const size_t len = rows * cols;
+    if (len == 0) return XN_OK;
+    XN_REQUIRE(dst && src && bias, "add_bias: null pointer");
+    const size_t blocks = (len + 255) / 256;
+    const unsigned grid = (unsigned)(blocks < (size_t)sm_count() * 32 ? blocks : (size_t)sm_count() * 32);
+    XN_DISPATCH_DTYPE(dtype, T, add_bias_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((T *)dst, (const T *)src,
+                                                                                          (const T *)bias, cols, len));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
 extern "C" int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_batch_stride,
                                const int64_t *index, size_t batch, size_t heads, size_t context, size_t head_dim,
                                void *stream) {

@@ -105,7 +105,12 @@ class Linear:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = matmul_t(x, self.weight)
         if self.bias is not None:
-            y += self.bias  # the reference's separate broadcast_add (nn/linear.rs:61-64)
+            # the reference's separate broadcast_add (nn/linear.rs:61-64)
+            _require_cuda(self.bias)
+            if self.bias.dtype != y.dtype or list(self.bias.shape) != [y.shape[-1]]:
+                raise XnError(1, f"bias shape mismatch: expected [{y.shape[-1]}] of {y.dtype}, got {list(self.bias.shape)} of {self.bias.dtype}")
+            check(lib().xn_mm_add_bias(_dtype_code(y), y.data_ptr(), y.data_ptr(), self.bias.contiguous().data_ptr(),
+                                       y.numel() // y.shape[-1], y.shape[-1], _stream()))
         return y
 
     __call__ = forward
