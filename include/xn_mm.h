@@ -22,7 +22,7 @@
  * during stream capture: run each shape once before capturing it, as a decode loop does anyway; a stream
  * under capture borrows the buffer of the stream that ran those shapes, so keep the graph's replays ordered
  * with that stream's own calls).  Calls on different streams use different buffers and may overlap.
- * The same buffer holds the repacked operands of an f32 xn_mm_gemm with 128 or more rows (three tf32
+ * The same buffer holds the repacked operands of an f32 xn_mm_gemm with 17 or more rows (three tf32
  * pieces per element: 12 bytes per operand element, refused above 2 GiB in favour of the plain f32
  * kernel; XN_MM_F32_TC=0 in the environment keeps every f32 call on the plain kernel).
  * Nothing else allocates;

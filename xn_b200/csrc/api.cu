@@ -114,6 +114,23 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                                      (cudaStream_t)stream);
         }
     }
+    // f32 matmul_t with 17..64 rows on a weight worth streaming: the same 3xTF32 weight-streaming kernel, 16 rows
+    // per pass (one pass per 16 rows re-reads the weight, but never writes a repacked copy of it, which the
+    // tensor-memory form below would; beyond 64 rows that form wins).
+    {
+        static const bool exact = [] { const char *e = getenv("XN_MM_F32_EXACT"); return e && atoi(e) != 0; }();
+        static const size_t pass_max = [] { const char *e = getenv("XN_MM_F32_PASS_MAX_M"); return e ? (size_t)atoi(e) : (size_t)64; }();
+        if (dtype == XN_F32 && !exact && m > 16 && m <= pass_max && lhs_b == 1 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 &&
+            k % 32 == 0 && n >= 256 && lhs_rs % 4 == 0 && rhs_cs % 4 == 0 && dst_rs >= n && aligned(l, 16) && aligned(r, 16)) {
+            for (size_t i0 = 0; i0 < m; i0 += 16) {
+                const size_t rows = m - i0 < 16 ? m - i0 : 16;
+                if (int rc = launch_gemv_f32x3((float *)dst + i0 * dst_rs, (const float *)l + i0 * lhs_rs, (const float *)r, rows, n, k,
+                                               dst_rs, lhs_rs, rhs_cs, (cudaStream_t)stream))
+                    return rc;
+            }
+            return XN_OK;
+        }
+    }
     // Linear::forward's form with 16-bit elements -- both operands k-contiguous, rows of dst
     // contiguous -- goes to the tcgen05 kernel when TMA can address it (16-byte pitches and bases).
     // The strided-batched / grouped form (lhs_b > 1 with per-batch weights) is one launch as well.

@@ -167,7 +167,8 @@ def sweep_f32(out, dev, pk):
     print(json.dumps(row), flush=True)
     # many rows: three tf32 pieces per operand on the tensor-memory kernel, repack passes included
     torch.backends.cuda.matmul.allow_tf32 = False
-    for m, n, k in ((128, 11264, 4096), (1024, 4096, 4096), (4096, 4096, 4096), (4096, 11264, 4096)):
+    for m, n, k in ((32, 11264, 4096), (64, 11264, 4096), (125, 1024, 4096), (128, 11264, 4096), (1024, 4096, 4096),
+                    (4096, 4096, 4096), (4096, 11264, 4096)):
         x = torch.randn(m, k, device=dev)
         w = torch.randn(n, k, device=dev) * 0.02
         y = torch.empty(m, n, device=dev)
@@ -287,8 +288,9 @@ def write_md(rows, path, what="all"):
                   % (r["us"], r["gbs"], r["frac_of_hbm"], pk["kind"], r["cublas_us"]), ""]
     fg = [r for r in rows if r.get("config") == "f32_gemm"]
     if fg:
-        L += ["## f32 matmul_t with many rows (three tf32 pieces per operand on kind::tf32, repack passes included;"
-              " accumulator promoted to f32 registers every 64 MMAs)", "",
+        L += ["## f32 matmul_t beyond 16 rows (up to 64 rows: 3xTF32 weight-streaming kernel in passes of 16 rows; beyond: three tf32"
+              " pieces per operand on kind::tf32, repack passes included, accumulator promoted to f32 registers every 64 MMAs,"
+              " split-k for few tiles; 125x1024x4096 is the shape of the reference's CPU benchmark)", "",
               "| M x N x K | µs | TFLOP/s | cuBLAS SGEMM (no TF32) µs | TFLOP/s |", "|---|---|---|---|---|"]
         for r in fg:
             L.append("| %dx%dx%d | %.1f | %.1f | %.1f | %.1f |" % (r["m"], r["n"], r["k"], r["us"], r["tflops"], r["cublas_us"],
