@@ -325,24 +325,34 @@ __device__ __forceinline__ void pack_store(T *row, int cin, int c, T v) {
 
 // xt[b][lead + l][c] = x[b][c][l]; rows outside [lead, lead + length) are zero.  32 x 32 tiles through
 // shared memory so that both the reads (along l) and the writes (along c) are coalesced.
+constexpr int PI_C = 128;   // channels per block of the input repack
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_pack_input_kernel(T *__restrict__ xt, const T *__restrict__ x, int cin, int length, int lead, int rows) {
-    __shared__ T tile[32][33];
-    const int b = blockIdx.z, r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    // 32 positions x 128 channels per block: 16 independent loads per thread in flight, output rows written in
+    // runs of 128 channels
+    __shared__ T tile[PI_C][33];
+    const int b = blockIdx.z, r0 = blockIdx.x * 32, c0 = blockIdx.y * PI_C;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const T *xb = x + (size_t)b * cin * length;
     T *xtb = xt + (size_t)b * rows * cin * pack_mult<T>();
-    for (int i = ty; i < 32; i += 8) {
-        const int c = c0 + i, l = r0 + tx - lead;
+    const int l = r0 + tx - lead;
+    const bool lok = l >= 0 && l < length;
+#pragma unroll 8
+    for (int i = ty; i < PI_C; i += 8) {
+        const int c = c0 + i;
         T v = from_f32<T>(0.f);
-        if (c < cin && l >= 0 && l < length) v = xb[(size_t)c * length + l];
+        if (lok && c < cin) v = xb[(size_t)c * length + l];
         tile[i][tx] = v;
     }
     __syncthreads();
-    for (int i = ty; i < 32; i += 8) {
-        const int r = r0 + i, c = c0 + tx;
-        if (r < rows && c < cin) pack_store<T, false>(xtb + (size_t)r * cin * pack_mult<T>(), cin, c, tile[tx][i]);
+    const int c = threadIdx.x & (PI_C - 1);
+    if (c0 + c < cin) {
+#pragma unroll 4
+        for (int i = threadIdx.x / PI_C; i < 32; i += 256 / PI_C) {
+            const int r = r0 + i;
+            if (r < rows) pack_store<T, false>(xtb + (size_t)r * cin * pack_mult<T>(), cin, c0 + c, tile[c][i]);
+        }
     }
 }
 
@@ -418,9 +428,9 @@ conv_pack_taps_tiled_kernel(T *__restrict__ wp, const T *__restrict__ w, int cin
     }
 }
 
-// Phase interleave through shared memory: one block per (batch entry, out channel, 128 values of q); rows of d
-// are read contiguously, the output run of 128 * stride positions is written contiguously.
-constexpr int IL_QT = 128;
+// Phase interleave through shared memory: one block per (batch entry, out channel, 512 values of q); rows of d
+// are read contiguously, the output run of 512 * stride positions is written contiguously.
+constexpr int IL_QT = 512;
 template <typename T>
 __global__ void __launch_bounds__(256)
 conv_interleave_tiled_kernel(T *__restrict__ out, const T *__restrict__ d, const T *__restrict__ bias, int cout, int out_length,
@@ -513,6 +523,12 @@ ConvPlan conv_plan(int dtype, const ConvArgs &a) {
         p.d_bytes = round256((size_t)a.batch * a.stride * cout * p.nq * es);
     }
     p.xt_bytes = round256((size_t)a.batch * p.rows * cin * mult * es);
+    // the GEMM kernel indexes rows, columns and k with 32-bit integers
+    if ((size_t)p.taps * cin * mult > 0x7fffffff || (size_t)a.stride * cin * mult > 0x7fffffff ||
+        (size_t)a.stride * cout > 0x7fffffff || (size_t)p.rows * cin * mult > ((size_t)1 << 40)) {
+        p = ConvPlan{};
+        return p;
+    }
     p.splits = 1;
     if (dtype == XN_F32 && a.batch == 1) {
         const size_t m = TR ? (size_t)a.stride * cout : cout, n = TR ? (size_t)p.nq : (size_t)a.out_length;
@@ -533,7 +549,7 @@ int launch_conv_gemm(xn_dtype dt, T *dst, const T *src, const T *kernel, const T
     T *wp = reinterpret_cast<T *>(ws + p.xt_bytes);
     T *d = reinterpret_cast<T *>(ws + p.xt_bytes + p.wp_bytes);
     const int lead = TR ? p.taps - 1 : a.padding;
-    dim3 pg((unsigned)((p.rows + 31) / 32), (unsigned)((cin + 31) / 32), (unsigned)a.batch);
+    dim3 pg((unsigned)((p.rows + 31) / 32), (unsigned)((cin + PI_C - 1) / PI_C), (unsigned)a.batch);
     conv_pack_input_kernel<T><<<pg, 256, 0, st>>>(xt, src, cin, a.length, lead, p.rows);
     const size_t wtotal = TR ? (size_t)a.stride * cout * p.taps * cin : (size_t)cout * a.ksize * cin;
     const unsigned wgrid = (unsigned)((wtotal + 255) / 256 < 4096 ? (wtotal + 255) / 256 : 4096);
