@@ -18,6 +18,12 @@
 //               kind::f8f6f4, the two pieces accumulate into the same TMEM tile, the epilogue
 //               applies x_scale[m] * w_scale[n] and rounds to bf16.
 //   BF16 / F16: kind::f16, the epilogue rounds the f32 accumulator to the element type.
+//   TF32 pieces: kind::tf32 on f32 words already on the tf32 grid, f32 out.  Callers carry f32 precision by
+//               laying three such pieces per operand along k (gemm_f32_tc.cu, conv1d.cu).  The accumulator is
+//               handed to the epilogue every 16 k stages and summed in registers, because tcgen05
+//               accumulates with truncation (see KCH in the kernel); tiles are at most 128 columns wide.
+// Batches: a third tensor-map dimension (strided-batched and grouped calls, split-k chunks), optionally with
+// one A matrix shared by every batch entry (the convolutions' packed taps) and a per-row bias.
 //
 // Every mbarrier wait is bounded; a wait that gives up records it in g_gemm_wait_timeouts and the
 // CTA drains through its common exit (tensor memory is always released).
@@ -150,7 +156,7 @@ struct GemmArgs {
     long long y_batch_stride;  // elements between consecutive outputs (m * n in Backend::gemm)
     int a_batch_inner, b_batch_inner;  // the tensor map's dimension order is (k, batch, rows) instead of (k, rows, batch)
     int a_bcast;          // every batch entry multiplies the same A matrix (the A map then holds one matrix)
-    const void *row_bias; // optional, 16-bit kinds only: added to every element of output row i (element type of y)
+    const void *row_bias; // optional, not for fp8: added to every element of output row i (element type of y)
 };
 
 // KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16, 3 = tf32 operands (f32 words already on
@@ -342,16 +348,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             if (F8 && row < args.M) xs = __ldg(args.x_scale + row);
             float rb = 0.0f;
             if (!F8 && args.row_bias && row < args.M)
-                rb = KIND == 3 ? reinterpret_cast<const float *>(args.row_bias)[row]
-                     : KIND == 2 ? __half2float(reinterpret_cast<const __half *>(args.row_bias)[row])
-                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(args.row_bias)[row]);
+                rb = KIND == 2 ? __half2float(reinterpret_cast<const __half *>(args.row_bias)[row])
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(args.row_bias)[row]);
             // Column groups of GC: the warp's 32 x GC slab goes through shared memory (16-byte chunks
             // XOR-swizzled by row) so that global stores are whole row segments of GC*2 bytes instead of
             // 16 bytes per row -- this matters most when the destination is a peer GPU.
-            constexpr bool F32OUT = KIND == 3;
-            constexpr int OES = F32OUT ? 4 : 2;         // bytes per output element
+            constexpr int OES = 2;                      // bytes per output element (the tf32 kind has its own epilogue above)
             constexpr int EPC = 16 / OES;               // output elements per 16-byte chunk
-            constexpr int GC = (BN % 128 == 0 && !F32OUT) ? 128 : (BN % 64 == 0 ? 64 : 32);  // columns per group (divides BN)
+            constexpr int GC = BN % 128 == 0 ? 128 : (BN % 64 == 0 ? 64 : 32);  // columns per group (divides BN)
             constexpr int CPR = GC / EPC;               // 16-byte chunks per slab row (a row is at most 256 bytes)
             constexpr int RPI = 32 / CPR;               // rows written per store instruction
             unsigned char *slab = epi_smem + (size_t)(warp - 2) * 32 * 256;
@@ -362,16 +366,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + g0 + c * 32), v);
                     const int col0 = n_blk * BN + g0 + c * 32;
-                    if constexpr (F32OUT) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int chunk = (c * 8 + j) ^ (lane & (CPR - 1));
-                            *reinterpret_cast<uint4 *>(slab + lane * (GC * OES) + chunk * 16) =
-                                make_uint4(__float_as_uint(__uint_as_float(v[4 * j]) + rb), __float_as_uint(__uint_as_float(v[4 * j + 1]) + rb),
-                                           __float_as_uint(__uint_as_float(v[4 * j + 2]) + rb), __float_as_uint(__uint_as_float(v[4 * j + 3]) + rb));
-                        }
-                        continue;
-                    }
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -409,17 +403,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     const int gcol = n_blk * BN + g0 + ch * EPC;
                     if (grow < args.M && gcol < args.N) {
                         for (int p = 0; p < args.ndst; ++p) {
-                            if constexpr (F32OUT) {
-                                uint32_t *dst = reinterpret_cast<uint32_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
-                                                (size_t)grow * args.ldy + args.col_offset + gcol;
-                                if (gcol + 4 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                                    *reinterpret_cast<uint4 *>(dst) = val;
-                                } else {
-                                    const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
-                                    for (int j = 0; j < 4 && gcol + j < args.N; ++j) dst[j] = w4[j];
-                                }
-                                continue;
-                            }
                             uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
                                             (size_t)grow * args.ldy + args.col_offset + gcol;
                             if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
