@@ -142,9 +142,9 @@ def test_f32_decode_linear_split_tf32_path(xn, oracle, cuda, m, n, k):
 
 @pytest.mark.parametrize("m,n,k,form", [(130, 70, 300, "t"), (300, 1000, 4096, "t"), (257, 264, 1028, "kn"),
                                          (128, 64, 32, "t"), (512, 200, 2052, "views"), (125, 1024, 4096, "t"),
-                                         (17, 300, 1024, "kn"), (40, 512, 2048, "t"), (64, 1000, 4096, "t"), (33, 256, 96, "views")])
+                                         (17, 300, 1024, "kn"), (40, 512, 2048, "t"), (64, 1000, 4096, "t"), (33, 256, 96, "views"), (90, 520, 1024, "t")])
 def test_f32_many_rows_tf32_piece_path(xn, oracle, cuda, m, n, k, form):
-    """f32 beyond 16 rows: matmul_t form up to 64 rows runs the 3xTF32 weight-streaming kernel in passes of 16
+    """f32 beyond 16 rows: matmul_t form up to 96 rows runs the 3xTF32 weight-streaming kernel in passes of 16
     rows; everything else with 17+ rows runs on the tensor-memory kernel as three tf32 pieces per operand, whatever
     the operand strides (the repack normalises them), split along k when there are few output tiles; the
     accumulator is handed to f32 registers every 64 MMAs, so the result stays at f32-accumulation accuracy,

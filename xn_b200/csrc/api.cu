@@ -114,12 +114,12 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                                      (cudaStream_t)stream);
         }
     }
-    // f32 matmul_t with 17..64 rows on a weight worth streaming: the same 3xTF32 weight-streaming kernel, 16 rows
+    // f32 matmul_t with 17..96 rows on a weight worth streaming: the same 3xTF32 weight-streaming kernel, 16 rows
     // per pass (one pass per 16 rows re-reads the weight, but never writes a repacked copy of it, which the
-    // tensor-memory form below would; beyond 64 rows that form wins).
+    // tensor-memory form below would; at ~45 us per pass on a [11264, 4096] weight the two meet near 100 rows).
     {
         static const bool exact = [] { const char *e = getenv("XN_MM_F32_EXACT"); return e && atoi(e) != 0; }();
-        static const size_t pass_max = [] { const char *e = getenv("XN_MM_F32_PASS_MAX_M"); return e ? (size_t)atoi(e) : (size_t)64; }();
+        static const size_t pass_max = [] { const char *e = getenv("XN_MM_F32_PASS_MAX_M"); return e ? (size_t)atoi(e) : (size_t)96; }();
         if (dtype == XN_F32 && !exact && m > 16 && m <= pass_max && lhs_b == 1 && lhs_cs == 1 && rhs_rs == 1 && dst_cs == 1 &&
             k % 32 == 0 && n >= 256 && lhs_rs % 4 == 0 && rhs_cs % 4 == 0 && dst_rs >= n && aligned(l, 16) && aligned(r, 16)) {
             for (size_t i0 = 0; i0 < m; i0 += 16) {

@@ -440,17 +440,26 @@ conv_interleave_tiled_kernel(T *__restrict__ out, const T *__restrict__ d, const
     constexpr int PITCH = IL_QT + 4 / (int)sizeof(T);   // an odd number of 32-bit words: phases fall in distinct banks
     const int q0 = blockIdx.x * IL_QT, co = blockIdx.y, b = blockIdx.z;
     const T *db = d + ((size_t)b * stride * cout + co) * nq;
+    const size_t row_pitch = (size_t)cout * nq;
+#pragma unroll 4
     for (int i = threadIdx.x; i < stride * IL_QT; i += 256) {
         const int r = i / IL_QT, q = i - r * IL_QT;
-        if (q0 + q < nq) tile[r * PITCH + q] = db[(size_t)r * cout * nq + q0 + q];
+        if (q0 + q < nq) tile[r * PITCH + q] = db[r * row_pitch + q0 + q];
     }
     __syncthreads();
     const float bv = bias ? to_f32(bias[co]) : 0.f;
     T *ob = out + ((size_t)b * cout + co) * out_length;
+    // output position q0 * stride + i - padding holds (q, r) = (i / stride, i % stride); i advances by 256 per
+    // iteration, so (q, r) advance by (256 / stride, 256 % stride) with a carry: one division per thread
+    const int lo0 = q0 * stride - padding, dq = 256 / stride, dr = 256 - dq * stride;
+    int q = threadIdx.x / stride, r = threadIdx.x - q * stride;
+#pragma unroll 4
     for (int i = threadIdx.x; i < stride * IL_QT; i += 256) {
-        const int q = i / stride, r = i - q * stride;
-        const int lo = (q0 + q) * stride + r - padding;
+        const int lo = lo0 + i;
         if (q0 + q < nq && lo >= 0 && lo < out_length) ob[lo] = from_f32<T>(to_f32(tile[r * PITCH + q]) + bv);
+        q += dq;
+        r += dr;
+        if (r >= stride) { r -= stride; ++q; }
     }
 }
 

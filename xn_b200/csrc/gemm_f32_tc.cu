@@ -9,7 +9,7 @@
 // three products are one ordinary dot product of length 3k, and the unmodified tf32 GEMM kernel computes
 // the f32 result.  The repack is one pass over each operand (any element strides: it also normalises the
 // layout to k-contiguous rows); it costs 4x the operand bytes in traffic and pays for itself once the GEMM
-// is compute-bound, which is why calls with up to 64 rows in matmul_t form go to the weight-streaming 3xTF32 kernel first (passes
+// is compute-bound, which is why calls with up to 96 rows in matmul_t form go to the weight-streaming 3xTF32 kernel first (passes
 // of 16 rows, no repacked weight); other stride patterns come here from 17 rows on.  Few output tiles with a
 // long k are split along k (partials summed in a fixed order).
 // The packed copies live in the library's per-(device, stream) scratch.
