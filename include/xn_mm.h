@@ -261,7 +261,8 @@ int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const uint8_t *wq
  *          (length-1)*stride + kernel_size + output_padding - 2*padding, as the reference computes it
  * Accumulation is f32 with one rounding to dtype (f32 operands: products to about 1e-6 relative,
  * exact on small integers).
- * workspace: f16 / bf16 calls with groups == 1, dilation == 1 and in_channels a multiple of 8 run on the
+ * workspace: calls with groups == 1, dilation == 1 and in_channels a multiple of 8 (f16 / bf16) or 4 (f32,
+ * computed as three tf32 pieces per operand) run on the
  * tensor-memory GEMM kernel over a channels-last copy of the input and repacked taps, which live in
  * caller-owned device scratch of xn_mm_conv*_workspace_bytes(...) bytes (256-byte aligned, reusable by
  * every call on the same stream; XN_ERR_WORKSPACE when absent or too small).  Every other call needs no
