@@ -167,6 +167,20 @@ def test_f32_many_rows_tf32_piece_path(xn, oracle, cuda, m, n, k, form):
     assert err < 5e-5, err
 
 
+def test_f32_matmul_linearity_at_prefill_size(xn, cuda):
+    """2048 x 4096 x 4096 in f32 (a size the oracle would take minutes on): (a*x + y) W^T == a * x W^T + y W^T
+    to f32-accumulation accuracy, and a slice of rows agrees with float64."""
+    g = torch.Generator(device=cuda).manual_seed(11)
+    x = torch.randn(2048, 4096, generator=g, device=cuda)
+    y = torch.randn(2048, 4096, generator=g, device=cuda)
+    w = torch.randn(4096, 4096, generator=g, device=cuda) * 0.02
+    lhs = xn.matmul_t(2.5 * x + y, w)
+    rhs = 2.5 * xn.matmul_t(x, w) + xn.matmul_t(y, w)
+    assert float((lhs - rhs).abs().max()) < 1e-4 * float(rhs.abs().max())
+    ref = (2.5 * x[:64] + y[:64]).double() @ w.double().t()
+    assert float((lhs[:64].double() - ref).abs().max()) < 2e-5 * float(ref.abs().max())
+
+
 @pytest.mark.parametrize("dt,m,n,k", [(2, 64, 256, 512), (1, 33, 130, 200), (0, 130, 70, 300), (2, 1, 512, 1024),
                                       (2, 16, 384, 2048)])
 def test_seeded_linear_shapes(xn, oracle, cuda, dt, m, n, k):
