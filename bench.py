@@ -1,21 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the int4 block-quantized decode linear (the configuration the headline metric,
-weight HBM GB/s against the roofline, is quoted on).
+weight HBM GB/s against the roofline, is quoted on), with the other measurements the metric names riding
+on the same JSON line.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Workload ("int4_decode_gemv"): W [11264, 4096] int4 in 32-element blocks with f32 block scales;
-activations [M, 4096] quantized per row to int8, M in {1, 4, 16}; f32 output.  One step = one pass
-over `replicas` distinct copies of the weights for each M (3 * replicas launches), so that the
+activations [M, 4096] quantized per row to int8, M in {1, 4, 16}; f32 output.  One step = `sweeps` passes
+over `replicas` distinct copies of the weights for each M (3 * replicas * sweeps launches), so that the
 working set (replicas * 28.8 MB) is several times the L2 and every launch streams its weights from
 HBM.  Inputs are synthetic (seeded normal draws with the stated shapes and scales).
 
 value   = weight-side bytes streamed per second with everything resident in HBM (kernel time only)
-e2e     = the same bytes per second through the public API with host buffers: every launch copies
-          its activations from pinned host memory, quantizes them on the device, runs the linear
+e2e     = the same bytes per second through the host-buffer entry point (xn_mm_linear_q4_host): every call
+          copies its activations from pinned host memory, quantizes them on the device, runs the linear
           and copies the result back; the weights stay resident (they are model parameters)
 N > 1   = one process per GPU, each with its own decode streams and a replica of the weights
           (rows of the batch are independent: no collective on the data path), weak scaling.
+
+Further keys of the line (each measured in this run, CUDA events, L2 flushed between timed launches):
+  fp8_prefill_gemm         fp8-e4m3 transformer linears at M = 4096 (W8A8 and W8A16), TFLOP/s and roofline
+  f32_linear               x [16,4096] * W [11264,4096]^T in f32 on the GPU, and the host-core baseline
+  decode_step              the 32-layer decoder step, 32 streams per GPU
+  prefill_column_parallel  (N > 1) the same linears with the weight rows split over the ranks and the
+                           outputs assembled on every rank: peer-store epilogue and NCCL all-gather routes
 """
 from __future__ import annotations
 
@@ -102,8 +110,17 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def make_config(world: int) -> dict:
+    """The workload description both arms print (identical text, so the two lines compare like for like)."""
+    return {"workload": "int4_decode_gemv", "n": N_OUT, "k": K_IN, "m": list(MS),
+            "l2": "inputs larger than L2: the GPU arm rotates over distinct weight copies (692 MB per M), the host arm "
+                  "streams a 46 MB weight through a far smaller cache",
+            "parallelism": f"streams sharded over {world} gpu(s), no collective"}
+
+
 class CpuPort:
-    """The oracle's int4 linear on the host cores (OpenMP): one pass = M in {1,4,16} over one weight copy."""
+    """The CPU restatement of the int4 linear on the host cores (OpenMP over output channels; AVX-512 VNNI
+    when the host has it): one pass = M in {1,4,16} over one weight copy."""
 
     def __init__(self):
         import numpy as np
@@ -111,17 +128,20 @@ class CpuPort:
         import oracle as O
         O.build()
         self.O = O
+        self.threads = O.use_all_cores()  # torchrun exports OMP_NUM_THREADS=1 to every rank
+        self.kind = O.linear_q_fast_kind()
         rng = np.random.default_rng(1)
         w = (rng.standard_normal((N_OUT, K_IN)) * 0.02).astype(np.float32)
+        self.w = w
         self.q, self.s = O.quantize_q4(w)
         self.x = {m: O.quantize_rows_i8(rng.standard_normal((m, K_IN)).astype(np.float32)) for m in MS}
-        self.threads = O.num_threads()
+        self.xf = rng.standard_normal((16, K_IN)).astype(np.float32)
         self.run_pass()  # warm-up
 
     def run_pass(self) -> float:
         t0 = time.perf_counter()
         for m in MS:
-            self.O.linear_q(*self.x[m], self.q, self.s, want_partials=False)
+            self.O.linear_q_fast(*self.x[m], self.q, self.s)
         return time.perf_counter() - t0
 
     def throughput(self, budget_s: float):
@@ -132,6 +152,19 @@ class CpuPort:
             passes += 1
         dt = time.perf_counter() - t0
         return passes * len(MS) * weight_bytes() / dt / 1e9, passes, dt
+
+    def f32_linear(self, runs: int = 10) -> dict:
+        """The reference's own CPU-runnable configuration: y = x W^T in f32 (x [16,4096], W [11264,4096])."""
+        self.O.linear_f32_fast(self.xf, self.w)
+        ts = []
+        for _ in range(runs):
+            t0 = time.perf_counter()
+            self.O.linear_f32_fast(self.xf, self.w)
+            ts.append(time.perf_counter() - t0)
+        best, med = min(ts), statistics.median(ts)
+        by, fl = 185532416, 1476395008
+        return {"ms_best": best * 1e3, "ms_median": med * 1e3, "gb_per_s": by / med / 1e9, "gflop_per_s": fl / med / 1e9,
+                "cores": self.threads, "runs": runs, "kind": "port (f32 FMA, compiler-vectorised, OpenMP over n)"}
 
 
 def run_reference(args) -> None:
@@ -152,14 +185,188 @@ def run_reference(args) -> None:
         if time.perf_counter() - t_start > 240:
             break
     value = len(MS) * weight_bytes() / statistics.mean(per_step) / 1e9
-    sample = "one pass of M in {1,4,16} over one weight copy per step (3 linears); int8 x int4 integer port, OpenMP"
+    sample = (f"one pass of M in {{1,4,16}} over one weight copy per step (3 linears); int8 x int4 integer port, "
+              f"{port.kind}, OpenMP on {port.threads} threads")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": len(per_step), "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(per_step),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4->int32",
-            "data": "synthetic", "config": {"workload": "int4_decode_gemv", "n": N_OUT, "k": K_IN, "m": list(MS)},
+            "data": "synthetic", "config": make_config(args.gpus),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": port.threads, "kind": "port", "sample": sample},
+            "f32_linear_cpu": port.f32_linear(),
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+# DRAM bytes per launch of the dominant kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum), keyed by
+# instantiation; the capture and its command are summarised in profiles/linear_q4_kernel_int4_decode_gemv.md.
+NCU_DRAM_BYTES_PER_LAUNCH = {"M<=8": 28875776, "M=9..16": None}
+
+
+class L2Flush:
+    """Writes a buffer larger than the 126 MB L2 between timed launches."""
+
+    def __init__(self, dev):
+        import torch
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.zero_()
+
+
+def time_launches(fn, iters: int, flush, torch) -> float:
+    """Median device time in ms of one call of fn, each call bracketed by its own pair of CUDA events on the
+    current stream, L2 flushed (untimed) before every call."""
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def measured_peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return json.load(open(p))
+    except Exception:
+        return {}
+
+
+SHAPES = [(12288, 4096, "qkv"), (4096, 4096, "out_proj"), (22528, 4096, "ffn_up"), (4096, 11264, "ffn_down")]
+
+
+def measure_fp8_prefill(dev, flush, xn, torch) -> dict:
+    """fp8-e4m3 linears at M = 4096 on the tcgen05 kernel: W8A8 (one e4m3 activation piece) and W8A16 (two
+    pieces, i.e. twice the tensor work for the same useful flops).  TFLOP/s counts 2*M*N*K once."""
+    m = 4096
+    peaks = measured_peaks()
+    bf16_burst = float(peaks.get("bf16_tflops", 1590.0))
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(2)
+    for n, k, name in SHAPES:
+        w = torch.randn(n, k, generator=g, device=dev) * 0.02
+        wq, ws = xn.quantize_weights_fp8(w)
+        del w
+        x = torch.randn(m, k, generator=g, device=dev).bfloat16()
+        hi, lo, xs = xn.split_rows_e4m3(x)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        st = torch.cuda.current_stream().cuda_stream
+        for variant, lo_ptr in (("W8A8", None), ("W8A16", lo.data_ptr())):
+            def call():
+                xn._lib.check(xn.lib().xn_mm_linear_fp8_pieces(y.data_ptr(), hi.data_ptr(), lo_ptr, xs.data_ptr(),
+                                                               wq.data_ptr(), ws.data_ptr(), m, n, k, st))
+            ms = time_launches(call, 10, flush, torch)
+            tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+            nominal = 4500.0 if variant == "W8A8" else 2250.0
+            rows.append({"name": name, "m": m, "n": n, "k": k, "variant": variant, "us": ms * 1e3, "tflops": tf,
+                         "roofline": {"bound": "tensor", "achieved": tf, "peak": nominal, "unit": "TFLOP/s",
+                                      "frac": tf / nominal, "peak_kind": "nominal dense " + ("fp8" if variant == "W8A8" else "bf16")},
+                         "frac_of_measured_bf16_burst": tf / bf16_burst})
+        del wq, ws, x, hi, lo, y
+    out = {"rows": rows, "measured_bf16_burst_tflops": bf16_burst,
+           "note": "W8A16 runs two e4m3 MMAs per product (hi + lo activation pieces); its useful flops are judged against "
+                   "the bf16 peak, W8A8's against the fp8 peak"}
+    # one library fp8 GEMM of the same size for context (cuBLASLt through torch; not part of the product path)
+    try:
+        a = torch.randn(4096, 4096, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(12288, 4096, device=dev).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev)
+
+        def lib_call():
+            torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        ms = time_launches(lib_call, 10, flush, torch)
+        out["library_fp8_gemm_4096x12288x4096_tflops"] = 2.0 * 4096 * 12288 * 4096 / (ms * 1e-3) / 1e12
+    except Exception as e:  # noqa: BLE001
+        out["library_fp8_gemm_4096x12288x4096_tflops"] = None
+        out["library_fp8_note"] = f"torch._scaled_mm unavailable: {type(e).__name__}"
+    return out
+
+
+def measure_f32_linear(dev, flush, xn, torch) -> dict:
+    """The CPU-runnable configuration on the GPU: x [16,4096] N(0,1), W [11264,4096] N(0,0.02), f32."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(16, K_IN, generator=g, device=dev)
+    w = torch.randn(N_OUT, K_IN, generator=g, device=dev) * 0.02
+    lin = xn.Linear(w)
+    ms = time_launches(lambda: lin(x), 20, flush, torch)
+    by, fl = 185532416, 1476395008
+    peak, kind = measured_peak_gbs()
+    ref = (x.double() @ w.double().t())
+    y = lin(x)
+    rms = float(ref.pow(2).mean().sqrt())
+    err = float(((y.double() - ref).abs() / ref.abs().clamp_min(1e-2 * rms)).max())
+    return {"us": ms * 1e3, "gb_per_s": by / (ms * 1e-3) / 1e9, "tflops": fl / (ms * 1e-3) / 1e12,
+            "roofline": {"bound": "hbm", "achieved": by / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": by / (ms * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}"},
+            "max_rel_err_vs_f64_floor_1e-2_rms": err}
+
+
+def measure_prefill_column_parallel(dev, world, rank, xn, torch, dist) -> dict:
+    """The four fp8 linears at M = 4096 with the weight rows split over the ranks and the [M, N] result assembled
+    on every rank, two routes: the GEMM epilogue storing its tiles into every rank's buffer over NVLink, and a local
+    GEMM + NCCL all_gather_into_tensor + re-layout.  Both are compared bit for bit with the one-GPU result."""
+    from xn_b200.prefill import PeerPrefillLinear, column_parallel_gather
+    m = 4096
+    rows = []
+
+    def timeit(fn, iters=10):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for n, k, name in SHAPES:
+        g = torch.Generator(device=dev).manual_seed(4)  # same weights and inputs on every rank
+        w = torch.randn(n, k, generator=g, device=dev) * 0.02
+        wq, ws = xn.quantize_weights_fp8(w)
+        del w
+        x = torch.randn(m, k, generator=g, device=dev).bfloat16()
+        hi, lo, xs = xn.split_rows_e4m3(x)
+        full = xn.linear_fp8(x, wq, ws, 0)
+        lin = PeerPrefillLinear(wq, ws, n, k, m)
+        y = lin.forward(hi, lo, xs, m)
+        torch.cuda.synchronize()
+        same_peer = bool(torch.equal(y, full))
+        wl, wsl = wq[lin.a:lin.b].contiguous(), ws[lin.a:lin.b].contiguous()
+
+        def local_linear(xx, a, b):
+            out = torch.empty(m, b - a, dtype=torch.bfloat16, device=dev)
+            xn._lib.check(xn.lib().xn_mm_linear_fp8_pieces(out.data_ptr(), hi.data_ptr(), lo.data_ptr(), xs.data_ptr(),
+                                                           wl.data_ptr(), wsl.data_ptr(), m, b - a, k,
+                                                           torch.cuda.current_stream().cuda_stream))
+            return out
+        y2 = column_parallel_gather(x, local_linear, n)
+        same_gather = bool(torch.equal(y2, full))
+        t_peer = timeit(lambda: lin.forward(hi, lo, xs, m))
+        t_gather = timeit(lambda: column_parallel_gather(x, local_linear, n))
+        t_full = timeit(lambda: xn.linear_fp8(x, wq, ws, 0))
+        flags = torch.tensor([int(same_peer), int(same_gather)], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        out_bytes = 2 * m * (lin.b - lin.a) * (world - 1)
+        rows.append({"name": name, "m": m, "n": n, "k": k, "identical_peer": bool(flags[0].item()),
+                     "identical_gather": bool(flags[1].item()), "ms_peer_store_epilogue": t_peer,
+                     "ms_nccl_all_gather": t_gather, "ms_one_gpu": t_full, "speedup_vs_one_gpu": t_full / t_peer,
+                     "tflops_all_gpus": 2.0 * m * n * k / (t_peer * 1e-3) / 1e12,
+                     "nvlink_bytes_out_per_rank": out_bytes, "nvlink_gb_per_s_out_per_rank": out_bytes / (t_peer * 1e-3) / 1e9})
+        del lin, wq, ws, x, hi, lo, full, y, y2
+        torch.cuda.empty_cache()
+    return {"world": world, "rows": rows, "scaling": "strong (one 4096-token prefill split over the ranks)",
+            "timing": "CUDA events, max over ranks, 10 back-to-back calls; collective: peer stores / NCCL all-gather"}
 
 
 def measure_decode(args, dev, world, rank, timed):
@@ -206,7 +413,11 @@ def main() -> None:
     ap.add_argument("--impl", default="xn_b200", choices=["xn_b200", "reference"])
     ap.add_argument("--replicas", type=int, default=24)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--sweeps", type=int, default=16, help="passes over all replicas and M values per step")
+    ap.add_argument("--sweeps", type=int, default=112,
+                    help="passes over all replicas and M values per step (a multiple of 16 beyond 16); the default makes a "
+                         "step about 50 ms, i.e. a timed region above one second at 20 steps")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the f32 linear, fp8 prefill GEMM and column-parallel prefill measurements")
     ap.add_argument("--no-decode", action="store_true", help="skip the decoder-stack step measurement")
     ap.add_argument("--decode-steps", type=int, default=8)
     ap.add_argument("--decode-only", action="store_true", help="measure only the decoder-stack step (profiling aid)")
@@ -271,11 +482,13 @@ def main() -> None:
     outs = {m: torch.empty(m, N_OUT, device=dev) for m in MS}
     host_x = {m: torch.randn(m, K_IN).pin_memory() for m in MS}
     host_y = {m: torch.empty(m, N_OUT).pin_memory() for m in MS}
-    SWEEPS = args.sweeps
+    GS = min(args.sweeps, 16)                 # sweeps captured in one graph
+    REPLAYS = max(1, args.sweeps // GS)       # graph replays per step
+    SWEEPS = GS * REPLAYS
     launches_per_step = len(MS) * R * SWEEPS
 
-    def enqueue_sweep():
-        for m in MS:
+    def enqueue_sweep(ms_list=MS):
+        for m in ms_list:
             xq, xs = acts[m]
             for lin in lins:
                 xn.linear_q4(xq, xs, lin.wq, N_OUT, out=outs[m])
@@ -285,31 +498,30 @@ def main() -> None:
     # measurement.  The end-to-end leg below goes through plain API calls instead.
     enqueue_sweep()
     torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            for _ in range(SWEEPS):
-                enqueue_sweep()
-    torch.cuda.synchronize()
+
+    def capture(ms_list, sweeps):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(gr, stream=side):
+                for _ in range(sweeps):
+                    enqueue_sweep(ms_list)
+        torch.cuda.synchronize()
+        return gr
+
+    graph = capture(MS, GS)
 
     def step():
-        graph.replay()
+        for _ in range(REPLAYS):
+            graph.replay()
 
-    # End to end: a serving loop keeps its device buffers, so the host->device copy, the activation
-    # quantizer and the linear all write into preallocated tensors; every call still goes through the
-    # Python API and copies its input from and its result to pinned host memory.
-    dev_x = {m: torch.empty(m, K_IN, device=dev) for m in MS}
-    dev_q = {m: (torch.empty(m, K_IN, dtype=torch.int8, device=dev), torch.empty(m, device=dev)) for m in MS}
-
+    # End to end through the host-buffer entry point: one library call per linear copies the activations from
+    # pinned host memory, quantizes them, runs the linear and copies the result back to pinned host memory.
     def step_e2e():
         for m in MS:
             for lin in lins:
-                dev_x[m].copy_(host_x[m], non_blocking=True)
-                xq, xs = xn.quantize_rows_i8(dev_x[m], out=dev_q[m])
-                xn.linear_q4(xq, xs, lin.wq, N_OUT, out=outs[m])
-                host_y[m].copy_(outs[m], non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the step's result is on the host
+                lin.forward_host(host_x[m], host_y[m])
+        torch.cuda.current_stream().synchronize()  # the step's results are on the host
 
     for _ in range(warmup):
         step()
@@ -320,14 +532,41 @@ def main() -> None:
     ms = timed(step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
+    # the same launches one M at a time: the per-M launch time behind the averaged roofline figure
+    per_m = {}
+    for m in MS:
+        gm = capture((m,), 4)
+        for _ in range(3):
+            gm.replay()
+        ms_m = timed(gm.replay, 10)
+        per_m[m] = ms_m * 1e-3 / (10 * 4 * R)
+        del gm
+
     for _ in range(2):
         step_e2e()
     e2e_steps = max(3, min(args.steps, 20))
     ms_e2e = timed(step_e2e, e2e_steps)
+    del graph
+    lins_keep = lins[:1]
+    del lins
+    torch.cuda.empty_cache()
+
+    flush = L2Flush(dev)
+    f32_linear = measure_f32_linear(dev, flush, xn, torch) if not args.no_extras else None
+    fp8_prefill = measure_fp8_prefill(dev, flush, xn, torch) if not args.no_extras else None
+    del flush
+    torch.cuda.empty_cache()
+    prefill_cp = None
+    if world > 1 and not args.no_extras:
+        try:
+            prefill_cp = measure_prefill_column_parallel(dev, world, rank, xn, torch, dist)
+        except Exception as e:  # noqa: BLE001  (symmetric memory unavailable, ...): report, keep the line
+            prefill_cp = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
 
     decode = None
     if not args.no_decode:
-        del lins, graph
+        del lins_keep
         torch.cuda.empty_cache()
         decode = measure_decode(args, dev, world, rank, timed)
 
@@ -341,32 +580,43 @@ def main() -> None:
         launch_s = ms * 1e-3 / (args.steps * launches_per_step)
         alg = sum(algorithmic_bytes(m) for m in MS) / len(MS)
         achieved = alg / launch_s / 1e9
-        cpu_baseline = None
-        if world == 1:  # the CPU leg runs at N = 1 only (torchrun pins OMP to one thread per rank)
+        cpu_baseline, f32_cpu = None, None
+        if world == 1:  # the CPU legs run at N = 1 only
             port = CpuPort()
             cpu_gbs, passes, cpu_dt = port.throughput(args.cpu_seconds)
             cpu_baseline = {"value": cpu_gbs, "unit": UNIT, "cores": port.threads, "kind": "port",
-                            "sample": f"{passes} pass(es) of M in {{1,4,16}} over one weight copy, {cpu_dt:.1f} s"}
+                            "sample": f"{passes} pass(es) of M in {{1,4,16}} over one weight copy, {cpu_dt:.1f} s; {port.kind}"}
+            f32_cpu = port.f32_linear()
+        if f32_linear is not None:
+            f32_linear["cpu_baseline"] = f32_cpu
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8xint4->int32", "data": "synthetic",
-            "config": {"workload": "int4_decode_gemv", "n": N_OUT, "k": K_IN, "m": list(MS), "replicas": R, "sweeps_per_step": SWEEPS,
-                       "launch": "one CUDA graph replay per step",
-                       "l2": f"inputs larger than L2: {R} distinct weight copies = {R * wb / 1e6:.0f} MB per M",
-                       "parallelism": f"streams sharded over {world} gpu(s), no collective"},
+            "config": make_config(world),
+            "run": {"replicas": R, "sweeps_per_step": SWEEPS, "launch": f"{REPLAYS} replay(s) of one CUDA graph of {GS} sweeps per step",
+                    "weight_copies_mb_per_m": R * wb / 1e6},
             "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": R * sum(m * K_IN * 4 for m in MS),
                     "d2h_bytes_per_step": R * sum(m * N_OUT * 4 for m in MS), "steps": e2e_steps,
-                    "ms_per_step": ms_e2e / e2e_steps},
+                    "ms_per_step": ms_e2e / e2e_steps, "calls_per_step": len(MS) * R,
+                    "api": "LinearQ4.forward_host -> xn_mm_linear_q4_host (copy in, quantize rows, linear, copy out)"},
             "gpu_launches": args.steps * launches_per_step,
+            "fp8_prefill_gemm": fp8_prefill,
+            "f32_linear": f32_linear,
+            "prefill_column_parallel": prefill_cp,
             "decode_step": decode,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "traffic": 28875776,
-                         "traffic_source": "dram__bytes_read+write per launch, ncu capture in profiles/linear_q4_kernel_int4_decode_gemv.md",
+                         "peak_kind": f"of {peak_kind}",
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH["M<=8"],
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the M <= 8 "
+                                           "instantiation (two of the three launches of a sweep)",
                          "kernel": "linear_q4_kernel",
-                         "algorithmic_bytes_per_launch": alg, "us_per_launch": launch_s * 1e6},
+                         "algorithmic_bytes_per_launch": alg, "us_per_launch": launch_s * 1e6,
+                         "per_m": {str(m): {"us_per_launch": per_m[m] * 1e6, "algorithmic_bytes": algorithmic_bytes(m),
+                                            "achieved": algorithmic_bytes(m) / per_m[m] / 1e9,
+                                            "frac": algorithmic_bytes(m) / per_m[m] / 1e9 / peak} for m in MS}},
             "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)

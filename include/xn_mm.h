@@ -47,12 +47,39 @@ typedef enum {
     XN_ERR_INVALID = 1,     /* shape / stride / null / alignment problem: the Rust side's bail!() */
     XN_ERR_UNSUPPORTED = 2, /* dtype or size outside what the engine implements */
     XN_ERR_CUDA = 3,        /* a CUDA runtime call failed (Error::CudaDriver in the reference) */
-    XN_ERR_WORKSPACE = 4    /* caller-provided workspace too small */
+    XN_ERR_WORKSPACE = 4,   /* caller-provided workspace too small */
+    XN_ERR_DEVICE = 5       /* a device-side wait ran out in an earlier launch (see xn_mm_device_status) */
 } xn_status;
 
 const char *xn_mm_last_error(void);
 /* Library version, bumped when the ABI changes. */
 int xn_mm_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Device-side failures.  The reference turns every CUDA failure into an Err at the call that hit it
+ * (xn-core/src/error.rs:71-92).  The kernels here wait on hardware barriers (copy completions, MMA
+ * completions); each such wait is bounded to 2 s, after which the kernel gives up, leaves through its
+ * normal exit and increments a status word in pinned host memory (one per device, allocated at the first
+ * launch that needs it -- make that launch outside stream capture).  From then on every entry point that
+ * would launch such a kernel on that device returns XN_ERR_DEVICE instead, because outputs written since
+ * are undefined.
+ *   xn_mm_device_status        non-blocking read of the current device's word: XN_OK when zero, XN_ERR_DEVICE
+ *                              otherwise; *timeouts_out (optional) receives the count.  Call it at your own
+ *                              synchronisation points to learn about a failure in work already completed.
+ *   xn_mm_clear_device_status  synchronises the device, zeroes the word and the library's scratch counters.
+ *   xn_mm_selftest_wait_timeout  launches one warp that waits, with the given limit, on a barrier nobody
+ *                              arrives on: the wait runs out, the kernel exits normally and the status word
+ *                              moves.  For tests of the reporting path; nothing faults or hangs.
+ * Library-owned scratch (see the top of this file) is kept per (device, stream) for the life of the process;
+ * a replaced block is kept too, since a captured graph may still point at it.  xn_mm_release_scratch
+ * synchronises the current device and frees the blocks of `stream` (or of every stream when all_streams != 0)
+ * together with all replaced blocks of the device; graphs captured earlier that ran the skinny kernel or the
+ * f32 repack must not be replayed afterwards.
+ * ------------------------------------------------------------------------------------------ */
+int xn_mm_device_status(unsigned *timeouts_out);
+int xn_mm_clear_device_status(void);
+int xn_mm_selftest_wait_timeout(unsigned long long limit_ns, void *stream);
+int xn_mm_release_scratch(void *stream, int all_streams);
 
 /* ------------------------------------------------------------------------------------------
  * Backend::gemm -- replaces the body of CudaDevice's `gemm` (xn-core/src/cuda_backend.rs:787-865,
@@ -74,6 +101,17 @@ int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const
                size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b, size_t lhs_b_stride,
                size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs,
                size_t rhs_cs, size_t rhs_rs, void *stream);
+
+/* Linear::forward (xn-core/src/nn/linear.rs:56-66): y [m,n] = x [m,k] * weight [n,k]^T (+ bias [n]), rows
+ * ldx / ldw / ldy elements apart.  Same arithmetic and kernels as xn_mm_gemm with
+ * (lhs_cs,lhs_rs) = (1,ldx), (rhs_cs,rhs_rs) = (ldw,1); the difference is a promise: `weight` is a model
+ * parameter that no work in flight on `stream` writes, so the weight-streaming kernels may start fetching it
+ * while the previous kernel on the stream is still running (programmatic dependent launch).  xn_mm_gemm
+ * makes no such assumption about rhs -- it may be the previous call's dst -- and reads it only after the
+ * stream order allows.  The same promise holds for the weight operand (wq / wq_packed and scales) of every
+ * quantized linear below.  x, bias and y follow the stream order as usual. */
+int xn_mm_linear(xn_dtype dtype, void *y, const void *x, const void *weight, const void *bias_or_null, size_t m,
+                 size_t n, size_t k, size_t ldx, size_t ldw, size_t ldy, void *stream);
 
 /* Host-only: Tensor::matmul_'s lowering of two views to the gemm arguments
  * (xn-core/src/inplace_ops.rs:318-436, shape rules of xn-core/src/ops.rs:640-700).
@@ -124,6 +162,15 @@ int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype d
  * time with the weights streamed once per 16 rows. */
 int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
                     size_t n, size_t k, int32_t *partials, void *stream);
+
+/* The same linear for a caller whose activations and results live in host memory (pinned, for the copies to
+ * be asynchronous): one call enqueues x_host [m,k] f32 -> device, the per-row int8 quantizer, the linear and
+ * y [m,n] f32 -> y_host on `stream`.  `workspace` is caller-owned device memory of
+ * xn_mm_linear_q4_host_workspace_bytes(m,n,k) bytes (256-byte aligned, reusable by every call on the stream);
+ * y_host is valid once the stream has been synchronised.  No counterpart in the reference. */
+size_t xn_mm_linear_q4_host_workspace_bytes(size_t m, size_t n, size_t k);
+int xn_mm_linear_q4_host(float *y_host, const float *x_host, const void *wq_packed, size_t m, size_t n, size_t k,
+                         void *workspace, size_t workspace_bytes, void *stream);
 
 /* int8 block-quantized weights: the same scheme with scale = max|w|/127 and one byte per weight.
  * "q8 tiles": tile (r/16, kk/128) is 2304 bytes, ordered [r/16][kk/128]; bytes 0..2047 = for each
@@ -239,7 +286,11 @@ int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, size_t q_ba
  * m*k <= xn_mm_linear_fp8_noalloc_max_elems() (262144); larger calls return XN_ERR_UNSUPPORTED.
  * All calls on a device share that array: calls that overlap on the GPU race, so keep them in one
  * stream order.  The first call on a device resolves the array's device address and should be made
- * outside any stream capture.  It runs only kernels that need no scratch of their own (the
+ * outside any stream capture; `stream` must belong to the device that is current at the call (the array
+ * is looked up for the current device).  Every argument is checked before anything is enqueued, so a
+ * rejected call leaves the shared array untouched.  A device-side wait that runs out inside this call is
+ * still bounded, but it is reported to xn_mm_device_status only if some other entry point has already
+ * set up the device's status word (this one must not allocate it).  It runs only kernels that need no scratch of their own (the
  * weight-streaming kernel up to 32 rows, the tiled tensor-memory kernel beyond), so from 9 rows on its
  * results can differ from xn_mm_linear_fp8 in the last bf16 bit (another summation order). */
 size_t xn_mm_linear_fp8_noalloc_max_elems(void);

@@ -312,6 +312,11 @@ void xo_pack_q8(const int8_t *q, const float *scales, size_t n, size_t k, uint8_
 /* Quantized linear: P[i,j,blk] = sum over the block of xq*wq as int32,
  * y[i,j] = x_scale[i] * sum_blk (float)P * w_scale[j,blk]  (f32, blocks in order).
  * partials may be NULL. wq is the logical (one value per int8) form. */
+/* The 32-element block (the only block size the engine uses) gets its own loop with a constant trip count so
+ * that the compiler turns the int8 x int8 -> int32 dot product into SIMD widening multiplies; the function is
+ * cloned per instruction set and dispatched at load time, so one binary runs at full width on whatever host
+ * it lands on (this is also the timed CPU baseline of the int4 configuration). */
+__attribute__((target_clones("arch=skylake-avx512", "avx2", "default")))
 void xo_linear_q(const int8_t *xq, const float *x_scale, const int8_t *wq, const float *w_scale,
                  size_t m, size_t n, size_t k, size_t block, int32_t *partials, float *y) {
     size_t nblk = k / block;
@@ -323,13 +328,88 @@ void xo_linear_q(const int8_t *xq, const float *x_scale, const int8_t *wq, const
             for (size_t b = 0; b < nblk; ++b) {
                 int32_t p = 0;
                 const int8_t *xa = xq + i * k + b * block, *wa = wq + j * k + b * block;
-                for (size_t e = 0; e < block; ++e) p += (int32_t)xa[e] * (int32_t)wa[e];
+                if (block == 32) {
+                    for (int e = 0; e < 32; ++e) p += (int32_t)xa[e] * (int32_t)wa[e];
+                } else {
+                    for (size_t e = 0; e < block; ++e) p += (int32_t)xa[e] * (int32_t)wa[e];
+                }
                 if (partials) partials[(i * n + j) * nblk + b] = p;
                 acc += (float)p * w_scale[j * nblk + b];
             }
             y[i * n + j] = x_scale[i] * acc;
         }
     }
+}
+
+/* Timed CPU baseline of the int4 configuration: the same linear as xo_linear_q, y only, written for the host's
+ * widest integer dot product (AVX-512 VNNI: vpdpbusd, u8 x s8 -> s32 over 64 bytes).  The activations are
+ * offset to unsigned (x + 128) and the surplus 128 * sum(w) is taken out per output channel; every 64-byte step
+ * of a weight row is loaded once and multiplied with all activation rows; the int32 lanes are scaled and
+ * accumulated as floats without a per-block horizontal sum.  The integer arithmetic is exact, the float sum
+ * runs in another order than the definition (xo_linear_q), against which tests check it to 1e-5.  Hosts without
+ * VNNI run xo_linear_q. */
+#if defined(__x86_64__)
+#include <immintrin.h>
+#define XO_VNNI __attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni")))
+/* one weight row against MI activation rows (MI a compile-time constant so the accumulators stay in registers) */
+XO_VNNI static inline __attribute__((always_inline)) void q32_row_vnni(const uint8_t *xu, const float *x_scale,
+                                                                       const int8_t *wr, const float *sr, size_t k,
+                                                                       size_t n, size_t j, float *y, const int MI) {
+    const __m512i lane_blk = _mm512_set_epi32(1, 1, 1, 1, 1, 1, 1, 1, 0, 0, 0, 0, 0, 0, 0, 0);
+    const __m512i off = _mm512_set1_epi8((char)0x80);
+    __m512 acc[16];
+    for (int i = 0; i < MI; ++i) acc[i] = _mm512_setzero_ps();
+    for (size_t c = 0; c < k / 64; ++c) {
+        const __m512i wv = _mm512_loadu_si512((const void *)(wr + c * 64));
+        /* the activations are offset by +128 to fit the unsigned operand: take 128 * w back out per lane */
+        const __m512i corr = _mm512_dpbusd_epi32(_mm512_setzero_si512(), off, wv);
+        const __m512 pair = _mm512_castpd_ps(_mm512_set1_pd(*(const double *)(const void *)(sr + 2 * c)));
+        const __m512 sc = _mm512_permutexvar_ps(lane_blk, pair);
+        for (int i = 0; i < MI; ++i) {
+            const __m512i xv = _mm512_loadu_si512((const void *)(xu + (size_t)i * k + c * 64));
+            const __m512i dp = _mm512_sub_epi32(_mm512_dpbusd_epi32(_mm512_setzero_si512(), xv, wv), corr);
+            acc[i] = _mm512_fmadd_ps(_mm512_cvtepi32_ps(dp), sc, acc[i]);
+        }
+    }
+    for (int i = 0; i < MI; ++i) y[(size_t)i * n + j] = x_scale[i] * _mm512_reduce_add_ps(acc[i]);
+}
+
+XO_VNNI static void linear_q32_vnni(const int8_t *xq, const float *x_scale, const int8_t *wq, const float *w_scale,
+                                    size_t m, size_t n, size_t k, float *y) {
+    const size_t nblk = k / 32;
+    uint8_t *xu = (uint8_t *)malloc(m * k);
+    for (size_t i = 0; i < m * k; ++i) xu[i] = (uint8_t)((int)xq[i] + 128);
+#pragma omp parallel for schedule(static)
+    for (long long jj = 0; jj < (long long)n; ++jj) {
+        const size_t j = (size_t)jj;
+        const int8_t *wr = wq + j * k;
+        const float *sr = w_scale + j * nblk;
+        size_t i0 = 0;
+        for (; i0 + 16 <= m; i0 += 16) q32_row_vnni(xu + i0 * k, x_scale + i0, wr, sr, k, n, j, y + i0 * n, 16);
+        for (; i0 + 4 <= m; i0 += 4) q32_row_vnni(xu + i0 * k, x_scale + i0, wr, sr, k, n, j, y + i0 * n, 4);
+        for (; i0 < m; ++i0) q32_row_vnni(xu + i0 * k, x_scale + i0, wr, sr, k, n, j, y + i0 * n, 1);
+    }
+    free(xu);
+}
+#endif
+
+void xo_linear_q_fast(const int8_t *xq, const float *x_scale, const int8_t *wq, const float *w_scale,
+                      size_t m, size_t n, size_t k, size_t block, float *y) {
+#if defined(__x86_64__)
+    if (block == 32 && k % 64 == 0 && __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw")) {
+        linear_q32_vnni(xq, x_scale, wq, w_scale, m, n, k, y);
+        return;
+    }
+#endif
+    xo_linear_q(xq, x_scale, wq, w_scale, m, n, k, block, NULL, y);
+}
+
+int xo_linear_q_fast_is_vnni(void) {
+#if defined(__x86_64__)
+    return __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw");
+#else
+    return 0;
+#endif
 }
 
 /* ------------------------------------------------------------------------- */
@@ -469,8 +549,10 @@ void xo_softmax(int dtype, void *dst, const void *src, size_t rows, size_t cols)
         for (size_t c = 0; c < cols; ++c) mx = fmaxf(mx, load_elem(dtype, src, r * cols + c));
         float sum = 0.0f;
         for (size_t c = 0; c < cols; ++c) {
-            /* the reference stores exp(x - max) in the element type before summing */
-            store_elem(dtype, dst, r * cols + c, expf(load_elem(dtype, src, r * cols + c) - mx));
+            /* `*d = (*s - max).exp()` on the element type (xn-core/src/cpu_backend.rs:756): the difference
+             * is rounded to the element type, then the exponential is, before the f32 sum */
+            store_elem(dtype, dst, r * cols + c, load_elem(dtype, src, r * cols + c) - mx);
+            store_elem(dtype, dst, r * cols + c, expf(load_elem(dtype, dst, r * cols + c)));
             sum += load_elem(dtype, dst, r * cols + c);
         }
         for (size_t c = 0; c < cols; ++c)
@@ -498,12 +580,69 @@ void xo_silu_mul(int dtype, void *dst, const void *src, size_t rows, size_t hidd
 /* compiler can vectorise it, threaded over n with OpenMP -- the stand-in for */
 /* crate gemm + rayon (xn-core/src/cpu_backend.rs:88, 1519-1526).             */
 /* ------------------------------------------------------------------------- */
-__attribute__((target_clones("avx512f", "avx2,fma", "default")))
-void xo_linear_f32_fast(const float *x, const float *w, float *y, size_t m, size_t n, size_t k) {
+#if defined(__x86_64__)
+/* AVX-512 form: one 16-float piece of a weight row is loaded once and multiplied into MI register accumulators. */
+__attribute__((target("avx512f"))) static inline __attribute__((always_inline)) void f32_row_avx512(
+    const float *x, const float *wr, float *y, size_t n, size_t k, size_t j, const int MI) {
+    __m512 acc[16];
+    for (int i = 0; i < MI; ++i) acc[i] = _mm512_setzero_ps();
+    size_t p = 0;
+    for (; p + 16 <= k; p += 16) {
+        const __m512 wv = _mm512_loadu_ps(wr + p);
+        for (int i = 0; i < MI; ++i) acc[i] = _mm512_fmadd_ps(_mm512_loadu_ps(x + (size_t)i * k + p), wv, acc[i]);
+    }
+    for (int i = 0; i < MI; ++i) {
+        float s = _mm512_reduce_add_ps(acc[i]);
+        for (size_t q = p; q < k; ++q) s += x[(size_t)i * k + q] * wr[q];
+        y[(size_t)i * n + j] = s;
+    }
+}
+__attribute__((target("avx512f"))) static void linear_f32_avx512(const float *x, const float *w, float *y, size_t m,
+                                                                 size_t n, size_t k) {
 #pragma omp parallel for schedule(static)
     for (long long jj = 0; jj < (long long)n; ++jj) {
         const float *wr = w + (size_t)jj * k;
-        for (size_t i = 0; i < m; ++i) {
+        size_t i0 = 0;
+        for (; i0 + 16 <= m; i0 += 16) f32_row_avx512(x + i0 * k, wr, y + i0 * n, n, k, (size_t)jj, 16);
+        for (; i0 + 4 <= m; i0 += 4) f32_row_avx512(x + i0 * k, wr, y + i0 * n, n, k, (size_t)jj, 4);
+        for (; i0 < m; ++i0) f32_row_avx512(x + i0 * k, wr, y + i0 * n, n, k, (size_t)jj, 1);
+    }
+}
+#endif
+
+static void linear_f32_portable(const float *x, const float *w, float *y, size_t m, size_t n, size_t k);
+void xo_linear_f32_fast(const float *x, const float *w, float *y, size_t m, size_t n, size_t k) {
+#if defined(__x86_64__)
+    if (__builtin_cpu_supports("avx512f")) {
+        linear_f32_avx512(x, w, y, m, n, k);
+        return;
+    }
+#endif
+    linear_f32_portable(x, w, y, m, n, k);
+}
+
+__attribute__((target_clones("avx2,fma", "default")))
+static void linear_f32_portable(const float *x, const float *w, float *y, size_t m, size_t n, size_t k) {
+#pragma omp parallel for schedule(static)
+    for (long long jj = 0; jj < (long long)n; ++jj) {
+        const float *wr = w + (size_t)jj * k;
+        size_t i0 = 0;
+        /* eight activation rows per pass over the weight row: each 16-float piece of the row is loaded once
+         * and multiplied into eight vector accumulators */
+        for (; i0 + 8 <= m; i0 += 8) {
+            float acc[8][16] = {{0}};
+            size_t p = 0;
+            for (; p + 16 <= k; p += 16)
+                for (int i = 0; i < 8; ++i)
+                    for (int l = 0; l < 16; ++l) acc[i][l] += x[(i0 + i) * k + p + l] * wr[p + l];
+            for (int i = 0; i < 8; ++i) {
+                float s = 0.0f;
+                for (int l = 0; l < 16; ++l) s += acc[i][l];
+                for (size_t q = p; q < k; ++q) s += x[(i0 + i) * k + q] * wr[q];
+                y[(i0 + i) * n + (size_t)jj] = s;
+            }
+        }
+        for (size_t i = i0; i < m; ++i) {
             const float *xr = x + i * k;
             float acc[16] = {0};
             size_t p = 0;
@@ -515,6 +654,17 @@ void xo_linear_f32_fast(const float *x, const float *w, float *y, size_t m, size
             y[i * n + (size_t)jj] = s;
         }
     }
+}
+
+/* The launcher of multi-process runs pins OpenMP to one thread per process; the timed CPU legs set the
+ * count back to the cores this process may run on. */
+void xo_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }
 
 int xo_num_threads(void) {

@@ -88,21 +88,32 @@ def _im2col1d(src, b, c, length, l_out, ks, stride, padding, dilation=1):
     return col.reshape(-1)
 
 
+def _expect(case, out):
+    """Exact unless the case carries a tolerance (the reference's f16 cases assert |r - e| < 0.1)."""
+    exp = np.array(case["expected"], np.float32)
+    if case.get("tol"):
+        assert np.all(np.abs(out.reshape(-1) - exp) < case["tol"]), (case["name"], out)
+    else:
+        assert np.array_equal(out.reshape(-1), exp), (case["name"], out)
+
+
 def run_conv1d_case(be, case):
     b, c_in, length = case["input_dims"]
     c_out, _, ks = case["kernel_dims"]
     stride, padding = case["stride"], case["padding"]
     l_out = (length + 2 * padding - (ks - 1) - 1) // stride + 1
     k = c_in * ks
+    dt = DT[case.get("dtype", "f32")]
     col = _im2col1d(np.array(case["input"], np.float32), b, c_in, length, l_out, ks, stride, padding)
     kernel = np.array(case["kernel"], np.float32)
     # xn-core/src/cpu_backend.rs:1001-1014
-    res = be.gemm(O.F32, b * l_out * c_out, col, 0, kernel, 0, l_out, c_out, k, b, l_out * k, 0, 1, c_out, 1, k, k, 1)
-    out = res.reshape(b, l_out, c_out).transpose(0, 2, 1).copy()
+    res = be.gemm(dt, b * l_out * c_out, O.from_f32(dt, col), 0, O.from_f32(dt, kernel), 0, l_out, c_out, k, b, l_out * k, 0, 1,
+                  c_out, 1, k, k, 1)
+    out = O.to_f32(dt, res).reshape(b, l_out, c_out).transpose(0, 2, 1).copy()
     if case["bias"] is not None:
         out += np.array(case["bias"], np.float32).reshape(1, c_out, 1)
     assert list(out.shape) == case["expected_dims"]
-    assert np.array_equal(out.reshape(-1), np.array(case["expected"], np.float32)), (case["name"], out)
+    _expect(case, out)
 
 
 def run_conv_transpose1d_case(be, case):
@@ -110,12 +121,14 @@ def run_conv_transpose1d_case(be, case):
     _, c_out, ks = case["kernel_dims"]
     stride = case["stride"]
     l_out = (length - 1) * stride + ks
+    dt = DT[case.get("dtype", "f32")]
     src_t = np.array(case["input"], np.float32).reshape(b, c_in, length).transpose(0, 2, 1).copy().reshape(-1)
     kernel = np.array(case["kernel"], np.float32)
     n = c_out * ks
     # xn-core/src/cpu_backend.rs:1097-1110
-    col = be.gemm(O.F32, b * length * n, src_t, 0, kernel, 0, length, n, c_in, b, length * c_in, 0, 1, n, 1, c_in, 1, n)
-    col = col.reshape(b, length, c_out, ks)
+    col = be.gemm(dt, b * length * n, O.from_f32(dt, src_t), 0, O.from_f32(dt, kernel), 0, length, n, c_in, b, length * c_in, 0,
+                  1, n, 1, c_in, 1, n)
+    col = O.to_f32(dt, col).reshape(b, length, c_out, ks)
     out = np.zeros((b, c_out, l_out), np.float32)
     for li in range(length):
         for kk in range(ks):
@@ -123,7 +136,7 @@ def run_conv_transpose1d_case(be, case):
     if case["bias"] is not None:
         out += np.array(case["bias"], np.float32).reshape(1, c_out, 1)
     assert list(out.shape) == case["expected_dims"]
-    assert np.array_equal(out.reshape(-1), np.array(case["expected"], np.float32)), (case["name"], out)
+    _expect(case, out)
 
 
 def conv1d_f64(x, w, stride, padding, dilation, groups):

@@ -51,7 +51,7 @@ class AbiBackend:
 
 
 def test_reference_kats_through_the_c_abi(xn, cuda):
-    assert kats.run_all(AbiBackend(xn, cuda)) == 12
+    assert kats.run_all(AbiBackend(xn, cuda)) == 19
 
 
 @pytest.mark.parametrize("dt", [0, 1, 2])

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libxn_mm.so")
 
 F32, F16, BF16 = 0, 1, 2
-OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE = 0, 1, 2, 3, 4
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE = 0, 1, 2, 3, 4, 5
 
 
 class XnError(RuntimeError):
@@ -28,6 +28,11 @@ SIGNATURES = {
     "xn_mm_last_error": (C.c_char_p, []),
     "xn_mm_abi_version": (_i, []),
     "xn_mm_gemm": (_i, [_i, _p, _p, _sz, _p, _sz] + [_sz] * 12 + [_p]),
+    "xn_mm_linear": (_i, [_i, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _p]),
+    "xn_mm_device_status": (_i, [_p]),
+    "xn_mm_clear_device_status": (_i, []),
+    "xn_mm_selftest_wait_timeout": (_i, [C.c_ulonglong, _p]),
+    "xn_mm_release_scratch": (_i, [_p, _i]),
     "xn_mm_matmul_plan": (_i, [_sz, _p, _p, _sz, _p, _p, _i, _sz, _p]),
     "xn_mm_q4_packed_bytes": (_sz, [_sz, _sz]),
     "xn_mm_quantize_weights_q4": (_i, [_p, _p, _i, _sz, _sz, _p]),
@@ -35,6 +40,8 @@ SIGNATURES = {
     "xn_mm_unpack_q4_host": (_i, [_p, _p, _p, _sz, _sz]),
     "xn_mm_quantize_rows_i8": (_i, [_p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_linear_q4": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _p, _p]),
+    "xn_mm_linear_q4_host_workspace_bytes": (_sz, [_sz, _sz, _sz]),
+    "xn_mm_linear_q4_host": (_i, [_p, _p, _p, _sz, _sz, _sz, _p, _sz, _p]),
     "xn_mm_q8_packed_bytes": (_sz, [_sz, _sz]),
     "xn_mm_quantize_weights_q8": (_i, [_p, _p, _i, _sz, _sz, _p]),
     "xn_mm_pack_q8_host": (_i, [_p, _p, _p, _sz, _sz]),

@@ -48,6 +48,11 @@ bool pdl_enabled() {
     return on;
 }
 
+static thread_local bool tl_rhs_static = false;
+bool rhs_is_static() { return tl_rhs_static; }
+StaticRhsScope::StaticRhsScope(bool on) : prev(tl_rhs_static) { tl_rhs_static = on; }
+StaticRhsScope::~StaticRhsScope() { tl_rhs_static = prev; }
+
 int ensure_dynamic_smem(const void *kernel, int *slot, size_t bytes) {
     int dev = 0;
     XN_CHECK_CUDA(cudaGetDevice(&dev));
@@ -68,10 +73,10 @@ using namespace xn;
 extern "C" const char *xn_mm_last_error(void) { return last_error().c_str(); }
 extern "C" int xn_mm_abi_version(void) { return 1; }
 
-extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const void *rhs,
-                          size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b,
-                          size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_cs, size_t dst_rs,
-                          size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream) {
+static int gemm_dispatch(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const void *rhs,
+                         size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b,
+                         size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_cs, size_t dst_rs,
+                         size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream) {
     // Same refusal as the reference for element types it has no GEMM for
     // (xn-core/src/cuda_backend.rs:862).
     if (!valid_dtype(dtype)) return fail(XN_ERR_UNSUPPORTED, "GEMM not supported for dtype %d", (int)dtype);
@@ -146,6 +151,39 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                                   m, n, k, dst_rs, lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
     return launch_gemm_generic(dtype, dst, l, r, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
                                lhs_cs, lhs_rs, rhs_cs, rhs_rs, (cudaStream_t)stream);
+}
+
+extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const void *rhs,
+                          size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b,
+                          size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_cs, size_t dst_rs,
+                          size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream) {
+    // Backend::gemm's rhs is any tensor, possibly the output of the kernel just enqueued on this stream: no
+    // kernel may read it ahead of its dependency wait.
+    StaticRhsScope scope(false);
+    return gemm_dispatch(dtype, dst, lhs, lhs_off, rhs, rhs_off, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
+                         lhs_cs, lhs_rs, rhs_cs, rhs_rs, stream);
+}
+
+extern "C" int xn_mm_linear(xn_dtype dtype, void *y, const void *x, const void *weight, const void *bias_or_null, size_t m,
+                            size_t n, size_t k, size_t ldx, size_t ldw, size_t ldy, void *stream) {
+    if (!valid_dtype(dtype)) return fail(XN_ERR_UNSUPPORTED, "linear: GEMM not supported for dtype %d", (int)dtype);
+    if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(y && x && weight, "linear: null pointer (y=%p x=%p weight=%p)", y, x, weight);
+    XN_REQUIRE(ldx >= k && ldw >= k && ldy >= n, "linear: row pitch smaller than the row (ldx=%zu ldw=%zu k=%zu ldy=%zu n=%zu)",
+               ldx, ldw, k, ldy, n);
+    int rc;
+    {
+        StaticRhsScope scope(true);  // the weight is a parameter: weight-streaming kernels may prefetch it
+        rc = gemm_dispatch(dtype, y, x, 0, weight, 0, m, n, k, 1, m * ldx, 1, 1, ldy, 1, ldx, ldw, 1, stream);
+    }
+    if (rc || !bias_or_null) return rc;
+    if (ldy == n) return xn_mm_add_bias(dtype, y, y, bias_or_null, m, n, stream);
+    const size_t es = dtype_size(dtype);
+    for (size_t i = 0; i < m; ++i) {  // pitched rows: one row at a time (rare; a view of a wider output)
+        char *row = static_cast<char *>(y) + i * ldy * es;
+        if (int r2 = xn_mm_add_bias(dtype, row, row, bias_or_null, 1, n, stream)) return r2;
+    }
+    return XN_OK;
 }
 
 extern "C" int xn_mm_matmul_plan(size_t lhs_rank, const size_t *lhs_dims, const size_t *lhs_strides,

@@ -39,6 +39,17 @@ int sm_count();
 // Programmatic dependent launch for the weight-streaming kernels (on unless XN_MM_PDL=0): a kernel
 // may begin, and prefetch weights, while its predecessor in the stream is still draining.
 bool pdl_enabled();
+// Whether the right-hand operand of the matmul being dispatched on this thread is a static weight (a model
+// parameter that no work in flight on the stream writes).  Only then may a weight-streaming kernel fetch it
+// before its programmatic-dependent-launch wait, i.e. while the previous kernel in the stream is still
+// running.  Backend::gemm's rhs can be any tensor -- the previous kernel's output included -- so xn_mm_gemm
+// leaves this false; the Linear entry points, whose weight operand is static by contract, set it.
+bool rhs_is_static();
+struct StaticRhsScope {
+    explicit StaticRhsScope(bool on);
+    ~StaticRhsScope();
+    bool prev;
+};
 
 // Raises a kernel's dynamic shared-memory limit once per (kernel, device); later calls with a
 // size already covered cost one atomic load.  `slot` is a per-kernel table of 64 ints.
@@ -116,7 +127,20 @@ int launch_gemm_tn_tf32_splitk(float *partials, const float *lhs, const float *r
                                size_t splits, size_t lda, size_t ldb, cudaStream_t st);
 int launch_gemm_tn_tf32(float *dst, const float *lhs, const float *rhs, size_t m, size_t n, size_t k, size_t ldd,
                         cudaStream_t st);
+// runtime.cu: library-owned scratch per (device, stream) and the device status word
+struct SkinnyScratch { float *partials = nullptr; size_t partial_bytes = 0; unsigned *counters = nullptr; size_t ncounters = 0; };
+int skinny_scratch(cudaStream_t st, size_t partial_bytes, size_t ncounters, SkinnyScratch *out);
 int library_scratch(cudaStream_t st, size_t bytes, void **out);
+struct WaitCtx;
+// Fills the bound and the status-word pointer every kernel with device-side waits takes; fails with
+// XN_ERR_DEVICE when an earlier launch on the current device has reported a wait that ran out.
+int wait_ctx(WaitCtx *out);
+// While alive on this thread, wait_ctx() does not allocate the status word if the device has none yet.
+struct NoAllocScope {
+    NoAllocScope();
+    ~NoAllocScope();
+    bool prev;
+};
 // f32 matmul with many rows on the kind::tf32 tensor-memory kernel (three tf32 pieces per operand); any strides
 bool gemm_f32_tc_fits(size_t m, size_t n, size_t k);
 int launch_gemm_f32_tc(float *dst, const float *lhs, const float *rhs, size_t m, size_t n, size_t k, size_t dst_rs,

@@ -31,9 +31,11 @@ gemm_generic_kernel(T *__restrict__ dst, const T *__restrict__ lhs, const T *__r
     for (size_t b = blockIdx.y; b < lhs_b; b += gridDim.y) {
         const T *A = lhs + b * lhs_b_stride;
         const T *B = rhs + b * rhs_b_stride;
-        // Two-level accumulation: each 16-deep slice is summed on its own and then added to the
-        // running total, which keeps the f32 rounding error near eps*sqrt(k/16) instead of eps*sqrt(k).
-        float acc[4][4] = {};
+        // Two-level accumulation: each 16-deep slice is summed on its own and then added to the running
+        // total -- for f32 outputs with a compensated (Kahan) add, so that the total carries one rounding
+        // however long k is (the f32 parity bound allows 1e-6 of the output's rms; k / 16 plain additions
+        // already exceed it at k = 4096).
+        float acc[4][4] = {}, comp[4][4] = {};
         for (size_t p0 = 0; p0 < k; p0 += BK) {
             float part[4][4] = {};
 #pragma unroll
@@ -66,7 +68,16 @@ gemm_generic_kernel(T *__restrict__ dst, const T *__restrict__ lhs, const T *__r
 #pragma unroll
             for (int r = 0; r < 4; ++r)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) acc[r][c] += part[r][c];
+                for (int c = 0; c < 4; ++c) {
+                    if constexpr (sizeof(T) == 4) {
+                        const float yv = part[r][c] - comp[r][c];
+                        const float tv = acc[r][c] + yv;
+                        comp[r][c] = (tv - acc[r][c]) - yv;
+                        acc[r][c] = tv;
+                    } else {
+                        acc[r][c] += part[r][c];
+                    }
+                }
             __syncthreads();
         }
         T *D = dst + b * m * n;

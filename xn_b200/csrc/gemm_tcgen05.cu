@@ -25,13 +25,12 @@
 // Batches: a third tensor-map dimension (strided-batched and grouped calls, split-k chunks), optionally with
 // one A matrix shared by every batch entry (the convolutions' packed taps) and a per-row bias.
 //
-// Every mbarrier wait is bounded; a wait that gives up records it in g_gemm_wait_timeouts and the
-// CTA drains through its common exit (tensor memory is always released).
+// Every mbarrier wait is bounded in time (wait.cuh); a wait that gives up reports it through the device's
+// host-visible status word and the CTA drains through its common exit (tensor memory is always released).
 #include <cuda.h>
 
-#include <mutex>
-
 #include "common.cuh"
+#include "wait.cuh"
 
 namespace xn {
 namespace {
@@ -40,10 +39,6 @@ constexpr int BM = 128;        // rows of A per tile = TMEM lanes
 constexpr int BKB = 128;       // bytes of K per stage = one 128-byte swizzle atom
 constexpr int UMMA_KB = 32;    // bytes of K per tcgen05.mma (32 x 8-bit or 16 x 16-bit)
 constexpr int NTHREADS = 192;
-constexpr unsigned WAIT_LIMIT = 1u << 26;
-
-__device__ unsigned g_gemm_wait_timeouts;
-
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t *b, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
@@ -57,18 +52,8 @@ __device__ __forceinline__ void mbar_expect_tx_only(uint64_t *b, unsigned bytes)
 __device__ __forceinline__ void mbar_arrive(uint64_t *b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity) {
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        unsigned ok;
-        asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-            : "=r"(ok)
-            : "r"(smem_u32(b)), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    atomicAdd(&g_gemm_wait_timeouts, 1u);
-    return false;
+__device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity, const WaitCtx &w) {
+    return mbar_wait_bounded(smem_u32(b), parity, w);
 }
 
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
@@ -142,6 +127,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31,%32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+        "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+        "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 constexpr int MAX_DST = 8;
 struct GemmArgs {
     void *y[MAX_DST];     // ndst destinations for the [M, N] result (own buffer and, in the column-parallel
@@ -157,6 +155,7 @@ struct GemmArgs {
     int a_batch_inner, b_batch_inner;  // the tensor map's dimension order is (k, batch, rows) instead of (k, rows, batch)
     int a_bcast;          // every batch entry multiplies the same A matrix (the A map then holds one matrix)
     const void *row_bias; // optional, not for fp8: added to every element of output row i (element type of y)
+    WaitCtx wait;         // bound and status word of the kernel's mbarrier waits
 };
 
 // KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16, 3 = tf32 operands (f32 words already on
@@ -171,14 +170,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB;
     constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES;
     // tcgen05 adds into its f32 accumulator with truncation: over n MMAs the result drifts by about n * 3e-8
-    // of the running sum (4e-5 at 1536 MMAs, measured).  The tf32 kind, whose callers expect f32 accuracy, therefore
-    // hands the accumulator to the epilogue every KCH k stages (64 MMAs); the epilogue warps keep the sum in
-    // registers, in round-to-nearest f32.
-    constexpr int KCH = KIND == 3 ? 16 : (1 << 30);
+    // of the running sum (4e-5 at 1536 MMAs, measured).  The tf32 kind, whose callers expect f32 accuracy (an
+    // absolute error below 1e-6 of the output's rms at k = 4096), therefore hands the accumulator to the
+    // epilogue every KCH k stages (8 MMAs).  The epilogue warps sum the hand-overs in registers in
+    // round-to-nearest f32, and every L2_EVERY hand-overs move that block sum into a second-level total kept in
+    // tensor memory (columns [2 BN, 3 BN), read and written with tcgen05.ld / tcgen05.st by the warp that owns
+    // the lanes), so that no sum ever runs over more than L2_EVERY terms at either level.
+    constexpr int KCH = KIND == 3 ? 2 : (1 << 30);
+    constexpr int L2_EVERY = 16;
     static_assert(KIND != 3 || BN <= 128, "the tf32 kind keeps BN accumulator registers per epilogue thread");
     constexpr uint32_t IDESC = F8 ? instr_desc(0, 0, BN)
                                : (KIND == 1 ? instr_desc(1, 1, BN) : (KIND == 3 ? instr_desc(2, 2, BN) : instr_desc(0, 0, BN)));
-    constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+    constexpr int ACC_COLS = (KIND == 3 ? 3 : 2) * BN;  // two accumulator buffers (+ the tf32 kind's second-level total)
+    constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -224,7 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
-                    if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
+                    if (!mbar_wait(&empty[s], ph ^ 1u, args.wait)) { ok = false; break; }
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
                     const int ga = args.a_bcast ? 0 : g;
@@ -245,14 +249,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             for (int kb0 = 0; (kb0 < num_kb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
                 const int acc = vt & 1;
                 const unsigned acc_ph = (unsigned)(vt >> 1) & 1u;
-                if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { ok = false; break; }
+                if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, args.wait)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 const int kend = num_kb - kb0 < KCH ? num_kb : kb0 + KCH;
                 for (int kb = kb0; kb < kend; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
-                    if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+                    if (!mbar_wait(&full[s], ph, args.wait)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     const uint64_t da0 = smem_desc(st), da1 = smem_desc(st + A_BYTES), db = smem_desc(st + NA * A_BYTES);
@@ -283,12 +287,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
                 const int m_blk = tin % num_m, n_blk = tin / num_m;
-                float racc[BN];
+                float racc[BN];  // sum of the hand-overs since the last move into the second-level total
 #pragma unroll
                 for (int i = 0; i < BN; ++i) racc[i] = 0.f;
+                const uint32_t l2_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(2 * BN);
+                bool l2_live = false;  // the second-level total of this tile has been written
+                int since = 0;
                 for (int kb0 = 0; (kb0 < num_kb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
                     const int acc = vt & 1;
-                    if (!mbar_wait(&tmem_full[acc], (unsigned)(vt >> 1) & 1u)) { ok = false; break; }
+                    if (!mbar_wait(&tmem_full[acc], (unsigned)(vt >> 1) & 1u, args.wait)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int c = 0; c < BN / 32; ++c) {
@@ -300,8 +307,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+                    if (++since == L2_EVERY && kb0 + KCH < num_kb) {
+                        since = 0;
+#pragma unroll
+                        for (int c = 0; c < BN / 32; ++c) {
+                            uint32_t v[32];
+                            if (l2_live) {
+                                tmem_ld32(l2_addr + (uint32_t)(c * 32), v);
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + racc[c * 32 + i]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(racc[c * 32 + i]);
+                            }
+                            tmem_st32(l2_addr + (uint32_t)(c * 32), v);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) racc[c * 32 + i] = 0.f;
+                        }
+                        l2_live = true;
+                    }
                 }
                 if (!ok) break;
+                if (l2_live) {
+#pragma unroll
+                    for (int c = 0; c < BN / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(l2_addr + (uint32_t)(c * 32), v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) racc[c * 32 + i] += __uint_as_float(v[i]);
+                    }
+                }
                 const int row = m_blk * BM + q * 32 + lane;
                 const float rb = (args.row_bias && row < args.M) ? reinterpret_cast<const float *>(args.row_bias)[row] : 0.f;
 #pragma unroll
@@ -341,7 +376,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             const int m_blk = tin % num_m, n_blk = tin / num_m;
             const int acc = t_local & 1;
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
-            if (!mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
+            if (!mbar_wait(&tmem_full[acc], acc_ph, args.wait)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m_blk * BM + q * 32 + lane;
             float xs = 1.0f;
@@ -449,6 +484,8 @@ struct SkinnyArgs {
     int nstage;
     int np;      // pieces (1 or 2)
     int uq, ur;  // stage units per CTA: total / grid and total % grid
+    int w_static;  // the weights are a model parameter: they may be fetched before the dependency wait
+    WaitCtx wait;  // bound and status word of the kernel's mbarrier waits
 };
 
 // Work is cut at k-stage granularity ("stream-K"): total = tiles * num_kb stage units, CTA c owns the
@@ -520,6 +557,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         if (lane == 0) {
             constexpr int BK = F8 ? BKB : BKB / 2;  // k elements per stage
             const int pre = min(NSTAGE, u1 - u0);
+            if (!args.w_static) asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel may have written w
             for (int it = 0; it < pre; ++it) {
                 const int u = u0 + it;
                 const int tile = (int)((unsigned)u / (unsigned)num_kb), kb = u - tile * num_kb;
@@ -539,7 +577,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     if (it < pre) {  // the weights of this stage are already on their way
                         mbar_expect_tx(&full[s], (unsigned)(args.np * X_BYTES));
                     } else {
-                        if (!mbar_wait(&empty[s], ph ^ 1u)) { ok = false; break; }
+                        if (!mbar_wait(&empty[s], ph ^ 1u, args.wait)) { ok = false; break; }
                         mbar_expect_tx(&full[s], STAGE_BYTES);
                         tma_load_2d(st, &map_w, kb * BK, tile * BM, &full[s]);
                     }
@@ -558,13 +596,13 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 const int kb1 = min(num_kb, kb0 + (u1 - u));
                 const int acc = t_local & 1;
                 const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
-                if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { ok = false; break; }
+                if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, args.wait)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NB);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
-                    if (!mbar_wait(&full[s], ph)) { ok = false; break; }
+                    if (!mbar_wait(&full[s], ph, args.wait)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     const uint64_t dw = smem_desc(st), dx = smem_desc(st + W_BYTES);
@@ -591,7 +629,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             const bool whole = kb0 == 0 && kb1 == num_kb;
             const int acc = t_local & 1;
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
-            if (!mbar_wait(&tmem_full[acc], acc_ph)) { ok = false; break; }
+            if (!mbar_wait(&tmem_full[acc], acc_ph, args.wait)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int ch = tile * BM + q * 32 + lane;  // output channel of this lane
             const float ws = !F8 ? 1.0f : (ch < args.N ? __ldg(args.w_scale + ch) : 0.0f);
@@ -766,6 +804,7 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
     CUtensorMap ma0, ma1, mb;
     GemmArgs args2 = args;
+    if (int rcw = wait_ctx(&args2.wait)) return rcw;
     const size_t a_batch = args.a_bcast ? 1 : bg.batch;
     int rc = make_map3(&ma0, a0, ELEM, args.M, args.K, lda, BM, a_batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
@@ -840,73 +879,6 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
 
 }  // namespace
 
-// Scratch of the skinny path (partial accumulators + arrival counters): one buffer per (device, stream),
-// allocated when a stream first needs it and grown on demand.  Calls on one stream are ordered, so they can
-// share; calls on different streams get different buffers and may overlap.  (xn drives a device through one
-// stream, xn-core/src/cuda_backend.rs:52: one buffer per GPU in practice.)  A stream that is being captured
-// cannot allocate: it borrows the largest buffer of its device -- the one of the stream that ran the same
-// shapes before the capture, which is how a CUDA graph is normally warmed up -- and is refused with a clear
-// message when no buffer is large enough.
-struct SkinnyScratch { float *partials = nullptr; size_t partial_bytes = 0; unsigned *counters = nullptr; size_t ncounters = 0; };
-int skinny_scratch(cudaStream_t st, size_t partial_bytes, size_t ncounters, SkinnyScratch *out) {
-    struct Entry { int dev; cudaStream_t st; SkinnyScratch s; };
-    static Entry table[256];
-    static int used = 0;
-    static std::mutex mu;
-    int dev = 0;
-    XN_CHECK_CUDA(cudaGetDevice(&dev));
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    XN_CHECK_CUDA(cudaStreamIsCapturing(st, &cap));
-    const bool capturing = cap != cudaStreamCaptureStatusNone;
-    std::lock_guard<std::mutex> lock(mu);
-    Entry *e = nullptr;
-    for (int i = 0; i < used; ++i)
-        if (table[i].dev == dev && table[i].st == st) { e = &table[i]; break; }
-    if (capturing) {
-        if (!e || e->s.partial_bytes < partial_bytes || e->s.ncounters < ncounters) {
-            e = nullptr;
-            for (int i = 0; i < used; ++i)
-                if (table[i].dev == dev && table[i].s.partial_bytes >= partial_bytes && table[i].s.ncounters >= ncounters &&
-                    (!e || table[i].s.partial_bytes > e->s.partial_bytes))
-                    e = &table[i];
-        }
-        if (!e)
-            return fail(XN_ERR_UNSUPPORTED,
-                        "skinny matmul: this shape needs %zu bytes of library scratch and the stream is being captured; "
-                        "run the call once outside stream capture first", partial_bytes);
-        *out = e->s;
-        return XN_OK;
-    }
-    if (!e) {
-        if (used == 256) return fail(XN_ERR_UNSUPPORTED, "skinny matmul: more than 256 (device, stream) pairs in use");
-        e = &table[used++];
-        e->dev = dev; e->st = st; e->s = SkinnyScratch();
-    }
-    SkinnyScratch &s = e->s;
-    if (s.partial_bytes < partial_bytes) {
-        if (s.partials) { XN_CHECK_CUDA(cudaDeviceSynchronize()); XN_CHECK_CUDA(cudaFree(s.partials)); s.partials = nullptr; s.partial_bytes = 0; }
-        XN_CHECK_CUDA(cudaMalloc(&s.partials, partial_bytes));
-        s.partial_bytes = partial_bytes;
-    }
-    if (s.ncounters < ncounters) {
-        if (s.counters) { XN_CHECK_CUDA(cudaDeviceSynchronize()); XN_CHECK_CUDA(cudaFree(s.counters)); s.counters = nullptr; s.ncounters = 0; }
-        XN_CHECK_CUDA(cudaMalloc(&s.counters, ncounters * sizeof(unsigned)));
-        XN_CHECK_CUDA(cudaMemset(s.counters, 0, ncounters * sizeof(unsigned)));
-        XN_CHECK_CUDA(cudaDeviceSynchronize());
-        s.ncounters = ncounters;
-    }
-    *out = s;
-    return XN_OK;
-}
-
-// The same per-(device, stream) buffer for other internal users (the f32 matmul's packed operands).
-int library_scratch(cudaStream_t st, size_t bytes, void **out) {
-    SkinnyScratch s;
-    if (int rc = skinny_scratch(st, bytes, 0, &s)) return rc;
-    *out = s.partials;
-    return XN_OK;
-}
-
 // Skinny path, m <= 64.  KIND 0: e4m3 pieces x0 (hi) and optional x1 (lo) with scales; KIND 1 / 2: bf16 / f16
 // operands (x1, scales unused).  Strides in elements.
 template <int KIND>
@@ -938,6 +910,8 @@ int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ld
     XN_REQUIRE(total < (1ll << 30), "skinny matmul: problem too large for the kernel's 32-bit unit index");
     a.uq = (int)(total / grid);
     a.ur = (int)(total % grid);
+    if (int rcw = wait_ctx(&a.wait)) return rcw;
+    a.w_static = (KIND == 0 || rhs_is_static()) ? 1 : 0;  // the fp8 entry points take a static weight by contract
     SkinnyScratch sc;
     int rc = skinny_scratch(st, (size_t)2 * grid * a.MB * BM * sizeof(float), (size_t)tiles * 4, &sc);
     if (rc) return rc;

@@ -3,16 +3,19 @@
 // f32) and the decode-time Linear::forward of an f32 model.  Reference path:
 // cublasGemmStridedBatchedEx with CUBLAS_COMPUTE_32F (xn-core/src/cuda_backend.rs:2109-2133).
 //
-// Arithmetic.  Every f32 operand is cut exactly into hi + lo, hi = the nearest tf32 number (10 mantissa
-// bits), lo = x - hi (exact in f32, |lo| <= 2^-11 |x|; the MMA reads its upper 10 mantissa bits).
-// x * w = xh*wh + xh*wl + xl*wh + xl*wl; the first three are tf32 MMAs (mma.sync.m16n8k8, a native
-// tensor instruction on sm_100a), the last (<= 2^-22 |x w|) is dropped, and truncating lo loses about
-// as much again: products are good to about 1e-6 relative (measured: 1e-5 in the test metric, whose
-// denominator has a floor of a tenth of the output's rms), inside the 1e-4 bound, where a plain FFMA
-// kernel is bound by the FP32 pipe (16 x 11264 x 4096 FMAs are 20 us of a fully busy B200) and measured
-// 82 us.  The MMA accumulates in f32; the running sum of every
-// 256-k chunk is folded into a separate f32 total with an ordinary add, so that the tensor core's
-// accumulation rounding cannot drift over a long k.
+// Arithmetic.  Every f32 operand is cut into hi + lo on the tf32 grid (10 mantissa bits): hi = the nearest
+// tf32 number, lo = the exact remainder x - hi (12 significant bits) rounded to tf32 as well, so hi + lo
+// carries x to 2^-23.  x * w = xh*wh + xh*wl + xl*wh + xl*wl; the first three are tf32 MMAs
+// (mma.sync.m16n8k8, a native tensor instruction on sm_100a), the last (<= 2^-22 |x w|) is dropped.
+// A plain FFMA kernel is bound by the FP32 pipe here (16 x 11264 x 4096 FMAs are 20 us of a fully busy
+// B200; it measured 82 us).
+// Accumulation.  The parity bound for f32 is 1e-4 relative with a floor of 1e-2 of the output's rms in the
+// denominator, i.e. an absolute error below 1e-6 of the rms at the maximum over 180 000 outputs -- tighter
+// than a sequential f32 sum over k = 4096 delivers, and the tensor core adds into its accumulator with
+// truncation, which is worse.  So nothing of full size is accumulated inside the MMA: every hi x hi MMA
+// starts from a zero accumulator (one rounding of an 8-term sum), the small cross terms of a 32-k step share
+// one accumulator, the five values are added with ordinary roundings, and the step's sum goes into the
+// running total with a compensated (Kahan) add.
 //
 // Data movement: like the fp8 GEMV.  Output rows ride the MMA's 16-row dimension, the activation rows
 // its 8 columns (two column groups for m = 9..16); a lane's two 128-bit loads of a row (8 consecutive
@@ -23,9 +26,8 @@
 namespace xn {
 namespace {
 
-constexpr int X_WARPS = 24;
+constexpr int X_WARPS = 20;
 constexpr int X_DEPTH = 2;   // 32-k steps in flight per warp (4 x 128-bit loads each)
-constexpr int X_FOLD = 8;    // steps between folds of the MMA accumulator into the f32 total
 constexpr int X_SMEM = 200 * 1024;
 
 __device__ __forceinline__ void mma_tf32(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -38,7 +40,17 @@ __device__ __forceinline__ void split(unsigned x, unsigned &hi, unsigned &lo) {
     // nearest tf32 (ties away from zero) with two integer ops: add half an ulp of the 10-bit mantissa to the
     // sign-magnitude bit pattern, clear the 13 low bits; a carry into the exponent is the correct rounding
     hi = (x + 0x00001000u) & 0xFFFFE000u;  // |x - hi| <= 2^-11 |x|
-    lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));         // exact; the MMA reads its top 10 mantissa bits
+    // the remainder is exact in f32 (12 significant bits); the MMA would cut it to its upper 11, so it is
+    // rounded to the tf32 grid here instead: half the error, and no bias towards zero
+    lo = (__float_as_uint(__uint_as_float(x) - __uint_as_float(hi)) + 0x00001000u) & 0xFFFFE000u;
+}
+// total += v with the rounding error of the addition carried in comp (Kahan): the sum of the per-step MMA
+// accumulators is then as good as one rounding, however long k is
+__device__ __forceinline__ void fold(float &total, float &comp, float v) {
+    const float yv = v - comp;
+    const float tv = total + yv;
+    comp = (tv - total) - yv;
+    total = tv;
 }
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool pred) {
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -53,7 +65,7 @@ __host__ __device__ inline int x_pitch(int kc) { return (kc + 31) / 32 * 128 + 1
 template <int MT>
 __global__ void __launch_bounds__(X_WARPS * 32, 1)
 gemv_f32x3_kernel(float *__restrict__ y, const float *__restrict__ x, const float *__restrict__ w, int m, size_t n, int k,
-                  size_t ldy, size_t ldx, size_t ldw, int kchunk, int tiles, int tpc, int ksplit) {
+                  size_t ldy, size_t ldx, size_t ldw, int kchunk, int tiles, int tpc, int ksplit, int w_static) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int RS = x_pitch(kchunk);
     unsigned char *sX = smem;  // MT*8 rows of f32
@@ -66,11 +78,15 @@ gemv_f32x3_kernel(float *__restrict__ y, const float *__restrict__ x, const floa
     const bool valid = tile < tiles;
     const size_t r0 = valid ? min((size_t)tile * 16 + g, n - 1) : 0, r1 = valid ? min((size_t)tile * 16 + g + 8, n - 1) : 0;
 
-    float total[MT][4];
+    float total[MT][4], comp[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) total[mt][i] = 0.0f;
+        for (int i = 0; i < 4; ++i) total[mt][i] = comp[mt][i] = 0.0f;
+
+    // A weight operand that the previous kernel in the stream may have written is read only after that kernel
+    // has completed; a static weight is prefetched ahead of the wait below.
+    if (!w_static) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     for (int kc0 = 0; kc0 < k; kc0 += kchunk) {
         const int kc = min(kchunk, k - kc0);
@@ -95,7 +111,7 @@ gemv_f32x3_kernel(float *__restrict__ y, const float *__restrict__ x, const floa
         for (int i = 0; i < X_DEPTH; ++i) load(i, st0 + i);
 
         if (kc0 == 0) {
-            // Everything so far read only the weights; the activations may come from the previous kernel.
+            // Everything so far read only the (static) weights; the activations may come from the previous kernel.
             asm volatile("griddepcontrol.wait;" ::: "memory");
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         } else {
@@ -110,12 +126,6 @@ gemv_f32x3_kernel(float *__restrict__ y, const float *__restrict__ x, const floa
         asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
         __syncthreads();
 
-        float acc[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-        int since_fold = 0;
         for (int st = st0; st < st1; st += X_DEPTH) {
 #pragma unroll
             for (int i = 0; i < X_DEPTH; ++i) {
@@ -134,35 +144,30 @@ gemv_f32x3_kernel(float *__restrict__ y, const float *__restrict__ x, const floa
                         const uint4 x0 = *reinterpret_cast<const uint4 *>(xr);
                         const uint4 x1 = *reinterpret_cast<const uint4 *>(xr + 16);
                         const unsigned xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                        // The tensor core adds into its accumulator with truncation, so nothing of full size is
+                        // ever accumulated there: each hi x hi MMA (8 k) starts from zero, the 2^-11 smaller cross
+                        // terms of the whole step share one accumulator, and the results are added with ordinary
+                        // roundings before the compensated fold into the running total.
+                        float sum[4], small[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             unsigned xh0, xl0, xh1, xl1;
                             split(xv[2 * q], xh0, xl0);
                             split(xv[2 * q + 1], xh1, xl1);
-                            // small terms first: lo(w) x hi(x), hi(w) x lo(x), then hi x hi
-                            mma_tf32(acc[mt], al[2 * q], bl[2 * q], al[2 * q + 1], bl[2 * q + 1], xh0, xh1);
-                            mma_tf32(acc[mt], ah[2 * q], bh[2 * q], ah[2 * q + 1], bh[2 * q + 1], xl0, xl1);
-                            mma_tf32(acc[mt], ah[2 * q], bh[2 * q], ah[2 * q + 1], bh[2 * q + 1], xh0, xh1);
+                            mma_tf32(small, al[2 * q], bl[2 * q], al[2 * q + 1], bl[2 * q + 1], xh0, xh1);
+                            mma_tf32(small, ah[2 * q], bh[2 * q], ah[2 * q + 1], bh[2 * q + 1], xl0, xl1);
+                            float big[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            mma_tf32(big, ah[2 * q], bh[2 * q], ah[2 * q + 1], bh[2 * q + 1], xh0, xh1);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) sum[e] = q == 0 ? big[e] : sum[e] + big[e];
                         }
-                    }
-                    if (++since_fold == X_FOLD) {
-                        since_fold = 0;
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                total[mt][e] += acc[mt][e];
-                                acc[mt][e] = 0.0f;
-                            }
+                        for (int e = 0; e < 4; ++e) fold(total[mt][e], comp[mt][e], sum[e] + small[e]);
                     }
                 }
                 load(i, st + i + X_DEPTH);
             }
         }
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) total[mt][e] += acc[mt][e];
     }
 
     // fixed-order reduction over the ksplit warps of a tile, then the store
@@ -221,7 +226,7 @@ int launch(float *y, const float *x, const float *w, int m, size_t n, int k, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, x, w, m, n, k, ldy, ldx, ldw, kchunk, tiles, tpc, ksplit));
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, x, w, m, n, k, ldy, ldx, ldw, kchunk, tiles, tpc, ksplit, rhs_is_static() ? 1 : 0));
     return XN_OK;
 }
 

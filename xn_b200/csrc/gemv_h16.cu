@@ -51,7 +51,7 @@ __host__ __device__ inline int h_pitch(int kc) { return (kc + 63) / 64 * 128 + 6
 template <typename T, int MT>
 __global__ void __launch_bounds__(H_WARPS * 32, 1)
 gemv_h16_kernel(T *__restrict__ y, const T *__restrict__ x, const T *__restrict__ w, int m, size_t n, int k, size_t ldy,
-                size_t ldx, size_t ldw, int kchunk, int tiles, int tpc, int ksplit) {
+                size_t ldx, size_t ldw, int kchunk, int tiles, int tpc, int ksplit, int w_static) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int RS = h_pitch(kchunk);
     unsigned char *sX = smem;  // MT*8 rows of 16-bit elements
@@ -69,6 +69,9 @@ gemv_h16_kernel(T *__restrict__ y, const T *__restrict__ x, const T *__restrict_
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
+    // A weight operand that the previous kernel in the stream may have written is read only after that kernel
+    // has completed; a static weight is prefetched ahead of the wait below.
+    if (!w_static) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     for (int kc0 = 0; kc0 < k; kc0 += kchunk) {
         const int kc = min(kchunk, k - kc0);
@@ -91,7 +94,7 @@ gemv_h16_kernel(T *__restrict__ y, const T *__restrict__ x, const T *__restrict_
         for (int i = 0; i < H_DEPTH; ++i) load(i, st0 + i);
 
         if (kc0 == 0) {
-            // Everything so far read only the weights; the activations may come from the previous kernel.
+            // Everything so far read only the (static) weights; the activations may come from the previous kernel.
             asm volatile("griddepcontrol.wait;" ::: "memory");
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         } else {
@@ -178,7 +181,7 @@ int launch(T *y, const T *x, const T *w, int m, size_t n, int k, size_t ldy, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, x, w, m, n, k, ldy, ldx, ldw, kchunk, tiles, tpc, ksplit));
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, x, w, m, n, k, ldy, ldx, ldw, kchunk, tiles, tpc, ksplit, rhs_is_static() ? 1 : 0));
     return XN_OK;
 }
 

@@ -32,6 +32,7 @@
 // CTA per 16-row band takes over: it reads the activation fragments straight from global memory
 // and has no limit on k.
 #include "common.cuh"
+#include "wait.cuh"
 
 namespace xn {
 namespace {
@@ -40,10 +41,6 @@ constexpr int MAX_WARPS = 20;
 template <int BITS> struct Tile { static constexpr int W = BITS == 4 ? 1024 : 2048, UNIT = W + 256; };  // bytes
 constexpr int MAGIC_I = 0x4B400000;
 constexpr float MAGIC_F = 12582912.0f;
-constexpr unsigned WAIT_LIMIT = 1u << 24;  // polls of one mbarrier before the warp gives up
-
-__device__ unsigned g_q4_wait_timeouts;  // counts abandoned waits (never expected to move)
-
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t *b, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
@@ -51,19 +48,8 @@ __device__ __forceinline__ void mbar_init(uint64_t *b, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *b, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *b, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(smem_u32(b)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity) {
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i)
-        if (mbar_try_wait(b, parity)) return true;
-    return false;
+__device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity, const WaitCtx &w) {
+    return mbar_wait_bounded(smem_u32(b), parity, w);
 }
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -155,7 +141,7 @@ template <int MT, bool DUMP, int BITS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
 linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const float *__restrict__ x_scale,
                  const unsigned char *__restrict__ wq, int m, size_t n, int k, int tiles, int tpc, int ksplit,
-                 int usplit, int urem, int depth, int32_t *__restrict__ partials) {
+                 int usplit, int urem, int depth, int32_t *__restrict__ partials, const WaitCtx wctx) {
     constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
     constexpr int UPC = 2;  // units per bulk copy and ring slot
     extern __shared__ __align__(128) unsigned char smem[];
@@ -254,7 +240,7 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-    bool timed_out = nu > 0 && !mbar_wait(&xbars[SLICED ? ks : 0], 0);
+    bool timed_out = nu > 0 && !mbar_wait(&xbars[SLICED ? ks : 0], 0, wctx);
     if (defer_ring && lane == 0)
         for (int c = 1; c < depth && c < nchunk; ++c) issue(c, c);
 
@@ -263,7 +249,7 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
     unsigned phase = 0;
     for (int c = 0; c < nchunk && !timed_out; ++c) {
         const int cu = min(UPC, nu - c * UPC);
-        if (!mbar_wait(&bar[slot], phase)) {
+        if (!mbar_wait(&bar[slot], phase, wctx)) {
             timed_out = true;
             break;
         }
@@ -290,9 +276,9 @@ linear_q4_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const flo
         }
     }
     if (timed_out) {
-        // A bulk copy never completed (not expected).  Record it, poison this warp's result so the
-        // failure is visible, and fall through to the barriers below: nothing spins for ever.
-        if (lane == 0) atomicAdd(&g_q4_wait_timeouts, 1u);
+        // A bulk copy never completed (not expected; the wait has reported it to the host).  Poison this
+        // warp's result so the failure is visible in the output too, and fall through to the barriers
+        // below: nothing spins for ever.
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -345,7 +331,7 @@ constexpr int TK_WARPS = 4;    // k split inside a CTA
 template <int MT, bool DUMP, int BITS>
 __global__ void __launch_bounds__(TK_WARPS * 32, 5)
 linear_q_tile_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const float *__restrict__ x_scale,
-                     const unsigned char *__restrict__ wq, int m, size_t n, int k, int32_t *__restrict__ partials) {
+                     const unsigned char *__restrict__ wq, int m, size_t n, int k, int32_t *__restrict__ partials, const WaitCtx wctx) {
     constexpr int UNIT_BYTES = Tile<BITS>::UNIT;
     constexpr int SU = BITS == 4 ? 4 : 2;  // units per ring slot: 5 KB either way (static shared memory < 48 KB)
     constexpr int SLOT_BYTES = SU * UNIT_BYTES;
@@ -420,7 +406,7 @@ linear_q_tile_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const
                 unsigned b[G][MT][8];
 #pragma unroll
                 for (int ug = 0; ug < G; ++ug) fetch_unit(b[ug], c * SU + h * G + ug);
-                if (h == 0 && !mbar_wait(&bars[warp][slot], (unsigned)(c >> 1) & 1u)) {
+                if (h == 0 && !mbar_wait(&bars[warp][slot], (unsigned)(c >> 1) & 1u, wctx)) {
                     timed_out = true;
                     break;
                 }
@@ -429,7 +415,7 @@ linear_q_tile_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const
                     unit_math(base + (h * G + ug) * UNIT_BYTES, b[ug], (sb0 + c * SU + h * G + ug) * 4);
             }
         } else {
-            if (!mbar_wait(&bars[warp][slot], (unsigned)(c >> 1) & 1u)) {
+            if (!mbar_wait(&bars[warp][slot], (unsigned)(c >> 1) & 1u, wctx)) {
                 timed_out = true;
                 break;
             }
@@ -443,7 +429,6 @@ linear_q_tile_kernel(float *__restrict__ y, const int8_t *__restrict__ xq, const
         if (lane == 0 && c + 2 < nchunk) issue(c + 2);
     }
     if (timed_out) {
-        if (lane == 0) atomicAdd(&g_q4_wait_timeouts, 1u);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -490,7 +475,9 @@ int launch_tile(float *y, const int8_t *xq, const float *x_scale, const void *wq
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, xq, x_scale, (const unsigned char *)wq, m, n, k, partials));
+    WaitCtx wctx;
+    if (int rcw = wait_ctx(&wctx)) return rcw;
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, xq, x_scale, (const unsigned char *)wq, m, n, k, partials, wctx));
     return XN_OK;
 }
 
@@ -532,8 +519,10 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    WaitCtx wctx;
+    if (int rcw = wait_ctx(&wctx)) return rcw;
     XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, y, xq, x_scale, (const unsigned char *)wq, m, n, k, tiles, tpc,
-                                     ksplit, nsb / ksplit, nsb % ksplit, depth, partials));
+                                     ksplit, nsb / ksplit, nsb % ksplit, depth, partials, wctx));
     return XN_OK;
 }
 
@@ -575,4 +564,35 @@ extern "C" int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale,
 extern "C" int xn_mm_linear_q8(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
                                size_t n, size_t k, int32_t *partials, void *stream) {
     return linear_q<8>("linear_q8", y, xq, x_scale, wq_packed, m, n, k, partials, stream);
+}
+
+// Host-buffer form: the decode call of a host that keeps its activations and results in (pinned) host memory.
+// One C call enqueues the host->device copy, the row quantizer, the linear and the device->host copy on
+// `stream`; the staging buffers live in a caller-owned device workspace.
+extern "C" size_t xn_mm_linear_q4_host_workspace_bytes(size_t m, size_t n, size_t k) {
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    return up(m * k * 4) + up(m * k) + up(m * 4) + up(m * n * 4);
+}
+
+extern "C" int xn_mm_linear_q4_host(float *y_host, const float *x_host, const void *wq_packed, size_t m, size_t n, size_t k,
+                                    void *workspace, size_t workspace_bytes, void *stream) {
+    XN_REQUIRE(k > 0 && k % 128 == 0, "linear_q4_host: k=%zu must be a positive multiple of 128", k);
+    if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(y_host && x_host && wq_packed && workspace, "linear_q4_host: null pointer");
+    XN_REQUIRE(aligned(workspace, 256), "linear_q4_host: workspace must be 256-byte aligned");
+    if (workspace_bytes < xn_mm_linear_q4_host_workspace_bytes(m, n, k))
+        return fail(XN_ERR_WORKSPACE, "linear_q4_host: workspace of %zu bytes, %zu needed", workspace_bytes,
+                    xn_mm_linear_q4_host_workspace_bytes(m, n, k));
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    unsigned char *p = static_cast<unsigned char *>(workspace);
+    float *x_dev = reinterpret_cast<float *>(p);
+    int8_t *xq = reinterpret_cast<int8_t *>(p + up(m * k * 4));
+    float *xs = reinterpret_cast<float *>(p + up(m * k * 4) + up(m * k));
+    float *y_dev = reinterpret_cast<float *>(p + up(m * k * 4) + up(m * k) + up(m * 4));
+    cudaStream_t st = (cudaStream_t)stream;
+    XN_CHECK_CUDA(cudaMemcpyAsync(x_dev, x_host, m * k * 4, cudaMemcpyHostToDevice, st));
+    if (int rc = xn_mm_quantize_rows_i8(xq, xs, x_dev, XN_F32, m, k, stream)) return rc;
+    if (int rc = linear_q<4>("linear_q4_host", y_dev, xq, xs, wq_packed, m, n, k, nullptr, stream)) return rc;
+    XN_CHECK_CUDA(cudaMemcpyAsync(y_host, y_dev, m * n * 4, cudaMemcpyDeviceToHost, st));
+    return XN_OK;
 }

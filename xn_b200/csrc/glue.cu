@@ -120,7 +120,8 @@ __global__ void softmax_kernel(T *__restrict__ dst, const T *__restrict__ src, s
     mx = warp_max(mx);
     float sum = 0.0f;
     for (size_t c = lane; c < cols; c += 32) {
-        const T e = from_f32<T>(expf(to_f32(x[c]) - mx));
+        // the reference subtracts in the element type: (x - max) is rounded before the exponential
+        const T e = from_f32<T>(expf(to_f32(from_f32<T>(to_f32(x[c]) - mx))));
         y[c] = e;
         sum += to_f32(e);
     }

@@ -142,7 +142,14 @@ extern "C" int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const 
                     "linear_fp8_noalloc: m=%zu k=%zu exceeds the built-in scratch (m <= %zu and m*k <= %zu); "
                     "use xn_mm_linear_fp8 with a caller workspace",
                     m, k, NOALLOC_MAX_ROWS, NOALLOC_MAX_ELEMS);
+    XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_noalloc: k=%zu must be a positive multiple of 16", k);
+    XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull, "linear_fp8_noalloc: dimension too large");
     if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(y_bf16 && x_bf16 && wq && w_scale, "linear_fp8_noalloc: null pointer");
+    XN_REQUIRE(aligned(wq, 16), "linear_fp8_noalloc: weights must be 16-byte aligned");
+    // Every argument check is above this line: nothing has been enqueued, and the shared scratch has not been
+    // touched, when a call is rejected.
+    NoAllocScope no_alloc;  // the kernels' wait-status word is not allocated on behalf of this entry point
     unsigned char *base = nullptr;
     int rc = noalloc_scratch(&base);
     if (rc) return rc;
@@ -154,10 +161,6 @@ extern "C" int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const 
     // Only kernels that need no scratch of their own: the weight-streaming GEMV up to 32 rows, the tiled
     // tensor-memory kernel beyond.  (xn_mm_linear_fp8_pieces would pick the skinny kernel from 9 rows on, whose
     // split-tile hand-over lives in a library-owned buffer that is allocated on first use.)
-    XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_noalloc: k=%zu must be a positive multiple of 16", k);
-    XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull, "linear_fp8_noalloc: dimension too large");
-    XN_REQUIRE(y_bf16 && wq && w_scale, "linear_fp8_noalloc: null pointer");
-    XN_REQUIRE(aligned(wq, 16), "linear_fp8_noalloc: weights must be 16-byte aligned");
     const uint8_t *lo_or_null = variant == 0 ? lo : nullptr;
     if (m <= 32) return launch_linear_fp8_gemv(y_bf16, hi, lo_or_null, xs, wq, w_scale, (int)m, n, (int)k, (cudaStream_t)stream);
     void *dst[1] = {y_bf16};

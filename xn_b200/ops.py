@@ -103,13 +103,26 @@ class Linear:
         return self
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = matmul_t(x, self.weight)
-        if self.bias is not None:
+        w, b = self.weight, self.bias
+        if b is not None:
+            _require_cuda(b)
+            if b.dtype != x.dtype or list(b.shape) != [w.shape[0]]:
+                raise XnError(1, f"bias shape mismatch: expected [{w.shape[0]}] of {x.dtype}, got {list(b.shape)} of {b.dtype}")
+        # Contiguous-row activations and weight (what every model layer passes): the Linear entry point, which
+        # may prefetch the weight -- a parameter, never the previous kernel's output -- ahead of the stream order.
+        if (x.is_cuda and w.is_cuda and x.dtype == w.dtype and x.dim() >= 2 and w.dim() == 2 and x.shape[-1] == w.shape[1]
+                and x.stride(-1) == 1 and w.stride(1) == 1 and x.is_contiguous()):
+            n, k = w.shape
+            m = x.numel() // k if k else 0
+            y = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+            check(lib().xn_mm_linear(_dtype_code(x), y.data_ptr(), x.data_ptr(), w.data_ptr(),
+                                     b.contiguous().data_ptr() if b is not None else None, m, n, k, k, w.stride(0), n,
+                                     _stream()))
+            return y
+        y = matmul_t(x, w)
+        if b is not None:
             # the reference's separate broadcast_add (nn/linear.rs:61-64)
-            _require_cuda(self.bias)
-            if self.bias.dtype != y.dtype or list(self.bias.shape) != [y.shape[-1]]:
-                raise XnError(1, f"bias shape mismatch: expected [{y.shape[-1]}] of {y.dtype}, got {list(self.bias.shape)} of {self.bias.dtype}")
-            check(lib().xn_mm_add_bias(_dtype_code(y), y.data_ptr(), y.data_ptr(), self.bias.contiguous().data_ptr(),
+            check(lib().xn_mm_add_bias(_dtype_code(y), y.data_ptr(), y.data_ptr(), b.contiguous().data_ptr(),
                                        y.numel() // y.shape[-1], y.shape[-1], _stream()))
         return y
 
@@ -192,6 +205,27 @@ class LinearQ4:
         return linear_q4(xq, xs, self.wq, self.n).reshape(*lead, self.n)
 
     __call__ = forward
+
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
+        """x_host [m,k] f32 and y_host [m,n] f32 in (pinned) host memory: one library call enqueues the copy in,
+        the row quantizer, the linear and the copy out on the current stream (xn_mm_linear_q4_host); the result
+        is valid after the stream has been synchronised.  Staging buffers are kept per batch size."""
+        m = x_host.shape[0]
+        if x_host.is_cuda or y_host.is_cuda or x_host.dtype != torch.float32 or y_host.dtype != torch.float32:
+            raise XnError(_lib.ERR_INVALID, "forward_host takes float32 host tensors")
+        if list(x_host.shape) != [m, self.k] or list(y_host.shape) != [m, self.n] or not x_host.is_contiguous() \
+                or not y_host.is_contiguous():
+            raise XnError(_lib.ERR_INVALID, f"forward_host: expected contiguous [{m},{self.k}] and [{m},{self.n}]")
+        ws = self._host_ws.get(m) if hasattr(self, "_host_ws") else None
+        if ws is None:
+            if not hasattr(self, "_host_ws"):
+                self._host_ws = {}
+            ws = torch.empty(lib().xn_mm_linear_q4_host_workspace_bytes(m, self.n, self.k), dtype=torch.uint8,
+                             device=self.wq.device)
+            self._host_ws[m] = ws
+        check(lib().xn_mm_linear_q4_host(y_host.data_ptr(), x_host.data_ptr(), self.wq.data_ptr(), m, self.n, self.k,
+                                         ws.data_ptr(), ws.numel(), _stream()))
+        return y_host
 
 
 def quantize_weights_fp8(w: torch.Tensor):
