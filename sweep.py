@@ -2,7 +2,7 @@
 the f32 linear, and the 16-bit dense GEMM, each with its roofline and (where the reference has a
 GPU path) the same call through cuBLAS as xn issues it (torch.matmul -> cublasGemmEx, f32 accumulate).
 
-    python -m xn_b200.sweep [--what fp8|dense|grouped|f32|conv|all] [--json out.json]
+    python sweep.py [--what fp8|dense|grouped|f32|conv|all] [--json out.json] [--md out.md]
 
 Timing: CUDA events around a CUDA-graph replay of `reps` launches that rotate over enough distinct
 weight copies to exceed the L2 several times for the bandwidth-bound points.
@@ -17,7 +17,7 @@ import time
 
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import xn_b200 as xn  # noqa: E402
 
@@ -124,6 +124,24 @@ def sweep_dense(out, dev, pk):
             t_ref = time_graph([lambda w=w: torch.matmul(x, w.t(), out=y) for w in ws], 1)
             roof = max(byts / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12))
             row = {"config": "dense_16bit", "dtype": str(dt), "m": m, "n": n, "k": k, "us": t * 1e6,
+                   "tflops": flops / t / 1e12, "cublas_us": t_ref * 1e6, "cublas_tflops": flops / t_ref / 1e12,
+                   "frac_of_roofline": roof / t}
+            out.append(row)
+            print(json.dumps(row), flush=True)
+            del ws
+        # `a.matmul(&b)` with a row-major (k, n) right-hand side: the reference's own CUDA matmul benchmark
+        # (xn-core/examples/basic_cuda.rs:35-56, (32, 1, 2048) x (2048, 11264)) and square prefill-sized products
+        for m, n, k in ((32, 11264, 2048), (4096, 4096, 4096), (256, 12288, 4096)):
+            R = replicas_for(2 * n * k, hi=8)
+            ws = [(torch.randn(k, n, device=dev) * 0.05).to(dt) for _ in range(R)]
+            x = torch.randn(m, k, device=dev).to(dt)
+            y = torch.empty(m, n, device=dev, dtype=dt)
+            flops = 2.0 * m * n * k
+            byts = 2 * (n * k + m * k + m * n)
+            t = time_graph([lambda w=w: xn.matmul_(y, x, w, False) for w in ws], 1)
+            t_ref = time_graph([lambda w=w: torch.matmul(x, w, out=y) for w in ws], 1)
+            roof = max(byts / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12))
+            row = {"config": "dense_16bit_kn_rhs", "dtype": str(dt), "m": m, "n": n, "k": k, "us": t * 1e6,
                    "tflops": flops / t / 1e12, "cublas_us": t_ref * 1e6, "cublas_tflops": flops / t_ref / 1e12,
                    "frac_of_roofline": roof / t}
             out.append(row)
@@ -244,7 +262,7 @@ def write_md(rows, path, what="all"):
     pk = rows[0]["peaks"]
     tag = "sweep_" + what
     L = ["# Shape sweeps (CUDA-event timing, graph replay, operands rotated over >= 600 MB of distinct weight copies)", "",
-         "Command: `python -m xn_b200.sweep --what %s --json gpurun_out/%s.json --md gpurun_out/%s.md` on one B200"
+         "Command: `python sweep.py --what %s --json %s.json --md %s.md` on one B200"
          " (committed files only)." % (what, tag, tag),
          "Roofline per point = max(algorithmic bytes / measured HBM GB/s, 2MNK / peak), peak = %s cuBLAS bf16 burst" % pk["kind"],
          "(%.0f TFLOP/s) for the W8A16 and 16-bit rows and twice that for W8A8; HBM = %.0f GB/s; `frac` = roofline time / measured time."
@@ -268,6 +286,16 @@ def write_md(rows, path, what="all"):
         L += ["## 16-bit dense matmul_t (tcgen05 tiled kernel; skinny tcgen05 form for 17-64 rows; mma.sync GEMV up to 16 rows)", "",
               "| dtype | M x N x K | µs | TFLOP/s | cuBLAS µs | cuBLAS TFLOP/s | frac |", "|---|---|---|---|---|---|---|"]
         for r in dense:
+            L.append("| %s | %dx%dx%d | %.1f | %.0f | %.1f | %.0f | %.2f |" % (
+                r["dtype"].replace("torch.", ""), r["m"], r["n"], r["k"], r["us"], r["tflops"], r["cublas_us"],
+                r["cublas_tflops"], r["frac_of_roofline"]))
+        L.append("")
+    kn = [r for r in rows if r.get("config") == "dense_16bit_kn_rhs"]
+    if kn:
+        L += ["## 16-bit matmul with a row-major (k, n) right-hand side (tcgen05 tiled kernel, B read as an MN-major operand;"
+              " first row = xn-core/examples/basic_cuda.rs)", "",
+              "| dtype | M x N x K | µs | TFLOP/s | cuBLAS µs | cuBLAS TFLOP/s | frac |", "|---|---|---|---|---|---|---|"]
+        for r in kn:
             L.append("| %s | %dx%dx%d | %.1f | %.0f | %.1f | %.0f | %.2f |" % (
                 r["dtype"].replace("torch.", ""), r["m"], r["n"], r["k"], r["us"], r["tflops"], r["cublas_us"],
                 r["cublas_tflops"], r["frac_of_roofline"]))

@@ -86,11 +86,12 @@ def test_conv1d_matches_oracle_and_definition(xn, oracle, cuda, dt, case):
     truth = kats.conv1d_f64(oracle.to_f32(dt, x), oracle.to_f32(dt, w), stride, pad, dil, groups)
     assert got.shape == truth.shape
     tol = 1e-4 if dt == 0 else 1e-2   # f32 / 16-bit output bars of the matmul path
-    assert oracle.rel_err(got, truth) < tol
+    assert oracle.rel_err(got, truth) < tol, oracle.rel_err_report(got, truth)
     want = oracle.to_f32(dt, oracle.conv1d(dt, x, w, stride, pad, dil, groups))
     # the reference's grouped CPU loops accumulate in the element type: for 16-bit types the oracle is
-    # itself a few element ulps away from the definition there
-    assert oracle.rel_err(got, want) <= tol + 1.5 * oracle.rel_err(want, truth)
+    # itself many element ulps away from the definition there, and only the definition is a meaningful bar
+    if oracle.rel_err(want, truth) < tol:
+        assert oracle.rel_err(got, want) <= 2 * tol
     with_bias = _host(oracle, dt, xn.ops.conv1d(_dev(dt, x, cuda), _dev(dt, w, cuda), _dev(dt, bias, cuda), stride, pad, dil, groups))
     assert _bias_ok(oracle, dt, with_bias, truth, bias, tol)
     # the direct kernel computes the same thing
@@ -129,9 +130,10 @@ def test_conv_transpose1d_matches_oracle_and_definition(xn, oracle, cuda, dt, ca
     truth = kats.conv_transpose1d_f64(oracle.to_f32(dt, x), oracle.to_f32(dt, w), stride, pad, opad, groups)
     assert got.shape == truth.shape
     tol = 1e-4 if dt == 0 else 1e-2
-    assert oracle.rel_err(got, truth) < tol
+    assert oracle.rel_err(got, truth) < tol, oracle.rel_err_report(got, truth)
     want = oracle.to_f32(dt, oracle.conv_transpose1d(dt, x, w, stride, pad, opad, groups))
-    assert oracle.rel_err(got, want) <= tol + 1.5 * oracle.rel_err(want, truth)
+    if oracle.rel_err(want, truth) < tol:
+        assert oracle.rel_err(got, want) <= 2 * tol
     with_bias = _host(oracle, dt, xn.ops.conv_transpose1d(_dev(dt, x, cuda), _dev(dt, w, cuda), _dev(dt, bias, cuda), stride, pad,
                                                       opad, groups))
     assert _bias_ok(oracle, dt, with_bias, truth, bias, tol)

@@ -143,7 +143,9 @@ def test_decoder_step_reduced_size(xn, oracle, cuda):
     rms = np.sqrt(np.mean(ref ** 2))
     err_rms, err_max = np.sqrt(np.mean((y - ref) ** 2)) / rms, np.max(np.abs(y - ref)) / rms
     print("decoder step: rms err", err_rms, "max err / rms", err_max)
-    assert err_rms < 1e-2 and err_max < 6e-2
+    # measured: rms 0.0075, max 0.032 of the output's rms (a wrong head or a skipped residual moves the rms error
+    # to order one)
+    assert err_rms < 1e-2 and err_max < 4.5e-2
 
 
 def test_decode_attention_full_width_slice(xn, oracle, cuda):

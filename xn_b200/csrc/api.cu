@@ -144,6 +144,20 @@ static int gemm_dispatch(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_
                         lhs_b_stride != 0)))
         return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
                                     (cudaStream_t)stream);
+    // 16-bit `matmul` with a row-major [k, n] right-hand side (n contiguous; cuBLAS's OP_N in the reference): the
+    // tcgen05 kernel reads it as an MN-major operand.  Worth it from a few thousand MACs per output row on; tiny
+    // products (decode attention's p.v with one query row) stay on the generic kernel.
+    {
+        static const bool kn_off = [] { const char *e = getenv("XN_MM_KN_TC"); return e && atoi(e) == 0; }();
+        const bool kn16_ok = !kn_off && dtype != XN_F32 && lhs_cs == 1 && rhs_cs == 1 && dst_cs == 1 && n >= 2 && k % 8 == 0 &&
+                             lhs_rs % 8 == 0 && rhs_rs % 8 == 0 && rhs_rs >= n && aligned(l, 16) && aligned(r, 16) &&
+                             m <= 0x7fffffff && n <= 0x7fffffff && k <= 0x7fffffff && dst_rs <= 0x7fffffff &&
+                             (m >= 8 || n * k >= (size_t)1 << 20);
+        if (kn16_ok && (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 &&
+                                       rhs_b_stride >= k * rhs_rs && lhs_b_stride != 0)))
+            return launch_gemm_kn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_rs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
+                                        (cudaStream_t)stream);
+    }
     // f32 with many rows, one batch, row-major dst: three tf32 pieces per operand on the tensor-memory kernel
     // (any operand strides; the repack normalises them).
     if (dtype == XN_F32 && lhs_b == 1 && dst_cs == 1 && dst_rs <= 0x7fffffff && gemm_f32_tc_fits(m, n, k))

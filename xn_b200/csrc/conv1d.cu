@@ -61,10 +61,16 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], 
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// x = hi + lo with hi on the tf32 grid (round to nearest by integer arithmetic) and lo exact in f32
+// x = hi + lo with both pieces on the tf32 grid (round to nearest by integer arithmetic): the remainder x - hi is
+// exact in f32 and would be cut, not rounded, by the MMA
 __device__ __forceinline__ void split_tf32(float x, unsigned &hi, unsigned &lo) {
     hi = (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u;
-    lo = __float_as_uint(x - __uint_as_float(hi));
+    lo = (__float_as_uint(x - __uint_as_float(hi)) + 0x1000u) & 0xFFFFE000u;
+}
+__device__ __forceinline__ void mma_tf32_zero(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 // One CTA: 64 output channels x 64 output positions of one (batch entry, group[, phase]).
@@ -97,13 +103,20 @@ conv_igemm_kernel(T *__restrict__ dst, const T *__restrict__ src, const T *__res
     const int cin = a.cin_g * a.groups, cout = a.cout_g * a.groups;
     const T *srcb = src + ((size_t)b * cin + (size_t)grp * a.cin_g) * a.length;
 
-    float acc[2][4][4];
+    // f32 only: the tensor core adds into its accumulator with truncation, so the full-size hi x hi products are
+    // never accumulated there -- each such MMA starts from zero and is added to `acc` with a compensated (Kahan)
+    // add (`comp`), while the 2^-11 smaller cross terms share the chained accumulator `small`
+    constexpr int NC = ES == 4 ? 4 : 1;
+    float acc[2][4][4], comp[2][4][NC], small[2][4][NC];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+            for (int e = 0; e < 4; ++e) {
+                acc[i][j][e] = 0.f;
+                if (e < NC) comp[i][j][e] = small[i][j][e] = 0.f;
+            }
 
     // per-lane fragment addresses (tap 0, k step 0)
     unsigned abase[2], bbase[4];
@@ -227,15 +240,32 @@ conv_igemm_kernel(T *__restrict__ dst, const T *__restrict__ src, const T *__res
                     for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
                         for (int ni = 0; ni < 4; ++ni) {
-                            mma_tf32(acc[mi][ni], al[mi], bh[ni][0], bh[ni][1]);
-                            mma_tf32(acc[mi][ni], ah[mi], bl[ni][0], bl[ni][1]);
-                            mma_tf32(acc[mi][ni], ah[mi], bh[ni][0], bh[ni][1]);
+                            float (&sm)[4] = reinterpret_cast<float (&)[4]>(small[mi][ni]);
+                            mma_tf32(sm, al[mi], bh[ni][0], bh[ni][1]);
+                            mma_tf32(sm, ah[mi], bl[ni][0], bl[ni][1]);
+                            float big[4];
+                            mma_tf32_zero(big, ah[mi], bh[ni][0], bh[ni][1]);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float yv = big[e] - comp[mi][ni][e % NC];
+                                const float tv = acc[mi][ni][e] + yv;
+                                comp[mi][ni][e % NC] = (tv - acc[mi][ni][e]) - yv;
+                                acc[mi][ni][e] = tv;
+                            }
                         }
                 }
             }
         }
     }
 
+    if constexpr (ES == 4) {
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[mi][ni][e] += small[mi][ni][e % NC];
+    }
     // epilogue: bias, one rounding to T, rows of the output are position-contiguous
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
@@ -271,23 +301,38 @@ conv_direct_kernel(T *__restrict__ dst, const T *__restrict__ src, const T *__re
         const int co = (int)(bc % cout), b = (int)(bc / cout);
         const int grp = co / a.cout_g, cog = co - grp * a.cout_g;
         const T *srcb = src + ((size_t)b * cin + (size_t)grp * a.cin_g) * a.length;
-        float s = 0.f;
+        // f32 products summed in runs of 16 channels; the runs go into the total with a compensated (Kahan) add, so
+        // that a long cin * ksize sum stays within the f32 parity bound (1e-6 of the output's rms)
+        float s = 0.f, comp = 0.f;
+        auto fold = [&](float part) {
+            const float yv = part - comp, tv = s + yv;
+            comp = (tv - s) - yv;
+            s = tv;
+        };
         if (!TR) {
             const T *w = kernel + (size_t)co * a.cin_g * a.ksize;
             for (int kk = 0; kk < a.ksize; ++kk) {
                 const int li = lo * a.stride + kk * a.dilation - a.padding;
                 if (li < 0 || li >= a.length) continue;
-                for (int ci = 0; ci < a.cin_g; ++ci)
-                    s += to_f32(srcb[(size_t)ci * a.length + li]) * to_f32(w[(size_t)ci * a.ksize + kk]);
+                for (int c0 = 0; c0 < a.cin_g; c0 += 16) {
+                    float part = 0.f;
+                    for (int ci = c0; ci < min(c0 + 16, a.cin_g); ++ci)
+                        part += to_f32(srcb[(size_t)ci * a.length + li]) * to_f32(w[(size_t)ci * a.ksize + kk]);
+                    fold(part);
+                }
             }
         } else {
             const int raw = lo + a.padding, r = raw % a.stride;
             for (int kk = r; kk < a.ksize; kk += a.stride) {
                 const int li = (raw - kk) / a.stride;
                 if (raw < kk || li >= a.length) continue;
-                for (int ci = 0; ci < a.cin_g; ++ci)
-                    s += to_f32(srcb[(size_t)ci * a.length + li]) *
-                         to_f32(kernel[(((size_t)grp * a.cin_g + ci) * a.cout_g + cog) * a.ksize + kk]);
+                for (int c0 = 0; c0 < a.cin_g; c0 += 16) {
+                    float part = 0.f;
+                    for (int ci = c0; ci < min(c0 + 16, a.cin_g); ++ci)
+                        part += to_f32(srcb[(size_t)ci * a.length + li]) *
+                                to_f32(kernel[(((size_t)grp * a.cin_g + ci) * a.cout_g + cog) * a.ksize + kk]);
+                    fold(part);
+                }
             }
         }
         if (bias) s += to_f32(bias[co]);

@@ -82,6 +82,20 @@ __device__ __forceinline__ uint64_t smem_desc(const void *tile) {
     return d;
 }
 
+// The same for an MN-major operand (the [K, N] right-hand side of a plain `matmul`, n contiguous): the tile is a
+// row of 64-column blocks, each block = BK k-rows of 128 bytes as TMA writes them with the 128-byte swizzle.
+// Within a block the 8-row groups along k are 1024 bytes apart (stride byte offset), the blocks along n
+// `block_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mn(const void *tile, unsigned block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(block_bytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 // Instruction descriptor: D = f32, A/B formats, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
 __host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int n) {
     return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(n >> 3) << 17) |
@@ -156,6 +170,7 @@ struct GemmArgs {
     int a_bcast;          // every batch entry multiplies the same A matrix (the A map then holds one matrix)
     const void *row_bias; // optional, not for fp8: added to every element of output row i (element type of y)
     WaitCtx wait;         // bound and status word of the kernel's mbarrier waits
+    int b_mn;             // 16-bit kinds: B is [K, N] with n contiguous (MN-major); its map is (n, k, batch), box 64 x BK
 };
 
 // KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16, 3 = tf32 operands (f32 words already on
@@ -236,7 +251,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     const int by = args.b_batch_inner ? g : n_blk * BN, bz = args.b_batch_inner ? n_blk * BN : g;
                     tma_load_3d(st, &map_a0, kb * BK, ay, az, &full[s]);
                     if (NA == 2) tma_load_3d(st + A_BYTES, &map_a1, kb * BK, ay, az, &full[s]);
-                    tma_load_3d(st + NA * A_BYTES, &map_b, kb * BK, by, bz, &full[s]);
+                    if (args.b_mn) {
+                        // one 64-column block (64 n x BK k, 8 KB) per copy
+                        for (int i = 0; i < BN / 64; ++i)
+                            tma_load_3d(st + NA * A_BYTES + i * (64 * BKB), &map_b, n_blk * BN + 64 * i, kb * BK, g, &full[s]);
+                    } else {
+                        tma_load_3d(st + NA * A_BYTES, &map_b, kb * BK, by, bz, &full[s]);
+                    }
                 }
             }
         }
@@ -259,15 +280,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     if (!mbar_wait(&full[s], ph, args.wait)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-                    const uint64_t da0 = smem_desc(st), da1 = smem_desc(st + A_BYTES), db = smem_desc(st + NA * A_BYTES);
+                    const uint64_t da0 = smem_desc(st), da1 = smem_desc(st + A_BYTES);
+                    const bool bmn = ELEM == 2 && args.b_mn;
+                    const uint64_t db = bmn ? smem_desc_mn(st + NA * A_BYTES, 64 * BKB) : smem_desc(st + NA * A_BYTES);
+                    const uint32_t idesc = bmn ? (IDESC | (1u << 16)) : IDESC;   // bit 16: B is MN-major
+                    // k advance per MMA: 32 bytes inside the swizzled row (K-major), 16 k-rows of 128 bytes (MN-major)
+                    const uint64_t badv = bmn ? (uint64_t)((UMMA_KB / ELEM) * 128 >> 4) : (uint64_t)(UMMA_KB >> 4);
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
                         if constexpr (KIND == 3) {
                             umma_tf32(d_tmem, da0 + adv, db + adv, IDESC, kb > kb0 || ks != 0);
                         } else {
-                            umma<F8>(d_tmem, da0 + adv, db + adv, IDESC, (kb | ks) != 0);
-                            if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + adv, IDESC, 1u);
+                            umma<F8>(d_tmem, da0 + adv, db + ks * badv, idesc, (kb | ks) != 0);
+                            if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + ks * badv, idesc, 1u);
                         }
                     }
                     umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
@@ -794,6 +820,23 @@ int make_map(CUtensorMap *map, const void *base, int elem, size_t rows, size_t k
     return XN_OK;
 }
 
+// [K, N] operand with n contiguous, k-rows `ld` elements apart, `batch` matrices batch_stride elements apart:
+// dimensions (n, k, batch), box 64 n x 64 k (128-byte rows, 128-byte swizzle).  16-bit elements only.
+int make_map_mn(CUtensorMap *map, const void *base, size_t n, size_t k, size_t ld, size_t batch, size_t batch_stride) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if (batch <= 1) { batch = 1; batch_stride = k * ld; }
+    cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)k, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)(BKB / 2), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled (n-contiguous operand) failed with code %d", (int)r);
+    return XN_OK;
+}
+
 struct BatchGeom { size_t batch = 1, a_stride = 0, b_stride = 0; };
 
 template <int KIND, int BN, int NA>
@@ -810,7 +853,12 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     if (rc) return rc;
     rc = make_map3(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM, a_batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
-    rc = make_map3(&mb, b, ELEM, args.N, args.K, ldb, BN, bg.batch, bg.b_stride, &args2.b_batch_inner);
+    if (args.b_mn) {
+        if constexpr (ELEM == 2 && BN % 64 == 0) rc = make_map_mn(&mb, b, args.N, args.K, ldb, bg.batch, bg.b_stride);
+        else rc = fail(XN_ERR_UNSUPPORTED, "n-contiguous right-hand side: tile width %d / element size %d not supported", BN, ELEM);
+    } else {
+        rc = make_map3(&mb, b, ELEM, args.N, args.K, ldb, BN, bg.batch, bg.b_stride, &args2.b_batch_inner);
+    }
     if (rc) return rc;
     auto kern = gemm_tcgen05_kernel<KIND, BN, NA, NSTAGE>;
     const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 4 * 32 * 256 + 1024;
@@ -844,13 +892,14 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
     const long long m_tiles = (long long)((args.M + BM - 1) / BM) * args.batch;
     int best = 256;
     long long best_cost = -1;
-    for (int bn = 256; bn >= 64; bn -= 32) {
+    const int bn_step = args.b_mn ? 64 : 32;  // an n-contiguous B arrives in 64-column blocks
+    for (int bn = 256; bn >= 64; bn -= bn_step) {
         const long long tiles = m_tiles * ((args.N + bn - 1) / bn);
         const long long waves = (tiles + sms - 1) / sms;
         const long long cost = waves * (NA * BM + bn);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
-    if (force_bn >= 64 && force_bn <= 256 && force_bn % 32 == 0) best = force_bn;
+    if (force_bn >= 64 && force_bn <= 256 && force_bn % bn_step == 0) best = force_bn;
     if constexpr (KIND == 3) {
         // the tf32 kind is instantiated up to 128 columns (its epilogue holds a row of the tile in registers)
         best = 128;
@@ -984,6 +1033,22 @@ int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rh
     GemmArgs a{};
     a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    BatchGeom bg;
+    bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;
+    return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
+                         : launch_kind<2, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg);
+}
+
+// `matmul` with a row-major [k, n] right-hand side (rhs rows ldb elements apart, n contiguous) -- cuBLAS's OP_N
+// form of the reference (xn-core/src/cuda_backend.rs:208-223), e.g. attn.matmul(&v)
+// (xn-moshi/src/batched_transformer.rs:190) and the reference's bf16 benchmark
+// (xn-core/examples/basic_cuda.rs:35-56).  The tiled kernel reads B as an MN-major operand; any row count.
+int launch_gemm_kn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
+                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st) {
+    GemmArgs a{};
+    a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
+    a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    a.b_mn = 1;
     BatchGeom bg;
     bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;
     return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
