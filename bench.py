@@ -338,10 +338,18 @@ def measure_prefill_column_parallel(dev, world, rank, xn, torch, dist) -> dict:
         x = torch.randn(m, k, generator=g, device=dev).bfloat16()
         hi, lo, xs = xn.split_rows_e4m3(x)
         full = xn.linear_fp8(x, wq, ws, 0)
-        lin = PeerPrefillLinear(wq, ws, n, k, m)
+        lin = PeerPrefillLinear(wq, ws, n, k, m, multicast=False)   # one plain store per peer
         y = lin.forward(hi, lo, xs, m)
         torch.cuda.synchronize()
         same_peer = bool(torch.equal(y, full))
+        lin_mc = PeerPrefillLinear(wq, ws, n, k, m, multicast=True)  # one multimem.st through the NVLink multicast mapping
+        same_mc, t_mc = None, None
+        if lin_mc.multicast:
+            lin_mc.out.zero_()
+            lin_mc.hdl.barrier()  # no rank stores into a buffer that its owner is still clearing
+            y_mc = lin_mc.forward(hi, lo, xs, m)
+            torch.cuda.synchronize()
+            same_mc = bool(torch.equal(y_mc, full))
         wl, wsl = wq[lin.a:lin.b].contiguous(), ws[lin.a:lin.b].contiguous()
 
         def local_linear(xx, a, b):
@@ -353,17 +361,24 @@ def measure_prefill_column_parallel(dev, world, rank, xn, torch, dist) -> dict:
         y2 = column_parallel_gather(x, local_linear, n)
         same_gather = bool(torch.equal(y2, full))
         t_peer = timeit(lambda: lin.forward(hi, lo, xs, m))
+        if lin_mc.multicast:
+            t_mc = timeit(lambda: lin_mc.forward(hi, lo, xs, m))
         t_gather = timeit(lambda: column_parallel_gather(x, local_linear, n))
         t_full = timeit(lambda: xn.linear_fp8(x, wq, ws, 0))
-        flags = torch.tensor([int(same_peer), int(same_gather)], device=dev)
+        flags = torch.tensor([int(same_peer), int(same_gather), int(same_mc is not False)], device=dev)
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
         out_bytes = 2 * m * (lin.b - lin.a) * (world - 1)
+        best = min(t_peer, t_mc) if t_mc is not None else t_peer
         rows.append({"name": name, "m": m, "n": n, "k": k, "identical_peer": bool(flags[0].item()),
-                     "identical_gather": bool(flags[1].item()), "ms_peer_store_epilogue": t_peer,
-                     "ms_nccl_all_gather": t_gather, "ms_one_gpu": t_full, "speedup_vs_one_gpu": t_full / t_peer,
-                     "tflops_all_gpus": 2.0 * m * n * k / (t_peer * 1e-3) / 1e12,
-                     "nvlink_bytes_out_per_rank": out_bytes, "nvlink_gb_per_s_out_per_rank": out_bytes / (t_peer * 1e-3) / 1e9})
-        del lin, wq, ws, x, hi, lo, full, y, y2
+                     "identical_gather": bool(flags[1].item()),
+                     "identical_multicast": bool(flags[2].item()) if t_mc is not None else None,
+                     "ms_peer_store_epilogue": t_peer, "ms_multicast_store_epilogue": t_mc,
+                     "ms_nccl_all_gather": t_gather, "ms_one_gpu": t_full, "speedup_vs_one_gpu": t_full / best,
+                     "tflops_all_gpus": 2.0 * m * n * k / (best * 1e-3) / 1e12,
+                     "nvlink_bytes_delivered_per_rank": out_bytes,
+                     "nvlink_gb_per_s_delivered_per_rank": out_bytes / (best * 1e-3) / 1e9,
+                     "nvlink_egress_bytes_per_rank": out_bytes if t_mc is None or t_peer <= t_mc else 2 * m * (lin.b - lin.a)})
+        del lin, lin_mc, wq, ws, x, hi, lo, full, y, y2
         torch.cuda.empty_cache()
     return {"world": world, "rows": rows, "scaling": "strong (one 4096-token prefill split over the ranks)",
             "timing": "CUDA events, max over ranks, 10 back-to-back calls; collective: peer stores / NCCL all-gather"}

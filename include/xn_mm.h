@@ -213,6 +213,14 @@ int xn_mm_linear_fp8_pieces_scatter(void *const *y_dsts, size_t num_dst, size_t 
                                     const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
                                     const uint8_t *wq, const float *w_scale, size_t m, size_t n, size_t k,
                                     void *stream);
+/* The same slice written through ONE address: y_multicast is an NVLink multicast (NVLS) mapping of the ranks'
+ * [m, ldy] buffers (cuMulticast* / a symmetric-memory allocation's multicast pointer); the epilogue issues
+ * multimem.st, NVSwitch replicates each 16-byte store into every GPU bound to the object, and the rank sends its
+ * slice once instead of once per peer.  n, col_offset and ldy must be multiples of 8.  Stores only: nothing is
+ * loaded through the multicast address.  The caller synchronises the ranks before the result is read. */
+int xn_mm_linear_fp8_pieces_multicast(void *y_multicast, size_t ldy, size_t col_offset, const uint8_t *x_hi,
+                                      const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
+                                      const float *w_scale, size_t m, size_t n, size_t k, void *stream);
 /* Convenience: split + linear.  workspace must hold xn_mm_linear_fp8_workspace_bytes(m,k). */
 size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k);
 int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,

@@ -51,6 +51,7 @@ SIGNATURES = {
     "xn_mm_split_rows_e4m3": (_i, [_p, _p, _p, _p, _i, _sz, _sz, _p]),
     "xn_mm_linear_fp8_pieces": (_i, [_p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "xn_mm_linear_fp8_pieces_scatter": (_i, [_p, _sz, _sz, _sz, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
+    "xn_mm_linear_fp8_pieces_multicast": (_i, [_p, _sz, _sz, _p, _p, _p, _p, _p, _sz, _sz, _sz, _p]),
     "xn_mm_linear_fp8_workspace_bytes": (_sz, [_sz, _sz]),
     "xn_mm_linear_fp8": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p, _sz, _p]),
     "xn_mm_conv1d_workspace_bytes": (_sz, [_i] + [_sz] * 9),

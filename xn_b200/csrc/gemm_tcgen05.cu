@@ -185,6 +185,7 @@ struct GemmArgs {
     const void *row_bias; // optional, not for fp8: added to every element of output row i (element type of y)
     WaitCtx wait;         // bound and status word of the kernel's mbarrier waits
     int group_m;          // m blocks per rasterisation group (see tile_coords)
+    int mc;               // y[0] is an NVLink multicast address: one multimem.st per 16 bytes reaches every GPU's copy
     int b_mn;             // 16-bit kinds: B is [K, N] with n contiguous (MN-major); its map is (n, k, batch), box 64 x BK
 };
 
@@ -257,7 +258,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs &args, uint32_t tme
                 for (int p = 0; p < args.ndst; ++p) {
                     uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
                                     (size_t)grow * args.ldy + args.col_offset + gcol;
-                    if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    if (args.mc) {
+                        // the switch replicates the store into every GPU bound to the multicast object (the host
+                        // checked that n is a multiple of 8 and the rows are 16-byte aligned)
+                        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                                     "f"(__uint_as_float(val.x)), "f"(__uint_as_float(val.y)), "f"(__uint_as_float(val.z)),
+                                     "f"(__uint_as_float(val.w))
+                                     : "memory");
+                    } else if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                         *reinterpret_cast<uint4 *>(dst) = val;
                     } else {
                         const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
@@ -1056,6 +1064,17 @@ int launch_linear_fp8_gemm_scatter(void *const *y_dsts, int ndst, size_t ldy, si
     GemmArgs a{};
     for (int p = 0; p < ndst; ++p) a.y[p] = y_dsts[p];
     a.ndst = ndst; a.col_offset = (int)col_offset; a.batch = 1; a.y_batch_stride = 0;
+    a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldy;
+    return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
+}
+
+// The same slice written once through an NVLink multicast address (NVSwitch replicates every store into all the
+// GPUs bound to it): the rank's egress is its slice once, not once per peer.
+int launch_linear_fp8_gemm_multicast(void *y_mc, size_t ldy, size_t col_offset, const uint8_t *x_hi, const uint8_t *x_lo,
+                                     const float *x_scale, const uint8_t *wq, const float *w_scale, size_t m, size_t n,
+                                     size_t k, cudaStream_t st) {
+    GemmArgs a{};
+    a.y[0] = y_mc; a.ndst = 1; a.mc = 1; a.col_offset = (int)col_offset; a.batch = 1; a.y_batch_stride = 0;
     a.x_scale = x_scale; a.w_scale = w_scale; a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldy;
     return x_lo ? launch_kind<0, 2>(x_hi, x_lo, wq, k, k, a, st) : launch_kind<0, 1>(x_hi, nullptr, wq, k, k, a, st);
 }

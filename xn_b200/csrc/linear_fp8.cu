@@ -15,6 +15,10 @@ int launch_linear_fp8_gemm_scatter(void *const *y_dsts, int ndst, size_t ldy, si
                                    const uint8_t *x_lo, const float *x_scale, const uint8_t *wq, const float *w_scale,
                                    size_t m, size_t n, size_t k, cudaStream_t st);
 
+int launch_linear_fp8_gemm_multicast(void *y_mc, size_t ldy, size_t col_offset, const uint8_t *x_hi, const uint8_t *x_lo,
+                                     const float *x_scale, const uint8_t *wq, const float *w_scale, size_t m, size_t n,
+                                     size_t k, cudaStream_t st);
+
 static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 }  // namespace xn
 
@@ -60,6 +64,24 @@ extern "C" int xn_mm_linear_fp8_pieces_scatter(void *const *y_dsts, size_t num_d
                "linear_fp8_scatter: weights and activation pieces must be 16-byte aligned");
     return launch_linear_fp8_gemm_scatter(y_dsts, (int)num_dst, ldy, col_offset, x_hi, x_lo, x_scale, wq, w_scale, m, n, k,
                                           (cudaStream_t)stream);
+}
+
+extern "C" int xn_mm_linear_fp8_pieces_multicast(void *y_multicast, size_t ldy, size_t col_offset, const uint8_t *x_hi,
+                                                 const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
+                                                 const float *w_scale, size_t m, size_t n, size_t k, void *stream) {
+    XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_multicast: k=%zu must be a positive multiple of 16", k);
+    XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull && ldy <= 0x7ffffff0ull, "linear_fp8_multicast: dimension too large");
+    XN_REQUIRE(col_offset + n <= ldy, "linear_fp8_multicast: columns [%zu, %zu) do not fit a row of %zu", col_offset,
+               col_offset + n, ldy);
+    XN_REQUIRE(n % 8 == 0 && col_offset % 8 == 0 && ldy % 8 == 0,
+               "linear_fp8_multicast: n=%zu, col_offset=%zu and ldy=%zu must be multiples of 8 (16-byte multicast stores)", n,
+               col_offset, ldy);
+    if (m == 0 || n == 0) return XN_OK;
+    XN_REQUIRE(y_multicast && x_hi && x_scale && wq && w_scale, "linear_fp8_multicast: null pointer");
+    XN_REQUIRE(aligned(y_multicast, 16) && aligned(wq, 16) && aligned(x_hi, 16) && (!x_lo || aligned(x_lo, 16)),
+               "linear_fp8_multicast: output, weights and activation pieces must be 16-byte aligned");
+    return launch_linear_fp8_gemm_multicast(y_multicast, ldy, col_offset, x_hi, x_lo, x_scale, wq, w_scale, m, n, k,
+                                            (cudaStream_t)stream);
 }
 
 extern "C" size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k) {

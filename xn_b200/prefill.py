@@ -6,8 +6,10 @@ describes: every rank holds the full activations x [M, K] and the rows [r*N/W, (
 
 Two assembly routes:
   "peer"   the GEMM epilogue stores each finished tile straight into every rank's [M, N] output
-           (symmetric memory, plain stores over NVLink; xn_mm_linear_fp8_pieces_scatter): transfer and
-           tensor-core work overlap tile by tile, no staging buffer, no re-layout pass;
+           (symmetric memory; xn_mm_linear_fp8_pieces_scatter): transfer and tensor-core work overlap tile
+           by tile, no staging buffer, no re-layout pass.  With an NVLink multicast mapping of the output
+           (NVSwitch) each 16-byte piece is ONE multimem.st that the switch replicates to every rank
+           (xn_mm_linear_fp8_pieces_multicast); otherwise one plain store per peer;
   "gather" local GEMM, then torch.distributed all_gather_into_tensor and a re-layout
            ([W, M, N/W] -> [M, N]); works with any backend (the CPU tests run it on gloo) and is the
            baseline the peer route is timed against.
@@ -72,7 +74,7 @@ def column_parallel_gather(x, local_linear, n: int, group=None, align: int = 16)
 class PeerPrefillLinear:
     """One fp8 linear, column-split, results assembled by epilogue stores into peer memory."""
 
-    def __init__(self, wq, ws, n: int, k: int, m_max: int, group=None):
+    def __init__(self, wq, ws, n: int, k: int, m_max: int, group=None, multicast: bool = True):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
@@ -84,12 +86,21 @@ class PeerPrefillLinear:
         self.hdl = symm.rendezvous(self.out, group=dist.group.WORLD if group is None else group)
         import ctypes as C
         self.ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.hdl.buffer_ptrs])
+        # NVLink multicast mapping of the same buffers, when the fabric offers one (NVSwitch): one store reaches
+        # every rank.  Usable when every rank's slice keeps the 16-byte store granularity.
+        self.mc_ptr = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        self.multicast = bool(self.mc_ptr) and multicast and n % 8 == 0 and self.a % 8 == 0 and (self.b - self.a) % 8 == 0
 
     def forward(self, hi, lo, xs, m: int):
         import torch
 
         from ._lib import check, lib
-        if self.b > self.a:
+        if self.b > self.a and self.multicast:
+            check(lib().xn_mm_linear_fp8_pieces_multicast(self.mc_ptr, self.n, self.a, hi.data_ptr(),
+                                                          lo.data_ptr() if lo is not None else None, xs.data_ptr(),
+                                                          self.wq.data_ptr(), self.ws.data_ptr(), m, self.b - self.a, self.k,
+                                                          torch.cuda.current_stream().cuda_stream))
+        elif self.b > self.a:
             check(lib().xn_mm_linear_fp8_pieces_scatter(self.ptrs, self.world, self.n, self.a, hi.data_ptr(),
                                                         lo.data_ptr() if lo is not None else None, xs.data_ptr(),
                                                         self.wq.data_ptr(), self.ws.data_ptr(), m, self.b - self.a, self.k,
