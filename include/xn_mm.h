@@ -285,6 +285,20 @@ int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, size_t q_ba
                                  size_t context, size_t head_dim, float scale, void *workspace, size_t workspace_bytes,
                                  void *stream);
 
+/* xn_mm_decode_attention_split followed by xn_mm_split_rows_e4m3 of its [batch, heads * 128] output, with the merge of
+ * the context slices and the e4m3 split of the row fused into one launch (the attention output is the activation
+ * of the output projection): identical results, one launch and one pass over the row less.  out_bf16 still
+ * receives the attention output. */
+int xn_mm_decode_attention_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *out_bf16, const void *q_bf16,
+                                      size_t q_batch_stride, const void *k_cache_bf16, const void *v_cache_bf16,
+                                      const float *mask_or_null, size_t batch, size_t heads, size_t context,
+                                      size_t head_dim, float scale, void *workspace, size_t workspace_bytes,
+                                      void *stream);
+/* xn_mm_kv_append for the key and the value cache in one launch (same index, same source layout). */
+int xn_mm_kv_append2(xn_dtype dtype, void *k_cache, void *v_cache, const void *k_src, const void *v_src,
+                     size_t src_batch_stride, const int64_t *index, size_t batch, size_t heads, size_t context,
+                     size_t head_dim, void *stream);
+
 /* Allocation-free form of xn_mm_linear_fp8.  It has no counterpart in the reference.  For hosts
  * that must not (or cannot) allocate device memory at call time -- a serving loop whose device
  * budget belongs to another allocator, a real-time audio callback that cannot afford a

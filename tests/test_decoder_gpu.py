@@ -237,3 +237,52 @@ def test_add_rms_norm_split_equals_the_two_separate_ops(xn, cuda, variant):
     assert torch.equal(s0, s1) and torch.equal(hi0, hi1) and torch.equal(xs0, xs1)
     if variant == 0:
         assert torch.equal(lo0, lo1)
+
+
+@pytest.mark.parametrize("B,H,ctx,variant", [(4, 32, 3000, 0), (2, 8, 700, 1), (40, 4, 96, 0)])
+def test_attention_with_fused_e4m3_split_equals_the_two_calls(xn, cuda, B, H, ctx, variant):
+    """xn_mm_decode_attention_split_e4m3 == xn_mm_decode_attention_split followed by xn_mm_split_rows_e4m3, bit for
+    bit (attention output, pieces, row scales) -- sliced contexts (fused merge + split kernel) and a context too
+    short to slice (fallback to the two kernels)."""
+    L = xn.lib()
+    hd = 128
+    g = torch.Generator(device=cuda).manual_seed(B + ctx)
+    qkv = torch.randn(B, 3 * H * hd, generator=g, device=cuda).bfloat16()
+    k = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    v = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    ws_bytes = int(L.xn_mm_decode_attention_workspace_bytes(B, H, ctx))
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=cuda)
+    u8 = dict(dtype=torch.uint8, device=cuda)
+    out0 = torch.empty(B, H * hd, dtype=torch.bfloat16, device=cuda)
+    hi0, lo0, xs0 = torch.empty(B, H * hd, **u8), torch.empty(B, H * hd, **u8), torch.empty(B, device=cuda)
+    sc = 1.0 / math.sqrt(hd)
+    xn._lib.check(L.xn_mm_decode_attention_split(out0.data_ptr(), qkv.data_ptr(), 3 * H * hd, k.data_ptr(), v.data_ptr(), None,
+                                                 B, H, ctx, hd, sc, ws.data_ptr(), ws_bytes, None))
+    xn._lib.check(L.xn_mm_split_rows_e4m3(hi0.data_ptr(), lo0.data_ptr() if variant == 0 else None, xs0.data_ptr(),
+                                          out0.data_ptr(), 2, B, H * hd, None))
+    out1 = torch.empty_like(out0)
+    hi1, lo1, xs1 = torch.empty(B, H * hd, **u8), torch.empty(B, H * hd, **u8), torch.empty(B, device=cuda)
+    xn._lib.check(L.xn_mm_decode_attention_split_e4m3(hi1.data_ptr(), lo1.data_ptr() if variant == 0 else None, xs1.data_ptr(),
+                                                      out1.data_ptr(), qkv.data_ptr(), 3 * H * hd, k.data_ptr(), v.data_ptr(),
+                                                      None, B, H, ctx, hd, sc, ws.data_ptr(), ws_bytes, None))
+    torch.cuda.synchronize()
+    assert torch.equal(out0, out1) and torch.equal(hi0, hi1) and torch.equal(xs0, xs1)
+    if variant == 0:
+        assert torch.equal(lo0, lo1)
+
+
+def test_kv_append2_equals_two_appends(xn, cuda):
+    g = torch.Generator(device=cuda).manual_seed(5)
+    B, H, ctx, hd = 3, 4, 10, 128
+    kc = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    vc = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    k2, v2 = kc.clone(), vc.clone()
+    qkv = torch.randn(B, 3 * H * hd, generator=g, device=cuda).bfloat16()
+    idx = torch.tensor([9, 0, 4], dtype=torch.int64, device=cuda)
+    L = xn.lib()
+    kn, vn = qkv.data_ptr() + 2 * H * hd, qkv.data_ptr() + 4 * H * hd
+    xn._lib.check(L.xn_mm_kv_append(2, kc.data_ptr(), kn, 3 * H * hd, idx.data_ptr(), B, H, ctx, hd, None))
+    xn._lib.check(L.xn_mm_kv_append(2, vc.data_ptr(), vn, 3 * H * hd, idx.data_ptr(), B, H, ctx, hd, None))
+    xn._lib.check(L.xn_mm_kv_append2(2, k2.data_ptr(), v2.data_ptr(), kn, vn, 3 * H * hd, idx.data_ptr(), B, H, ctx, hd, None))
+    torch.cuda.synchronize()
+    assert torch.equal(kc, k2) and torch.equal(vc, v2)

@@ -107,6 +107,174 @@ rms_norm_kernel(T *__restrict__ dst, uint8_t *__restrict__ hi, uint8_t *__restri
     }
 }
 
+// 16-bit fast paths of the two kernels above: 128-bit loads, the row held in registers between the passes (one
+// read of the inputs, no recomputation), 8-byte piece stores.  Element arithmetic and roundings are those of the
+// scalar kernels; only the order of the f32 sum of squares differs.
+constexpr int NTV = 512;
+
+template <typename T> __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
+    const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = to_f32(e[j]);
+}
+template <typename T> __device__ __forceinline__ uint4 pack8(const T (&y)[8]) {
+    uint4 r;
+    T *e = reinterpret_cast<T *>(&r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = y[j];
+    return r;
+}
+// the e4m3 pieces of eight values already divided by the row scale
+__device__ __forceinline__ void store_pieces8(uint8_t *hi, uint8_t *lo, size_t off, const float (&yv)[8]) {
+    uint8_t h[8], l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        h[j] = (uint8_t)__nv_cvt_float_to_fp8(yv[j], __NV_SATFINITE, __NV_E4M3);
+        l[j] = (uint8_t)__nv_cvt_float_to_fp8(yv[j] - e4m3_f32(h[j]), __NV_SATFINITE, __NV_E4M3);
+    }
+    *reinterpret_cast<uint2 *>(hi + off) = *reinterpret_cast<const uint2 *>(h);
+    if (lo) *reinterpret_cast<uint2 *>(lo + off) = *reinterpret_cast<const uint2 *>(l);
+}
+
+template <typename T, int VPT, bool SPLIT>
+__global__ void __launch_bounds__(NTV)
+rms_norm_vec_kernel(T *__restrict__ dst, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo, float *__restrict__ scale,
+                    const T *__restrict__ src, const T *__restrict__ alpha, int cols, float eps, const T *__restrict__ res,
+                    T *sum_out) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x, base = row * (size_t)cols;
+    const int nvec = cols / 8;
+    uint4 v[VPT];
+    float s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = i * NTV + threadIdx.x;
+        if (idx >= nvec) { v[i] = make_uint4(0, 0, 0, 0); continue; }
+        v[i] = __ldg(reinterpret_cast<const uint4 *>(src + base) + idx);
+        float f[8];
+        unpack8<T>(v[i], f);
+        if (res) {
+            float r[8];
+            unpack8<T>(__ldg(reinterpret_cast<const uint4 *>(res + base) + idx), r);
+            T sum[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { sum[j] = from_f32<T>(f[j] + r[j]); f[j] = to_f32(sum[j]); }
+            v[i] = pack8<T>(sum);
+            reinterpret_cast<uint4 *>(sum_out + base)[idx] = v[i];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s2 += f[j] * f[j];
+    }
+    s2 = block_sum(s2, red);
+    const float denom = sqrtf(s2 / (float)cols + eps);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = i * NTV + threadIdx.x;
+        if (idx >= nvec) continue;
+        float f[8], al[8];
+        unpack8<T>(v[i], f);
+        unpack8<T>(__ldg(reinterpret_cast<const uint4 *>(alpha) + idx), al);
+        T y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            y[j] = from_f32<T>(f[j] / denom * al[j]);
+            if (SPLIT) amax = fmaxf(amax, fabsf(to_f32(y[j])));
+        }
+        v[i] = pack8<T>(y);
+        if (dst) reinterpret_cast<uint4 *>(dst + base)[idx] = v[i];
+    }
+    if (SPLIT) {
+        amax = block_max2(amax, red);
+        const float sc = pow2_scale(amax), inv = 1.0f / sc;
+        if (threadIdx.x == 0) scale[row] = sc;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = i * NTV + threadIdx.x;
+            if (idx >= nvec) continue;
+            float f[8];
+            unpack8<T>(v[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] *= inv;
+            store_pieces8(hi, lo, base + (size_t)idx * 8, f);
+        }
+    }
+}
+
+template <typename T, int VPT, bool SPLIT>
+__global__ void __launch_bounds__(NTV)
+silu_mul_vec_kernel(T *__restrict__ dst, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo, float *__restrict__ scale,
+                    const T *__restrict__ src, int hidden) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x, obase = row * (size_t)hidden;
+    const uint4 *a = reinterpret_cast<const uint4 *>(src + row * 2 * (size_t)hidden);
+    const uint4 *b = reinterpret_cast<const uint4 *>(src + row * 2 * (size_t)hidden + hidden);
+    const int nvec = hidden / 8;
+    uint4 v[VPT];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = i * NTV + threadIdx.x;
+        if (idx >= nvec) { v[i] = make_uint4(0, 0, 0, 0); continue; }
+        float av[8], bv[8];
+        unpack8<T>(__ldg(a + idx), av);
+        unpack8<T>(__ldg(b + idx), bv);
+        T y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float sl = to_f32(from_f32<T>(av[j] / (1.0f + expf(-av[j]))));
+            y[j] = from_f32<T>(sl * bv[j]);
+            if (SPLIT) amax = fmaxf(amax, fabsf(to_f32(y[j])));
+        }
+        v[i] = pack8<T>(y);
+        if (dst) reinterpret_cast<uint4 *>(dst + obase)[idx] = v[i];
+    }
+    if (SPLIT) {
+        amax = block_max2(amax, red);
+        const float sc = pow2_scale(amax), inv = 1.0f / sc;
+        if (threadIdx.x == 0) scale[row] = sc;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = i * NTV + threadIdx.x;
+            if (idx >= nvec) continue;
+            float f[8];
+            unpack8<T>(v[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] *= inv;
+            store_pieces8(hi, lo, obase + (size_t)idx * 8, f);
+        }
+    }
+}
+
+// Picks the vector kernels for 16-bit rows that fit (8-element vectors, 16-byte aligned rows); returns false when the
+// scalar kernel has to run.
+template <typename T, bool SPLIT>
+bool launch_rms_norm_vec(T *dst, uint8_t *hi, uint8_t *lo, float *scale, const T *src, const T *alpha, size_t rows, size_t cols,
+                         float eps, const T *res, T *sum_out, cudaStream_t st) {
+    if (sizeof(T) != 2 || cols % 8 != 0 || cols > (size_t)NTV * 8 * 4 || !aligned(src, 16) || !aligned(alpha, 16) ||
+        (dst && !aligned(dst, 16)) || (res && (!aligned(res, 16) || !aligned(sum_out, 16))) || (hi && !aligned(hi, 8)) ||
+        (lo && !aligned(lo, 8)))
+        return false;
+    if (cols <= (size_t)NTV * 8)
+        rms_norm_vec_kernel<T, 1, SPLIT><<<(unsigned)rows, NTV, 0, st>>>(dst, hi, lo, scale, src, alpha, (int)cols, eps, res, sum_out);
+    else
+        rms_norm_vec_kernel<T, 4, SPLIT><<<(unsigned)rows, NTV, 0, st>>>(dst, hi, lo, scale, src, alpha, (int)cols, eps, res, sum_out);
+    return true;
+}
+template <typename T, bool SPLIT>
+bool launch_silu_mul_vec(T *dst, uint8_t *hi, uint8_t *lo, float *scale, const T *src, size_t rows, size_t hidden, cudaStream_t st) {
+    if (sizeof(T) != 2 || hidden % 8 != 0 || hidden > (size_t)NTV * 8 * 8 || !aligned(src, 16) || (dst && !aligned(dst, 16)) ||
+        (hi && !aligned(hi, 8)) || (lo && !aligned(lo, 8)))
+        return false;
+    if (hidden <= (size_t)NTV * 8)
+        silu_mul_vec_kernel<T, 1, SPLIT><<<(unsigned)rows, NTV, 0, st>>>(dst, hi, lo, scale, src, (int)hidden);
+    else if (hidden <= (size_t)NTV * 8 * 3)
+        silu_mul_vec_kernel<T, 3, SPLIT><<<(unsigned)rows, NTV, 0, st>>>(dst, hi, lo, scale, src, (int)hidden);
+    else
+        silu_mul_vec_kernel<T, 8, SPLIT><<<(unsigned)rows, NTV, 0, st>>>(dst, hi, lo, scale, src, (int)hidden);
+    return true;
+}
+
 // One warp per row: max-subtract, exp rounded to T, f32 sum of the rounded values, divide.
 template <typename T>
 __global__ void softmax_kernel(T *__restrict__ dst, const T *__restrict__ src, size_t rows, size_t cols) {
@@ -210,21 +378,31 @@ decode_attention_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__
     const float *mrow = mask ? mask + b * context : nullptr;
     float m_run = -INFINITY, l_run = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     constexpr int U = 4;
+    // Software pipeline: the loads of the next 8 * U rows are in flight while this group's scores and products are
+    // computed, so the memory system always has a full set of requests from every warp (without it a warp's
+    // requests drain during its shuffle / exp chain and the kernel sat at 83 % of the copy bandwidth).
+    uint4 kn[U], vn[U];
+    auto fetch = [&](size_t base) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const size_t r = base + group + 8 * u;
+            if (r < row_hi) {
+                kn[u] = ldg_stream(kb + r * HD + l16 * 8);
+                vn[u] = ldg_stream(vb + r * HD + l16 * 8);
+            } else {
+                kn[u] = make_uint4(0, 0, 0, 0);
+                vn[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    fetch(row_lo);
     for (size_t base = row_lo; base < row_hi; base += 8 * U) {  // uniform trip count across the CTA
         const size_t r0 = base + group;
         uint4 kr[U], vr[U];
         float s[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const size_t r = r0 + 8 * u;
-            if (r < row_hi) {
-                kr[u] = ldg_stream(kb + r * HD + l16 * 8);
-                vr[u] = ldg_stream(vb + r * HD + l16 * 8);
-            } else {
-                kr[u] = make_uint4(0, 0, 0, 0);
-                vr[u] = make_uint4(0, 0, 0, 0);
-            }
-        }
+        for (int u = 0; u < U; ++u) { kr[u] = kn[u]; vr[u] = vn[u]; }
+        if (base + 8 * U < row_hi) fetch(base + 8 * U);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&kr[u]);
@@ -302,6 +480,66 @@ decode_attention_combine_kernel(__nv_bfloat16 *__restrict__ out, const float *__
     out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
 }
 
+constexpr int AHD = 128;  // head dimension of the attention kernels
+// The same merge for a whole stream row (all heads), followed by the e4m3 split of that row: the attention output is
+// the activation of the output projection, whose fp8 pieces need the row's maximum over all heads.  One CTA of
+// 1024 threads per stream; a thread owns 4 consecutive dimensions of up to two heads (heads <= 64).
+__global__ void __launch_bounds__(1024)
+decode_attention_combine_split_kernel(__nv_bfloat16 *__restrict__ out, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo,
+                                      float *__restrict__ xs, const float *__restrict__ partial, int splits, int heads) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float red[32];
+    const size_t b = blockIdx.x;
+    const int items = heads * (AHD / 4);
+    float val[2][4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int it = i * 1024 + (int)threadIdx.x;
+        if (it >= items) continue;
+        const int h = it / (AHD / 4), d0 = (it % (AHD / 4)) * 4;
+        const float *p = partial + (b * heads + h) * (size_t)splits * (AHD + 2);
+        float mx = -INFINITY;
+        for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p[(size_t)s * (AHD + 2)]);
+        float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int s = 0; s < splits; ++s) {
+            const float m = p[(size_t)s * (AHD + 2)];
+            const float w = m == -INFINITY ? 0.0f : __expf(m - mx);
+            l += w * p[(size_t)s * (AHD + 2) + 1];
+            // a slice's record is 130 floats: its output vector is 8-byte, not 16-byte, aligned
+            const float2 o01 = *reinterpret_cast<const float2 *>(p + (size_t)s * (AHD + 2) + 2 + d0);
+            const float2 o23 = *reinterpret_cast<const float2 *>(p + (size_t)s * (AHD + 2) + 4 + d0);
+            o[0] += w * o01.x; o[1] += w * o01.y; o[2] += w * o23.x; o[3] += w * o23.y;
+        }
+        __nv_bfloat16 y[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            y[j] = __float2bfloat16_rn(o[j] / l);
+            val[i][j] = __bfloat162float(y[j]);
+            amax = fmaxf(amax, fabsf(val[i][j]));
+        }
+        *reinterpret_cast<uint2 *>(out + (b * heads + h) * AHD + d0) = *reinterpret_cast<const uint2 *>(y);
+    }
+    amax = block_max2(amax, red);
+    const float sc = pow2_scale(amax), inv = 1.0f / sc;
+    if (threadIdx.x == 0) xs[b] = sc;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int it = i * 1024 + (int)threadIdx.x;
+        if (it >= items) continue;
+        uint8_t hh[4], ll[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float yv = val[i][j] * inv;
+            hh[j] = (uint8_t)__nv_cvt_float_to_fp8(yv, __NV_SATFINITE, __NV_E4M3);
+            ll[j] = (uint8_t)__nv_cvt_float_to_fp8(yv - e4m3_f32(hh[j]), __NV_SATFINITE, __NV_E4M3);
+        }
+        const size_t off = b * (size_t)heads * AHD + (size_t)it * 4;
+        *reinterpret_cast<uint32_t *>(hi + off) = *reinterpret_cast<const uint32_t *>(hh);
+        if (lo) *reinterpret_cast<uint32_t *>(lo + off) = *reinterpret_cast<const uint32_t *>(ll);
+    }
+}
+
 }  // namespace
 }  // namespace xn
 
@@ -313,8 +551,11 @@ extern "C" int xn_mm_rms_norm(xn_dtype dtype, void *dst, const void *src, const 
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(dst && src && alpha, "rms_norm: null pointer");
     XN_REQUIRE(rows <= 0x7fffffffull, "rms_norm: too many rows");
-    XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, false><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
-                                    (T *)dst, nullptr, nullptr, nullptr, (const T *)src, (const T *)alpha, cols, eps));
+    XN_DISPATCH_DTYPE(dtype, T,
+        if (!launch_rms_norm_vec<T, false>((T *)dst, nullptr, nullptr, nullptr, (const T *)src, (const T *)alpha, rows, cols, eps,
+                                           nullptr, nullptr, (cudaStream_t)stream))
+            rms_norm_kernel<T, false><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                (T *)dst, nullptr, nullptr, nullptr, (const T *)src, (const T *)alpha, cols, eps));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -326,8 +567,11 @@ extern "C" int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && src && alpha, "rms_norm_split: null pointer");
     XN_REQUIRE(rows <= 0x7fffffffull, "rms_norm_split: too many rows");
-    XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
-                                    (T *)dst_or_null, x_hi, x_lo, x_scale, (const T *)src, (const T *)alpha, cols, eps));
+    XN_DISPATCH_DTYPE(dtype, T,
+        if (!launch_rms_norm_vec<T, true>((T *)dst_or_null, x_hi, x_lo, x_scale, (const T *)src, (const T *)alpha, rows, cols, eps,
+                                          nullptr, nullptr, (cudaStream_t)stream))
+            rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                (T *)dst_or_null, x_hi, x_lo, x_scale, (const T *)src, (const T *)alpha, cols, eps));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -339,9 +583,11 @@ extern "C" int xn_mm_add_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && sum_out && a && b && alpha, "add_rms_norm_split: null pointer");
     XN_REQUIRE(rows <= 0x7fffffffull, "add_rms_norm_split: too many rows");
-    XN_DISPATCH_DTYPE(dtype, T, rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
-                                    (T *)nullptr, x_hi, x_lo, x_scale, (const T *)a, (const T *)alpha, cols, eps,
-                                    (const T *)b, (T *)sum_out));
+    XN_DISPATCH_DTYPE(dtype, T,
+        if (!launch_rms_norm_vec<T, true>((T *)nullptr, x_hi, x_lo, x_scale, (const T *)a, (const T *)alpha, rows, cols, eps,
+                                          (const T *)b, (T *)sum_out, (cudaStream_t)stream))
+            rms_norm_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                (T *)nullptr, x_hi, x_lo, x_scale, (const T *)a, (const T *)alpha, cols, eps, (const T *)b, (T *)sum_out));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -363,8 +609,10 @@ extern "C" int xn_mm_silu_mul(xn_dtype dtype, void *dst, const void *src, size_t
     if (rows == 0 || hidden == 0) return XN_OK;
     XN_REQUIRE(dst && src, "silu_mul: null pointer");
     XN_REQUIRE(rows <= 0x7fffffffull, "silu_mul: too many rows");
-    XN_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T, false><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
-                                    (T *)dst, nullptr, nullptr, nullptr, (const T *)src, hidden));
+    XN_DISPATCH_DTYPE(dtype, T,
+        if (!launch_silu_mul_vec<T, false>((T *)dst, nullptr, nullptr, nullptr, (const T *)src, rows, hidden, (cudaStream_t)stream))
+            silu_mul_kernel<T, false><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                (T *)dst, nullptr, nullptr, nullptr, (const T *)src, hidden));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -375,8 +623,10 @@ extern "C" int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_
     if (rows == 0 || hidden == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && src, "silu_mul_split: null pointer");
     XN_REQUIRE(rows <= 0x7fffffffull, "silu_mul_split: too many rows");
-    XN_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
-                                    (T *)nullptr, x_hi, x_lo, x_scale, (const T *)src, hidden));
+    XN_DISPATCH_DTYPE(dtype, T,
+        if (!launch_silu_mul_vec<T, true>((T *)nullptr, x_hi, x_lo, x_scale, (const T *)src, rows, hidden, (cudaStream_t)stream))
+            silu_mul_kernel<T, true><<<(unsigned)rows, NT, 0, (cudaStream_t)stream>>>(
+                (T *)nullptr, x_hi, x_lo, x_scale, (const T *)src, hidden));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }
@@ -396,6 +646,21 @@ extern "C" int xn_mm_add(xn_dtype dtype, void *dst, const void *a, const void *b
 // dst[r][c] = src[r][c] + bias[c]: the broadcast_add that follows Linear::forward's matmul
 // (xn-core/src/nn/linear.rs:61-64); the sum is formed in f32 and rounded once to the element type, as the
 // reference's binary Add does for f16 / bf16.  dst may alias src.
+// Both caches in one launch: blockIdx.y = 0 appends to the key cache, 1 to the value cache.
+template <typename T>
+__global__ void kv_append2_kernel(T *__restrict__ k_cache, T *__restrict__ v_cache, const T *__restrict__ k_src,
+                                  const T *__restrict__ v_src, const int64_t *__restrict__ idx, size_t heads, size_t context,
+                                  size_t hd, size_t src_batch_stride, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    T *cache = blockIdx.y ? v_cache : k_cache;
+    const T *src = blockIdx.y ? v_src : k_src;
+    const size_t d = i % hd, h = (i / hd) % heads, b = i / (hd * heads);
+    const int64_t p = idx[b];
+    if (p < 0 || (size_t)p >= context) return;  // out-of-range index: nothing is written
+    cache[((b * heads + h) * context + (size_t)p) * hd + d] = src[b * src_batch_stride + h * hd + d];
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) add_bias_kernel(T *dst, const T *src, const T *__restrict__ bias, size_t cols, size_t len) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < len; i += (size_t)gridDim.x * blockDim.x)
@@ -432,19 +697,23 @@ extern "C" int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, siz
 }
 
 namespace {
-// Slices of the context per (stream, head): enough CTAs to keep every SM busy with several of them
-// (one slice already does that from about 24 streams x 32 heads on), each slice at least 256 rows.
+// Slices of the context per (stream, head).  The kernel keeps two sets of loads per warp in flight (96 registers:
+// five CTAs per SM), so 32 streams x 32 heads as one slice each would be 1024 CTAs on 740 slots -- a full wave and
+// a 38 % one.  The context is therefore cut until there are about eight CTAs per slot (the hardware hands the next
+// slice to whichever slot frees up first, so the tail is a fraction of one short slice), each slice at least 128
+// rows; the log-sum-exp combine of the slices moves a few MB.
 int attention_splits(size_t batch, size_t heads, size_t context) {
-    const size_t want = (size_t)sm_count() * 6;
-    size_t s = (want + batch * heads - 1) / (batch * heads);
-    if (s > context / 256) s = context / 256;
-    if (s > 16) s = 16;
+    const size_t slots = (size_t)sm_count() * 5, bh = batch * heads;
+    size_t s = (slots * 8 + bh - 1) / bh;
+    if (s > context / 128) s = context / 128;
+    if (s > 32) s = 32;
     return s < 1 ? 1 : (int)s;
 }
 
 int decode_attention_impl(void *out_bf16, const void *q_bf16, size_t q_batch_stride, const void *k_cache_bf16,
                           const void *v_cache_bf16, const float *mask_or_null, size_t batch, size_t heads, size_t context,
-                          size_t head_dim, float scale, void *workspace, size_t workspace_bytes, bool use_ws, void *stream) {
+                          size_t head_dim, float scale, void *workspace, size_t workspace_bytes, bool use_ws, void *stream,
+                          uint8_t *x_hi = nullptr, uint8_t *x_lo = nullptr, float *x_scale = nullptr) {
     XN_REQUIRE(head_dim == 128, "decode_attention: head_dim %zu is not supported (128 only)", head_dim);
     if (batch == 0 || heads == 0) return XN_OK;
     XN_REQUIRE(context > 0, "decode_attention: empty context");
@@ -482,9 +751,17 @@ int decode_attention_impl(void *out_bf16, const void *q_bf16, size_t q_batch_str
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        if (x_hi && heads <= 64) {  // merge + e4m3 split of the whole row in one launch
+            cfg.gridDim = dim3((unsigned)batch);
+            cfg.blockDim = dim3(1024);
+            XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, xn::decode_attention_combine_split_kernel, (__nv_bfloat16 *)out_bf16, x_hi, x_lo,
+                                             x_scale, (const float *)workspace, splits, (int)heads));
+            return XN_OK;
+        }
         XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_combine_kernel, (__nv_bfloat16 *)out_bf16,
                                          (const float *)workspace, splits));
     }
+    if (x_hi) return xn_mm_split_rows_e4m3(x_hi, x_lo, x_scale, out_bf16, XN_BF16, batch, heads * head_dim, stream);
     return XN_OK;
 }
 }  // namespace
@@ -501,6 +778,33 @@ extern "C" int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, 
                                             void *workspace, size_t workspace_bytes, void *stream) {
     return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
                                  context, head_dim, scale, workspace, workspace_bytes, true, stream);
+}
+
+extern "C" int xn_mm_decode_attention_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *out_bf16,
+                                                 const void *q_bf16, size_t q_batch_stride, const void *k_cache_bf16,
+                                                 const void *v_cache_bf16, const float *mask_or_null, size_t batch,
+                                                 size_t heads, size_t context, size_t head_dim, float scale, void *workspace,
+                                                 size_t workspace_bytes, void *stream) {
+    XN_REQUIRE(x_hi && x_scale, "decode_attention_split_e4m3: null pointer");
+    XN_REQUIRE(aligned(x_hi, 4) && (!x_lo || aligned(x_lo, 4)), "decode_attention_split_e4m3: pieces must be 4-byte aligned");
+    return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
+                                 context, head_dim, scale, workspace, workspace_bytes, true, stream, x_hi, x_lo, x_scale);
+}
+
+extern "C" int xn_mm_kv_append2(xn_dtype dtype, void *k_cache, void *v_cache, const void *k_src, const void *v_src,
+                                size_t src_batch_stride, const int64_t *index, size_t batch, size_t heads, size_t context,
+                                size_t head_dim, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "kv_append2: unknown dtype %d", (int)dtype);
+    const size_t total = batch * heads * head_dim;
+    if (total == 0) return XN_OK;
+    XN_REQUIRE(k_cache && v_cache && k_src && v_src && index, "kv_append2: null pointer");
+    const size_t blocks = (total + 255) / 256;
+    XN_REQUIRE(blocks <= 0x7fffffffull, "kv_append2: too many elements");
+    XN_DISPATCH_DTYPE(dtype, T, kv_append2_kernel<T><<<dim3((unsigned)blocks, 2), 256, 0, (cudaStream_t)stream>>>(
+                                    (T *)k_cache, (T *)v_cache, (const T *)k_src, (const T *)v_src, index, heads, context, head_dim,
+                                    src_batch_stride, total));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
 }
 
 extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t q_batch_stride,

@@ -93,14 +93,15 @@ class DecoderStack:
                                                   lay["norm1"].data_ptr(), BF16, B, d, self.eps, s))
             self._linear(self.qkv, lay["in_proj"], B, 3 * d, d)
             q, kn, vn = self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * d, self.qkv.data_ptr() + 4 * d
-            check(L.xn_mm_kv_append(BF16, lay["k"].data_ptr(), kn, 3 * d, self.pos.data_ptr(), B, H, ctx, 128, s))
-            check(L.xn_mm_kv_append(BF16, lay["v"].data_ptr(), vn, 3 * d, self.pos.data_ptr(), B, H, ctx, 128, s))
-            check(L.xn_mm_decode_attention_split(self.attn.data_ptr(), q, 3 * d, lay["k"].data_ptr(), lay["v"].data_ptr(),
-                                                 self.mask.data_ptr() if self.mask is not None else None, B, H, ctx, 128,
-                                                 1.0 / math.sqrt(128.0), self.attn_ws.data_ptr() if self.attn_ws is not None else None,
-                                                 self.attn_ws_bytes, s))
-            check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn.data_ptr(), BF16,
-                                          B, d, s))
+            check(L.xn_mm_kv_append2(BF16, lay["k"].data_ptr(), lay["v"].data_ptr(), kn, vn, 3 * d, self.pos.data_ptr(), B, H,
+                                     ctx, 128, s))
+            # attention over the cache; the merge of the context slices also writes the e4m3 pieces of the output row
+            check(L.xn_mm_decode_attention_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn.data_ptr(),
+                                                      q, 3 * d, lay["k"].data_ptr(), lay["v"].data_ptr(),
+                                                      self.mask.data_ptr() if self.mask is not None else None, B, H, ctx, 128,
+                                                      1.0 / math.sqrt(128.0),
+                                                      self.attn_ws.data_ptr() if self.attn_ws is not None else None,
+                                                      self.attn_ws_bytes, s))
             self._linear(self.proj, lay["out_proj"], B, d, d)
             check(L.xn_mm_add_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.x_mid.data_ptr(),
                                                   cur.data_ptr(), self.proj.data_ptr(), lay["norm2"].data_ptr(), BF16, B, d,
@@ -125,6 +126,7 @@ class DecoderStack:
         return {"weights": w, "kv": kv, "total": w + kv}
 
     def launches_per_step(self) -> int:
-        # per layer: in_proj, 2 kv appends, attention (+ its combine when the context is split), split, out_proj,
-        # add+norm, linear_in, silu*mul, linear_out, add+norm (plain add after the last layer); one norm up front
-        return self.L * (11 + (1 if self.attn_ws_bytes else 0)) + 1
+        # per layer: in_proj, kv append (both caches), attention, merge of the context slices + e4m3 split (two launches
+        # when the context is not sliced), out_proj, add+norm, linear_in, silu*mul, linear_out, add+norm (plain add after
+        # the last layer); one norm up front
+        return self.L * 10 + 1
