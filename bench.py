@@ -23,7 +23,8 @@ Further keys of the line (each measured in this run, CUDA events, L2 flushed bet
   f32_linear               x [16,4096] * W [11264,4096]^T in f32 on the GPU, and the host-core baseline
   decode_step              the 32-layer decoder step, 32 streams per GPU
   prefill_column_parallel  (N > 1) the same linears with the weight rows split over the ranks and the
-                           outputs assembled on every rank: peer-store epilogue and NCCL all-gather routes
+                           outputs assembled on every rank: peer-store epilogue, NVLink multicast and NCCL routes
+  prefill_stack            a 4096-token prefill of one stream through the 32-layer stack, weights split over the ranks
 """
 from __future__ import annotations
 
@@ -384,6 +385,46 @@ def measure_prefill_column_parallel(dev, world, rank, xn, torch, dist) -> dict:
             "timing": "CUDA events, max over ranks, 10 back-to-back calls; collective: peer stores / NCCL all-gather"}
 
 
+def measure_prefill_stack(args, dev, world, rank, timed, torch, dist) -> dict:
+    """The prefill half of the decoder configuration: 4096 tokens of one stream through the 32-layer stack with every
+    weight split by output channel over the ranks (xn_b200.prefill.PrefillStack): local attention on the rank's heads,
+    four exchanges per layer (attention output, out_proj, gated FFN activations, linear_out) written into every
+    rank's buffers by store epilogues / an all-gather kernel over NVLink.  Strong scaling: the work is fixed."""
+    from xn_b200.prefill import PrefillStack
+    T, L = 4096, 32
+    identical = None
+    if world > 1:  # two layers of the split stack against the same two layers on one rank, bit for bit
+        g = torch.Generator(device=dev).manual_seed(11)
+        xs = torch.randn(T, 4096, generator=g, device=dev).bfloat16()
+        a = PrefillStack(2, 4096, 32, 11264, T, dev, seed=4).forward(xs).clone()
+        b = PrefillStack(2, 4096, 32, 11264, T, dev, seed=4, single=True).forward(xs)
+        torch.cuda.synchronize()
+        flag = torch.tensor([int(torch.equal(a, b))], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        identical = bool(flag.item())
+        del a, b
+        torch.cuda.empty_cache()
+    try:
+        st = PrefillStack(L, 4096, 32, 11264, T, dev, seed=4)
+    except torch.cuda.OutOfMemoryError:
+        return {"unavailable": "not enough free device memory for the prefill stack"}
+    g = torch.Generator(device=dev).manual_seed(12)
+    x = torch.randn(T, 4096, generator=g, device=dev).bfloat16()
+    st.forward(x)
+    torch.cuda.synchronize()
+    steps = 3
+    ms = timed(lambda: st.forward(x), steps) / steps
+    out = {"tokens": T, "layers": L, "ms": ms, "tokens_per_s": T / (ms * 1e-3), "tflops_all_gpus": st.flops() / (ms * 1e-3) / 1e12,
+           "world": world, "scaling": "strong", "identical_to_one_gpu_two_layers": identical,
+           "nvlink_bytes_out_per_rank": st.exchanged_bytes_per_rank(),
+           "route": "multimem.st through an NVLink multicast mapping" if st.proj_full.mc_ptr else
+                    ("plain stores into peer buffers" if world > 1 else "one rank: no exchange"),
+           "variant": "W8A16", "attention": "causal, per head: batched tcgen05 q.k^T, one-pass scale/mask/softmax, batched p.v"}
+    del st
+    torch.cuda.empty_cache()
+    return out
+
+
 def measure_decode(args, dev, world, rank, timed):
     """Decoder-stack configuration: 32 layers, d_model 4096, 32 heads x 128, gated SiLU FFN hidden 11264,
     fp8-e4m3 weights (W8A16 form), 32 independent streams per GPU each with a 3000-token bf16 KV cache.
@@ -579,6 +620,14 @@ def main() -> None:
             prefill_cp = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.empty_cache()
 
+    prefill_stack = None
+    if not args.no_extras and not args.no_decode:
+        try:
+            prefill_stack = measure_prefill_stack(args, dev, world, rank, timed, torch, dist)
+        except Exception as e:  # noqa: BLE001
+            prefill_stack = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+
     decode = None
     if not args.no_decode:
         del lins_keep
@@ -620,6 +669,7 @@ def main() -> None:
             "fp8_prefill_gemm": fp8_prefill,
             "f32_linear": f32_linear,
             "prefill_column_parallel": prefill_cp,
+            "prefill_stack": prefill_stack,
             "decode_step": decode,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

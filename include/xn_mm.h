@@ -251,6 +251,23 @@ int xn_mm_add_bias(xn_dtype dtype, void *dst, const void *src, const void *bias,
 int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_batch_stride, const int64_t *index,
                     size_t batch, size_t heads, size_t context, size_t head_dim, void *stream);
 
+/* Causal attention probabilities for a block of t_rows query rows per batch entry against `context` keys, the last
+ * t_rows of which are the block's own: dst[b][i][j] = softmax_j(T(src[b][i][j] * scale)) over j <= i + (context -
+ * t_rows), 0 beyond -- the scale -> +mask -> softmax sequence of the unfused attention
+ * (xn-moshi/src/batched_transformer.rs:176-189, mask as IndicesAndMask builds it) in one pass, with the same
+ * roundings to the element type.  src / dst: [batch, t_rows, context] contiguous (batch = streams x heads); dst may
+ * be src. */
+int xn_mm_softmax_causal(xn_dtype dtype, void *dst, const void *src, size_t batch, size_t t_rows, size_t context,
+                         float scale, void *stream);
+/* All-gather of a locally computed slice (no counterpart in the reference): copies src, [m] rows of row_bytes bytes
+ * laid out [groups][m][row_bytes / groups] (groups = 1: plain row-major; groups = heads: the (heads, tokens, head_dim)
+ * output of a batched attention matmul), into bytes [col_offset_bytes, col_offset_bytes + row_bytes) of every row of
+ * each of the num_dst destination buffers (row pitch ldy_bytes) -- the rank's own and its peers', mapped into this
+ * process.  multicast != 0: dsts[0] is an NVLink multicast address and every 16-byte piece is one multimem.st.
+ * Everything in multiples of 16 bytes.  The caller synchronises the ranks before the result is read. */
+int xn_mm_scatter_columns(void *const *dsts, size_t num_dst, int multicast, size_t ldy_bytes, size_t col_offset_bytes,
+                          const void *src, size_t m, size_t row_bytes, size_t groups, void *stream);
+
 /* Fusions with no counterpart in the reference (it runs every op as its own kernel):
  * the norm / the gating write the e4m3 activation pieces (and power-of-two row scale) of the next
  * fp8 linear directly -- identical to running the plain op and then xn_mm_split_rows_e4m3;

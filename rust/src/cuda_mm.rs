@@ -99,6 +99,11 @@ extern "C" {
     pub fn xn_mm_kv_append(dtype: XnDtype, cache: *mut c_void, src: *const c_void, src_batch_stride: usize,
         index: *const i64, batch: usize, heads: usize, context: usize, head_dim: usize,
         stream: *mut c_void) -> c_int;
+    pub fn xn_mm_softmax_causal(dtype: XnDtype, dst: *mut c_void, src: *const c_void, batch: usize,
+        t_rows: usize, context: usize, scale: f32, stream: *mut c_void) -> c_int;
+    pub fn xn_mm_scatter_columns(dsts: *const *mut c_void, num_dst: usize, multicast: c_int,
+        ldy_bytes: usize, col_offset_bytes: usize, src: *const c_void, m: usize, row_bytes: usize,
+        groups: usize, stream: *mut c_void) -> c_int;
     pub fn xn_mm_rms_norm_split_e4m3(x_hi: *mut u8, x_lo: *mut u8, x_scale: *mut f32,
         dst_or_null: *mut c_void, src: *const c_void, alpha: *const c_void, dtype: XnDtype, rows: usize,
         cols: usize, eps: f32, stream: *mut c_void) -> c_int;

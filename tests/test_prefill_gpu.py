@@ -1,0 +1,108 @@
+"""GPU: the pieces of the tensor-parallel prefill (causal softmax, the column all-gather kernel, batched matmuls over
+per-head views of a fused projection) and the whole stack at reduced size against float64."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,T,ctx", [(3, 37, 37), (2, 16, 50), (1, 300, 300)])
+def test_softmax_causal_vs_float64(xn, oracle, cuda, dt, B, T, ctx):
+    g = torch.Generator(device=cuda).manual_seed(T + ctx)
+    s = (torch.randn(B, T, ctx, generator=g, device=cuda) * 4).to(dt)
+    out = torch.full_like(s, float("nan"))
+    code = 0 if dt == torch.float32 else 2
+    scale = 0.37
+    xn._lib.check(xn.lib().xn_mm_softmax_causal(code, out.data_ptr(), s.data_ptr(), B, T, ctx, scale, None))
+    ref = s.double() * scale
+    i = torch.arange(T, device=cuda)[:, None]
+    j = torch.arange(ctx, device=cuda)[None, :]
+    ref = ref.masked_fill(j > i + (ctx - T), float("-inf"))
+    ref = torch.softmax(ref, -1)
+    torch.cuda.synchronize()
+    assert not torch.isnan(out).any()
+    tol = 1e-5 if dt == torch.float32 else 2e-2   # bf16: scaled scores, exponentials and quotients are each rounded
+    assert float((out.double() - ref).abs().max()) < tol
+    assert float(out.double().masked_select((j > i + (ctx - T)).expand_as(out)).abs().sum()) == 0.0
+    # in place
+    xn._lib.check(xn.lib().xn_mm_softmax_causal(code, s.data_ptr(), s.data_ptr(), B, T, ctx, scale, None))
+    torch.cuda.synchronize()
+    assert torch.equal(s, out)
+
+
+def test_scatter_columns_fills_the_slice_of_every_destination(xn, cuda):
+    """Two destination buffers on the one GPU stand in for two ranks' copies; plain and head-grouped sources."""
+    L = xn.lib()
+    m, n_total, nl = 33, 512, 128
+    d0 = torch.zeros(m, n_total, dtype=torch.bfloat16, device=cuda)
+    d1 = torch.zeros_like(d0)
+    src = torch.randn(m, nl, device=cuda).bfloat16()
+    ptrs = (C.c_void_p * 2)(d0.data_ptr(), d1.data_ptr())
+    xn._lib.check(L.xn_mm_scatter_columns(ptrs, 2, 0, 2 * n_total, 2 * 256, src.data_ptr(), m, 2 * nl, 1, None))
+    grouped = torch.randn(4, m, 32, device=cuda).bfloat16()           # (heads, tokens, head_dim) of a batched matmul
+    xn._lib.check(L.xn_mm_scatter_columns(ptrs, 2, 0, 2 * n_total, 0, grouped.data_ptr(), m, 2 * 128, 4, None))
+    torch.cuda.synchronize()
+    for d in (d0, d1):
+        assert torch.equal(d[:, 256:384], src)
+        assert torch.equal(d[:, :128], grouped.permute(1, 0, 2).reshape(m, 128))
+        assert float(d[:, 128:256].abs().sum()) == 0 and float(d[:, 384:].abs().sum()) == 0
+    assert L.xn_mm_scatter_columns(ptrs, 2, 0, 2 * n_total, 2 * 450, src.data_ptr(), m, 2 * nl, 1, None) == 1  # does not fit
+    assert L.xn_mm_scatter_columns(ptrs, 2, 1, 2 * n_total, 0, src.data_ptr(), m, 2 * nl, 1, None) == 1        # multicast: one dst
+
+
+def test_batched_matmuls_over_per_head_views_of_a_fused_projection(xn, oracle, cuda):
+    """q.k^T and p.v of the prefill attention read q, k, v as [heads, T, 128] views of one [T, 3 * heads * 128]
+    projection (matrices interleaved row by row): both run as one batched tensor-core launch."""
+    T, H = 200, 3
+    g = torch.Generator(device=cuda).manual_seed(1)
+    qkv = torch.randn(T, 3 * H * 128, generator=g, device=cuda).bfloat16()
+    v4 = qkv.view(T, 3, H, 128)
+    q, k, v = (v4[:, j].transpose(0, 1) for j in range(3))
+    sc = xn.matmul_t(q, k)
+    ref = torch.einsum("htd,hsd->hts", q.double(), k.double()).cpu().numpy()
+    assert oracle.rel_err(sc.float().cpu().numpy(), ref) < 1e-2
+    p = torch.softmax(sc.float() / math.sqrt(128), -1).bfloat16()
+    o = xn.matmul(p, v)
+    ref2 = torch.einsum("hts,hsd->htd", p.double(), v.double()).cpu().numpy()
+    assert oracle.rel_err(o.float().cpu().numpy(), ref2) < 1e-2
+
+
+def test_prefill_stack_reduced_size_vs_float64(xn, oracle, cuda):
+    """2 layers, d_model 512 (4 heads), FFN hidden 1408, 192 tokens, one rank: the device stack against a float64
+    restatement built from the same quantized weights (causal attention, gated SiLU FFN, pre-norm residuals)."""
+    from xn_b200.prefill import PrefillStack
+    L, d, H, hid, T = 2, 512, 4, 1408, 192
+    st = PrefillStack(L, d, H, hid, T, cuda, seed=4)
+    g = torch.Generator(device=cuda).manual_seed(9)
+    x = torch.randn(T, d, generator=g, device=cuda).bfloat16()
+    y = st.forward(x).float().cpu().numpy()
+    torch.cuda.synchronize()
+    tab = torch.from_numpy(oracle.e4m3_decode_table()).double().to(cuda)
+
+    def deq(qs):
+        q, s = qs
+        return tab[q.long()] * s.double()[:, None]
+
+    def rms(t):
+        return t / torch.sqrt((t * t).mean(-1, keepdim=True) + 1e-5)
+
+    cur = x.double()
+    mask = torch.triu(torch.full((T, T), float("-inf"), device=cuda, dtype=torch.float64), 1)
+    for lay in st.layers:
+        qkv = rms(cur) @ deq(lay["in_proj"]).T
+        q, k, v = (qkv[:, j * d:(j + 1) * d].view(T, H, 128).transpose(0, 1) for j in range(3))
+        p = torch.softmax(q @ k.transpose(1, 2) / math.sqrt(128) + mask, -1)
+        att = (p @ v).transpose(0, 1).reshape(T, d)
+        mid = cur + att @ deq(lay["out_proj"]).T
+        h = rms(mid) @ deq(lay["linear_in"]).T
+        cur = mid + (torch.nn.functional.silu(h[:, :hid]) * h[:, hid:]) @ deq(lay["linear_out"]).T
+    ref = cur.cpu().numpy()
+    r = np.sqrt(np.mean(ref ** 2))
+    err_rms, err_max = np.sqrt(np.mean((y - ref) ** 2)) / r, np.max(np.abs(y - ref)) / r
+    print("prefill stack: rms err", err_rms, "max err / rms", err_max)
+    assert err_rms < 7e-3 and err_max < 4.5e-2   # measured 0.0034 / 0.027

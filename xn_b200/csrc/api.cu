@@ -153,8 +153,9 @@ static int gemm_dispatch(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_
                              lhs_rs % 8 == 0 && rhs_rs % 8 == 0 && rhs_rs >= n && aligned(l, 16) && aligned(r, 16) &&
                              m <= 0x7fffffff && n <= 0x7fffffff && k <= 0x7fffffff && dst_rs <= 0x7fffffff &&
                              (m >= 8 || n * k >= (size_t)1 << 20);
-        if (kn16_ok && (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 &&
-                                       rhs_b_stride >= k * rhs_rs && lhs_b_stride != 0)))
+        // batched: one matrix after the other, or interleaved row by row (per-head slices of a wider row)
+        if (kn16_ok && (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 && lhs_b_stride != 0 &&
+                                       (rhs_b_stride >= k * rhs_rs || (rhs_b_stride >= n && lhs_b * rhs_b_stride <= rhs_rs)))))
             return launch_gemm_kn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_rs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
                                         (cudaStream_t)stream);
     }

@@ -361,7 +361,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     if (args.b_mn) {
                         // one 64-column block (64 n x BK k, 8 KB) per copy
                         for (int i = 0; i < BN / 64; ++i)
-                            tma_load_3d(st + NA * A_BYTES + i * (64 * BKB), &map_b, n_blk * BN + 64 * i, kb * BK, g, &full[s]);
+                            tma_load_3d(st + NA * A_BYTES + i * (64 * BKB), &map_b, n_blk * BN + 64 * i,
+                                        args.b_batch_inner ? g : kb * BK, args.b_batch_inner ? kb * BK : g, &full[s]);
                     } else {
                         tma_load_3d(st + NA * A_BYTES, &map_b, kb * BK, by, bz, &full[s]);
                     }
@@ -858,13 +859,19 @@ int make_map(CUtensorMap *map, const void *base, int elem, size_t rows, size_t k
 
 // [K, N] operand with n contiguous, k-rows `ld` elements apart, `batch` matrices batch_stride elements apart:
 // dimensions (n, k, batch), box 64 n x 64 k (128-byte rows, 128-byte swizzle).  16-bit elements only.
-int make_map_mn(CUtensorMap *map, const void *base, size_t n, size_t k, size_t ld, size_t batch, size_t batch_stride) {
+// As in make_map3 the dimensions are ordered by increasing stride: when the matrices interleave (batch stride
+// smaller than the k-row pitch, e.g. the per-head value slices of a fused qkv projection) the map is (n, batch, k)
+// and *batch_inner is set.
+int make_map_mn(CUtensorMap *map, const void *base, size_t n, size_t k, size_t ld, size_t batch, size_t batch_stride,
+                int *batch_inner) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(XN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if (batch <= 1) { batch = 1; batch_stride = k * ld; }
-    cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)k, (cuuint64_t)batch};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)batch_stride * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)(BKB / 2), 1};
+    const bool inner = batch_stride < ld;
+    *batch_inner = inner ? 1 : 0;
+    cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)(inner ? batch : k), (cuuint64_t)(inner ? k : batch)};
+    cuuint64_t strides[2] = {(cuuint64_t)(inner ? batch_stride : ld) * 2, (cuuint64_t)(inner ? ld : batch_stride) * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)(inner ? 1 : BKB / 2), (cuuint32_t)(inner ? BKB / 2 : 1)};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -904,7 +911,7 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     rc = make_map3(&ma1, NA == 2 ? a1 : a0, ELEM, args.M, args.K, lda, BM, a_batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
     if (args.b_mn) {
-        if constexpr (ELEM == 2 && BN % 64 == 0) rc = make_map_mn(&mb, b, args.N, args.K, ldb, bg.batch, bg.b_stride);
+        if constexpr (ELEM == 2 && BN % 64 == 0) rc = make_map_mn(&mb, b, args.N, args.K, ldb, bg.batch, bg.b_stride, &args2.b_batch_inner);
         else rc = fail(XN_ERR_UNSUPPORTED, "n-contiguous right-hand side: tile width %d / element size %d not supported", BN, ELEM);
     } else {
         rc = make_map3(&mb, b, ELEM, args.N, args.K, ldb, BN, bg.batch, bg.b_stride, &args2.b_batch_inner);

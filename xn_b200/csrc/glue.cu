@@ -540,6 +540,61 @@ decode_attention_combine_split_kernel(__nv_bfloat16 *__restrict__ out, uint8_t *
     }
 }
 
+
+// Causal attention probabilities for a block of T query rows against ctx keys (the last T keys are the block's
+// own): row i sees keys j <= i + (ctx - T).  y = softmax(T(s * scale)) over the visible keys with the roundings of
+// the unfused route (scores scaled and rounded to the element type, exp and quotient rounded as in softmax_kernel),
+// zeros elsewhere -- the scale -> +mask -> softmax sequence of xn-moshi/src/batched_transformer.rs:176-189 in one
+// pass.  One CTA of 256 threads per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_causal_kernel(T *dst, const T *src, size_t t_rows, size_t ctx, float scale) {  // dst may be src
+    __shared__ float red[32];
+    const size_t row = blockIdx.x, i = row % t_rows;
+    const size_t vis = i + (ctx - t_rows) + 1;  // visible keys
+    const T *x = src + row * ctx;
+    T *y = dst + row * ctx;
+    float mx = -INFINITY;
+    for (size_t c = threadIdx.x; c < vis; c += 256) mx = fmaxf(mx, to_f32(from_f32<T>(to_f32(x[c]) * scale)));
+    mx = block_max2(mx, red);
+    float sum = 0.0f;
+    for (size_t c = threadIdx.x; c < vis; c += 256) {
+        const float sv = to_f32(from_f32<T>(to_f32(x[c]) * scale));
+        const T e = from_f32<T>(expf(to_f32(from_f32<T>(sv - mx))));
+        y[c] = e;
+        sum += to_f32(e);
+    }
+    sum = block_sum(sum, red);
+    for (size_t c = threadIdx.x; c < ctx; c += 256) y[c] = c < vis ? from_f32<T>(to_f32(y[c]) / sum) : from_f32<T>(0.0f);
+}
+
+// dst_p[row][col_offset + c] = src element (row, c) for every destination p: the all-gather of a locally computed
+// [m, n] slice into the [m, ldy] result of every rank (destinations are the rank's own buffer and its peers', mapped
+// into this process; plain 16-byte stores over NVLink, or ONE multimem.st per piece when `mc` is set and dsts[0]
+// is an NVLink multicast address).  The source is [groups][m][n / groups] (groups = 1: plain row-major [m, n]).
+struct ScatterArgs {
+    void *dst[8];
+    int ndst, mc;
+};
+__global__ void __launch_bounds__(256)
+scatter_columns_kernel(ScatterArgs a, const unsigned char *__restrict__ src, size_t m, size_t row_bytes, size_t group_row_bytes,
+                       size_t ldy_bytes, size_t col_offset_bytes) {
+    const size_t chunks_per_row = row_bytes / 16, total = m * chunks_per_row;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / chunks_per_row, cb = (i - row * chunks_per_row) * 16;
+        const size_t g = cb / group_row_bytes, within = cb - g * group_row_bytes;
+        const uint4 v = *reinterpret_cast<const uint4 *>(src + (g * m + row) * group_row_bytes + within);
+        const size_t off = row * ldy_bytes + col_offset_bytes + cb;
+        if (a.mc) {
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                             static_cast<unsigned char *>(a.dst[0]) + off),
+                         "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                         : "memory");
+        } else {
+            for (int p = 0; p < a.ndst; ++p) *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(a.dst[p]) + off) = v;
+        }
+    }
+}
 }  // namespace
 }  // namespace xn
 
@@ -813,4 +868,43 @@ extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t
                                       void *stream) {
     return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
                                  context, head_dim, scale, nullptr, 0, false, stream);
+}
+
+extern "C" int xn_mm_softmax_causal(xn_dtype dtype, void *dst, const void *src, size_t batch, size_t t_rows, size_t context,
+                                    float scale, void *stream) {
+    XN_REQUIRE(valid_dtype(dtype), "softmax_causal: unknown dtype %d", (int)dtype);
+    if (batch == 0 || t_rows == 0 || context == 0) return XN_OK;
+    XN_REQUIRE(dst && src, "softmax_causal: null pointer");
+    XN_REQUIRE(t_rows <= context, "softmax_causal: %zu query rows but only %zu keys", t_rows, context);
+    XN_REQUIRE(batch * t_rows <= 0x7fffffffull, "softmax_causal: too many rows");
+    XN_DISPATCH_DTYPE(dtype, T, xn::softmax_causal_kernel<T><<<(unsigned)(batch * t_rows), 256, 0, (cudaStream_t)stream>>>(
+                                    (T *)dst, (const T *)src, t_rows, context, scale));
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" int xn_mm_scatter_columns(void *const *dsts, size_t num_dst, int multicast, size_t ldy_bytes, size_t col_offset_bytes,
+                                     const void *src, size_t m, size_t row_bytes, size_t groups, void *stream) {
+    XN_REQUIRE(num_dst >= 1 && num_dst <= 8, "scatter_columns: %zu destinations (1..8 supported)", num_dst);
+    XN_REQUIRE(!multicast || num_dst == 1, "scatter_columns: a multicast address is one destination");
+    if (m == 0 || row_bytes == 0) return XN_OK;
+    XN_REQUIRE(dsts && src, "scatter_columns: null pointer");
+    XN_REQUIRE(groups >= 1 && row_bytes % groups == 0 && (row_bytes / groups) % 16 == 0 && ldy_bytes % 16 == 0 &&
+                   col_offset_bytes % 16 == 0 && aligned(src, 16),
+               "scatter_columns: rows, groups, pitch and offset must be multiples of 16 bytes");
+    XN_REQUIRE(col_offset_bytes + row_bytes <= ldy_bytes, "scatter_columns: slice does not fit the destination row");
+    xn::ScatterArgs a{};
+    for (size_t p = 0; p < num_dst; ++p) {
+        XN_REQUIRE(dsts[p] && aligned(dsts[p], 16), "scatter_columns: destination %zu is null or not 16-byte aligned", p);
+        a.dst[p] = dsts[p];
+    }
+    a.ndst = (int)num_dst;
+    a.mc = multicast ? 1 : 0;
+    const size_t total = m * (row_bytes / 16);
+    const size_t blocks = (total + 255) / 256;
+    const unsigned grid = (unsigned)(blocks < (size_t)sm_count() * 8 ? blocks : (size_t)sm_count() * 8);
+    xn::scatter_columns_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a, (const unsigned char *)src, m, row_bytes, row_bytes / groups,
+                                                                       ldy_bytes, col_offset_bytes);
+    XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
 }
