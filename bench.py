@@ -391,7 +391,7 @@ def measure_prefill_stack(args, dev, world, rank, timed, torch, dist) -> dict:
     four exchanges per layer (attention output, out_proj, gated FFN activations, linear_out) written into every
     rank's buffers by store epilogues / an all-gather kernel over NVLink.  Strong scaling: the work is fixed."""
     from xn_b200.prefill import PrefillStack
-    T, L = 4096, 32
+    T, L = 4096, args.prefill_layers
     identical = None
     if world > 1:  # two layers of the split stack against the same two layers on one rank, bit for bit
         g = torch.Generator(device=dev).manual_seed(11)
@@ -477,6 +477,8 @@ def main() -> None:
     ap.add_argument("--no-decode", action="store_true", help="skip the decoder-stack step measurement")
     ap.add_argument("--decode-steps", type=int, default=8)
     ap.add_argument("--decode-only", action="store_true", help="measure only the decoder-stack step (profiling aid)")
+    ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill stack (profiling aid)")
+    ap.add_argument("--prefill-layers", type=int, default=32)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -522,6 +524,14 @@ def main() -> None:
         d = measure_decode(args, dev, world, rank, timed)
         if rank == 0:
             print(json.dumps({"decode_step": d}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    if args.prefill_only:
+        d = measure_prefill_stack(args, dev, world, rank, timed, torch, dist)
+        if rank == 0:
+            print(json.dumps({"prefill_stack": d}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return

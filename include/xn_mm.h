@@ -102,6 +102,21 @@ int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const
                size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs,
                size_t rhs_cs, size_t rhs_rs, void *stream);
 
+/* The two batched matmuls of causal attention over a block of query rows (xn-moshi/src/batched_transformer.rs:175,
+ * 190, with the mask IndicesAndMask builds): key j is visible to query row i iff j <= i + causal_offset
+ * (causal_offset = context - rows).  Same arguments and arithmetic as xn_mm_gemm; what differs is the work skipped:
+ *   mode 1 (scores, q.k^T: m = query rows, n = keys)  output tiles that lie entirely beyond the horizon of their
+ *          last row are neither computed nor written: dst is defined for j <= i + causal_offset (and, tile-wise,
+ *          a little beyond); the rest keeps whatever it held.  xn_mm_softmax_causal reads only the visible part.
+ *   mode 2 (values, p.v: m = query rows, k = keys)     the k loop of a 128-row tile stops at the horizon of its
+ *          last row; lhs entries beyond it are never read (xn_mm_softmax_causal writes zeros up to that bound
+ *          and nothing beyond).  16-bit elements with an n-contiguous rhs only (XN_ERR_UNSUPPORTED otherwise).
+ * No counterpart in the reference, which multiplies the full squares. */
+int xn_mm_gemm_causal(int mode, size_t causal_offset, xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off,
+                      const void *rhs, size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b, size_t lhs_b_stride,
+                      size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs, size_t rhs_cs,
+                      size_t rhs_rs, void *stream);
+
 /* Linear::forward (xn-core/src/nn/linear.rs:56-66): y [m,n] = x [m,k] * weight [n,k]^T (+ bias [n]), rows
  * ldx / ldw / ldy elements apart.  Same arithmetic and kernels as xn_mm_gemm with
  * (lhs_cs,lhs_rs) = (1,ldx), (rhs_cs,rhs_rs) = (ldw,1); the difference is a promise: `weight` is a model
@@ -256,9 +271,11 @@ int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_bat
  * t_rows), 0 beyond -- the scale -> +mask -> softmax sequence of the unfused attention
  * (xn-moshi/src/batched_transformer.rs:176-189, mask as IndicesAndMask builds it) in one pass, with the same
  * roundings to the element type.  src / dst: [batch, t_rows, context] contiguous (batch = streams x heads); dst may
- * be src. */
+ * be src.  Only the visible part of src is read.  The zeros are written up to the end of the row's 128-row tile
+ * horizon, ((i / 128) + 1) * 128 + (context - t_rows) -- what xn_mm_gemm_causal mode 2 reads -- when
+ * zero_fill_all == 0, over the whole row otherwise. */
 int xn_mm_softmax_causal(xn_dtype dtype, void *dst, const void *src, size_t batch, size_t t_rows, size_t context,
-                         float scale, void *stream);
+                         float scale, int zero_fill_all, void *stream);
 /* All-gather of a locally computed slice (no counterpart in the reference): copies src, [m] rows of row_bytes bytes
  * laid out [groups][m][row_bytes / groups] (groups = 1: plain row-major; groups = heads: the (heads, tokens, head_dim)
  * output of a batched attention matmul), into bytes [col_offset_bytes, col_offset_bytes + row_bytes) of every row of

@@ -40,6 +40,10 @@ extern "C" {
         rhs: *const c_void, rhs_off: usize, m: usize, n: usize, k: usize, lhs_b: usize, lhs_b_stride: usize,
         rhs_b_stride: usize, dst_cs: usize, dst_rs: usize, lhs_cs: usize, lhs_rs: usize, rhs_cs: usize,
         rhs_rs: usize, stream: *mut c_void) -> c_int;
+    pub fn xn_mm_gemm_causal(mode: c_int, causal_offset: usize, dtype: XnDtype, dst: *mut c_void,
+        lhs: *const c_void, lhs_off: usize, rhs: *const c_void, rhs_off: usize, m: usize, n: usize, k: usize,
+        lhs_b: usize, lhs_b_stride: usize, rhs_b_stride: usize, dst_cs: usize, dst_rs: usize, lhs_cs: usize,
+        lhs_rs: usize, rhs_cs: usize, rhs_rs: usize, stream: *mut c_void) -> c_int;
     pub fn xn_mm_linear(dtype: XnDtype, y: *mut c_void, x: *const c_void, weight: *const c_void,
         bias_or_null: *const c_void, m: usize, n: usize, k: usize, ldx: usize, ldw: usize, ldy: usize,
         stream: *mut c_void) -> c_int;
@@ -100,7 +104,7 @@ extern "C" {
         index: *const i64, batch: usize, heads: usize, context: usize, head_dim: usize,
         stream: *mut c_void) -> c_int;
     pub fn xn_mm_softmax_causal(dtype: XnDtype, dst: *mut c_void, src: *const c_void, batch: usize,
-        t_rows: usize, context: usize, scale: f32, stream: *mut c_void) -> c_int;
+        t_rows: usize, context: usize, scale: f32, zero_fill_all: c_int, stream: *mut c_void) -> c_int;
     pub fn xn_mm_scatter_columns(dsts: *const *mut c_void, num_dst: usize, multicast: c_int,
         ldy_bytes: usize, col_offset_bytes: usize, src: *const c_void, m: usize, row_bytes: usize,
         groups: usize, stream: *mut c_void) -> c_int;

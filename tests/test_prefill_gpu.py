@@ -11,14 +11,14 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,ctx", [(3, 37, 37), (2, 16, 50), (1, 300, 300)])
+@pytest.mark.parametrize("B,T,ctx", [(3, 37, 37), (2, 16, 50), (1, 300, 300), (2, 64, 64), (2, 24, 2056), (1, 8, 4104)])
 def test_softmax_causal_vs_float64(xn, oracle, cuda, dt, B, T, ctx):
     g = torch.Generator(device=cuda).manual_seed(T + ctx)
     s = (torch.randn(B, T, ctx, generator=g, device=cuda) * 4).to(dt)
     out = torch.full_like(s, float("nan"))
     code = 0 if dt == torch.float32 else 2
     scale = 0.37
-    xn._lib.check(xn.lib().xn_mm_softmax_causal(code, out.data_ptr(), s.data_ptr(), B, T, ctx, scale, None))
+    xn._lib.check(xn.lib().xn_mm_softmax_causal(code, out.data_ptr(), s.data_ptr(), B, T, ctx, scale, 1, None))
     ref = s.double() * scale
     i = torch.arange(T, device=cuda)[:, None]
     j = torch.arange(ctx, device=cuda)[None, :]
@@ -30,7 +30,7 @@ def test_softmax_causal_vs_float64(xn, oracle, cuda, dt, B, T, ctx):
     assert float((out.double() - ref).abs().max()) < tol
     assert float(out.double().masked_select((j > i + (ctx - T)).expand_as(out)).abs().sum()) == 0.0
     # in place
-    xn._lib.check(xn.lib().xn_mm_softmax_causal(code, s.data_ptr(), s.data_ptr(), B, T, ctx, scale, None))
+    xn._lib.check(xn.lib().xn_mm_softmax_causal(code, s.data_ptr(), s.data_ptr(), B, T, ctx, scale, 1, None))
     torch.cuda.synchronize()
     assert torch.equal(s, out)
 
@@ -106,3 +106,43 @@ def test_prefill_stack_reduced_size_vs_float64(xn, oracle, cuda):
     err_rms, err_max = np.sqrt(np.mean((y - ref) ** 2)) / r, np.max(np.abs(y - ref)) / r
     print("prefill stack: rms err", err_rms, "max err / rms", err_max)
     assert err_rms < 7e-3 and err_max < 4.5e-2   # measured 0.0034 / 0.027
+
+
+@pytest.mark.parametrize("T,ctx", [(304, 304), (256, 512), (130, 200)])
+def test_causal_attention_matmuls_skip_only_what_is_masked(xn, oracle, cuda, T, ctx):
+    """q.k^T (mode 1) -> causal softmax with the bounded zero fill -> p.v (mode 2), each stage against float64 on
+    what it is defined to produce, although scores beyond the horizon are never written (the buffers are
+    NaN-poisoned first): visible scores, visible probabilities, zeros up to the tile horizon, and the values
+    product of exactly those probabilities."""
+    H, off = 3, ctx - T
+    g = torch.Generator(device=cuda).manual_seed(T)
+    q = torch.randn(H, T, 128, generator=g, device=cuda).bfloat16()
+    k = torch.randn(H, ctx, 128, generator=g, device=cuda).bfloat16()
+    v = torch.randn(H, ctx, 128, generator=g, device=cuda).bfloat16()
+    i = torch.arange(T, device=cuda)[:, None]
+    j = torch.arange(ctx, device=cuda)[None, :]
+    vis = j <= i + off
+    sc = torch.full((H, T, ctx), float("nan"), dtype=torch.bfloat16, device=cuda)
+    xn.ops.matmul_causal_(sc, q, k, True, 1, off)
+    torch.cuda.synchronize()
+    s_ref = q.double() @ k.double().transpose(1, 2)
+    err = torch.where(vis.expand_as(sc), (sc.double() - s_ref).abs(), torch.zeros_like(s_ref))
+    assert not torch.isnan(err).any() and float(err.max()) <= 2.0 ** -8 * float(s_ref.abs().max())   # one bf16 rounding
+    p = sc.clone()
+    xn._lib.check(xn.lib().xn_mm_softmax_causal(2, p.data_ptr(), p.data_ptr(), H, T, ctx, 1 / math.sqrt(128), 0, None))
+    torch.cuda.synchronize()
+    p_ref = torch.softmax((s_ref / math.sqrt(128)).masked_fill(~vis, float("-inf")), -1)
+    perr = torch.where(vis.expand_as(p), (p.double() - p_ref).abs(), torch.zeros_like(p_ref))
+    assert not torch.isnan(perr).any() and float(perr.max()) < 1e-2
+    zend = torch.clamp(((i // 128 + 1) * 128 + off + 63) // 64 * 64, max=ctx)
+    fill = (~vis) & (j < zend)
+    assert float(torch.where(fill.expand_as(p), torch.nan_to_num(p.float(), nan=1e9).abs(), torch.zeros_like(p.float())).max()) == 0
+    out = torch.full((H, T, 128), float("nan"), dtype=torch.bfloat16, device=cuda)
+    xn.ops.matmul_causal_(out, p, v, False, 2, off)
+    torch.cuda.synchronize()
+    p0 = torch.where(vis.expand_as(p), p, torch.zeros_like(p))
+    ref = (p0.double() @ v.double()).cpu().numpy()
+    assert not torch.isnan(out).any()
+    assert oracle.rel_err(out.float().cpu().numpy(), ref) < 1e-2
+    with pytest.raises(xn.XnError):   # the values form has no fallback that could read the unwritten tail
+        xn.ops.matmul_causal_(torch.empty(H, T, 128, device=cuda), p.float(), v.float(), False, 2, off)

@@ -76,7 +76,8 @@ extern "C" int xn_mm_abi_version(void) { return 1; }
 static int gemm_dispatch(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const void *rhs,
                          size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b,
                          size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_cs, size_t dst_rs,
-                         size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream) {
+                         size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream, int causal = 0,
+                         int causal_off = 0) {
     // Same refusal as the reference for element types it has no GEMM for
     // (xn-core/src/cuda_backend.rs:862).
     if (!valid_dtype(dtype)) return fail(XN_ERR_UNSUPPORTED, "GEMM not supported for dtype %d", (int)dtype);
@@ -143,7 +144,7 @@ static int gemm_dispatch(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_
         (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 && rhs_b_stride != 0 &&
                         lhs_b_stride != 0)))
         return launch_gemm_tn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_cs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
-                                    (cudaStream_t)stream);
+                                    (cudaStream_t)stream, causal == 1 ? 1 : 0, causal_off);
     // 16-bit `matmul` with a row-major [k, n] right-hand side (n contiguous; cuBLAS's OP_N in the reference): the
     // tcgen05 kernel reads it as an MN-major operand.  Worth it from a few thousand MACs per output row on; tiny
     // products (decode attention's p.v with one query row) stay on the generic kernel.
@@ -157,8 +158,11 @@ static int gemm_dispatch(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_
         if (kn16_ok && (lhs_b == 1 || (lhs_b <= 0x7fffffff && lhs_b_stride % 8 == 0 && rhs_b_stride % 8 == 0 && lhs_b_stride != 0 &&
                                        (rhs_b_stride >= k * rhs_rs || (rhs_b_stride >= n && lhs_b * rhs_b_stride <= rhs_rs)))))
             return launch_gemm_kn_16bit(dtype, dst, l, r, m, n, k, lhs_rs, rhs_rs, dst_rs, lhs_b, lhs_b_stride, rhs_b_stride,
-                                        (cudaStream_t)stream);
+                                        (cudaStream_t)stream, causal == 2 ? 2 : 0, causal_off);
     }
+    if (causal == 2)
+        return fail(XN_ERR_UNSUPPORTED, "gemm_causal (values): needs 16-bit elements, an n-contiguous right-hand side and "
+                                        "16-byte aligned pitches (the masked probabilities are not read, so no other kernel may run it)");
     // f32 with many rows, one batch, row-major dst: three tf32 pieces per operand on the tensor-memory kernel
     // (any operand strides; the repack normalises them).
     if (dtype == XN_F32 && lhs_b == 1 && dst_cs == 1 && dst_rs <= 0x7fffffff && gemm_f32_tc_fits(m, n, k))
@@ -177,6 +181,17 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
     StaticRhsScope scope(false);
     return gemm_dispatch(dtype, dst, lhs, lhs_off, rhs, rhs_off, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
                          lhs_cs, lhs_rs, rhs_cs, rhs_rs, stream);
+}
+
+extern "C" int xn_mm_gemm_causal(int mode, size_t causal_offset, xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off,
+                                 const void *rhs, size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b, size_t lhs_b_stride,
+                                 size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs, size_t rhs_cs,
+                                 size_t rhs_rs, void *stream) {
+    XN_REQUIRE(mode == 1 || mode == 2, "gemm_causal: mode %d (1 = scores q.k^T, 2 = values p.v)", mode);
+    XN_REQUIRE(causal_offset <= 0x3fffffffull, "gemm_causal: offset too large");
+    StaticRhsScope scope(false);
+    return gemm_dispatch(dtype, dst, lhs, lhs_off, rhs, rhs_off, m, n, k, lhs_b, lhs_b_stride, rhs_b_stride, dst_cs, dst_rs,
+                         lhs_cs, lhs_rs, rhs_cs, rhs_rs, stream, mode, (int)causal_offset);
 }
 
 extern "C" int xn_mm_linear(xn_dtype dtype, void *y, const void *x, const void *weight, const void *bias_or_null, size_t m,

@@ -116,9 +116,11 @@ int launch_gemv_dense(xn_dtype dt, void *dst, const void *lhs, const void *rhs, 
                       size_t lhs_b, size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_rs, size_t lhs_rs, size_t rhs_cs,
                       cudaStream_t st);
 int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
-                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st);
+                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st,
+                         int causal = 0, int causal_off = 0);
 int launch_gemm_kn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
-                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st);
+                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st,
+                         int causal = 0, int causal_off = 0);
 int launch_gemm_tn_16bit_shared_lhs(xn_dtype dt, void *dst, const void *lhs, const void *rhs, const void *row_bias, size_t m,
                                     size_t n, size_t k, size_t lda, size_t ldb, size_t ldd, size_t batch, size_t rhs_bs,
                                     size_t dst_bs, cudaStream_t st);

@@ -185,9 +185,22 @@ struct GemmArgs {
     const void *row_bias; // optional, not for fp8: added to every element of output row i (element type of y)
     WaitCtx wait;         // bound and status word of the kernel's mbarrier waits
     int group_m;          // m blocks per rasterisation group (see tile_coords)
+    int causal, causal_off;  // causal attention (16-bit kinds): 1 = q.k^T, tiles whose keys all lie beyond the last query row's
+                          // horizon (key j visible to row i iff j <= i + causal_off) are skipped and left unwritten; 2 = p.v, the k
+                          // loop of a row tile stops at that horizon (the probabilities beyond it are zero and never read)
     int mc;               // y[0] is an NVLink multicast address: one multimem.st per 16 bytes reaches every GPU's copy
     int b_mn;             // 16-bit kinds: B is [K, N] with n contiguous (MN-major); its map is (n, k, batch), box 64 x BK
 };
+
+__device__ __forceinline__ bool tile_masked(const GemmArgs &a, int m_blk, int n_blk, int bn) {
+    return a.causal == 1 && n_blk * bn > m_blk * BM + BM - 1 + a.causal_off;
+}
+__device__ __forceinline__ int tile_kb(const GemmArgs &a, int m_blk, int num_kb, int bk) {
+    if (a.causal != 2) return num_kb;
+    const int lim = min(a.K, (m_blk + 1) * BM + a.causal_off);
+    const int kb = (lim + bk - 1) / bk;
+    return kb < 1 ? 1 : min(kb, num_kb);
+}
 
 // Epilogue of one output tile for the fp8 / bf16 / f16 kinds: this warp's 32 accumulator rows (tensor-memory lanes
 // 32 q .. 32 q + 31 of buffer `acc`, output rows m_row0 + 32 q ..) x BN columns are scaled / biased, rounded to the
@@ -347,7 +360,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                 const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
                 int m_blk, n_blk;
                 tile_coords(tin, num_m, num_n, args.group_m, m_blk, n_blk);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                if (KIND != 3 && tile_masked(args, m_blk, n_blk, BN)) continue;
+                const int nkb = KIND != 3 ? tile_kb(args, m_blk, num_kb, BK) : num_kb;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u, args.wait)) { ok = false; break; }
@@ -374,14 +389,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         if (lane == 0) {
             int it = 0, vt = 0;   // vt: accumulator hand-overs to the epilogue so far (one per tile, or per k chunk)
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
-            for (int kb0 = 0; (kb0 < num_kb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int nkb = num_kb;
+            if (KIND != 3 && args.causal) {
+                int m_blk, n_blk;
+                tile_coords(tile % tiles_per_batch, num_m, num_n, args.group_m, m_blk, n_blk);
+                if (tile_masked(args, m_blk, n_blk, BN)) continue;
+                nkb = tile_kb(args, m_blk, num_kb, BK);
+            }
+            for (int kb0 = 0; (kb0 < nkb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
                 const int acc = vt & 1;
                 const unsigned acc_ph = (unsigned)(vt >> 1) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, args.wait)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                const int kend = num_kb - kb0 < KCH ? num_kb : kb0 + KCH;
+                const int kend = nkb - kb0 < KCH ? nkb : kb0 + KCH;
                 for (int kb = kb0; kb < kend; ++kb, ++it) {
                     const int s = it % NSTAGE;
                     const unsigned ph = (unsigned)(it / NSTAGE) & 1u;
@@ -407,6 +429,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
                 }
                 if (ok) umma_commit(&tmem_full[acc]);
+            }
             }
         }
     } else {
@@ -506,10 +529,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                 }
             }
         } else
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             const int g = tile / tiles_per_batch, tin = tile % tiles_per_batch;
             int m_blk, n_blk;
             tile_coords(tin, num_m, num_n, args.group_m, m_blk, n_blk);
+            if (tile_masked(args, m_blk, n_blk, BN)) continue;
             const int acc = t_local & 1;
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
             if (!mbar_wait(&tmem_full[acc], acc_ph, args.wait)) { ok = false; break; }
@@ -518,6 +542,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            ++t_local;
         }
     }
 
@@ -1089,18 +1114,20 @@ int launch_linear_fp8_gemm_multicast(void *y_mc, size_t ldy, size_t col_offset, 
 // dst [b][m,n] (row stride ldd, batch stride m*n) = lhs [b][m,k] (row stride lda, batch stride lhs_bs) *
 // rhs [b][n,k]^T (row stride ldb, batch stride rhs_bs); dt BF16 or F16; one launch for all batches.
 int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
-                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st) {
+                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st,
+                         int causal, int causal_off) {
     // Up to 64 rows, one batch: the skinny form (weights on the tensor-memory lanes, work split at k-stage
     // granularity over all SMs) -- a tiled launch would have too few tiles and too many MMAs per CTA.
     static const size_t skinny_max = [] { const char *e = getenv("XN_MM_SKINNY16_MAX_M"); return e ? (size_t)atoi(e) : (size_t)64; }();
     // (measured on the transformer shapes: always better up to 32 rows; from 33 to 64 only when the tiled kernel
     // would have fewer 64-column tiles than there are SMs)
-    if (batch == 1 && m <= skinny_max && (m <= 32 || (m <= 64 && (n + 63) / 64 < (size_t)sm_count())))
+    if (!causal && batch == 1 && m <= skinny_max && (m <= 32 || (m <= 64 && (n + 63) / 64 < (size_t)sm_count())))
         return dt == XN_BF16 ? launch_skinny<1>(dst, ldd, lhs, nullptr, lda, nullptr, rhs, ldb, nullptr, m, n, k, st)
                              : launch_skinny<2>(dst, ldd, lhs, nullptr, lda, nullptr, rhs, ldb, nullptr, m, n, k, st);
     GemmArgs a{};
     a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    a.causal = causal; a.causal_off = causal_off;
     BatchGeom bg;
     bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;
     return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)
@@ -1112,10 +1139,12 @@ int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rh
 // (xn-moshi/src/batched_transformer.rs:190) and the reference's bf16 benchmark
 // (xn-core/examples/basic_cuda.rs:35-56).  The tiled kernel reads B as an MN-major operand; any row count.
 int launch_gemm_kn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rhs, size_t m, size_t n, size_t k,
-                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st) {
+                         size_t lda, size_t ldb, size_t ldd, size_t batch, size_t lhs_bs, size_t rhs_bs, cudaStream_t st,
+                         int causal, int causal_off) {
     GemmArgs a{};
     a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
+    a.causal = causal; a.causal_off = causal_off;
     a.b_mn = 1;
     BatchGeom bg;
     bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;

@@ -548,7 +548,7 @@ decode_attention_combine_split_kernel(__nv_bfloat16 *__restrict__ out, uint8_t *
 // pass.  One CTA of 256 threads per row.
 template <typename T>
 __global__ void __launch_bounds__(256)
-softmax_causal_kernel(T *dst, const T *src, size_t t_rows, size_t ctx, float scale) {  // dst may be src
+softmax_causal_kernel(T *dst, const T *src, size_t t_rows, size_t ctx, float scale, int fill_all) {  // dst may be src
     __shared__ float red[32];
     const size_t row = blockIdx.x, i = row % t_rows;
     const size_t vis = i + (ctx - t_rows) + 1;  // visible keys
@@ -565,7 +565,130 @@ softmax_causal_kernel(T *dst, const T *src, size_t t_rows, size_t ctx, float sca
         sum += to_f32(e);
     }
     sum = block_sum(sum, red);
-    for (size_t c = threadIdx.x; c < ctx; c += 256) y[c] = c < vis ? from_f32<T>(to_f32(y[c]) / sum) : from_f32<T>(0.0f);
+    // the values matmul reads whole 64-element k stages up to the horizon of the row's 128-row tile
+    const size_t zend = fill_all ? ctx : min(ctx, ((i / 128 + 1) * 128 + (ctx - t_rows) + 63) / 64 * 64);
+    for (size_t c = threadIdx.x; c < zend; c += 256) y[c] = c < vis ? from_f32<T>(to_f32(y[c]) / sum) : from_f32<T>(0.0f);
+}
+
+// 16-bit fast path: the row in registers (128-bit loads of the visible part only, one read, one write).
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+softmax_causal_vec_kernel(T *dst, const T *src, size_t t_rows, size_t ctx, float scale, int fill_all) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x, i = row % t_rows;
+    const int vis = (int)(i + (ctx - t_rows) + 1), nvec = (int)(ctx / 8);
+    const uint4 *x = reinterpret_cast<const uint4 *>(src + row * ctx);
+    uint4 *y = reinterpret_cast<uint4 *>(dst + row * ctx);
+    float v[VPT][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = u * 256 + (int)threadIdx.x, c0 = idx * 8;
+        if (idx < nvec && c0 < vis) {
+            unpack8<T>(x[idx], v[u]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[u][j] = c0 + j < vis ? to_f32(from_f32<T>(v[u][j] * scale)) : -INFINITY;
+                mx = fmaxf(mx, v[u][j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[u][j] = -INFINITY;
+        }
+    }
+    mx = block_max2(mx, red);
+    float sum = 0.0f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // masked positions (-inf) give exp = 0 and stay 0 after the division
+            v[u][j] = v[u][j] == -INFINITY ? 0.0f : to_f32(from_f32<T>(expf(to_f32(from_f32<T>(v[u][j] - mx)))));
+            sum += v[u][j];
+        }
+    sum = block_sum(sum, red);
+#pragma unroll
+    const int zend = fill_all ? (int)ctx : (int)min(ctx, ((i / 128 + 1) * 128 + (ctx - t_rows) + 63) / 64 * 64);
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = u * 256 + (int)threadIdx.x;
+        if (idx >= nvec || idx * 8 >= zend) continue;
+        T o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(v[u][j] / sum);
+        y[idx] = pack8<T>(o);
+    }
+}
+
+// One warp per row, the row packed in registers in the element type (every intermediate of the computation is
+// rounded to it anyway): no CTA-wide barriers, VPT 128-bit loads per lane in flight -- a CTA per row is bound by
+// its own latency when there are 10^5 rows of a few KB (prefill attention: heads x tokens rows).
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256, 2)
+softmax_causal_warp_kernel(T *dst, const T *src, size_t rows, size_t t_rows, size_t ctx, float scale, int fill_all) {
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const size_t i = row % t_rows;
+    const int vis = (int)(i + (ctx - t_rows) + 1), nvec = (int)(ctx / 8);
+    const int zend = fill_all ? (int)ctx : (int)min(ctx, ((i / 128 + 1) * 128 + (ctx - t_rows) + 63) / 64 * 64);
+    const uint4 *x = reinterpret_cast<const uint4 *>(src + row * ctx);
+    uint4 *y = reinterpret_cast<uint4 *>(dst + row * ctx);
+    // groups of 256 columns (one vector per lane) that lie entirely beyond the row's horizon are skipped by the whole
+    // warp in every pass; they only receive zeros
+    uint4 v[VPT];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = u * 32 + lane;
+        v[u] = (u * 256 < vis && idx < nvec && idx * 8 < vis) ? x[idx] : make_uint4(0, 0, 0, 0);
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        if (u * 256 >= vis) continue;
+        const int c0 = (u * 32 + lane) * 8;
+        float f[8];
+        unpack8<T>(v[u], f);
+        T o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j] = c0 + j < vis ? from_f32<T>(f[j] * scale) : from_f32<T>(-INFINITY);
+            mx = fmaxf(mx, to_f32(o[j]));
+        }
+        v[u] = pack8<T>(o);
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        if (u * 256 >= vis) continue;
+        float f[8];
+        unpack8<T>(v[u], f);
+        T o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // the exponential is rounded to a 16-bit type right away: the fast form (2^-21 relative) rounds to the same value
+            o[j] = f[j] == -INFINITY ? from_f32<T>(0.0f) : from_f32<T>(__expf(to_f32(from_f32<T>(f[j] - mx))));
+            sum += to_f32(o[j]);
+        }
+        v[u] = pack8<T>(o);
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int idx = u * 32 + lane;
+        if (idx >= nvec || idx * 8 >= zend) continue;
+        T o[8];
+        if (u * 256 < vis) {
+            float f[8];
+            unpack8<T>(v[u], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(__fdividef(f[j], sum));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(0.0f);
+        }
+        y[idx] = pack8<T>(o);
+    }
 }
 
 // dst_p[row][col_offset + c] = src element (row, c) for every destination p: the all-gather of a locally computed
@@ -871,14 +994,37 @@ extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t
 }
 
 extern "C" int xn_mm_softmax_causal(xn_dtype dtype, void *dst, const void *src, size_t batch, size_t t_rows, size_t context,
-                                    float scale, void *stream) {
+                                    float scale, int zero_fill_all, void *stream) {
     XN_REQUIRE(valid_dtype(dtype), "softmax_causal: unknown dtype %d", (int)dtype);
     if (batch == 0 || t_rows == 0 || context == 0) return XN_OK;
     XN_REQUIRE(dst && src, "softmax_causal: null pointer");
     XN_REQUIRE(t_rows <= context, "softmax_causal: %zu query rows but only %zu keys", t_rows, context);
     XN_REQUIRE(batch * t_rows <= 0x7fffffffull, "softmax_causal: too many rows");
+    if (dtype != XN_F32 && context % 8 == 0 && context <= 8 * 32 * 16 && aligned(src, 16) && aligned(dst, 16)) {
+        const size_t rows = batch * t_rows;
+        const unsigned grid = (unsigned)((rows + 7) / 8);
+        cudaStream_t st = (cudaStream_t)stream;
+        const int vpt = context <= 1024 ? 4 : (context <= 2048 ? 8 : 16);
+#define XN_SMW(T, V) xn::softmax_causal_warp_kernel<T, V><<<grid, 256, 0, st>>>((T *)dst, (const T *)src, rows, t_rows, context, scale, zero_fill_all)
+        if (dtype == XN_BF16) { if (vpt == 4) XN_SMW(__nv_bfloat16, 4); else if (vpt == 8) XN_SMW(__nv_bfloat16, 8); else XN_SMW(__nv_bfloat16, 16); }
+        else { if (vpt == 4) XN_SMW(__half, 4); else if (vpt == 8) XN_SMW(__half, 8); else XN_SMW(__half, 16); }
+#undef XN_SMW
+        XN_CHECK_CUDA(cudaGetLastError());
+        return XN_OK;
+    }
+    if (dtype != XN_F32 && context % 8 == 0 && context <= 8 * 256 * 4 && aligned(src, 16) && aligned(dst, 16)) {
+        const unsigned grid = (unsigned)(batch * t_rows);
+        cudaStream_t st = (cudaStream_t)stream;
+        const int vpt = context <= 2048 ? 1 : (context <= 4096 ? 2 : 4);
+#define XN_SMC(T, V) xn::softmax_causal_vec_kernel<T, V><<<grid, 256, 0, st>>>((T *)dst, (const T *)src, t_rows, context, scale, zero_fill_all)
+        if (dtype == XN_BF16) { if (vpt == 1) XN_SMC(__nv_bfloat16, 1); else if (vpt == 2) XN_SMC(__nv_bfloat16, 2); else XN_SMC(__nv_bfloat16, 4); }
+        else { if (vpt == 1) XN_SMC(__half, 1); else if (vpt == 2) XN_SMC(__half, 2); else XN_SMC(__half, 4); }
+#undef XN_SMC
+        XN_CHECK_CUDA(cudaGetLastError());
+        return XN_OK;
+    }
     XN_DISPATCH_DTYPE(dtype, T, xn::softmax_causal_kernel<T><<<(unsigned)(batch * t_rows), 256, 0, (cudaStream_t)stream>>>(
-                                    (T *)dst, (const T *)src, t_rows, context, scale));
+                                    (T *)dst, (const T *)src, t_rows, context, scale, zero_fill_all));
     XN_CHECK_CUDA(cudaGetLastError());
     return XN_OK;
 }

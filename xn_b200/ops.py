@@ -74,6 +74,19 @@ def matmul_(dst: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool
                            rhs.storage_offset(), *a, _stream()))
 
 
+def matmul_causal_(dst: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool, mode: int, offset: int) -> None:
+    """``matmul_`` for the two products of causal attention (xn_mm_gemm_causal): mode 1 = scores ``q @ k^T`` (tiles
+    beyond the causal horizon are skipped and left unwritten), mode 2 = values ``p @ v`` (the masked tail of every
+    row of p is not read).  Key j is visible to query row i iff j <= i + offset."""
+    _require_cuda(dst, lhs, rhs)
+    if not (dst.dtype == lhs.dtype == rhs.dtype):
+        raise XnError(_lib.ERR_INVALID, f"matmul dtype mismatch: {dst.dtype}, {lhs.dtype}, {rhs.dtype}")
+    dt = _dtype_code(dst)
+    a = matmul_plan(lhs, rhs, rhs_t, dst.numel())
+    check(lib().xn_mm_gemm_causal(mode, offset, dt, dst.data_ptr(), _base_ptr(lhs), lhs.storage_offset(), _base_ptr(rhs),
+                                  rhs.storage_offset(), *a, _stream()))
+
+
 def matmul_with_t(lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool) -> torch.Tensor:
     """``ops::matmul_with_t``: output shape = lhs batch dims + [M, N], allocated uninitialised."""
     if lhs.dim() < 2 or rhs.dim() < 2:

@@ -254,7 +254,7 @@ class PrefillStack:
         import math
 
         from ._lib import BF16, check, lib
-        from .ops import matmul_
+        from .ops import matmul_causal_
         L, T, d, hid, dl, hl, Hl = lib(), self.T, self.d, self.hid, self.dl, self.hl, self.Hl
         s = self._s()
         cur = x
@@ -265,10 +265,12 @@ class PrefillStack:
             self._linear_local(self.qkv, lay["in_proj"], 3 * dl, d)
             qkv4 = self.qkv.view(T, 3, Hl, 128)
             q, k, v = (qkv4[:, j].transpose(0, 1) for j in range(3))      # [Hl, T, 128] views, rows 3*dl apart
-            matmul_(self.scores, q, k, True)                               # q.k^T, one launch for the rank's heads
+            # q.k^T, one launch for the rank's heads; tiles beyond the causal horizon are skipped
+            matmul_causal_(self.scores, q, k, True, 1, 0)
             check(L.xn_mm_softmax_causal(BF16, self.scores.data_ptr(), self.scores.data_ptr(), Hl, T, T,
-                                         1.0 / math.sqrt(128.0), s))
-            matmul_(self.attn_l, self.scores, v, False)                    # p.v, [T, 128] right-hand side per head
+                                         1.0 / math.sqrt(128.0), 0, s))
+            # p.v, [T, 128] right-hand side per head; every row tile stops at its horizon
+            matmul_causal_(self.attn_l, self.scores, v, False, 2, 0)
             self._gather(self.attn_full, self.attn_l, d, Hl)
             check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn_full.t.data_ptr(), BF16,
                                           T, d, s))
