@@ -139,10 +139,11 @@ class CpuPort:
         self.xf = rng.standard_normal((16, K_IN)).astype(np.float32)
         self.run_pass()  # warm-up
 
-    def run_pass(self) -> float:
+    def run_pass(self, repeats: int = 1) -> float:
         t0 = time.perf_counter()
-        for m in MS:
-            self.O.linear_q_fast(*self.x[m], self.q, self.s)
+        for _ in range(repeats):
+            for m in MS:
+                self.O.linear_q_fast(*self.x[m], self.q, self.s)
         return time.perf_counter() - t0
 
     def throughput(self, budget_s: float):
@@ -180,13 +181,14 @@ def run_reference(args) -> None:
         port.run_pass()
         if time.perf_counter() - t_start > 60:
             break
+    REP = 64  # passes per step: a step is a bounded sample of the workload, about 0.1-0.5 s of host time
     per_step = []
     for _ in range(args.steps):
-        per_step.append(port.run_pass())
+        per_step.append(port.run_pass(REP))
         if time.perf_counter() - t_start > 240:
             break
-    value = len(MS) * weight_bytes() / statistics.mean(per_step) / 1e9
-    sample = (f"one pass of M in {{1,4,16}} over one weight copy per step (3 linears); int8 x int4 integer port, "
+    value = REP * len(MS) * weight_bytes() / statistics.mean(per_step) / 1e9
+    sample = (f"{REP} passes of M in {{1,4,16}} over one weight copy per step ({3 * REP} linears); int8 x int4 integer port, "
               f"{port.kind}, OpenMP on {port.threads} threads")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": len(per_step), "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(per_step),
@@ -200,7 +202,7 @@ def run_reference(args) -> None:
 
 # DRAM bytes per launch of the dominant kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum), keyed by
 # instantiation; the capture and its command are summarised in profiles/linear_q4_kernel_int4_decode_gemv.md.
-NCU_DRAM_BYTES_PER_LAUNCH = {"M<=8": 28875776, "M=9..16": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"M<=8": 28874304, "M=9..16": 28927232}
 
 
 class L2Flush:
@@ -583,11 +585,20 @@ def main() -> None:
 
     # End to end through the host-buffer entry point: one library call per linear copies the activations from
     # pinned host memory, quantizes them, runs the linear and copies the result back to pinned host memory.
+    # The calls of a step are independent decode requests, so a serving loop spreads them over a few streams: the
+    # copies of one call overlap the kernels of another (every call still pays its own copy in and copy out).
+    E2E_STREAMS = [torch.cuda.Stream() for _ in range(4)]
+    host_ys = {(m, i): torch.empty(m, N_OUT).pin_memory() for m in MS for i in range(R)}
+
     def step_e2e():
+        n = 0
         for m in MS:
-            for lin in lins:
-                lin.forward_host(host_x[m], host_y[m])
-        torch.cuda.current_stream().synchronize()  # the step's results are on the host
+            for i, lin in enumerate(lins):
+                with torch.cuda.stream(E2E_STREAMS[n % len(E2E_STREAMS)]):
+                    lin.forward_host(host_x[m], host_ys[(m, i)])
+                n += 1
+        for st_ in E2E_STREAMS:
+            st_.synchronize()  # the step's results are on the host
 
     for _ in range(warmup):
         step()
@@ -674,7 +685,8 @@ def main() -> None:
                     "h2d_bytes_per_step": R * sum(m * K_IN * 4 for m in MS),
                     "d2h_bytes_per_step": R * sum(m * N_OUT * 4 for m in MS), "steps": e2e_steps,
                     "ms_per_step": ms_e2e / e2e_steps, "calls_per_step": len(MS) * R,
-                    "api": "LinearQ4.forward_host -> xn_mm_linear_q4_host (copy in, quantize rows, linear, copy out)"},
+                    "api": "LinearQ4.forward_host -> xn_mm_linear_q4_host (copy in, quantize rows, linear, copy out), "
+                           "calls spread round-robin over 4 streams"},
             "gpu_launches": args.steps * launches_per_step,
             "fp8_prefill_gemm": fp8_prefill,
             "f32_linear": f32_linear,
@@ -684,9 +696,10 @@ def main() -> None:
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}",
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH["M<=8"],
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the M <= 8 "
-                                           "instantiation (two of the three launches of a sweep)",
+                         "traffic": (2 * NCU_DRAM_BYTES_PER_LAUNCH["M<=8"] + NCU_DRAM_BYTES_PER_LAUNCH["M=9..16"]) / 3,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, recorded per "
+                                           "instantiation (M <= 8: 28874304 B, M = 16: 28927232 B) and weighted by the sweep's "
+                                           "launch mix (2 : 1); capture summarised in profiles/linear_q4_kernel_int4_decode_gemv.md",
                          "kernel": "linear_q4_kernel",
                          "algorithmic_bytes_per_launch": alg, "us_per_launch": launch_s * 1e6,
                          "per_m": {str(m): {"us_per_launch": per_m[m] * 1e6, "algorithmic_bytes": algorithmic_bytes(m),

@@ -157,8 +157,12 @@ def test_decode_attention_full_width_slice(xn, oracle, cuda):
     k = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
     v = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
     out = torch.empty(B, H * hd, dtype=torch.bfloat16, device=cuda)
-    xn._lib.check(xn.lib().xn_mm_decode_attention(out.data_ptr(), qkv.data_ptr(), 3 * H * hd, k.data_ptr(), v.data_ptr(), None,
-                                                  B, H, ctx, hd, 1 / math.sqrt(hd), torch.cuda.current_stream().cuda_stream))
+    L = xn.lib()
+    ws_bytes = int(L.xn_mm_decode_attention_workspace_bytes(B, H, ctx))
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=cuda)
+    xn._lib.check(L.xn_mm_decode_attention_split(out.data_ptr(), qkv.data_ptr(), 3 * H * hd, k.data_ptr(), v.data_ptr(), None,
+                                                 B, H, ctx, hd, 1 / math.sqrt(hd), ws.data_ptr(), ws_bytes,
+                                                 torch.cuda.current_stream().cuda_stream))
     q = qkv[:, : H * hd].double().view(B, H, hd)
     sc = torch.einsum("bhd,bhcd->bhc", q, k.double()) / math.sqrt(hd)
     ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(sc, -1), v.double()).reshape(B, H * hd).cpu().numpy()
