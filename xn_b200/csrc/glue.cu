@@ -124,6 +124,30 @@ template <typename T> __device__ __forceinline__ uint4 pack8(const T (&y)[8]) {
     for (int j = 0; j < 8; ++j) e[j] = y[j];
     return r;
 }
+// two 16-bit elements in one 32-bit word: widen, round a pair with one conversion, packed maximum
+template <typename T> __device__ __forceinline__ float2 unpack2(unsigned w);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(unsigned w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(unsigned w) { return __half22float2(*reinterpret_cast<const __half2 *>(&w)); }
+template <typename T> __device__ __forceinline__ unsigned pack2(float a, float b);
+template <> __device__ __forceinline__ unsigned pack2<__nv_bfloat16>(float a, float b) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const unsigned *>(&r);
+}
+template <> __device__ __forceinline__ unsigned pack2<__half>(float a, float b) {
+    const __half2 r = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const unsigned *>(&r);
+}
+template <typename T> __device__ __forceinline__ unsigned max2(unsigned a, unsigned b);
+template <> __device__ __forceinline__ unsigned max2<__nv_bfloat16>(unsigned a, unsigned b) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&a), *reinterpret_cast<const __nv_bfloat162 *>(&b));
+    return *reinterpret_cast<const unsigned *>(&r);
+}
+template <> __device__ __forceinline__ unsigned max2<__half>(unsigned a, unsigned b) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&b));
+    return *reinterpret_cast<const unsigned *>(&r);
+}
 // the e4m3 pieces of eight values already divided by the row scale
 __device__ __forceinline__ void store_pieces8(uint8_t *hi, uint8_t *lo, size_t off, const float (&yv)[8]) {
     uint8_t h[8], l[8];
@@ -639,55 +663,67 @@ softmax_causal_warp_kernel(T *dst, const T *src, size_t rows, size_t t_rows, siz
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
         const int idx = u * 32 + lane;
-        v[u] = (u * 256 < vis && idx < nvec && idx * 8 < vis) ? x[idx] : make_uint4(0, 0, 0, 0);
+        v[u] = (u * 256 < vis && idx * 8 < vis) ? x[idx] : make_uint4(0, 0, 0, 0);
     }
-    float mx = -INFINITY;
+    // the three passes work on 32-bit words of two elements: one conversion instruction rounds a pair, the running
+    // maximum is a packed maximum, and only the vector that straddles the horizon tests its columns one by one
+    unsigned m2 = pack2<T>(-INFINITY, -INFINITY);
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
         if (u * 256 >= vis) continue;
         const int c0 = (u * 32 + lane) * 8;
-        float f[8];
-        unpack8<T>(v[u], f);
-        T o[8];
+        unsigned w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        const bool edge = c0 + 8 > vis;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            o[j] = c0 + j < vis ? from_f32<T>(f[j] * scale) : from_f32<T>(-INFINITY);
-            mx = fmaxf(mx, to_f32(o[j]));
+        for (int p = 0; p < 4; ++p) {
+            float2 f = unpack2<T>(w[p]);
+            f.x *= scale;
+            f.y *= scale;
+            if (edge) {
+                if (c0 + 2 * p >= vis) f.x = -INFINITY;
+                if (c0 + 2 * p + 1 >= vis) f.y = -INFINITY;
+            }
+            w[p] = pack2<T>(f.x, f.y);
+            m2 = max2<T>(m2, w[p]);
         }
-        v[u] = pack8<T>(o);
+        v[u] = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    mx = warp_max(mx);
+    const float2 mm = unpack2<T>(m2);
+    const float mx = warp_max(fmaxf(mm.x, mm.y));
     float sum = 0.0f;
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
         if (u * 256 >= vis) continue;
-        float f[8];
-        unpack8<T>(v[u], f);
-        T o[8];
+        unsigned w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            // the exponential is rounded to a 16-bit type right away: the fast form (2^-21 relative) rounds to the same value
-            o[j] = f[j] == -INFINITY ? from_f32<T>(0.0f) : from_f32<T>(__expf(to_f32(from_f32<T>(f[j] - mx))));
-            sum += to_f32(o[j]);
+        for (int p = 0; p < 4; ++p) {
+            const float2 f = unpack2<T>(w[p]);
+            const float2 d = unpack2<T>(pack2<T>(f.x - mx, f.y - mx));
+            // the exponential is rounded to a 16-bit type right away: the fast form (2^-21 relative) rounds to the same
+            // value; a masked column holds -inf and comes out as zero
+            w[p] = pack2<T>(__expf(d.x), __expf(d.y));
+            const float2 e = unpack2<T>(w[p]);
+            sum += e.x;
+            sum += e.y;
         }
-        v[u] = pack8<T>(o);
+        v[u] = make_uint4(w[0], w[1], w[2], w[3]);
     }
     sum = warp_sum(sum);
+    const float inv = __fdividef(1.0f, sum);
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
         const int idx = u * 32 + lane;
         if (idx >= nvec || idx * 8 >= zend) continue;
-        T o[8];
+        unsigned w[4] = {0u, 0u, 0u, 0u};
         if (u * 256 < vis) {
-            float f[8];
-            unpack8<T>(v[u], f);
+            const unsigned s[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(__fdividef(f[j], sum));
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(0.0f);
+            for (int p = 0; p < 4; ++p) {
+                const float2 e = unpack2<T>(s[p]);
+                w[p] = pack2<T>(e.x * inv, e.y * inv);
+            }
         }
-        y[idx] = pack8<T>(o);
+        y[idx] = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
