@@ -20,6 +20,7 @@ N > 1   = one process per GPU, each with its own decode streams and a replica of
 
 Further keys of the line (each measured in this run, CUDA events, L2 flushed between timed launches):
   fp8_prefill_gemm         fp8-e4m3 transformer linears at M = 4096 (W8A8 and W8A16), TFLOP/s and roofline
+  int4_prefill_gemm        the benchmark's int4 weight with 256 / 1024 / 4096 activation rows (kind::i8 tensor-memory kernel)
   f32_linear               x [16,4096] * W [11264,4096]^T in f32 on the GPU, and the host-core baseline
   decode_step              the 32-layer decoder step, 32 streams per GPU
   prefill_column_parallel  (N > 1) the same linears with the weight rows split over the ranks and the
@@ -289,6 +290,30 @@ def measure_fp8_prefill(dev, flush, xn, torch) -> dict:
         out["library_fp8_gemm_4096x12288x4096_tflops"] = None
         out["library_fp8_note"] = f"torch._scaled_mm unavailable: {type(e).__name__}"
     return out
+
+
+def measure_q4_prefill(dev, flush, xn, torch) -> dict:
+    """The benchmark's int4 weight [11264, 4096] with many activation rows: one unpack of the q4 tiles plus one
+    launch of the kind::i8 tensor-memory kernel per call (both inside the timed region).  TOP/s counts 2*M*N*K."""
+    g = torch.Generator(device=dev).manual_seed(4)
+    w = torch.randn(N_OUT, K_IN, generator=g, device=dev) * 0.02
+    lin = xn.LinearQ4.from_weight(w)
+    del w
+    rows = []
+    for m in (256, 1024, 4096):
+        x = torch.randn(m, K_IN, generator=g, device=dev)
+        xq, xs = xn.quantize_rows_i8(x)
+        y = torch.empty(m, N_OUT, device=dev)
+        ms = time_launches(lambda: xn.linear_q4(xq, xs, lin.wq, N_OUT, out=y), 10, flush, torch)
+        tops = 2.0 * m * N_OUT * K_IN / (ms * 1e-3) / 1e12
+        rows.append({"m": m, "n": N_OUT, "k": K_IN, "us": ms * 1e3, "tops": tops,
+                     "decode_kernel_passes_us_estimate": (m // 16) * 8.1,
+                     "roofline": {"bound": "tensor", "achieved": tops, "peak": 4500.0, "unit": "TOP/s", "frac": tops / 4500.0,
+                                  "peak_kind": "nominal dense int8"}})
+        del x, xq, xs, y
+    return {"rows": rows,
+            "note": "one MMA per 32-element block with a hand-over to the CUDA cores for the f32 block scale: bound by the "
+                    "hand-over round trip and the per-block scaling, not by the tensor pipe"}
 
 
 def measure_f32_linear(dev, flush, xn, torch) -> dict:
@@ -631,6 +656,7 @@ def main() -> None:
     flush = L2Flush(dev)
     f32_linear = measure_f32_linear(dev, flush, xn, torch) if not args.no_extras else None
     fp8_prefill = measure_fp8_prefill(dev, flush, xn, torch) if not args.no_extras else None
+    q4_prefill = measure_q4_prefill(dev, flush, xn, torch) if not args.no_extras else None
     del flush
     torch.cuda.empty_cache()
     prefill_cp = None
@@ -689,6 +715,7 @@ def main() -> None:
                            "calls spread round-robin over 4 streams"},
             "gpu_launches": args.steps * launches_per_step,
             "fp8_prefill_gemm": fp8_prefill,
+            "int4_prefill_gemm": q4_prefill,
             "f32_linear": f32_linear,
             "prefill_column_parallel": prefill_cp,
             "prefill_stack": prefill_stack,

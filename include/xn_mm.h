@@ -173,8 +173,12 @@ int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype d
                            size_t k, void *stream);
 
 /* Device: y [m,n] f32 = int4 linear as specified above.  partials (optional, may be NULL)
- * receives the int32 block sums as [m][n][k/32].  Any m >= 1; rows are processed 16 at a
- * time with the weights streamed once per 16 rows. */
+ * receives the int32 block sums as [m][n][k/32].  Any m >= 1.  Up to 159 rows (and whenever partials is
+ * given) the rows are processed 16 at a time with the weights streamed once per 16 rows; from 160 rows on the
+ * tiles are unpacked once into library scratch (row-major int8 + block scales) and one launch of a
+ * tensor-memory kernel (tcgen05.mma kind::i8, one exact int32 block sum per MMA, scaled in f32 per block)
+ * serves all rows.  Same arithmetic on both routes; the f32 sum over the blocks may differ in order.
+ * xn_mm_linear_q8 below does the same. */
 int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
                     size_t n, size_t k, int32_t *partials, void *stream);
 

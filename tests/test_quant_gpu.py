@@ -237,6 +237,52 @@ def test_linear_q8_block_int8_weights(xn, oracle, cuda, m, n, k):
     assert oracle.rel_err(y.cpu().numpy(), want_y) < 1e-4
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m,n,k", [(160, 80, 512), (200, 200, 384), (300, 1000, 1024), (161, 41, 4096)])
+def test_linear_q_many_rows_tensor_memory_path(xn, oracle, cuda, bits, m, n, k):
+    """From 160 rows on the block-quantized linears unpack the weight once and run kind::i8 tensor-memory MMAs with
+    one hand-over per 32-block: f32 output within 1e-4 of the oracle and within 5e-5 of the decode kernel (f32 sums over the blocks in a different order) (which
+    the debug output of the block sums selects), exact linearity in the activation scales."""
+    rng = np.random.default_rng(bits * 1000 + m)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    q, s = (oracle.quantize_q4 if bits == 4 else oracle.quantize_q8)(w)
+    xq, xs = oracle.quantize_rows_i8(x)
+    want_y, want_p = oracle.linear_q(xq, xs, q, s)
+    packed = torch.from_numpy((oracle.pack_q4 if bits == 4 else oracle.pack_q8)(q, s)).to(cuda)
+    dxq, dxs = torch.from_numpy(xq).to(cuda), torch.from_numpy(xs).to(cuda)
+    linear = xn.linear_q4 if bits == 4 else xn.linear_q8
+    y = torch.full((m, n), float("nan"), device=cuda)
+    linear(dxq, dxs, packed, n, out=y)
+    part = torch.empty((m, n, k // 32), dtype=torch.int32, device=cuda)
+    y_decode = linear(dxq, dxs, packed, n, partials=part)
+    torch.cuda.synchronize()
+    assert np.array_equal(part.cpu().numpy(), want_p)
+    assert oracle.rel_err(y.cpu().numpy(), want_y) < 1e-4
+    assert oracle.rel_err(y.cpu().numpy(), y_decode.cpu().numpy()) < 5e-5
+    assert torch.equal(linear(dxq, dxs * 2, packed, n), y * 2)
+
+
+def test_linear_q4_prefill_size_matches_the_decode_kernel(xn, oracle, cuda):
+    """W [11264, 4096] int4, 1024 rows: the tensor-memory path against 64 passes of the decode kernel (whose block sums
+    are pinned bit for bit to the oracle at this size) and against the oracle itself on sampled rows."""
+    rng = np.random.default_rng(1)
+    n, k, m = 11264, 4096, 1024
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    lin = xn.LinearQ4.from_weight(torch.from_numpy(w).to(cuda))
+    xq, xs = xn.quantize_rows_i8(torch.from_numpy(x).to(cuda))
+    y = xn.linear_q4(xq, xs, lin.wq, n)
+    y_decode = torch.cat([xn.linear_q4(xq[i : i + 16], xs[i : i + 16], lin.wq, n) for i in range(0, m, 16)])
+    torch.cuda.synchronize()
+    assert oracle.rel_err(y.cpu().numpy(), y_decode.cpu().numpy()) < 2e-4  # two f32 summation orders over 128 blocks
+    rows = [0, 517, 1023]
+    q, s = oracle.quantize_q4(w)
+    oxq, oxs = oracle.quantize_rows_i8(x[rows])
+    want, _ = oracle.linear_q(oxq, oxs, q, s, want_partials=False)
+    assert oracle.rel_err(y[rows].cpu().numpy(), want) < 1e-4
+
+
 def test_quantized_checkpoint_feeds_the_kernels_unchanged(xn, oracle, cuda, tmp_path):
     """Weights quantized on the host, written to a quantized safetensors file, read back and uploaded as
     stored give bit-identical packed bytes to the device quantizers, and the linears run from them."""

@@ -826,6 +826,213 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Block-quantized integer weights with many activation rows: kind::i8 MMAs (s8 x s8 -> s32, exact) with one
+// hand-over per 32-element block.  The operands swap roles as in the skinny form: the 128 TMEM lanes carry 128
+// output channels (row-major int8 weights, unpacked from the q4 / q8 tiles by a pre-pass), the MMA's N dimension
+// BN activation rows.  Every MMA covers exactly one quantization block (32 bytes of k), starts from a zero
+// accumulator and is handed to the epilogue warps through a ring of 512 / BN tensor-memory buffers; each epilogue
+// thread owns one output channel and half of the tile's activation rows, turns the int32 block sums into floats
+// without the conversion unit and adds scale[channel, block] * sum to its f32 accumulators in block order -- the
+// arithmetic of the specification (exact int32 block sums, f32 sum over the blocks), so the result matches the
+// decode kernel's.  The tensor pipe idles most of the time by design: the kernel is bound by the CUDA-core work
+// per (channel, row, block), i.e. per 32 multiply-adds.
+// ---------------------------------------------------------------------------------------------
+struct QGemmArgs {
+    float *y;              // [MA, ldy] f32
+    int ldy;
+    const float *x_scale;  // [MA]
+    const float *w_scale;  // [n_pad, K / 32] row-major
+    int NW, NPAD;          // output channels, and the row count of the unpacked weights (multiple of 16)
+    int MA, K;
+    WaitCtx wait;
+};
+
+__host__ __device__ constexpr uint32_t instr_desc_i8(int n) {  // D = s32, A and B signed 8-bit, both K-major
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {  // D = A * B
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc)
+        : "memory");
+}
+// issue only: the caller waits once for all its loads
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
+// An int32 block sum plus 0x4B400000, read as a float, is 1.5 * 2^23 + sum exactly (|sum| <= 32 * 127 * 127 < 2^22):
+// one integer add per element and one packed subtraction per pair replace the integer-to-float conversion.
+constexpr uint32_t Q_MAGIC_I = 0x4B400000u;
+constexpr float Q_MAGIC_F = 12582912.0f;
+constexpr int Q_NTHREADS = 64 + 256;  // producer, MMA issuer, eight epilogue warps (two per tensor-memory lane quarter)
+
+template <int BN>
+__global__ void __launch_bounds__(Q_NTHREADS, 1)
+gemm_q8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const QGemmArgs args) {
+    constexpr int NACC = 512 / BN > 4 ? 4 : 512 / BN;   // accumulator buffers in flight
+    constexpr int W_BYTES = BM * BKB, X_BYTES = BN * BKB, STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr int NSTAGE = 4;
+    constexpr uint32_t IDESC = instr_desc_i8(BN);
+    constexpr int BPS = BKB / UMMA_KB;  // quantization blocks (= MMAs) per stage
+    constexpr int HALF = BN / 2;        // columns per epilogue warp
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full[NSTAGE], empty[NSTAGE], acc_full[NACC], acc_empty[NACC];
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_w = (args.NPAD + BM - 1) / BM, num_x = (args.MA + BN - 1) / BN;
+    const int num_tiles = num_w * num_x;
+    const int num_kb = args.K / BKB;
+    const int nblk = args.K / 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < NACC; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int x_blk = tile / num_w, w_blk = tile - x_blk * num_w;  // consecutive CTAs share the activation tile
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % NSTAGE;
+                    if (!mbar_wait(&empty[s], ((unsigned)(it / NSTAGE) & 1u) ^ 1u, args.wait)) { ok = false; break; }
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(st, &map_w, kb * BKB, w_blk * BM, &full[s]);
+                    tma_load_2d(st + W_BYTES, &map_x, kb * BKB, x_blk * BN, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0;
+            unsigned vt = 0;  // hand-overs so far
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+                    const int s = it % NSTAGE;
+                    if (!mbar_wait(&full[s], (unsigned)(it / NSTAGE) & 1u, args.wait)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+                    const uint64_t dw = smem_desc(st), dx = smem_desc(st + W_BYTES);
+                    for (int ks = 0; ks < BPS; ++ks, ++vt) {
+                        const unsigned a = vt % NACC;
+                        if (!mbar_wait(&acc_empty[a], ((vt / NACC) & 1u) ^ 1u, args.wait)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
+                        umma_i8(tmem_base + a * BN, dw + adv, dx + adv, IDESC);
+                        umma_commit(&acc_full[a]);
+                    }
+                    if (ok) umma_commit(&empty[s]);
+                }
+            }
+        }
+    } else {
+        const int q = warp & 3, half = warp >= 6 ? 1 : 0;  // tensor-memory lane quarter, column half
+        unsigned vt = 0;
+        bool ok = true;
+        unsigned long long neg2;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(neg2) : "f"(-Q_MAGIC_F), "f"(-Q_MAGIC_F));
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * HALF);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int x_blk = tile / num_w, w_blk = tile - x_blk * num_w;
+            const int ch = w_blk * BM + q * 32 + lane;  // this thread's output channel
+            const float4 *srow = reinterpret_cast<const float4 *>(args.w_scale + (size_t)(ch < args.NPAD ? ch : 0) * nblk);
+            unsigned long long acc2[HALF / 2];  // f32 pairs
+#pragma unroll
+            for (int i = 0; i < HALF / 2; ++i) acc2[i] = 0ull;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const float4 s4 = ch < args.NPAD ? __ldg(srow + kb) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float sc[BPS] = {s4.x, s4.y, s4.z, s4.w};
+                // The stage's BPS blocks x CPB 32-column chunks form one software pipeline: the tensor-memory load of
+                // chunk j + 1 is in flight while chunk j is scaled and added.
+                constexpr int CPB = HALF / 32, NCH = BPS * CPB;
+                uint32_t v[2][32];
+                if (!mbar_wait(&acc_full[vt % NACC], (vt / NACC) & 1u, args.wait)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tmem_ld32_nowait(lane_addr + (vt % NACC) * BN, v[0]);
+#pragma unroll
+                for (int j = 0; j < NCH; ++j) {
+                    const int ks = j / CPB, c = j % CPB;
+                    const unsigned a = (vt + ks) % NACC;
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c == CPB - 1) {  // the block has been read: its buffer goes back to the MMA issuer
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[a]);
+                    }
+                    if (j + 1 < NCH) {
+                        const int ks1 = (j + 1) / CPB, c1 = (j + 1) % CPB;
+                        const unsigned vt1 = vt + ks1, a1 = vt1 % NACC;
+                        if (c1 == 0) {
+                            if (!mbar_wait(&acc_full[a1], (vt1 / NACC) & 1u, args.wait)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        tmem_ld32_nowait(lane_addr + a1 * BN + c1 * 32, v[(j + 1) & 1]);
+                    }
+                    unsigned long long s2;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "f"(sc[ks]), "f"(sc[ks]));
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        unsigned long long p;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(v[j & 1][i] + Q_MAGIC_I), "r"(v[j & 1][i + 1] + Q_MAGIC_I));
+                        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(p) : "l"(p), "l"(neg2));
+                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(acc2[c * 16 + i / 2]) : "l"(s2), "l"(p), "l"(acc2[c * 16 + i / 2]));
+                    }
+                }
+                vt += BPS;
+            }
+            if (!ok) break;
+            if (ch < args.NW) {
+#pragma unroll
+                for (int i = 0; i < HALF; i += 2) {
+                    float a0, a1;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc2[i / 2]));
+                    const int row = x_blk * BN + half * HALF + i;  // 32 lanes = 32 consecutive channels of one activation row
+                    if (row < args.MA) args.y[(size_t)row * args.ldy + ch] = __ldg(args.x_scale + row) * a0;
+                    if (row + 1 < args.MA) args.y[(size_t)(row + 1) * args.ldy + ch] = __ldg(args.x_scale + row + 1) * a1;
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 // ---- host side ----
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1069,6 +1276,39 @@ int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ld
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, mw, mx0, mx1, a));
+    return XN_OK;
+}
+
+// y f32 [m, ldy] = x_scale[i] * sum over 32-blocks of scale[j, blk] * (int32 block sum of xq[i] . w8[j]); w8 is the
+// row-major int8 image [n_pad, k] of a q4 / q8 weight, w_scale its [n_pad, k / 32] block scales.
+int launch_gemm_q8_block(float *y, size_t ldy, const int8_t *xq, const float *x_scale, const int8_t *w8, const float *w_scale,
+                         size_t m, size_t n, size_t n_pad, size_t k, cudaStream_t st) {
+    QGemmArgs a{};
+    a.y = y; a.ldy = (int)ldy; a.x_scale = x_scale; a.w_scale = w_scale;
+    a.NW = (int)n; a.NPAD = (int)n_pad; a.MA = (int)m; a.K = (int)k;
+    if (int rcw = wait_ctx(&a.wait)) return rcw;
+    constexpr int bn = 128;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w8, 1, n_pad, k, k, BM);
+    if (rc) return rc;
+    rc = make_map(&mx, xq, 1, m, k, k, bn);
+    if (rc) return rc;
+    const size_t smem = (size_t)4 * (BM * BKB + bn * BKB) + 1024;
+    const long long tiles = (long long)((n_pad + BM - 1) / BM) * ((m + bn - 1) / bn);
+    const int sms = sm_count();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
+    cfg.blockDim = dim3(Q_NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    auto kern = gemm_q8_block_kernel<bn>;
+    XN_ENSURE_SMEM(kern, smem);
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, mw, mx, a));
     return XN_OK;
 }
 

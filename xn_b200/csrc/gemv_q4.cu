@@ -526,6 +526,82 @@ int launch(float *y, const int8_t *xq, const float *x_scale, const void *wq, int
     return XN_OK;
 }
 
+// q4 / q8 tiles -> row-major int8 weights [n_pad, k] and row-major block scales [n_pad, k / 32]: the operand
+// images of the tensor-memory kernel that serves many activation rows.  One warp per 16-row x 128-k tile; the
+// tile is rebuilt in shared memory (row pitch 144 bytes: the 4-byte scatter is free of bank conflicts) and leaves
+// as whole 128-byte row segments.
+template <int BITS>
+__global__ void __launch_bounds__(256)
+unpack_q_tiles_kernel(int8_t *__restrict__ w8, float *__restrict__ scales, const unsigned char *__restrict__ wq, size_t tiles,
+                      int nsb, size_t k) {
+    constexpr int UNIT = Tile<BITS>::UNIT, W = Tile<BITS>::W, PITCH = 144;
+    __shared__ __align__(16) unsigned char stage[8][16 * PITCH];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char *sm = stage[warp];
+    const int nblk = nsb * 4;
+    for (size_t tile = (size_t)blockIdx.x * 8 + warp; tile < tiles; tile += (size_t)gridDim.x * 8) {
+        const size_t band = tile / nsb;
+        const int kt = (int)(tile - band * nsb);
+        const unsigned char *u = wq + tile * UNIT;
+        if (BITS == 4) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int g = lane >> 2, t = lane & 3;
+                const uint4 c = *reinterpret_cast<const uint4 *>(u + (32 * h + lane) * 16);
+                const unsigned w[4] = {c.x, c.y, c.z, c.w};
+                unsigned char *row = sm + (8 * h + g) * PITCH;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned lo = w[j] & 0x0F0F0F0Fu, hi = (w[j] >> 4) & 0x0F0F0F0Fu;
+                    *reinterpret_cast<unsigned *>(row + 32 * j + 4 * t) = __vsub4(lo ^ 0x08080808u, 0x08080808u);
+                    *reinterpret_cast<unsigned *>(row + 32 * j + 16 + 4 * t) = __vsub4(hi ^ 0x08080808u, 0x08080808u);
+                }
+            }
+        } else {
+            const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 c = *reinterpret_cast<const uint4 *>(u + j * 512 + lane * 16);
+                *reinterpret_cast<unsigned *>(sm + g * PITCH + 32 * j + 4 * t) = c.x;
+                *reinterpret_cast<unsigned *>(sm + (g + 8) * PITCH + 32 * j + 4 * t) = c.y;
+                *reinterpret_cast<unsigned *>(sm + g * PITCH + 32 * j + 16 + 4 * t) = c.z;
+                *reinterpret_cast<unsigned *>(sm + (g + 8) * PITCH + 32 * j + 16 + 4 * t) = c.w;
+            }
+        }
+#pragma unroll
+        for (int e0 = 0; e0 < 64; e0 += 32) {
+            const int e = e0 + lane, h = e & 1, g = (e >> 1) >> 2, j = (e >> 1) & 3;
+            scales[(band * 16 + 8 * h + g) * nblk + kt * 4 + j] = *reinterpret_cast<const float *>(u + W + e * 4);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = it * 32 + lane, r = idx >> 3, piece = idx & 7;
+            *reinterpret_cast<uint4 *>(w8 + (band * 16 + r) * k + (size_t)kt * 128 + piece * 16) =
+                *reinterpret_cast<const uint4 *>(sm + r * PITCH + piece * 16);
+        }
+        __syncwarp();
+    }
+}
+
+// Many activation rows: unpack once, then the kind::i8 tensor-memory kernel (exact block sums, the same f32
+// arithmetic per block as the decode kernel).  The unpacked image lives in the stream's library scratch.
+template <int BITS>
+int linear_q_tensor(float *y, const int8_t *xq, const float *x_scale, const void *wq, size_t m, size_t n, size_t k, cudaStream_t st) {
+    const size_t n_pad = (n + 15) / 16 * 16, nblk = k / 32;
+    const size_t w_bytes = (n_pad * k + 255) / 256 * 256;
+    void *ws = nullptr;
+    if (int rc = library_scratch(st, w_bytes + n_pad * nblk * sizeof(float), &ws)) return rc;
+    int8_t *w8 = static_cast<int8_t *>(ws);
+    float *scales = reinterpret_cast<float *>(static_cast<unsigned char *>(ws) + w_bytes);
+    const size_t tiles = (n_pad / 16) * (k / 128);
+    const size_t blocks = (tiles + 7) / 8;
+    const unsigned grid = (unsigned)(blocks < (size_t)sm_count() * 16 ? blocks : (size_t)sm_count() * 16);
+    unpack_q_tiles_kernel<BITS><<<grid, 256, 0, st>>>(w8, scales, (const unsigned char *)wq, tiles, (int)(k / 128), k);
+    XN_CHECK_CUDA(cudaGetLastError());
+    return launch_gemm_q8_block(y, n, xq, x_scale, w8, scales, m, n, n_pad, k, st);
+}
+
 }  // namespace
 }  // namespace xn
 
@@ -541,6 +617,11 @@ static int linear_q(const char *name, float *y, const int8_t *xq, const float *x
     XN_REQUIRE(aligned(wq_packed, 16), "%s: packed weights must be 16-byte aligned", name);
     XN_REQUIRE(aligned(xq, 16), "%s: xq must be 16-byte aligned", name);
     cudaStream_t st = (cudaStream_t)stream;
+    // from this many rows on (and when the caller does not ask for the block sums), the weights are unpacked once
+    // and the tensor-memory kernel takes all rows in one launch instead of one weight pass per 16 rows (measured
+    // break-even on [4096, 4096] and [11264, 4096]: 128 to 160 rows)
+    static const size_t tensor_min_m = [] { const char *e = getenv("XN_Q_TENSOR_MIN_M"); return e ? (size_t)atoi(e) : (size_t)160; }();
+    if (!partials && m >= tensor_min_m && m <= 0x7fffffffull) return linear_q_tensor<BITS>(y, xq, x_scale, wq_packed, m, n, k, st);
     for (size_t i0 = 0; i0 < m; i0 += 16) {
         const int mc = (int)((m - i0) < 16 ? (m - i0) : 16);
         int32_t *pp = partials ? partials + i0 * n * (k / 32) : nullptr;
