@@ -126,3 +126,25 @@ def test_row_op_and_scatter_validation_on_the_host(xn):
     assert lib.xn_mm_linear_fp8_pieces_scatter(ptrs, 2, 40, 16, 1, 1, 1, 1, 1, 64, 32, 128, None) == 1
     assert b"do not fit" in lib.xn_mm_last_error()
     assert lib.xn_mm_linear_fp8_noalloc(None, None, None, None, 65, 16, 128, 0, None) == 2
+
+
+def test_entry_points_work_with_nvtx_ranges_switched_on():
+    """XN_MM_NVTX=1 wraps every entry point in an NVTX range; without a profiler attached the ranges are no-ops and
+    the host-only entry points behave as before (checked in a child process: the switch is read once)."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import ctypes as C, os\n"
+        "lib = C.CDLL(os.path.join(%r, 'xn_b200', 'libxn_mm.so'))\n"
+        "dims = (C.c_size_t * 2)(3, 4); st = (C.c_size_t * 2)(4, 1)\n"
+        "rd = (C.c_size_t * 2)(5, 4); rs = (C.c_size_t * 2)(4, 1)\n"
+        "out = (C.c_size_t * 16)()\n"
+        "rc = lib.xn_mm_matmul_plan(C.c_size_t(2), dims, st, C.c_size_t(2), rd, rs, 1, C.c_size_t(15), out)\n"
+        "assert rc == 0, rc\n"
+        "rc = lib.xn_mm_matmul_plan(C.c_size_t(2), dims, st, C.c_size_t(2), rd, rs, 0, C.c_size_t(15), out)\n"
+        "assert rc != 0\n"
+        "print('ok')\n" % root)
+    env = dict(os.environ, XN_MM_NVTX="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr

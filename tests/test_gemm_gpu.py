@@ -230,6 +230,31 @@ def test_dense_16bit_tensor_core_path(xn, oracle, cuda, dt, m, n, k):
     assert oracle.rel_err(got, truth) < TOL[dt]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(300, 1000, 512), (128, 72, 64), (4096, 4096, 1024)])
+def test_linear_bias_fused_in_the_tiled_epilogue(xn, oracle, cuda, dtype, m, n, k):
+    """nn::Linear with a bias and more than 64 rows: the tiled tensor-memory kernel adds the bias to the rounded
+    product in its epilogue (xn-core/src/nn/linear.rs:61-64 is matmul_t followed by broadcast_add: two roundings).
+    Bit-identical to the two-launch form."""
+    g = torch.Generator(device=cuda).manual_seed(m + k)
+    x = torch.randn(m, k, generator=g, device=cuda).to(dtype)
+    w = (torch.randn(n, k, generator=g, device=cuda) * 0.05).to(dtype)
+    b = torch.randn(n, generator=g, device=cuda).to(dtype)
+    y = xn.Linear(w, b)(x)
+    y_plain = xn.Linear(w)(x)
+    y0 = y_plain.clone()
+    xn._lib.check(xn.lib().xn_mm_add_bias(xn.ops._dtype_code(y0), y0.data_ptr(), y0.data_ptr(), b.data_ptr(), m, n,
+                                          torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(y, y0)
+    # the product itself against f64 (the sum with the bias cancels for some elements, and two 16-bit roundings of
+    # a cancelling sum are not within 1e-2 of anything: that is the reference's arithmetic, reproduced exactly above)
+    rows = torch.arange(0, m, max(1, m // 37), device=cuda)
+    ref = (x[rows].double() @ w.double().t()).cpu().numpy()
+    assert oracle.rel_err(y_plain[rows].float().cpu().numpy(), ref) < 1e-2
+    assert torch.equal(y, (y_plain.float() + b.float()).to(dtype))
+
+
 def test_dense_16bit_views_with_row_pitch(xn, oracle, cuda):
     """narrow()-ed operands: row pitches larger than k, non-zero offsets (multiples of 8 elements)."""
     g = torch.Generator(device=cuda).manual_seed(5)

@@ -53,6 +53,16 @@ bool rhs_is_static() { return tl_rhs_static; }
 StaticRhsScope::StaticRhsScope(bool on) : prev(tl_rhs_static) { tl_rhs_static = on; }
 StaticRhsScope::~StaticRhsScope() { tl_rhs_static = prev; }
 
+static thread_local const void *tl_col_bias = nullptr;
+static thread_local bool tl_col_bias_taken = false;
+ColBiasScope::ColBiasScope(const void *bias) { tl_col_bias = bias; tl_col_bias_taken = false; }
+ColBiasScope::~ColBiasScope() { tl_col_bias = nullptr; tl_col_bias_taken = false; }
+bool ColBiasScope::taken() const { return tl_col_bias_taken; }
+const void *take_fused_col_bias() {
+    if (tl_col_bias) tl_col_bias_taken = true;
+    return tl_col_bias;
+}
+
 int ensure_dynamic_smem(const void *kernel, int *slot, size_t bytes) {
     int dev = 0;
     XN_CHECK_CUDA(cudaGetDevice(&dev));
@@ -176,6 +186,7 @@ extern "C" int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs
                           size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b,
                           size_t lhs_b_stride, size_t rhs_b_stride, size_t dst_cs, size_t dst_rs,
                           size_t lhs_cs, size_t lhs_rs, size_t rhs_cs, size_t rhs_rs, void *stream) {
+    XN_API_RANGE("xn_mm_gemm");
     // Backend::gemm's rhs is any tensor, possibly the output of the kernel just enqueued on this stream: no
     // kernel may read it ahead of its dependency wait.
     StaticRhsScope scope(false);
@@ -187,6 +198,7 @@ extern "C" int xn_mm_gemm_causal(int mode, size_t causal_offset, xn_dtype dtype,
                                  const void *rhs, size_t rhs_off, size_t m, size_t n, size_t k, size_t lhs_b, size_t lhs_b_stride,
                                  size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs, size_t rhs_cs,
                                  size_t rhs_rs, void *stream) {
+    XN_API_RANGE("xn_mm_gemm_causal");
     XN_REQUIRE(mode == 1 || mode == 2, "gemm_causal: mode %d (1 = scores q.k^T, 2 = values p.v)", mode);
     XN_REQUIRE(causal_offset <= 0x3fffffffull, "gemm_causal: offset too large");
     StaticRhsScope scope(false);
@@ -196,6 +208,7 @@ extern "C" int xn_mm_gemm_causal(int mode, size_t causal_offset, xn_dtype dtype,
 
 extern "C" int xn_mm_linear(xn_dtype dtype, void *y, const void *x, const void *weight, const void *bias_or_null, size_t m,
                             size_t n, size_t k, size_t ldx, size_t ldw, size_t ldy, void *stream) {
+    XN_API_RANGE("xn_mm_linear");
     if (!valid_dtype(dtype)) return fail(XN_ERR_UNSUPPORTED, "linear: GEMM not supported for dtype %d", (int)dtype);
     if (m == 0 || n == 0) return XN_OK;
     XN_REQUIRE(y && x && weight, "linear: null pointer (y=%p x=%p weight=%p)", y, x, weight);
@@ -204,7 +217,9 @@ extern "C" int xn_mm_linear(xn_dtype dtype, void *y, const void *x, const void *
     int rc;
     {
         StaticRhsScope scope(true);  // the weight is a parameter: weight-streaming kernels may prefetch it
+        ColBiasScope bias_scope(bias_or_null);  // the tiled tensor-memory kernel adds it in its epilogue
         rc = gemm_dispatch(dtype, y, x, 0, weight, 0, m, n, k, 1, m * ldx, 1, 1, ldy, 1, ldx, ldw, 1, stream);
+        if (bias_scope.taken()) return rc;
     }
     if (rc || !bias_or_null) return rc;
     if (ldy == n) return xn_mm_add_bias(dtype, y, y, bias_or_null, m, n, stream);
@@ -219,6 +234,7 @@ extern "C" int xn_mm_linear(xn_dtype dtype, void *y, const void *x, const void *
 extern "C" int xn_mm_matmul_plan(size_t lhs_rank, const size_t *lhs_dims, const size_t *lhs_strides,
                                  size_t rhs_rank, const size_t *rhs_dims, const size_t *rhs_strides,
                                  int rhs_t, size_t dst_capacity, size_t *out) {
+    XN_API_RANGE("xn_mm_matmul_plan");
     XN_REQUIRE(lhs_dims && lhs_strides && rhs_dims && rhs_strides && out, "matmul: null pointer");
     XN_REQUIRE(lhs_rank >= 2 && rhs_rank >= 2, "matmul requires at least 2D tensors, got lhs rank %zu, rhs rank %zu",
                lhs_rank, rhs_rank);
@@ -266,6 +282,7 @@ static inline size_t q4_scale_offset(size_t r, size_t blk, size_t k) {  // byte 
 }
 
 extern "C" int xn_mm_pack_q4_host(uint8_t *packed, const int8_t *q, const float *scales, size_t n, size_t k) {
+    XN_API_RANGE("xn_mm_pack_q4_host");
     XN_REQUIRE(k % 128 == 0, "pack_q4: k=%zu must be a multiple of 128", k);
     if (n == 0 || k == 0) return XN_OK;
     XN_REQUIRE(packed && q && scales, "pack_q4: null pointer");
@@ -285,6 +302,7 @@ extern "C" int xn_mm_pack_q4_host(uint8_t *packed, const int8_t *q, const float 
 }
 
 extern "C" int xn_mm_unpack_q4_host(int8_t *q, float *scales, const uint8_t *packed, size_t n, size_t k) {
+    XN_API_RANGE("xn_mm_unpack_q4_host");
     XN_REQUIRE(k % 128 == 0, "unpack_q4: k=%zu must be a multiple of 128", k);
     if (n == 0 || k == 0) return XN_OK;
     XN_REQUIRE(packed && q && scales, "unpack_q4: null pointer");
@@ -313,6 +331,7 @@ static inline size_t q8_scale_offset(size_t r, size_t blk, size_t k) {
 }
 
 extern "C" int xn_mm_pack_q8_host(uint8_t *packed, const int8_t *q, const float *scales, size_t n, size_t k) {
+    XN_API_RANGE("xn_mm_pack_q8_host");
     XN_REQUIRE(k % 128 == 0, "pack_q8: k=%zu must be a multiple of 128", k);
     if (n == 0 || k == 0) return XN_OK;
     XN_REQUIRE(packed && q && scales, "pack_q8: null pointer");
@@ -326,6 +345,7 @@ extern "C" int xn_mm_pack_q8_host(uint8_t *packed, const int8_t *q, const float 
 }
 
 extern "C" int xn_mm_unpack_q8_host(int8_t *q, float *scales, const uint8_t *packed, size_t n, size_t k) {
+    XN_API_RANGE("xn_mm_unpack_q8_host");
     XN_REQUIRE(k % 128 == 0, "unpack_q8: k=%zu must be a multiple of 128", k);
     if (n == 0 || k == 0) return XN_OK;
     XN_REQUIRE(packed && q && scales, "unpack_q8: null pointer");

@@ -51,6 +51,26 @@ struct StaticRhsScope {
     bool prev;
 };
 
+// NVTX range around a C-ABI entry point (host-side marker for timeline tools), off unless XN_MM_NVTX=1 is set
+// when the library is first used.  The NVTX v3 header resolves the tool's injection library at run time: no link
+// dependency, and a no-op without a tool attached.
+struct ApiRange {
+    explicit ApiRange(const char *name);
+    ~ApiRange();
+    bool on;
+};
+#define XN_API_RANGE(name) ::xn::ApiRange _xn_api_range(name)
+
+// A per-column bias offered to the next matmul launched on this thread (nn::Linear's bias).  The tiled tensor-memory
+// kernel adds it in its epilogue and calls take_fused_col_bias(); a route that cannot leaves it, and the caller
+// adds the bias with a launch of its own when `taken` is still false at the end of the scope.
+struct ColBiasScope {
+    explicit ColBiasScope(const void *bias);
+    ~ColBiasScope();
+    bool taken() const;
+};
+const void *take_fused_col_bias();  // the offered bias (null if none); marks it taken
+
 // Raises a kernel's dynamic shared-memory limit once per (kernel, device); later calls with a
 // size already covered cost one atomic load.  `slot` is a per-kernel table of 64 ints.
 int ensure_dynamic_smem(const void *kernel, int *slot, size_t bytes);

@@ -723,6 +723,7 @@ extern "C" int xn_mm_conv1d(xn_dtype dtype, void *dst, const void *src, const vo
                             size_t in_channels, size_t out_channels, size_t length, size_t out_length, size_t kernel_size,
                             size_t stride, size_t padding, size_t dilation, size_t groups, void *workspace,
                             size_t workspace_bytes, void *stream) {
+    XN_API_RANGE("xn_mm_conv1d");
     if (int rc = check_common(dst, src, kernel, dtype, batch, in_channels, out_channels, length, out_length, kernel_size,
                               stride, groups))
         return rc;
@@ -747,6 +748,7 @@ extern "C" int xn_mm_conv_transpose1d(xn_dtype dtype, void *dst, const void *src
                                       size_t out_length, size_t kernel_size, size_t stride, size_t padding,
                                       size_t output_padding, size_t groups, void *workspace, size_t workspace_bytes,
                                       void *stream) {
+    XN_API_RANGE("xn_mm_conv_transpose1d");
     if (int rc = check_common(dst, src, kernel, dtype, batch, in_channels, out_channels, length, out_length, kernel_size,
                               stride, groups))
         return rc;

@@ -183,6 +183,8 @@ struct GemmArgs {
     int a_batch_inner, b_batch_inner;  // the tensor map's dimension order is (k, batch, rows) instead of (k, rows, batch)
     int a_bcast;          // every batch entry multiplies the same A matrix (the A map then holds one matrix)
     const void *row_bias; // optional, not for fp8: added to every element of output row i (element type of y)
+    const void *col_bias; // optional, 16-bit kinds: bias[j] (element type of y) added to the ROUNDED product of column j and
+                          // rounded again -- nn::Linear's matmul followed by broadcast_add, bit for bit
     WaitCtx wait;         // bound and status word of the kernel's mbarrier waits
     int group_m;          // m blocks per rasterisation group (see tile_coords)
     int causal, causal_off;  // causal attention (16-bit kinds): 1 = q.k^T, tiles whose keys all lie beyond the last query row's
@@ -246,9 +248,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs &args, uint32_t tme
                 }
                 if (KIND == 2) {
                     __half2 h = __floats2half2_rn(f0, f1);
+                    if (args.col_bias) {
+                        const __half *cb = reinterpret_cast<const __half *>(args.col_bias);
+                        const float2 r = __half22float2(h);
+                        h = __floats2half2_rn(r.x + __half2float(cb[min(col0 + 2 * j, args.N - 1)]),
+                                              r.y + __half2float(cb[min(col0 + 2 * j + 1, args.N - 1)]));
+                    }
                     packed[j] = *reinterpret_cast<uint32_t *>(&h);
                 } else {
                     __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                    if (!F8 && args.col_bias) {
+                        const __nv_bfloat16 *cb = reinterpret_cast<const __nv_bfloat16 *>(args.col_bias);
+                        const float2 r = __bfloat1622float2(h);
+                        h = __floats2bfloat162_rn(r.x + __bfloat162float(cb[min(col0 + 2 * j, args.N - 1)]),
+                                                  r.y + __bfloat162float(cb[min(col0 + 2 * j + 1, args.N - 1)]));
+                    }
                     packed[j] = *reinterpret_cast<uint32_t *>(&h);
                 }
             }
@@ -1368,6 +1382,7 @@ int launch_gemm_tn_16bit(xn_dtype dt, void *dst, const void *lhs, const void *rh
     a.y[0] = dst; a.ndst = 1; a.col_offset = 0; a.batch = (int)batch; a.y_batch_stride = (long long)(m * n);
     a.M = (int)m; a.N = (int)n; a.K = (int)k; a.ldy = (int)ldd;
     a.causal = causal; a.causal_off = causal_off;
+    if (batch == 1 && !causal) a.col_bias = take_fused_col_bias();
     BatchGeom bg;
     bg.batch = batch; bg.a_stride = lhs_bs; bg.b_stride = rhs_bs;
     return dt == XN_BF16 ? launch_kind<1, 1>(lhs, nullptr, rhs, lda, ldb, a, st, bg)

@@ -639,11 +639,13 @@ static int linear_q(const char *name, float *y, const int8_t *xq, const float *x
 
 extern "C" int xn_mm_linear_q4(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
                                size_t n, size_t k, int32_t *partials, void *stream) {
+    XN_API_RANGE("xn_mm_linear_q4");
     return linear_q<4>("linear_q4", y, xq, x_scale, wq_packed, m, n, k, partials, stream);
 }
 
 extern "C" int xn_mm_linear_q8(float *y, const int8_t *xq, const float *x_scale, const void *wq_packed, size_t m,
                                size_t n, size_t k, int32_t *partials, void *stream) {
+    XN_API_RANGE("xn_mm_linear_q8");
     return linear_q<8>("linear_q8", y, xq, x_scale, wq_packed, m, n, k, partials, stream);
 }
 
@@ -657,6 +659,7 @@ extern "C" size_t xn_mm_linear_q4_host_workspace_bytes(size_t m, size_t n, size_
 
 extern "C" int xn_mm_linear_q4_host(float *y_host, const float *x_host, const void *wq_packed, size_t m, size_t n, size_t k,
                                     void *workspace, size_t workspace_bytes, void *stream) {
+    XN_API_RANGE("xn_mm_linear_q4_host");
     XN_REQUIRE(k > 0 && k % 128 == 0, "linear_q4_host: k=%zu must be a positive multiple of 128", k);
     if (m == 0 || n == 0) return XN_OK;
     XN_REQUIRE(y_host && x_host && wq_packed && workspace, "linear_q4_host: null pointer");

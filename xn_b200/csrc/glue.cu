@@ -761,6 +761,7 @@ using namespace xn;
 
 extern "C" int xn_mm_rms_norm(xn_dtype dtype, void *dst, const void *src, const void *alpha, size_t rows, size_t cols,
                               float eps, void *stream) {
+    XN_API_RANGE("xn_mm_rms_norm");
     XN_REQUIRE(valid_dtype(dtype), "rms_norm: unknown dtype %d", (int)dtype);
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(dst && src && alpha, "rms_norm: null pointer");
@@ -777,6 +778,7 @@ extern "C" int xn_mm_rms_norm(xn_dtype dtype, void *dst, const void *src, const 
 extern "C" int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *dst_or_null,
                                          const void *src, const void *alpha, xn_dtype dtype, size_t rows, size_t cols,
                                          float eps, void *stream) {
+    XN_API_RANGE("xn_mm_rms_norm_split_e4m3");
     XN_REQUIRE(valid_dtype(dtype), "rms_norm_split: unknown dtype %d", (int)dtype);
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && src && alpha, "rms_norm_split: null pointer");
@@ -793,6 +795,7 @@ extern "C" int xn_mm_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_
 extern "C" int xn_mm_add_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *sum_out, const void *a,
                                              const void *b, const void *alpha, xn_dtype dtype, size_t rows, size_t cols,
                                              float eps, void *stream) {
+    XN_API_RANGE("xn_mm_add_rms_norm_split_e4m3");
     XN_REQUIRE(valid_dtype(dtype), "add_rms_norm_split: unknown dtype %d", (int)dtype);
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && sum_out && a && b && alpha, "add_rms_norm_split: null pointer");
@@ -807,6 +810,7 @@ extern "C" int xn_mm_add_rms_norm_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float
 }
 
 extern "C" int xn_mm_softmax(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t cols, void *stream) {
+    XN_API_RANGE("xn_mm_softmax");
     XN_REQUIRE(valid_dtype(dtype), "softmax: unknown dtype %d", (int)dtype);
     if (rows == 0 || cols == 0) return XN_OK;
     XN_REQUIRE(dst && src, "softmax: null pointer");
@@ -819,6 +823,7 @@ extern "C" int xn_mm_softmax(xn_dtype dtype, void *dst, const void *src, size_t 
 }
 
 extern "C" int xn_mm_silu_mul(xn_dtype dtype, void *dst, const void *src, size_t rows, size_t hidden, void *stream) {
+    XN_API_RANGE("xn_mm_silu_mul");
     XN_REQUIRE(valid_dtype(dtype), "silu_mul: unknown dtype %d", (int)dtype);
     if (rows == 0 || hidden == 0) return XN_OK;
     XN_REQUIRE(dst && src, "silu_mul: null pointer");
@@ -833,6 +838,7 @@ extern "C" int xn_mm_silu_mul(xn_dtype dtype, void *dst, const void *src, size_t
 
 extern "C" int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const void *src,
                                          xn_dtype dtype, size_t rows, size_t hidden, void *stream) {
+    XN_API_RANGE("xn_mm_silu_mul_split_e4m3");
     XN_REQUIRE(valid_dtype(dtype), "silu_mul_split: unknown dtype %d", (int)dtype);
     if (rows == 0 || hidden == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && src, "silu_mul_split: null pointer");
@@ -846,6 +852,7 @@ extern "C" int xn_mm_silu_mul_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_
 }
 
 extern "C" int xn_mm_add(xn_dtype dtype, void *dst, const void *a, const void *b, size_t len, void *stream) {
+    XN_API_RANGE("xn_mm_add");
     XN_REQUIRE(valid_dtype(dtype), "add: unknown dtype %d", (int)dtype);
     if (len == 0) return XN_OK;
     XN_REQUIRE(dst && a && b, "add: null pointer");
@@ -883,6 +890,7 @@ __global__ void __launch_bounds__(256) add_bias_kernel(T *dst, const T *src, con
 
 extern "C" int xn_mm_add_bias(xn_dtype dtype, void *dst, const void *src, const void *bias, size_t rows, size_t cols,
                               void *stream) {
+    XN_API_RANGE("xn_mm_add_bias");
     XN_REQUIRE(valid_dtype(dtype), "add_bias: unknown dtype %d", (int)dtype);
     const size_t len = rows * cols;
     if (len == 0) return XN_OK;
@@ -898,6 +906,7 @@ extern "C" int xn_mm_add_bias(xn_dtype dtype, void *dst, const void *src, const 
 extern "C" int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, size_t src_batch_stride,
                                const int64_t *index, size_t batch, size_t heads, size_t context, size_t head_dim,
                                void *stream) {
+    XN_API_RANGE("xn_mm_kv_append");
     XN_REQUIRE(valid_dtype(dtype), "kv_append: unknown dtype %d", (int)dtype);
     const size_t total = batch * heads * head_dim;
     if (total == 0) return XN_OK;
@@ -990,6 +999,7 @@ extern "C" int xn_mm_decode_attention_split(void *out_bf16, const void *q_bf16, 
                                             const void *k_cache_bf16, const void *v_cache_bf16, const float *mask_or_null,
                                             size_t batch, size_t heads, size_t context, size_t head_dim, float scale,
                                             void *workspace, size_t workspace_bytes, void *stream) {
+    XN_API_RANGE("xn_mm_decode_attention_split");
     return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
                                  context, head_dim, scale, workspace, workspace_bytes, true, stream);
 }
@@ -999,6 +1009,7 @@ extern "C" int xn_mm_decode_attention_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, f
                                                  const void *v_cache_bf16, const float *mask_or_null, size_t batch,
                                                  size_t heads, size_t context, size_t head_dim, float scale, void *workspace,
                                                  size_t workspace_bytes, void *stream) {
+    XN_API_RANGE("xn_mm_decode_attention_split_e4m3");
     XN_REQUIRE(x_hi && x_scale, "decode_attention_split_e4m3: null pointer");
     XN_REQUIRE(aligned(x_hi, 4) && (!x_lo || aligned(x_lo, 4)), "decode_attention_split_e4m3: pieces must be 4-byte aligned");
     return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
@@ -1008,6 +1019,7 @@ extern "C" int xn_mm_decode_attention_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, f
 extern "C" int xn_mm_kv_append2(xn_dtype dtype, void *k_cache, void *v_cache, const void *k_src, const void *v_src,
                                 size_t src_batch_stride, const int64_t *index, size_t batch, size_t heads, size_t context,
                                 size_t head_dim, void *stream) {
+    XN_API_RANGE("xn_mm_kv_append2");
     XN_REQUIRE(valid_dtype(dtype), "kv_append2: unknown dtype %d", (int)dtype);
     const size_t total = batch * heads * head_dim;
     if (total == 0) return XN_OK;
@@ -1025,12 +1037,14 @@ extern "C" int xn_mm_decode_attention(void *out_bf16, const void *q_bf16, size_t
                                       const void *k_cache_bf16, const void *v_cache_bf16, const float *mask_or_null,
                                       size_t batch, size_t heads, size_t context, size_t head_dim, float scale,
                                       void *stream) {
+    XN_API_RANGE("xn_mm_decode_attention");
     return decode_attention_impl(out_bf16, q_bf16, q_batch_stride, k_cache_bf16, v_cache_bf16, mask_or_null, batch, heads,
                                  context, head_dim, scale, nullptr, 0, false, stream);
 }
 
 extern "C" int xn_mm_softmax_causal(xn_dtype dtype, void *dst, const void *src, size_t batch, size_t t_rows, size_t context,
                                     float scale, int zero_fill_all, void *stream) {
+    XN_API_RANGE("xn_mm_softmax_causal");
     XN_REQUIRE(valid_dtype(dtype), "softmax_causal: unknown dtype %d", (int)dtype);
     if (batch == 0 || t_rows == 0 || context == 0) return XN_OK;
     XN_REQUIRE(dst && src, "softmax_causal: null pointer");
@@ -1067,6 +1081,7 @@ extern "C" int xn_mm_softmax_causal(xn_dtype dtype, void *dst, const void *src, 
 
 extern "C" int xn_mm_scatter_columns(void *const *dsts, size_t num_dst, int multicast, size_t ldy_bytes, size_t col_offset_bytes,
                                      const void *src, size_t m, size_t row_bytes, size_t groups, void *stream) {
+    XN_API_RANGE("xn_mm_scatter_columns");
     XN_REQUIRE(num_dst >= 1 && num_dst <= 8, "scatter_columns: %zu destinations (1..8 supported)", num_dst);
     XN_REQUIRE(!multicast || num_dst == 1, "scatter_columns: a multicast address is one destination");
     if (m == 0 || row_bytes == 0) return XN_OK;

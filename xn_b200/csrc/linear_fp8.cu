@@ -27,6 +27,7 @@ using namespace xn;
 extern "C" int xn_mm_linear_fp8_pieces(void *y_bf16, const uint8_t *x_hi, const uint8_t *x_lo,
                                        const float *x_scale, const uint8_t *wq, const float *w_scale,
                                        size_t m, size_t n, size_t k, void *stream) {
+    XN_API_RANGE("xn_mm_linear_fp8_pieces");
     XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8: k=%zu must be a positive multiple of 16", k);
     XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull, "linear_fp8: dimension too large");
     if (m == 0 || n == 0) return XN_OK;
@@ -52,6 +53,7 @@ extern "C" int xn_mm_linear_fp8_pieces_scatter(void *const *y_dsts, size_t num_d
                                                const uint8_t *x_hi, const uint8_t *x_lo, const float *x_scale,
                                                const uint8_t *wq, const float *w_scale, size_t m, size_t n, size_t k,
                                                void *stream) {
+    XN_API_RANGE("xn_mm_linear_fp8_pieces_scatter");
     XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_scatter: k=%zu must be a positive multiple of 16", k);
     XN_REQUIRE(num_dst >= 1 && num_dst <= 8, "linear_fp8_scatter: %zu destinations (1..8 supported)", num_dst);
     XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull && ldy <= 0x7ffffff0ull, "linear_fp8_scatter: dimension too large");
@@ -69,6 +71,7 @@ extern "C" int xn_mm_linear_fp8_pieces_scatter(void *const *y_dsts, size_t num_d
 extern "C" int xn_mm_linear_fp8_pieces_multicast(void *y_multicast, size_t ldy, size_t col_offset, const uint8_t *x_hi,
                                                  const uint8_t *x_lo, const float *x_scale, const uint8_t *wq,
                                                  const float *w_scale, size_t m, size_t n, size_t k, void *stream) {
+    XN_API_RANGE("xn_mm_linear_fp8_pieces_multicast");
     XN_REQUIRE(k > 0 && k % 16 == 0, "linear_fp8_multicast: k=%zu must be a positive multiple of 16", k);
     XN_REQUIRE(k <= 0x7ffffff0ull && n <= 0x7ffffff0ull && ldy <= 0x7ffffff0ull, "linear_fp8_multicast: dimension too large");
     XN_REQUIRE(col_offset + n <= ldy, "linear_fp8_multicast: columns [%zu, %zu) do not fit a row of %zu", col_offset,
@@ -91,6 +94,7 @@ extern "C" size_t xn_mm_linear_fp8_workspace_bytes(size_t m, size_t k) {
 extern "C" int xn_mm_linear_fp8(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
                                 size_t m, size_t n, size_t k, int variant, void *workspace,
                                 size_t workspace_bytes, void *stream) {
+    XN_API_RANGE("xn_mm_linear_fp8");
     XN_REQUIRE(variant == 0 || variant == 1, "linear_fp8: variant must be 0 (W8A16) or 1 (W8A8), got %d", variant);
     if (m == 0 || n == 0) return XN_OK;
     XN_REQUIRE(workspace && aligned(workspace, 256), "linear_fp8: workspace must be a 256-byte aligned device buffer");
@@ -157,6 +161,7 @@ extern "C" size_t xn_mm_linear_fp8_noalloc_max_elems(void) { return NOALLOC_MAX_
 
 extern "C" int xn_mm_linear_fp8_noalloc(void *y_bf16, const void *x_bf16, const uint8_t *wq, const float *w_scale,
                                         size_t m, size_t n, size_t k, int variant, void *stream) {
+    XN_API_RANGE("xn_mm_linear_fp8_noalloc");
     XN_REQUIRE(variant == 0 || variant == 1, "linear_fp8_noalloc: variant must be 0 (W8A16) or 1 (W8A8), got %d",
                variant);
     if (m > NOALLOC_MAX_ROWS || (k != 0 && m > NOALLOC_MAX_ELEMS / k))

@@ -204,6 +204,7 @@ using namespace xn;
 
 extern "C" int xn_mm_quantize_rows_i8(int8_t *xq, float *x_scale, const void *x, xn_dtype dtype,
                                       size_t m, size_t k, void *stream) {
+    XN_API_RANGE("xn_mm_quantize_rows_i8");
     XN_REQUIRE(valid_dtype(dtype), "quantize_rows_i8: unknown dtype %d", (int)dtype);
     if (m == 0 || k == 0) return XN_OK;
     XN_REQUIRE(xq && x_scale && x, "quantize_rows_i8: null pointer");
@@ -219,6 +220,7 @@ extern "C" size_t xn_mm_q4_packed_bytes(size_t n, size_t k) { return ((n + 15) /
 
 extern "C" int xn_mm_quantize_weights_q4(void *wq_packed, const void *w, xn_dtype dtype, size_t n, size_t k,
                                          void *stream) {
+    XN_API_RANGE("xn_mm_quantize_weights_q4");
     XN_REQUIRE(valid_dtype(dtype), "quantize_weights_q4: unknown dtype %d", (int)dtype);
     XN_REQUIRE(k % 128 == 0 && k > 0, "quantize_weights_q4: k=%zu must be a positive multiple of 128", k);
     if (n == 0) return XN_OK;
@@ -240,6 +242,7 @@ extern "C" size_t xn_mm_q8_packed_bytes(size_t n, size_t k) { return ((n + 15) /
 
 extern "C" int xn_mm_quantize_weights_q8(void *wq_packed, const void *w, xn_dtype dtype, size_t n, size_t k,
                                          void *stream) {
+    XN_API_RANGE("xn_mm_quantize_weights_q8");
     XN_REQUIRE(valid_dtype(dtype), "quantize_weights_q8: unknown dtype %d", (int)dtype);
     XN_REQUIRE(k % 128 == 0 && k > 0, "quantize_weights_q8: k=%zu must be a positive multiple of 128", k);
     if (n == 0) return XN_OK;
@@ -258,6 +261,7 @@ extern "C" int xn_mm_quantize_weights_q8(void *wq_packed, const void *w, xn_dtyp
 
 extern "C" int xn_mm_quantize_weights_fp8(uint8_t *wq, float *w_scale, const void *w, xn_dtype dtype,
                                           size_t n, size_t k, void *stream) {
+    XN_API_RANGE("xn_mm_quantize_weights_fp8");
     XN_REQUIRE(valid_dtype(dtype), "quantize_weights_fp8: unknown dtype %d", (int)dtype);
     if (n == 0 || k == 0) return XN_OK;
     XN_REQUIRE(wq && w_scale && w, "quantize_weights_fp8: null pointer");
@@ -271,6 +275,7 @@ extern "C" int xn_mm_quantize_weights_fp8(uint8_t *wq, float *w_scale, const voi
 
 extern "C" int xn_mm_split_rows_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, const void *x,
                                      xn_dtype dtype, size_t m, size_t k, void *stream) {
+    XN_API_RANGE("xn_mm_split_rows_e4m3");
     XN_REQUIRE(valid_dtype(dtype), "split_rows_e4m3: unknown dtype %d", (int)dtype);
     if (m == 0 || k == 0) return XN_OK;
     XN_REQUIRE(x_hi && x_scale && x, "split_rows_e4m3: null pointer");

@@ -11,9 +11,22 @@
 #include <vector>
 
 #include "common.cuh"
+#include <nvtx3/nvToolsExt.h>
 #include "wait.cuh"
 
 namespace xn {
+
+static bool nvtx_enabled() {
+    static const bool on = [] { const char *e = getenv("XN_MM_NVTX"); return e && atoi(e) != 0; }();
+    return on;
+}
+ApiRange::ApiRange(const char *name) : on(nvtx_enabled()) {
+    if (on) nvtxRangePushA(name);
+}
+ApiRange::~ApiRange() {
+    if (on) nvtxRangePop();
+}
+
 namespace {
 
 constexpr int MAX_DEV = 64;
@@ -159,6 +172,7 @@ int library_scratch(cudaStream_t st, size_t bytes, void **out) {
 using namespace xn;
 
 extern "C" int xn_mm_device_status(unsigned *timeouts_out) {
+    XN_API_RANGE("xn_mm_device_status");
     int dev = 0;
     if (int rc = current_device(&dev)) return rc;
     volatile unsigned *w = g_status[dev];
@@ -169,6 +183,7 @@ extern "C" int xn_mm_device_status(unsigned *timeouts_out) {
 }
 
 extern "C" int xn_mm_clear_device_status(void) {
+    XN_API_RANGE("xn_mm_clear_device_status");
     int dev = 0;
     if (int rc = current_device(&dev)) return rc;
     XN_CHECK_CUDA(cudaDeviceSynchronize());
@@ -181,6 +196,7 @@ extern "C" int xn_mm_clear_device_status(void) {
 }
 
 extern "C" int xn_mm_release_scratch(void *stream, int all_streams) {
+    XN_API_RANGE("xn_mm_release_scratch");
     int dev = 0;
     if (int rc = current_device(&dev)) return rc;
     XN_CHECK_CUDA(cudaDeviceSynchronize());
@@ -207,6 +223,7 @@ extern "C" int xn_mm_release_scratch(void *stream, int all_streams) {
 }
 
 extern "C" int xn_mm_selftest_wait_timeout(unsigned long long limit_ns, void *stream) {
+    XN_API_RANGE("xn_mm_selftest_wait_timeout");
     WaitCtx w;
     if (int rc = wait_ctx(&w)) return rc;
     XN_REQUIRE(limit_ns > 0 && limit_ns <= WAIT_LIMIT_NS, "selftest: limit_ns=%llu outside (0, %llu]", limit_ns, WAIT_LIMIT_NS);
