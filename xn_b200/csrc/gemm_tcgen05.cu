@@ -3,12 +3,13 @@
 // the reference sends to cublasGemmStridedBatchedEx (xn-core/src/cuda_backend.rs:2109-2133).
 // Written for sm_100a: TMA (cp.async.bulk.tensor, no multicast) stages 128-byte-swizzled tiles in
 // shared memory, one elected thread issues tcgen05.mma with the accumulators in tensor memory, and
-// four epilogue warps read them back with tcgen05.ld.
+// the epilogue warps read them back with tcgen05.ld.
 //
 //   warp 0      producer: TMA loads into a ring of NSTAGE stages, mbarrier full/empty pairs
 //   warp 1      tensor-memory allocation; MMA issue; tcgen05.commit releases stages / publishes tiles
-//   warps 2..5  epilogue: TMEM -> registers -> scale/convert -> global (each warp owns the 32 TMEM
-//               lanes of its warp-id-mod-4 quarter)
+//   warps 2..9  epilogue: TMEM -> registers -> scale/convert -> shared-memory transpose -> global (each warp owns
+//               the 32 TMEM lanes of its warp-id-mod-4 quarter and half of the tile's columns; the tf32 kind,
+//               whose epilogue keeps a row of the tile in registers, runs with warps 2..5 only)
 //
 // The kernel is persistent (grid = #SMs, tiles round-robin) and keeps two accumulator buffers in
 // TMEM so the epilogue of one tile overlaps the MMAs of the next.
@@ -20,7 +21,7 @@
 //   BF16 / F16: kind::f16, the epilogue rounds the f32 accumulator to the element type.
 //   TF32 pieces: kind::tf32 on f32 words already on the tf32 grid, f32 out.  Callers carry f32 precision by
 //               laying three such pieces per operand along k (gemm_f32_tc.cu, conv1d.cu).  The accumulator is
-//               handed to the epilogue every 16 k stages and summed in registers, because tcgen05
+//               handed to the epilogue every 2 k stages and summed in registers, because tcgen05
 //               accumulates with truncation (see KCH in the kernel); tiles are at most 128 columns wide.
 // Batches: a third tensor-map dimension (strided-batched and grouped calls, split-k chunks), optionally with
 // one A matrix shared by every batch entry (the convolutions' packed taps) and a per-row bias.
@@ -141,6 +142,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// issue only: the caller waits once for all its loads
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -192,6 +206,7 @@ struct GemmArgs {
                           // loop of a row tile stops at that horizon (the probabilities beyond it are zero and never read)
     int mc;               // y[0] is an NVLink multicast address: one multimem.st per 16 bytes reaches every GPU's copy
     int b_mn;             // 16-bit kinds: B is [K, N] with n contiguous (MN-major); its map is (n, k, batch), box 64 x BK
+    int fast_store;       // one destination, no multicast, and every 16-byte output chunk of an interior tile is aligned
 };
 
 __device__ __forceinline__ bool tile_masked(const GemmArgs &a, int m_blk, int n_blk, int bn) {
@@ -204,13 +219,18 @@ __device__ __forceinline__ int tile_kb(const GemmArgs &a, int m_blk, int num_kb,
     return kb < 1 ? 1 : min(kb, num_kb);
 }
 
-// Epilogue of one output tile for the fp8 / bf16 / f16 kinds: this warp's 32 accumulator rows (tensor-memory lanes
-// 32 q .. 32 q + 31 of buffer `acc`, output rows m_row0 + 32 q ..) x BN columns are scaled / biased, rounded to the
-// output type, transposed through the warp's shared-memory slab and stored as whole row segments into every
-// destination.
+// Epilogue of one output tile for the fp8 / bf16 / f16 kinds.  Eight warps share a tile: warp (q, half) owns the
+// 32 accumulator rows of tensor-memory lane quarter q (output rows m_row0 + 32 q ..) and the 32-column chunks
+// [c_begin, c_end) of buffer `acc`.  Two chunks at a time are loaded together, scaled / biased, rounded to the
+// output type, transposed through the warp's 4 KB shared-memory slab (16-byte pieces XOR-swizzled by row) and
+// stored as 128-byte row segments into every destination.  With one warp per scheduler the epilogue of a
+// 128 x 256 tile took 4.7 us -- a chain of dependent instructions with nothing to overlap it -- which bounded every
+// product with few k stages per tile (attention's q.k^T: two stages); two warps per scheduler and both
+// tensor-memory loads of a group in flight bring it under the time of four k stages.
+constexpr int EPI_WARPS_16 = 8;  // epilogue warps of the fp8 / 16-bit kinds (the tf32 kind keeps four)
 template <int KIND, int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs &args, uint32_t tmem_base, int acc, int q, int lane, int m_row0,
-                                              int n_blk, int g, unsigned char *slab) {
+                                              int n_blk, int g, unsigned char *slab, int c_begin, int c_end) {
     constexpr bool F8 = KIND == 0;
     const int row = m_row0 + q * 32 + lane;
     float xs = 1.0f;
@@ -219,85 +239,120 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs &args, uint32_t tme
     if (!F8 && args.row_bias && row < args.M)
         rb = KIND == 2 ? __half2float(reinterpret_cast<const __half *>(args.row_bias)[row])
                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(args.row_bias)[row]);
-    // Column groups of GC: the warp's 32 x GC slab goes through shared memory (16-byte chunks
-    // XOR-swizzled by row) so that global stores are whole row segments of GC*2 bytes instead of
-    // 16 bytes per row -- this matters most when the destination is a peer GPU.
-    constexpr int OES = 2;                      // bytes per output element (the tf32 kind has its own epilogue above)
-    constexpr int EPC = 16 / OES;               // output elements per 16-byte chunk
-    constexpr int GC = BN % 128 == 0 ? 128 : (BN % 64 == 0 ? 64 : 32);  // columns per group (divides BN)
-    constexpr int CPR = GC / EPC;               // 16-byte chunks per slab row (a row is at most 256 bytes)
-    constexpr int RPI = 32 / CPR;               // rows written per store instruction
+    // Interior tiles of a plain single-destination launch (the host has checked the 16-byte alignment of every
+    // row segment) take a lean store loop: one address per warp and tile, no per-store bounds or alignment tests.
+    const bool fast = args.fast_store && m_row0 + BM <= args.M && (n_blk + 1) * BN <= args.N;
+    uint16_t *warp_out = reinterpret_cast<uint16_t *>(args.y[0]) + (size_t)g * args.y_batch_stride +
+                         (size_t)(m_row0 + q * 32) * args.ldy + args.col_offset + n_blk * BN;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-    for (int g0 = 0; g0 < BN; g0 += GC) {
-#pragma unroll 1
-        for (int c = 0; c < GC / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + g0 + c * 32), v);
-            const int col0 = n_blk * BN + g0 + c * 32;
-            uint32_t packed[16];
+    for (int c0 = c_begin; c0 < c_end; c0 += 2) {
+        const int nch = c_end - c0 < 2 ? 1 : 2;   // 32-column chunks in this group
+        const int cpr = nch * 4;                  // 16-byte pieces per slab row
+        const int row_bytes = nch * 64;
+        uint32_t v[2][32];
+        tmem_ld32_nowait(lane_addr + c0 * 32, v[0]);
+        if (nch == 2) tmem_ld32_nowait(lane_addr + c0 * 32 + 32, v[1]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                float f0 = __uint_as_float(v[2 * j]), f1 = __uint_as_float(v[2 * j + 1]);
-                if (F8) {
-                    const int c0 = min(col0 + 2 * j, args.N - 1), c1 = min(col0 + 2 * j + 1, args.N - 1);
-                    f0 = __ldg(args.w_scale + c0) * (xs * f0);
-                    f1 = __ldg(args.w_scale + c1) * (xs * f1);
-                } else {
-                    f0 += rb;
-                    f1 += rb;
+        for (int h = 0; h < 2; ++h) {
+            if (h >= nch) break;
+            const int col0 = n_blk * BN + (c0 + h) * 32;
+            uint32_t packed[16];
+            if (F8 && fast) {
+                const float4 *ws4 = reinterpret_cast<const float4 *>(args.w_scale + col0);
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 w = __ldg(ws4 + j4);
+                    const float f0 = w.x * (xs * __uint_as_float(v[h][4 * j4])), f1 = w.y * (xs * __uint_as_float(v[h][4 * j4 + 1]));
+                    const float f2 = w.z * (xs * __uint_as_float(v[h][4 * j4 + 2])), f3 = w.w * (xs * __uint_as_float(v[h][4 * j4 + 3]));
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(f0, f1), h1 = __floats2bfloat162_rn(f2, f3);
+                    packed[2 * j4] = *reinterpret_cast<uint32_t *>(&h0);
+                    packed[2 * j4 + 1] = *reinterpret_cast<uint32_t *>(&h1);
                 }
-                if (KIND == 2) {
-                    __half2 h = __floats2half2_rn(f0, f1);
-                    if (args.col_bias) {
+            } else if (F8) {  // edge tile or unaligned scales: one guarded scale load per column
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int i0 = min(col0 + 2 * j, args.N - 1), i1 = min(col0 + 2 * j + 1, args.N - 1);
+                    const float f0 = __ldg(args.w_scale + i0) * (xs * __uint_as_float(v[h][2 * j]));
+                    const float f1 = __ldg(args.w_scale + i1) * (xs * __uint_as_float(v[h][2 * j + 1]));
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                    packed[j] = *reinterpret_cast<uint32_t *>(&hh);
+                }
+            } else if (!args.col_bias) {  // plain product (rb is zero without a row bias): one conversion per pair
+                // (the branches on the kind of epilogue are taken once per chunk, outside the unrolled loops: tested
+                // per element they cost more than the conversions themselves)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float f0 = __uint_as_float(v[h][2 * j]) + rb, f1 = __uint_as_float(v[h][2 * j + 1]) + rb;
+                    if (KIND == 2) {
+                        __half2 hh = __floats2half2_rn(f0, f1);
+                        packed[j] = *reinterpret_cast<uint32_t *>(&hh);
+                    } else {
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                        packed[j] = *reinterpret_cast<uint32_t *>(&hh);
+                    }
+                }
+            } else {  // nn::Linear's bias: added to the rounded product, rounded again
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float f0 = __uint_as_float(v[h][2 * j]) + rb, f1 = __uint_as_float(v[h][2 * j + 1]) + rb;
+                    const int i0 = min(col0 + 2 * j, args.N - 1), i1 = min(col0 + 2 * j + 1, args.N - 1);
+                    if (KIND == 2) {
                         const __half *cb = reinterpret_cast<const __half *>(args.col_bias);
-                        const float2 r = __half22float2(h);
-                        h = __floats2half2_rn(r.x + __half2float(cb[min(col0 + 2 * j, args.N - 1)]),
-                                              r.y + __half2float(cb[min(col0 + 2 * j + 1, args.N - 1)]));
-                    }
-                    packed[j] = *reinterpret_cast<uint32_t *>(&h);
-                } else {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                    if (!F8 && args.col_bias) {
+                        const float2 r = __half22float2(__floats2half2_rn(f0, f1));
+                        __half2 hh = __floats2half2_rn(r.x + __half2float(cb[i0]), r.y + __half2float(cb[i1]));
+                        packed[j] = *reinterpret_cast<uint32_t *>(&hh);
+                    } else {
                         const __nv_bfloat16 *cb = reinterpret_cast<const __nv_bfloat16 *>(args.col_bias);
-                        const float2 r = __bfloat1622float2(h);
-                        h = __floats2bfloat162_rn(r.x + __bfloat162float(cb[min(col0 + 2 * j, args.N - 1)]),
-                                                  r.y + __bfloat162float(cb[min(col0 + 2 * j + 1, args.N - 1)]));
+                        const float2 r = __bfloat1622float2(__floats2bfloat162_rn(f0, f1));
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(r.x + __bfloat162float(cb[i0]), r.y + __bfloat162float(cb[i1]));
+                        packed[j] = *reinterpret_cast<uint32_t *>(&hh);
                     }
-                    packed[j] = *reinterpret_cast<uint32_t *>(&h);
                 }
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int chunk = (c * 4 + j) ^ (lane & (CPR - 1));
-                *reinterpret_cast<uint4 *>(slab + lane * (GC * OES) + chunk * 16) =
+                const int piece = (h * 4 + j) ^ (lane & (cpr - 1));
+                *reinterpret_cast<uint4 *>(slab + lane * row_bytes + piece * 16) =
                     make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
             }
         }
         __syncwarp();
-        const int sub = lane / CPR, ch = lane % CPR;  // this lane's row within a store instruction, chunk
+        const int sub = lane / cpr, pc = lane % cpr;  // this lane's row within a store instruction, 16-byte piece
+        const int rpi = 32 / cpr;                     // rows written per store instruction
+        if (fast) {
+            uint16_t *p = warp_out + (size_t)sub * args.ldy + c0 * 32 + pc * 8;
+            const size_t step = (size_t)rpi * args.ldy;
+#pragma unroll 4
+            for (int r = sub; r < 32; r += rpi) {
+                *reinterpret_cast<uint4 *>(p) = *reinterpret_cast<const uint4 *>(slab + r * row_bytes + ((pc ^ (r & (cpr - 1))) * 16));
+                p += step;
+            }
+        } else {
 #pragma unroll 1
-        for (int r0 = 0; r0 < 32; r0 += RPI) {
-            const int r = r0 + sub;
-            const uint4 val = *reinterpret_cast<const uint4 *>(slab + r * (GC * OES) + ((ch ^ (r & (CPR - 1))) * 16));
-            const int grow = m_row0 + q * 32 + r;
-            const int gcol = n_blk * BN + g0 + ch * EPC;
-            if (grow < args.M && gcol < args.N) {
-                for (int p = 0; p < args.ndst; ++p) {
-                    uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
-                                    (size_t)grow * args.ldy + args.col_offset + gcol;
-                    if (args.mc) {
-                        // the switch replicates the store into every GPU bound to the multicast object (the host
-                        // checked that n is a multiple of 8 and the rows are 16-byte aligned)
-                        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
-                                     "f"(__uint_as_float(val.x)), "f"(__uint_as_float(val.y)), "f"(__uint_as_float(val.z)),
-                                     "f"(__uint_as_float(val.w))
-                                     : "memory");
-                    } else if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                        *reinterpret_cast<uint4 *>(dst) = val;
-                    } else {
-                        const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
-                        for (int j = 0; j < 8 && gcol + j < args.N; ++j)
-                            dst[j] = (uint16_t)(w4[j >> 1] >> ((j & 1) * 16));
+            for (int r = sub; r < 32; r += rpi) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(slab + r * row_bytes + ((pc ^ (r & (cpr - 1))) * 16));
+                const int grow = m_row0 + q * 32 + r;
+                const int gcol = n_blk * BN + c0 * 32 + pc * 8;
+                if (grow < args.M && gcol < args.N) {
+                    for (int p = 0; p < args.ndst; ++p) {
+                        uint16_t *dst = reinterpret_cast<uint16_t *>(args.y[p]) + (size_t)g * args.y_batch_stride +
+                                        (size_t)grow * args.ldy + args.col_offset + gcol;
+                        if (args.mc) {
+                            // the switch replicates the store into every GPU bound to the multicast object (the host
+                            // checked that n is a multiple of 8 and the rows are 16-byte aligned)
+                            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                                         "f"(__uint_as_float(val.x)), "f"(__uint_as_float(val.y)), "f"(__uint_as_float(val.z)),
+                                         "f"(__uint_as_float(val.w))
+                                         : "memory");
+                        } else if (gcol + 8 <= args.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                            *reinterpret_cast<uint4 *>(dst) = val;
+                        } else {
+                            const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                            for (int j = 0; j < 8 && gcol + j < args.N; ++j)
+                                dst[j] = (uint16_t)(w4[j >> 1] >> ((j & 1) * 16));
+                        }
                     }
                 }
             }
@@ -309,7 +364,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs &args, uint32_t tme
 // KIND: 0 = fp8 pieces -> bf16 out, 1 = bf16 -> bf16, 2 = f16 -> f16, 3 = tf32 operands (f32 words already on
 // the tf32 grid) -> f32 out
 template <int KIND, int BN, int NA, int NSTAGE>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(KIND == 3 ? NTHREADS : 64 + 32 * EPI_WARPS_16, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                     const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
     constexpr bool F8 = KIND == 0;
@@ -334,7 +389,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char *epi_smem = smem + (size_t)NSTAGE * STAGE_BYTES;  // 4 epilogue slabs of 32 rows x 256 bytes
+    unsigned char *epi_smem = smem + (size_t)NSTAGE * STAGE_BYTES;  // epilogue slabs: 8 x 4 KB (fp8 / 16-bit kinds) or 4 x 8 KB (tf32 kind)
     __shared__ __align__(8) uint64_t full[NSTAGE], empty[NSTAGE], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_slot;
 
@@ -346,7 +401,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], KIND == 3 ? 4 : EPI_WARPS_16); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -552,7 +607,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
             if (!mbar_wait(&tmem_full[acc], acc_ph, args.wait)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            epilogue_tile<KIND, BN>(args, tmem_base, acc, q, lane, m_blk * BM, n_blk, g, epi_smem + (size_t)(warp - 2) * 32 * 256);
+            // warps 2-5 take the first half of the tile's 32-column chunks, warps 6-9 the second (odd counts: one more first)
+            constexpr int NCHUNK = BN / 32, FIRST = (NCHUNK + 1) / 2;
+            const int half = (warp - 2) >> 2;
+            epilogue_tile<KIND, BN>(args, tmem_base, acc, q, lane, m_blk * BM, n_blk, g, epi_smem + (size_t)(warp - 2) * 4096,
+                                    half ? FIRST : 0, half ? NCHUNK : FIRST);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -872,19 +931,6 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t a_desc, uint64
         "l"(a_desc), "l"(b_desc), "r"(idesc)
         : "memory");
 }
-// issue only: the caller waits once for all its loads
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t *v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-        "%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr));
-}
-
 // An int32 block sum plus 0x4B400000, read as a float, is 1.5 * 2^23 + sum exactly (|sum| <= 32 * 127 * 127 < 2^22):
 // one integer add per element and one packed subtraction per pair replace the integer-to-float conversion.
 constexpr uint32_t Q_MAGIC_I = 0x4B400000u;
@@ -1151,6 +1197,10 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
         args2.group_m = gm < num_m ? gm : num_m;
         if (args2.group_m < 1) args2.group_m = 1;
     }
+    args2.fast_store = (args.ndst == 1 && !args.mc && args.ldy % 8 == 0 && args.col_offset % 8 == 0 &&
+                        args.y_batch_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(args.y[0]) & 15) == 0 &&
+                        (KIND != 0 || (reinterpret_cast<uintptr_t>(args.w_scale) & 15) == 0))
+                           ? 1 : 0;
     const size_t a_batch = args.a_bcast ? 1 : bg.batch;
     int rc = make_map3(&ma0, a0, ELEM, args.M, args.K, lda, BM, a_batch, bg.a_stride, &args2.a_batch_inner);
     if (rc) return rc;
@@ -1171,7 +1221,7 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     const int grid = (int)(tiles < sms ? tiles : sms);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(NTHREADS);
+    cfg.blockDim = dim3(KIND == 3 ? NTHREADS : 64 + 32 * EPI_WARPS_16);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
