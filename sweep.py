@@ -317,7 +317,7 @@ def write_md(rows, path, what="all"):
     fg = [r for r in rows if r.get("config") == "f32_gemm"]
     if fg:
         L += ["## f32 matmul_t beyond 16 rows (up to 64 rows: 3xTF32 weight-streaming kernel in passes of 16 rows; beyond: three tf32"
-              " pieces per operand on kind::tf32, repack passes included, accumulator promoted to f32 registers every 64 MMAs,"
+              " pieces per operand on kind::tf32, repack passes included, accumulator handed to f32 registers every 8 MMAs with a second-level total in tensor memory,"
               " split-k for few tiles; 125x1024x4096 is the shape of the reference's CPU benchmark)", "",
               "| M x N x K | µs | TFLOP/s | cuBLAS SGEMM (no TF32) µs | TFLOP/s |", "|---|---|---|---|---|"]
         for r in fg:
