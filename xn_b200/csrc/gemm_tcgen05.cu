@@ -206,6 +206,8 @@ struct GemmArgs {
                           // loop of a row tile stops at that horizon (the probabilities beyond it are zero and never read)
     int mc;               // y[0] is an NVLink multicast address: one multimem.st per 16 bytes reaches every GPU's copy
     int b_mn;             // 16-bit kinds: B is [K, N] with n contiguous (MN-major); its map is (n, k, batch), box 64 x BK
+    int rows2;            // NA = 2 instantiations: the two A tiles are rows [256 i, +128) and [256 i + 128, +128) of ONE matrix
+                          // (a 256 x BN tile: both accumulator buffers belong to one tile, the B stage is read by two MMAs)
     int fast_store;       // one destination, no multicast, and every 16-byte output chunk of an interior tile is aligned
 };
 
@@ -394,7 +396,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_m = (args.M + BM - 1) / BM, num_n = (args.N + BN - 1) / BN;
+    const int BMT = (NA == 2 && args.rows2) ? 2 * BM : BM;  // rows of A per tile
+    const int num_m = (args.M + BMT - 1) / BMT, num_n = (args.N + BN - 1) / BN;
     const int tiles_per_batch = num_m * num_n;
     const int num_tiles = tiles_per_batch * args.batch;
     const int num_kb = (args.K + BK - 1) / BK;
@@ -438,10 +441,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                     unsigned char *st = smem + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
                     const int ga = args.a_bcast ? 0 : g;
-                    const int ay = args.a_batch_inner ? ga : m_blk * BM, az = args.a_batch_inner ? m_blk * BM : ga;
+                    const int ay = args.a_batch_inner ? ga : m_blk * BMT, az = args.a_batch_inner ? m_blk * BMT : ga;
                     const int by = args.b_batch_inner ? g : n_blk * BN, bz = args.b_batch_inner ? n_blk * BN : g;
                     tma_load_3d(st, &map_a0, kb * BK, ay, az, &full[s]);
-                    if (NA == 2) tma_load_3d(st + A_BYTES, &map_a1, kb * BK, ay, az, &full[s]);
+                    if (NA == 2) {
+                        const int second = args.rows2 ? BM : 0;  // the second A tile: the next 128 rows, or the second piece
+                        tma_load_3d(st + A_BYTES, &map_a1, kb * BK, args.a_batch_inner ? ay : ay + second,
+                                    args.a_batch_inner ? az + second : az, &full[s]);
+                    }
                     if (args.b_mn) {
                         // one 64-column block (64 n x BK k, 8 KB) per copy
                         for (int i = 0; i < BN / 64; ++i)
@@ -467,8 +474,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                 nkb = tile_kb(args, m_blk, num_kb, BK);
             }
             for (int kb0 = 0; (kb0 < nkb || kb0 == 0) && ok; kb0 += KCH, ++vt) {
-                const int acc = vt & 1;
-                const unsigned acc_ph = (unsigned)(vt >> 1) & 1u;
+                const bool rows2 = NA == 2 && args.rows2;  // both buffers belong to this tile: one barrier pair, phase per tile
+                const int acc = rows2 ? 0 : (vt & 1);
+                const unsigned acc_ph = rows2 ? ((unsigned)vt & 1u) : ((unsigned)(vt >> 1) & 1u);
                 if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, args.wait)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -492,7 +500,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
                             umma_tf32(d_tmem, da0 + adv, db + adv, IDESC, kb > kb0 || ks != 0);
                         } else {
                             umma<F8>(d_tmem, da0 + adv, db + ks * badv, idesc, (kb | ks) != 0);
-                            if (NA == 2) umma<F8>(d_tmem, da1 + adv, db + ks * badv, idesc, 1u);
+                            if (NA == 2) umma<F8>(rows2 ? d_tmem + BN : d_tmem, da1 + adv, db + ks * badv, idesc, rows2 ? (uint32_t)((kb | ks) != 0) : 1u);
                         }
                     }
                     umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
@@ -603,15 +611,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             int m_blk, n_blk;
             tile_coords(tin, num_m, num_n, args.group_m, m_blk, n_blk);
             if (tile_masked(args, m_blk, n_blk, BN)) continue;
-            const int acc = t_local & 1;
-            const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
+            const bool rows2 = NA == 2 && args.rows2;
+            const int acc = rows2 ? 0 : (t_local & 1);
+            const unsigned acc_ph = rows2 ? ((unsigned)t_local & 1u) : ((unsigned)(t_local >> 1) & 1u);
             if (!mbar_wait(&tmem_full[acc], acc_ph, args.wait)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // warps 2-5 take the first half of the tile's 32-column chunks, warps 6-9 the second (odd counts: one more first)
             constexpr int NCHUNK = BN / 32, FIRST = (NCHUNK + 1) / 2;
             const int half = (warp - 2) >> 2;
-            epilogue_tile<KIND, BN>(args, tmem_base, acc, q, lane, m_blk * BM, n_blk, g, epi_smem + (size_t)(warp - 2) * 4096,
+            epilogue_tile<KIND, BN>(args, tmem_base, acc, q, lane, m_blk * BMT, n_blk, g, epi_smem + (size_t)(warp - 2) * 4096,
                                     half ? FIRST : 0, half ? NCHUNK : FIRST);
+            if (rows2)  // rows 128..255 of the tile sit in the second buffer
+                epilogue_tile<KIND, BN>(args, tmem_base, 1, q, lane, m_blk * BMT + BM, n_blk, g, epi_smem + (size_t)(warp - 2) * 4096,
+                                        half ? FIRST : 0, half ? NCHUNK : FIRST);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -1188,10 +1200,11 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
         // there.  Operands that fit in L2 together (about half of its 126 MB, leaving room for the output) keep the
         // plain m-fastest order, which measured 2-4 % faster on them (4096^3: 104.5 vs 108.5 us).
         static const int force_gm = [] { const char *e = getenv("XN_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
-        const int num_m = (args.M + BM - 1) / BM;
+        const int bmt = (NA == 2 && args.rows2) ? 2 * BM : BM;
+        const int num_m = (args.M + bmt - 1) / bmt;
         int gm = 1;
-        while ((gm + 1) * (gm + 1) * BM <= sm_count() * BN) ++gm;
-        const double operand_bytes = ((double)args.M * (NA) + (double)args.N) * (double)args.K * ELEM;
+        while ((gm + 1) * (gm + 1) * bmt <= sm_count() * BN) ++gm;
+        const double operand_bytes = ((double)args.M * ((NA == 2 && !args.rows2) ? 2 : 1) + (double)args.N) * (double)args.K * ELEM;
         if (operand_bytes <= 64.0 * 1024 * 1024) gm = num_m;
         if (force_gm > 0) gm = force_gm;
         args2.group_m = gm < num_m ? gm : num_m;
@@ -1216,7 +1229,8 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     auto kern = gemm_tcgen05_kernel<KIND, BN, NA, NSTAGE>;
     const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 4 * 32 * 256 + 1024;
     XN_ENSURE_SMEM(kern, smem);
-    const long long tiles = (long long)((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) * args.batch;
+    const int bmt_rows = (NA == 2 && args.rows2) ? 2 * BM : BM;
+    const long long tiles = (long long)((args.M + bmt_rows - 1) / bmt_rows) * ((args.N + BN - 1) / BN) * args.batch;
     const int sms = sm_count();
     const int grid = (int)(tiles < sms ? tiles : sms);
     cudaLaunchConfig_t cfg = {};
@@ -1253,6 +1267,28 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
     if (force_bn >= 64 && force_bn <= 256 && force_bn % bn_step == 0) best = force_bn;
+    if constexpr ((KIND == 1 || KIND == 2) && NA == 1) {
+        // 256 x 256 tiles (two row blocks share every B stage; both accumulator buffers belong to one tile) when the
+        // problem is large enough to fill the machine with them.  A k stage of a 128 x 256 tile moves 96 KB through
+        // shared memory for 512 tensor cycles (the SM moves 128 B per clock: 0.67 of the tensor rate); the 256-row tile
+        // moves 160 KB for 1024 cycles (0.8) at the price of an epilogue that is no longer hidden behind the next tile.
+        // Measured: bf16 4096^3 105.2 -> 97.0 us, 8192^3 794 -> 712 us (cuBLAS 93 / 690 us); a 256-row tile costs 1.84 x
+        // a 128-row one, which is what the wave count below is weighed with.  The fp8 kinds stay on 128-row tiles: W8A8
+        // runs under the power cap and measured slower with the exposed epilogue (qkv at 4096 rows 152 -> 168 us).
+        static const int force_rows2 = [] { const char *e = getenv("XN_GEMM_ROWS2"); return e ? atoi(e) : -1; }();
+        if (best == 256 && !args.causal && !args.a_bcast && args.ndst == 1 && !args.mc) {
+            const long long n_tiles = (args.N + 255) / 256;
+            const long long t1 = m_tiles * n_tiles, t2 = (long long)((args.M + 2 * BM - 1) / (2 * BM)) * args.batch * n_tiles;
+            const double c1 = (double)((t1 + sms - 1) / sms) * 1.0, c2 = (double)((t2 + sms - 1) / sms) * 1.84;
+            bool rows2 = t2 >= sms && args.K >= 1024 && c2 < 0.97 * c1;
+            if (force_rows2 >= 0) rows2 = force_rows2 != 0;
+            if (rows2) {
+                GemmArgs a2 = args;
+                a2.rows2 = 1;
+                return launch_cfg<KIND, 256, 2>(a0, a0, b, lda, ldb, a2, st, bg);
+            }
+        }
+    }
     if constexpr (KIND == 3) {
         // the tf32 kind is instantiated up to 128 columns (its epilogue holds a row of the tile in registers)
         best = 128;
