@@ -102,6 +102,17 @@ int xn_mm_gemm(xn_dtype dtype, void *dst, const void *lhs, size_t lhs_off, const
                size_t rhs_b_stride, size_t dst_cs, size_t dst_rs, size_t lhs_cs, size_t lhs_rs,
                size_t rhs_cs, size_t rhs_rs, void *stream);
 
+/* Causal attention over a block of query rows as one kernel (prefill): for every head h < heads and query row i < t_rows,
+ *   out[i][128 h .. 128 h + 127] = softmax_j(scale * q[i,h,:] . k[j,h,:]) v[j,h,:]   over the keys j <= i + (context - t_rows),
+ * the block of xn-moshi/src/batched_transformer.rs:174-190 (matmul_t, scale, mask, softmax, matmul) for t_rows > 1.
+ * q is [t_rows][heads][128], k and v are [context][heads][128]: row pitch `ld` elements, heads `head_stride` elements
+ * apart (the three slices of a fused qkv projection, or separate tensors); out row pitch ldo.  bf16 / f16, head_dim
+ * 128.  Scores and probabilities stay on the SM (tensor memory and shared memory): f32 scores, exact row maximum,
+ * probabilities rounded to the element type before the product with v, f32 row sums, one division at the end. */
+int xn_mm_attention_prefill(xn_dtype dtype, void *out, size_t ldo, const void *q, const void *k, const void *v,
+                            size_t ld, size_t head_stride, size_t heads, size_t head_dim, size_t t_rows, size_t context,
+                            float scale, void *stream);
+
 /* The two batched matmuls of causal attention over a block of query rows (xn-moshi/src/batched_transformer.rs:175,
  * 190, with the mask IndicesAndMask builds): key j is visible to query row i iff j <= i + causal_offset
  * (causal_offset = context - rows).  Same arguments and arithmetic as xn_mm_gemm; what differs is the work skipped:

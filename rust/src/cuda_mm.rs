@@ -40,6 +40,9 @@ extern "C" {
         rhs: *const c_void, rhs_off: usize, m: usize, n: usize, k: usize, lhs_b: usize, lhs_b_stride: usize,
         rhs_b_stride: usize, dst_cs: usize, dst_rs: usize, lhs_cs: usize, lhs_rs: usize, rhs_cs: usize,
         rhs_rs: usize, stream: *mut c_void) -> c_int;
+    pub fn xn_mm_attention_prefill(dtype: XnDtype, out: *mut c_void, ldo: usize, q: *const c_void,
+        k: *const c_void, v: *const c_void, ld: usize, head_stride: usize, heads: usize, head_dim: usize,
+        t_rows: usize, context: usize, scale: f32, stream: *mut c_void) -> c_int;
     pub fn xn_mm_gemm_causal(mode: c_int, causal_offset: usize, dtype: XnDtype, dst: *mut c_void,
         lhs: *const c_void, lhs_off: usize, rhs: *const c_void, rhs_off: usize, m: usize, n: usize, k: usize,
         lhs_b: usize, lhs_b_stride: usize, rhs_b_stride: usize, dst_cs: usize, dst_rs: usize, lhs_cs: usize,

@@ -72,12 +72,14 @@ def test_batched_matmuls_over_per_head_views_of_a_fused_projection(xn, oracle, c
     assert oracle.rel_err(o.float().cpu().numpy(), ref2) < 1e-2
 
 
-def test_prefill_stack_reduced_size_vs_float64(xn, oracle, cuda):
+@pytest.mark.parametrize("fused", [True, False])
+def test_prefill_stack_reduced_size_vs_float64(xn, oracle, cuda, fused):
     """2 layers, d_model 512 (4 heads), FFN hidden 1408, 192 tokens, one rank: the device stack against a float64
-    restatement built from the same quantized weights (causal attention, gated SiLU FFN, pre-norm residuals)."""
+    restatement built from the same quantized weights (causal attention, gated SiLU FFN, pre-norm residuals); with
+    the attention as one kernel and as the q.k^T / softmax / p.v sequence."""
     from xn_b200.prefill import PrefillStack
     L, d, H, hid, T = 2, 512, 4, 1408, 192
-    st = PrefillStack(L, d, H, hid, T, cuda, seed=4)
+    st = PrefillStack(L, d, H, hid, T, cuda, seed=4, fused_attention=fused)
     g = torch.Generator(device=cuda).manual_seed(9)
     x = torch.randn(T, d, generator=g, device=cuda).bfloat16()
     y = st.forward(x).float().cpu().numpy()
@@ -146,3 +148,36 @@ def test_causal_attention_matmuls_skip_only_what_is_masked(xn, oracle, cuda, T, 
     assert oracle.rel_err(out.float().cpu().numpy(), ref) < 1e-2
     with pytest.raises(xn.XnError):   # the values form has no fallback that could read the unwritten tail
         xn.ops.matmul_causal_(torch.empty(H, T, 128, device=cuda), p.float(), v.float(), False, 2, off)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,T,ctx", [(2, 128, 128), (3, 300, 300), (2, 130, 400), (4, 1024, 1024), (1, 64, 64)])
+def test_fused_prefill_attention_against_f64(xn, cuda, dtype, H, T, ctx):
+    """xn_mm_attention_prefill: causal attention over a block of query rows in one kernel, per-head views of a fused
+    qkv buffer (heads interleaved within a row), against softmax(q k^T / sqrt(d)) v in f64.  Probabilities are
+    rounded to the element type before the product with v, as in the unfused sequence."""
+    from xn_b200.ops import attention_prefill_
+    hd = 128
+    g = torch.Generator(device=cuda).manual_seed(H * 1000 + T)
+    qkv = torch.randn(ctx, 3 * H * hd, generator=g, device=cuda).to(dtype)
+    v4 = qkv.view(ctx, 3, H, hd)
+    q = v4[ctx - T:, 0].transpose(0, 1)        # [H, T, hd]: the last T positions are the queries
+    k, v = v4[:, 1].transpose(0, 1), v4[:, 2].transpose(0, 1)
+    out = torch.full((T, H * hd), float("nan"), dtype=dtype, device=cuda)
+    scale = 1.0 / math.sqrt(hd)
+    attention_prefill_(out, q, k, v, scale)
+    torch.cuda.synchronize()
+    assert not torch.isnan(out).any()
+    s = torch.einsum("htd,hcd->htc", q.double(), k.double()) * scale
+    i = torch.arange(T, device=cuda)[:, None] + (ctx - T)
+    j = torch.arange(ctx, device=cuda)[None, :]
+    s = s.masked_fill(j > i, float("-inf"))
+    ref = torch.einsum("htc,hcd->thd", torch.softmax(s, dim=-1), v.double()).reshape(T, H * hd)
+    err = (out.double() - ref).abs()
+    rms = ref.pow(2).mean().sqrt()
+    # error of every element relative to |ref| + rms, and the rms error relative to the rms
+    e_max, e_rms = float((err / (ref.abs() + rms)).max()), float(err.pow(2).mean().sqrt() / rms)
+    print("fused attention", dtype, H, T, ctx, "max", e_max, "rms", e_rms)
+    # rounding of the probabilities and of the output to the element type is all there is: measured 0.012 / 0.0022 (bf16,
+    # 8 mantissa bits, the maximum over 5e5 elements) and 0.0013 / 0.00028 (f16, 11 bits)
+    assert (e_max < 2e-2 and e_rms < 4e-3) if dtype == torch.bfloat16 else (e_max < 3e-3 and e_rms < 6e-4)

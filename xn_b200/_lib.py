@@ -74,6 +74,7 @@ SIGNATURES = {
     "xn_mm_kv_append2": (_i, [_i, _p, _p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _p]),
     "xn_mm_softmax_causal": (_i, [_i, _p, _p, _sz, _sz, _sz, C.c_float, _i, _p]),
     "xn_mm_gemm_causal": (_i, [_i, _sz, _i, _p, _p, _sz, _p, _sz] + [_sz] * 12 + [_p]),
+    "xn_mm_attention_prefill": (_i, [_i, _p, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, C.c_float, _p]),
     "xn_mm_scatter_columns": (_i, [_p, _sz, _i, _sz, _sz, _p, _sz, _sz, _sz, _p]),
     "xn_mm_linear_fp8_noalloc_max_elems": (_sz, []),
     "xn_mm_linear_fp8_noalloc": (_i, [_p, _p, _p, _p, _sz, _sz, _sz, _i, _p]),

@@ -356,3 +356,20 @@ extern "C" int xn_mm_unpack_q8_host(int8_t *q, float *scales, const uint8_t *pac
     }
     return XN_OK;
 }
+
+extern "C" int xn_mm_attention_prefill(xn_dtype dtype, void *out, size_t ldo, const void *q, const void *k, const void *v,
+                                       size_t ld, size_t head_stride, size_t heads, size_t head_dim, size_t t_rows,
+                                       size_t context, float scale, void *stream) {
+    XN_API_RANGE("xn_mm_attention_prefill");
+    XN_REQUIRE(dtype == XN_BF16 || dtype == XN_F16, "attention_prefill: 16-bit element types only (dtype %d)", (int)dtype);
+    XN_REQUIRE(head_dim == 128, "attention_prefill: head_dim %zu (128 supported)", head_dim);
+    if (heads == 0 || t_rows == 0) return XN_OK;
+    XN_REQUIRE(out && q && k && v, "attention_prefill: null pointer");
+    XN_REQUIRE(context >= t_rows && context <= 0x3fffffffull && heads <= 65535,
+               "attention_prefill: context %zu must be at least the %zu query rows", context, t_rows);
+    XN_REQUIRE(ld % 8 == 0 && head_stride % 8 == 0 && ldo % 8 == 0 && ldo >= heads * 128 && aligned(out, 16) && aligned(q, 16) &&
+                   aligned(k, 16) && aligned(v, 16),
+               "attention_prefill: pointers, row pitches and the head stride must be multiples of 16 bytes");
+    XN_REQUIRE(head_stride >= 128 || heads == 1, "attention_prefill: heads overlap (head stride %zu)", head_stride);
+    return launch_attention_prefill(dtype, out, ldo, q, k, v, ld, head_stride, heads, t_rows, context, scale, (cudaStream_t)stream);
+}

@@ -154,6 +154,9 @@ int launch_gemm_tn_tf32(float *dst, const float *lhs, const float *rhs, size_t m
 // int8 x int8 -> int32 block sums on kind::i8 tensor-memory MMAs, scaled per 32-block in f32 (q4 / q8 weights, many rows)
 int launch_gemm_q8_block(float *y, size_t ldy, const int8_t *xq, const float *x_scale, const int8_t *w8, const float *w_scale,
                          size_t m, size_t n, size_t n_pad, size_t k, cudaStream_t st);
+// fused causal attention over a block of query rows (prefill), head_dim 128, 16-bit elements
+int launch_attention_prefill(xn_dtype dt, void *out, size_t ldo, const void *q, const void *k, const void *v, size_t ld,
+                             size_t head_stride, size_t heads, size_t t_rows, size_t ctx, float scale, cudaStream_t st);
 // runtime.cu: library-owned scratch per (device, stream) and the device status word
 struct SkinnyScratch { float *partials = nullptr; size_t partial_bytes = 0; unsigned *counters = nullptr; size_t ncounters = 0; };
 int skinny_scratch(cudaStream_t st, size_t partial_bytes, size_t ncounters, SkinnyScratch *out);

@@ -1105,6 +1105,287 @@ gemm_q8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Causal attention over a block of query rows as ONE kernel (prefill): scores never leave the SM.
+// One CTA per (head, 128-query block), heaviest blocks first.  Two passes over the visible 128-key blocks:
+//   pass 1   S = Q K^T into tensor memory (two buffers), the softmax warps read it back and keep the exact row
+//            maximum -- no exponentials, no rescaling of anything later;
+//   pass 2   S again (the tensor pipe has time to spare: the exponentials bound the kernel), p = 2^((s - m) c)
+//            with c = scale * log2(e), row sums in f32, P rounded to the element type and written into shared
+//            memory in the K-major 128-byte-swizzled layout of an A operand, O += P V accumulated in tensor memory
+//            over all key blocks (V is read as it lies in memory, keys x head_dim, as an MN-major B operand);
+//   end      O / l, rounded, stored.
+// Thread layout: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = softmax (two per tensor-memory lane
+// quarter: a thread owns one query row and 64 of a block's 128 keys; the halves meet through shared memory once
+// per pass).  Key j is visible to query row i iff j <= i + off and j < ctx.  head_dim = 128, 16-bit elements.
+// ---------------------------------------------------------------------------------------------
+struct AttnArgs {
+    void *out;         // [T][ldo] elements; head h at columns [128 h, 128 h + 128)
+    long long ldo;
+    int T, ctx, off, heads;
+    int nqb;           // query blocks per head
+    float c;           // scale * log2(e)
+    int q_inner, k_inner, v_inner;  // dimension order of the three tensor maps (see make_map3 / make_map_mn)
+    WaitCtx wait;
+};
+constexpr int ATT_THREADS = 64 + 256;
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr int ATT_TILE = 128 * BKB;  // one 128-row x 128-byte tile: 16 KB
+
+template <int KIND>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const AttnArgs args) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char *sQ = smem;                       // 2 tiles (head_dim halves)
+    unsigned char *sK = sQ + 2 * ATT_TILE;          // 2 stages x 2 tiles
+    unsigned char *sV = sK + 4 * ATT_TILE;          // 2 stages x 2 key halves x (2 blocks of 64 head_dim columns)
+    unsigned char *sP = sV + 4 * ATT_TILE;          // 2 buffers x 2 tiles (key halves)
+    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
+        p_empty[2], o_full;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float red[2][128];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heaviest query blocks first: block index 0 is the last query block of head 0
+    const int head = (int)(blockIdx.x % (unsigned)args.heads);
+    const int qb = args.nqb - 1 - (int)(blockIdx.x / (unsigned)args.heads);
+    const int q0 = qb * 128;
+    int nkb = (min(args.ctx - 1, q0 + 127 + args.off) >> 7) + 1;  // visible 128-key blocks
+    if (nkb < 1) nkb = 1;
+    constexpr uint32_t IDESC = KIND == 1 ? instr_desc(1, 1, 128) : instr_desc(0, 0, 128);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        mbar_init(&o_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
+            mbar_init(&p_full[i], 8); mbar_init(&p_empty[i], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(&q_full, 2 * ATT_TILE);
+            for (int h = 0; h < 2; ++h)
+                tma_load_3d(sQ + h * ATT_TILE, &map_q, h * 64, args.q_inner ? head : q0, args.q_inner ? q0 : head, &q_full);
+            int it = 0;
+            for (int pass = 0; pass < 2 && ok; ++pass)
+                for (int j = 0; j < nkb && ok; ++j, ++it) {
+                    const int s = it & 1;
+                    if (!mbar_wait(&k_empty[s], (((unsigned)it >> 1) & 1u) ^ 1u, args.wait)) { ok = false; break; }
+                    mbar_expect_tx(&k_full[s], 2 * ATT_TILE);
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_3d(sK + (2 * s + h) * ATT_TILE, &map_k, h * 64, args.k_inner ? head : j * 128,
+                                    args.k_inner ? j * 128 : head, &k_full[s]);
+                    if (pass == 1) {
+                        const int vs = j & 1;
+                        if (!mbar_wait(&v_empty[vs], (((unsigned)j >> 1) & 1u) ^ 1u, args.wait)) { ok = false; break; }
+                        mbar_expect_tx(&v_full[vs], 2 * ATT_TILE);
+                        for (int kh = 0; kh < 2; ++kh)      // 64 keys each
+                            for (int nb = 0; nb < 2; ++nb)  // 64 head_dim columns each
+                                tma_load_3d(sV + (2 * vs + kh) * ATT_TILE + nb * (64 * BKB), &map_v, nb * 64,
+                                            args.v_inner ? head : j * 128 + kh * 64, args.v_inner ? j * 128 + kh * 64 : head,
+                                            &v_full[vs]);
+                    }
+                }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait(&q_full, 0, args.wait);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            int kit = 0, sv = 0;
+            // S[sv & 1] = Q K_j^T for the next key block of the K ring
+            auto issue_s = [&]() -> bool {
+                const int s = kit & 1, b = sv & 1;
+                if (!mbar_wait(&k_full[s], ((unsigned)kit >> 1) & 1u, args.wait)) return false;
+                if (!mbar_wait(&s_empty[b], (((unsigned)sv >> 1) & 1u) ^ 1u, args.wait)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint64_t da = smem_desc(sQ + h * ATT_TILE), db = smem_desc(sK + (2 * s + h) * ATT_TILE);
+#pragma unroll
+                    for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
+                        const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
+                        umma<false>(tmem_base + b * 128, da + adv, db + adv, IDESC, (h | ks) != 0);
+                    }
+                }
+                umma_commit(&k_empty[s]);
+                umma_commit(&s_full[b]);
+                ++kit;
+                ++sv;
+                return true;
+            };
+            for (int j = 0; j < nkb && ok; ++j) ok = issue_s();  // pass 1
+            if (ok) ok = issue_s();                              // pass 2, block 0
+            for (int j = 0; j < nkb && ok; ++j) {
+                if (j + 1 < nkb) ok = issue_s();
+                if (!ok) break;
+                const int b = j & 1;
+                if (!mbar_wait(&p_full[b], ((unsigned)j >> 1) & 1u, args.wait) || !mbar_wait(&v_full[b], ((unsigned)j >> 1) & 1u, args.wait)) {
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh) {
+                    const uint64_t da = smem_desc(sP + (2 * b + kh) * ATT_TILE);
+                    const uint64_t db = smem_desc_mn(sV + (2 * b + kh) * ATT_TILE, 64 * BKB);
+#pragma unroll
+                    for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
+                        const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
+                        const uint64_t badv = (uint64_t)((UMMA_KB / 2) * 128 >> 4);  // 16 key rows of 128 bytes per MMA
+                        umma<false>(tmem_o, da + adv, db + ks * badv, IDESC | (1u << 16), (j | kh | ks) != 0);
+                    }
+                }
+                umma_commit(&p_empty[b]);
+                umma_commit(&v_empty[b]);
+            }
+            if (ok) umma_commit(&o_full);
+        }
+    } else {
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        const int row_local = q * 32 + lane, row = q0 + row_local;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 64);
+        const int horizon = min(args.ctx - 1, row + args.off);  // last visible key of this row
+        bool ok = true;
+        unsigned sv = 0;
+        float m = -INFINITY;
+        for (int j = 0; j < nkb && ok; ++j, ++sv) {
+            const unsigned b = sv & 1u;
+            if (!mbar_wait(&s_full[b], (sv >> 1) & 1u, args.wait)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t v[2][32];
+            tmem_ld32_nowait(lane_addr + b * 128, v[0]);
+            tmem_ld32_nowait(lane_addr + b * 128 + 32, v[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[b]);
+            const int col0 = j * 128 + half * 64;
+            if (col0 + 63 <= horizon) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) m = fmaxf(m, __uint_as_float(v[i >> 5][i & 31]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    if (col0 + i <= horizon) m = fmaxf(m, __uint_as_float(v[i >> 5][i & 31]));
+            }
+        }
+        red[half][row_local] = m;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        m = fmaxf(red[0][row_local], red[1][row_local]);
+        if (m == -INFINITY) m = 0.0f;  // a row without a visible key (context 0): keep the arithmetic finite
+        const float mc = m * args.c;
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // red is reused for the row sums
+        float l = 0.0f;
+        for (int j = 0; j < nkb && ok; ++j, ++sv) {
+            const unsigned b = sv & 1u, pb = (unsigned)j & 1u;
+            if (!mbar_wait(&s_full[b], (sv >> 1) & 1u, args.wait)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t v[2][32];
+            tmem_ld32_nowait(lane_addr + b * 128, v[0]);
+            tmem_ld32_nowait(lane_addr + b * 128 + 32, v[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[b]);
+            const int col0 = j * 128 + half * 64;
+            const bool full = col0 + 63 <= horizon;
+            uint32_t packed[32];
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+                float p0 = ex2_approx(fmaf(__uint_as_float(v[i >> 5][i & 31]), args.c, -mc));
+                float p1 = ex2_approx(fmaf(__uint_as_float(v[(i + 1) >> 5][(i + 1) & 31]), args.c, -mc));
+                if (!full) {
+                    if (col0 + i > horizon) p0 = 0.0f;
+                    if (col0 + i + 1 > horizon) p1 = 0.0f;
+                }
+                l += p0;
+                l += p1;
+                if (KIND == 2) {
+                    __half2 hh = __floats2half2_rn(p0, p1);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
+                } else {
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
+                }
+            }
+            // this buffer of P is free once the MMAs of block j - 2 have read it
+            if (!mbar_wait(&p_empty[pb], (((unsigned)j >> 1) & 1u) ^ 1u, args.wait)) { ok = false; break; }
+            unsigned char *prow = sP + (2 * pb + half) * ATT_TILE + row_local * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4 *>(prow + ((ch ^ (row_local & 7)) * 16)) =
+                    make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[pb]);
+        }
+        red[half][row_local] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        l = red[0][row_local] + red[1][row_local];
+        if (ok && mbar_wait(&o_full, 0, args.wait)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t v[2][32];
+            const uint32_t o_addr = tmem_o + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 64);
+            tmem_ld32_nowait(o_addr, v[0]);
+            tmem_ld32_nowait(o_addr + 32, v[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < args.T) {
+                const float inv = 1.0f / l;
+                uint16_t *dst = reinterpret_cast<uint16_t *>(args.out) + (size_t)row * args.ldo + (size_t)head * 128 + half * 64;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 8 * ch + 2 * e;
+                        const float f0 = __uint_as_float(v[i >> 5][i & 31]) * inv, f1 = __uint_as_float(v[(i + 1) >> 5][(i + 1) & 31]) * inv;
+                        if (KIND == 2) {
+                            __half2 hh = __floats2half2_rn(f0, f1);
+                            w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                        } else {
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                            w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                        }
+                    }
+                    *reinterpret_cast<uint4 *>(dst + 8 * ch) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 // ---- host side ----
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1409,6 +1690,45 @@ int launch_gemm_q8_block(float *y, size_t ldy, const int8_t *xq, const float *x_
     auto kern = gemm_q8_block_kernel<bn>;
     XN_ENSURE_SMEM(kern, smem);
     XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, mw, mx, a));
+    return XN_OK;
+}
+
+// out [T][ldo] = causal softmax(scale * q k^T) v per head; q, k, v are [rows][head][128] views (row pitch ld elements,
+// heads head_stride elements apart: the slices of a fused qkv projection, or separate contiguous tensors).
+int launch_attention_prefill(xn_dtype dt, void *out, size_t ldo, const void *q, const void *k, const void *v, size_t ld,
+                             size_t head_stride, size_t heads, size_t t_rows, size_t ctx, float scale, cudaStream_t st) {
+    AttnArgs a{};
+    a.out = out; a.ldo = (long long)ldo; a.T = (int)t_rows; a.ctx = (int)ctx; a.off = (int)(ctx - t_rows); a.heads = (int)heads;
+    a.nqb = (int)((t_rows + 127) / 128);
+    a.c = scale * 1.4426950408889634f;
+    if (int rcw = wait_ctx(&a.wait)) return rcw;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map3(&mq, q, 2, t_rows, 128, ld, 128, heads, head_stride, &a.q_inner);
+    if (rc) return rc;
+    rc = make_map3(&mk, k, 2, ctx, 128, ld, 128, heads, head_stride, &a.k_inner);
+    if (rc) return rc;
+    rc = make_map_mn(&mv, v, 128, ctx, ld, heads, head_stride, &a.v_inner);
+    if (rc) return rc;
+    const size_t smem = (size_t)14 * ATT_TILE + 1024;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(heads * a.nqb));
+    cfg.blockDim = dim3(ATT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    if (dt == XN_BF16) {
+        auto kern = attention_prefill_kernel<1>;
+        XN_ENSURE_SMEM(kern, smem);
+        XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, a));
+    } else {
+        auto kern = attention_prefill_kernel<2>;
+        XN_ENSURE_SMEM(kern, smem);
+        XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, a));
+    }
     return XN_OK;
 }
 

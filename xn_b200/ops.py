@@ -87,6 +87,26 @@ def matmul_causal_(dst: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor, rhs_
                                   rhs.storage_offset(), *a, _stream()))
 
 
+def attention_prefill_(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> None:
+    """Causal attention over a block of query rows in one kernel (xn_mm_attention_prefill).  q: [heads, T, 128] view,
+    k, v: [heads, context, 128] views with a common row pitch and head stride (e.g. the slices of a fused qkv projection
+    viewed per head); out: [T, heads * 128] rows (row pitch out.stride(0)).  Key j is visible to row i iff
+    j <= i + (context - T)."""
+    _require_cuda(out, q, k, v)
+    heads, t_rows, hd = q.shape
+    ctx = k.shape[1]
+    if not (q.dtype == k.dtype == v.dtype == out.dtype):
+        raise XnError(_lib.ERR_INVALID, "attention_prefill: dtype mismatch")
+    if not (q.stride(2) == k.stride(2) == v.stride(2) == 1 and q.stride(1) == k.stride(1) == v.stride(1)
+            and q.stride(0) == k.stride(0) == v.stride(0) and out.stride(1) == 1):
+        raise XnError(_lib.ERR_INVALID, "attention_prefill: q, k, v must share one row pitch and one head stride")
+    es = q.element_size()
+    check(lib().xn_mm_attention_prefill(_dtype_code(q), out.data_ptr(), out.stride(0),
+                                        _base_ptr(q) + q.storage_offset() * es, _base_ptr(k) + k.storage_offset() * es,
+                                        _base_ptr(v) + v.storage_offset() * es, q.stride(1), q.stride(0), heads, hd, t_rows, ctx,
+                                        float(scale), _stream()))
+
+
 def matmul_with_t(lhs: torch.Tensor, rhs: torch.Tensor, rhs_t: bool) -> torch.Tensor:
     """``ops::matmul_with_t``: output shape = lhs batch dims + [M, N], allocated uninitialised."""
     if lhs.dim() < 2 or rhs.dim() < 2:

@@ -158,10 +158,12 @@ class PrefillStack:
     same weights from the seed and keep their slices."""
 
     def __init__(self, n_layers: int, d_model: int, n_heads: int, ffn_hidden: int, tokens: int, device, group=None,
-                 eps: float = 1e-5, seed: int = 4, variant: int = 0, multicast: bool = True, single: bool = False):
+                 eps: float = 1e-5, seed: int = 4, variant: int = 0, multicast: bool = True, single: bool = False,
+                 fused_attention: bool = True):
         import torch
 
         from .ops import quantize_weights_fp8
+        self.fused_attention = fused_attention
         if not single and (group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized())):
             import torch.distributed as dist
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -199,8 +201,11 @@ class PrefillStack:
         self.hi, self.lo = torch.empty(T * kmax, **u8), torch.empty(T * kmax, **u8)
         self.xs = torch.empty(T, dtype=torch.float32, device=device)
         self.qkv = torch.empty(T, 3 * dl, **bf)
-        self.scores = torch.empty(self.Hl, T, T, **bf)
-        self.attn_l = torch.empty(self.Hl, T, 128, **bf)
+        if fused_attention:
+            self.attn_rows = torch.empty(T, dl, **bf)  # heads side by side in a row, as the out projection reads them
+        else:
+            self.scores = torch.empty(self.Hl, T, T, **bf)
+            self.attn_l = torch.empty(self.Hl, T, 128, **bf)
         self.h_l = torch.empty(T, 2 * hl, **bf)
         self.g_l = torch.empty(T, hl, **bf)
         self.x_mid = torch.empty(T, d, **bf)
@@ -254,7 +259,7 @@ class PrefillStack:
         import math
 
         from ._lib import BF16, check, lib
-        from .ops import matmul_causal_
+        from .ops import attention_prefill_, matmul_causal_
         L, T, d, hid, dl, hl, Hl = lib(), self.T, self.d, self.hid, self.dl, self.hl, self.Hl
         s = self._s()
         cur = x
@@ -265,13 +270,20 @@ class PrefillStack:
             self._linear_local(self.qkv, lay["in_proj"], 3 * dl, d)
             qkv4 = self.qkv.view(T, 3, Hl, 128)
             q, k, v = (qkv4[:, j].transpose(0, 1) for j in range(3))      # [Hl, T, 128] views, rows 3*dl apart
-            # q.k^T, one launch for the rank's heads; tiles beyond the causal horizon are skipped
-            matmul_causal_(self.scores, q, k, True, 1, 0)
-            check(L.xn_mm_softmax_causal(BF16, self.scores.data_ptr(), self.scores.data_ptr(), Hl, T, T,
-                                         1.0 / math.sqrt(128.0), 0, s))
-            # p.v, [T, 128] right-hand side per head; every row tile stops at its horizon
-            matmul_causal_(self.attn_l, self.scores, v, False, 2, 0)
-            self._gather(self.attn_full, self.attn_l, d, Hl)
+            if self.fused_attention:
+                # one kernel for the rank's heads: scores and probabilities never leave the SM
+                attention_prefill_(self.attn_rows, q, k, v, 1.0 / math.sqrt(128.0))
+            else:
+                # q.k^T, one launch for the rank's heads; tiles beyond the causal horizon are skipped
+                matmul_causal_(self.scores, q, k, True, 1, 0)
+                check(L.xn_mm_softmax_causal(BF16, self.scores.data_ptr(), self.scores.data_ptr(), Hl, T, T,
+                                             1.0 / math.sqrt(128.0), 0, s))
+                # p.v, [T, 128] right-hand side per head; every row tile stops at its horizon
+                matmul_causal_(self.attn_l, self.scores, v, False, 2, 0)
+            if self.fused_attention:
+                self._gather(self.attn_full, self.attn_rows, d, 1)
+            else:
+                self._gather(self.attn_full, self.attn_l, d, Hl)
             check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn_full.t.data_ptr(), BF16,
                                           T, d, s))
             self._linear_gathered(self.proj_full, lay["out_proj"], d, d)
