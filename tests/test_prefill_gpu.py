@@ -181,3 +181,30 @@ def test_fused_prefill_attention_against_f64(xn, cuda, dtype, H, T, ctx):
     # rounding of the probabilities and of the output to the element type is all there is: measured 0.012 / 0.0022 (bf16,
     # 8 mantissa bits, the maximum over 5e5 elements) and 0.0013 / 0.00028 (f16, 11 bits)
     assert (e_max < 2e-2 and e_rms < 4e-3) if dtype == torch.bfloat16 else (e_max < 3e-3 and e_rms < 6e-4)
+
+
+def test_fused_prefill_attention_moves_its_reference_point(xn, cuda):
+    """Scores that keep growing along the keys (the keys' norms ramp up by 12x), so that every few key blocks the
+    running reference of the exponentials is left behind by more than 2^8 and the accumulator is rescaled in tensor
+    memory; and rows whose second half of a key block is never visible."""
+    from xn_b200.ops import attention_prefill_
+    H, T, hd = 2, 1024, 128
+    g = torch.Generator(device=cuda).manual_seed(77)
+    qkv = torch.randn(T, 3 * H * hd, generator=g, device=cuda)
+    v4 = qkv.view(T, 3, H, hd)
+    v4[:, 1] *= torch.linspace(1.0, 12.0, T, device=cuda)[:, None, None]
+    qkv = qkv.bfloat16()
+    v4 = qkv.view(T, 3, H, hd)
+    q, k, v = (v4[:, j].transpose(0, 1) for j in range(3))
+    out = torch.full((T, H * hd), float("nan"), dtype=torch.bfloat16, device=cuda)
+    scale = 1.0 / math.sqrt(hd)
+    attention_prefill_(out, q, k, v, scale)
+    torch.cuda.synchronize()
+    s = torch.einsum("htd,hcd->htc", q.double(), k.double()) * scale
+    s = s.masked_fill(torch.triu(torch.ones(T, T, device=cuda, dtype=torch.bool), 1), float("-inf"))
+    ref = torch.einsum("htc,hcd->thd", torch.softmax(s, dim=-1), v.double()).reshape(T, H * hd)
+    err = (out.double() - ref).abs()
+    rms = ref.pow(2).mean().sqrt()
+    e_max, e_rms = float((err / (ref.abs() + rms)).max()), float(err.pow(2).mean().sqrt() / rms)
+    print("fused attention, ramped keys: max", e_max, "rms", e_rms)
+    assert not torch.isnan(out).any() and e_max < 2e-2 and e_rms < 4e-3

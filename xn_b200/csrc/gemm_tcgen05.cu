@@ -1107,17 +1107,21 @@ gemm_q8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
 // ---------------------------------------------------------------------------------------------
 // Causal attention over a block of query rows as ONE kernel (prefill): scores never leave the SM.
-// One CTA per (head, 128-query block), heaviest blocks first.  Two passes over the visible 128-key blocks:
-//   pass 1   S = Q K^T into tensor memory (two buffers), the softmax warps read it back and keep the exact row
-//            maximum -- no exponentials, no rescaling of anything later;
-//   pass 2   S again (the tensor pipe has time to spare: the exponentials bound the kernel), p = 2^((s - m) c)
-//            with c = scale * log2(e), row sums in f32, P rounded to the element type and written into shared
-//            memory in the K-major 128-byte-swizzled layout of an A operand, O += P V accumulated in tensor memory
-//            over all key blocks (V is read as it lies in memory, keys x head_dim, as an MN-major B operand);
-//   end      O / l, rounded, stored.
-// Thread layout: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = softmax (two per tensor-memory lane
-// quarter: a thread owns one query row and 64 of a block's 128 keys; the halves meet through shared memory once
-// per pass).  Key j is visible to query row i iff j <= i + off and j < ctx.  head_dim = 128, 16-bit elements.
+// One CTA per (head, 128-query block), heaviest blocks first; one pass over the visible 128-key blocks:
+//   S = Q K^T into tensor memory (two buffers); the softmax warps read it back, p = 2^((s - m) c) with
+//   c = scale * log2(e) and m the running row maximum, row sums in f32, P rounded to the element type and written
+//   into shared memory in the K-major 128-byte-swizzled layout of an A operand; O += P V accumulated in tensor memory
+//   (V is read as it lies in memory, keys x head_dim, as an MN-major B operand); at the end O / l, rounded, stored.
+// Thread layout: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = softmax, two per tensor-memory lane
+// quarter.  A softmax thread owns one query row and ONE HALF of every key block (keys 0..63 or 64..127 of the block),
+// and the two halves are two independent online-softmax streams: each has its own running maximum, its own row sum
+// and its own accumulator in tensor memory (O_0 += P[:, :64] V[:64], O_1 += P[:, 64:] V[64:]; S0 S1 O_0 O_1 fill the
+// 512 columns), so the warps never exchange anything per block; the streams are merged once at the end with the
+// usual log-sum-exp weights.  When a block raises a stream's maximum, the thread rescales its row of that stream's
+// accumulator in place (tcgen05.ld / st, after the previous block's P V has completed); the reference point of a
+// stream's exponentials moves only when a block exceeds it by 2^8, so this is rare.  Key j is visible to query row i iff j <= i + off and j < ctx.
+// head_dim = 128, 16-bit elements.  The kernel is bound by its tensor-memory MMAs (16 per key block, each costing
+// about the same for N = 128 as for N = 256) and by the exponentials, in that order.
 // ---------------------------------------------------------------------------------------------
 struct AttnArgs {
     void *out;         // [T][ldo] elements; head h at columns [128 h, 128 h + 128)
@@ -1129,12 +1133,12 @@ struct AttnArgs {
     WaitCtx wait;
 };
 constexpr int ATT_THREADS = 64 + 256;
+constexpr int ATT_TILE = 128 * BKB;  // one 128-row x 128-byte tile: 16 KB
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-constexpr int ATT_TILE = 128 * BKB;  // one 128-row x 128-byte tile: 16 KB
 
 template <int KIND>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -1147,9 +1151,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char *sV = sK + 4 * ATT_TILE;          // 2 stages x 2 key halves x (2 blocks of 64 head_dim columns)
     unsigned char *sP = sV + 4 * ATT_TILE;          // 2 buffers x 2 tiles (key halves)
     __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
-        p_empty[2], o_full;
+        p_empty[2], pv_done[2], o_full;
     __shared__ uint32_t tmem_slot;
-    __shared__ float red[2][128];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heaviest query blocks first: block index 0 is the last query block of head 0
@@ -1168,6 +1171,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
             mbar_init(&p_full[i], 8); mbar_init(&p_empty[i], 1);
+            mbar_init(&pv_done[i], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1181,7 +1185,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256;
+    const uint32_t tmem_o = tmem_base + 256;  // O_0 at columns [256, 384), O_1 at [384, 512)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -1191,130 +1195,129 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             mbar_expect_tx(&q_full, 2 * ATT_TILE);
             for (int h = 0; h < 2; ++h)
                 tma_load_3d(sQ + h * ATT_TILE, &map_q, h * 64, args.q_inner ? head : q0, args.q_inner ? q0 : head, &q_full);
-            int it = 0;
-            for (int pass = 0; pass < 2 && ok; ++pass)
-                for (int j = 0; j < nkb && ok; ++j, ++it) {
-                    const int s = it & 1;
-                    if (!mbar_wait(&k_empty[s], (((unsigned)it >> 1) & 1u) ^ 1u, args.wait)) { ok = false; break; }
-                    mbar_expect_tx(&k_full[s], 2 * ATT_TILE);
-                    for (int h = 0; h < 2; ++h)
-                        tma_load_3d(sK + (2 * s + h) * ATT_TILE, &map_k, h * 64, args.k_inner ? head : j * 128,
-                                    args.k_inner ? j * 128 : head, &k_full[s]);
-                    if (pass == 1) {
-                        const int vs = j & 1;
-                        if (!mbar_wait(&v_empty[vs], (((unsigned)j >> 1) & 1u) ^ 1u, args.wait)) { ok = false; break; }
-                        mbar_expect_tx(&v_full[vs], 2 * ATT_TILE);
-                        for (int kh = 0; kh < 2; ++kh)      // 64 keys each
-                            for (int nb = 0; nb < 2; ++nb)  // 64 head_dim columns each
-                                tma_load_3d(sV + (2 * vs + kh) * ATT_TILE + nb * (64 * BKB), &map_v, nb * 64,
-                                            args.v_inner ? head : j * 128 + kh * 64, args.v_inner ? j * 128 + kh * 64 : head,
-                                            &v_full[vs]);
-                    }
-                }
+            for (int j = 0; j < nkb && ok; ++j) {
+                const int s = j & 1;
+                const unsigned ph = (((unsigned)j >> 1) & 1u) ^ 1u;
+                if (!mbar_wait(&k_empty[s], ph, args.wait)) { ok = false; break; }
+                mbar_expect_tx(&k_full[s], 2 * ATT_TILE);
+                for (int h = 0; h < 2; ++h)
+                    tma_load_3d(sK + (2 * s + h) * ATT_TILE, &map_k, h * 64, args.k_inner ? head : j * 128,
+                                args.k_inner ? j * 128 : head, &k_full[s]);
+                if (!mbar_wait(&v_empty[s], ph, args.wait)) { ok = false; break; }
+                mbar_expect_tx(&v_full[s], 2 * ATT_TILE);
+                for (int kh = 0; kh < 2; ++kh)      // 64 keys each
+                    for (int nb = 0; nb < 2; ++nb)  // 64 head_dim columns each
+                        tma_load_3d(sV + (2 * s + kh) * ATT_TILE + nb * (64 * BKB), &map_v, nb * 64,
+                                    args.v_inner ? head : j * 128 + kh * 64, args.v_inner ? j * 128 + kh * 64 : head, &v_full[s]);
+            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = mbar_wait(&q_full, 0, args.wait);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            int kit = 0, sv = 0;
-            // S[sv & 1] = Q K_j^T for the next key block of the K ring
-            auto issue_s = [&]() -> bool {
-                const int s = kit & 1, b = sv & 1;
-                if (!mbar_wait(&k_full[s], ((unsigned)kit >> 1) & 1u, args.wait)) return false;
-                if (!mbar_wait(&s_empty[b], (((unsigned)sv >> 1) & 1u) ^ 1u, args.wait)) return false;
+            // S[j & 1] = Q K_j^T
+            auto issue_s = [&](int j) -> bool {
+                const int b = j & 1;
+                const unsigned ph = ((unsigned)j >> 1) & 1u;
+                if (!mbar_wait(&k_full[b], ph, args.wait)) return false;
+                if (!mbar_wait(&s_empty[b], ph ^ 1u, args.wait)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint64_t da = smem_desc(sQ + h * ATT_TILE), db = smem_desc(sK + (2 * s + h) * ATT_TILE);
+                    const uint64_t da = smem_desc(sQ + h * ATT_TILE), db = smem_desc(sK + (2 * b + h) * ATT_TILE);
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
                         umma<false>(tmem_base + b * 128, da + adv, db + adv, IDESC, (h | ks) != 0);
                     }
                 }
-                umma_commit(&k_empty[s]);
+                umma_commit(&k_empty[b]);
                 umma_commit(&s_full[b]);
-                ++kit;
-                ++sv;
                 return true;
             };
-            for (int j = 0; j < nkb && ok; ++j) ok = issue_s();  // pass 1
-            if (ok) ok = issue_s();                              // pass 2, block 0
+            if (ok) ok = issue_s(0);
             for (int j = 0; j < nkb && ok; ++j) {
-                if (j + 1 < nkb) ok = issue_s();
+                if (j + 1 < nkb) ok = issue_s(j + 1);
                 if (!ok) break;
                 const int b = j & 1;
-                if (!mbar_wait(&p_full[b], ((unsigned)j >> 1) & 1u, args.wait) || !mbar_wait(&v_full[b], ((unsigned)j >> 1) & 1u, args.wait)) {
-                    ok = false;
-                    break;
-                }
+                const unsigned ph = ((unsigned)j >> 1) & 1u;
+                if (!mbar_wait(&p_full[b], ph, args.wait) || !mbar_wait(&v_full[b], ph, args.wait)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int kh = 0; kh < 2; ++kh) {
+                for (int kh = 0; kh < 2; ++kh) {  // stream kh: O_kh += P[:, keys of half kh] V[keys of half kh]
                     const uint64_t da = smem_desc(sP + (2 * b + kh) * ATT_TILE);
                     const uint64_t db = smem_desc_mn(sV + (2 * b + kh) * ATT_TILE, 64 * BKB);
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
                         const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
                         const uint64_t badv = (uint64_t)((UMMA_KB / 2) * 128 >> 4);  // 16 key rows of 128 bytes per MMA
-                        umma<false>(tmem_o, da + adv, db + ks * badv, IDESC | (1u << 16), (j | kh | ks) != 0);
+                        umma<false>(tmem_o + kh * 128, da + adv, db + ks * badv, IDESC | (1u << 16), (j | ks) != 0);
                     }
                 }
                 umma_commit(&p_empty[b]);
                 umma_commit(&v_empty[b]);
+                umma_commit(&pv_done[b]);
             }
             if (ok) umma_commit(&o_full);
         }
     } else {
         const int q = warp & 3, half = (warp - 2) >> 2;
         const int row_local = q * 32 + lane, row = q0 + row_local;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 64);
-        const int horizon = min(args.ctx - 1, row + args.off);  // last visible key of this row
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t s_addr = lane_base + (uint32_t)(half * 64);
+        const uint32_t o_mine = lane_base + 256 + (uint32_t)(half * 128);  // this stream's accumulator row
+        const int horizon = min(args.ctx - 1, row + args.off);             // last visible key of this row
         bool ok = true;
-        unsigned sv = 0;
-        float m = -INFINITY;
-        for (int j = 0; j < nkb && ok; ++j, ++sv) {
-            const unsigned b = sv & 1u;
-            if (!mbar_wait(&s_full[b], (sv >> 1) & 1u, args.wait)) { ok = false; break; }
+        float m = -INFINITY, l = 0.0f;
+        for (int j = 0; j < nkb && ok; ++j) {
+            const unsigned b = (unsigned)j & 1u, ph = ((unsigned)j >> 1) & 1u;
+            if (!mbar_wait(&s_full[b], ph, args.wait)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t v[2][32];
-            tmem_ld32_nowait(lane_addr + b * 128, v[0]);
-            tmem_ld32_nowait(lane_addr + b * 128 + 32, v[1]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[b]);
-            const int col0 = j * 128 + half * 64;
-            if (col0 + 63 <= horizon) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) m = fmaxf(m, __uint_as_float(v[i >> 5][i & 31]));
-            } else {
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (col0 + i <= horizon) m = fmaxf(m, __uint_as_float(v[i >> 5][i & 31]));
-            }
-        }
-        red[half][row_local] = m;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        m = fmaxf(red[0][row_local], red[1][row_local]);
-        if (m == -INFINITY) m = 0.0f;  // a row without a visible key (context 0): keep the arithmetic finite
-        const float mc = m * args.c;
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // red is reused for the row sums
-        float l = 0.0f;
-        for (int j = 0; j < nkb && ok; ++j, ++sv) {
-            const unsigned b = sv & 1u, pb = (unsigned)j & 1u;
-            if (!mbar_wait(&s_full[b], (sv >> 1) & 1u, args.wait)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t v[2][32];
-            tmem_ld32_nowait(lane_addr + b * 128, v[0]);
-            tmem_ld32_nowait(lane_addr + b * 128 + 32, v[1]);
+            tmem_ld32_nowait(s_addr + b * 128, v[0]);
+            tmem_ld32_nowait(s_addr + b * 128 + 32, v[1]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[b]);
             const int col0 = j * 128 + half * 64;
             const bool full = col0 + 63 <= horizon;
+            float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maximum is on the critical path
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(v[i >> 5][i & 31]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    if (col0 + i <= horizon) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(v[i >> 5][i & 31]));
+            }
+            const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
+            // The reference point m of the stream's exponentials moves only when a block exceeds it by more than 2^8:
+            // any reference gives the same quotient at the end, probabilities up to 256 are harmless in f32 and in the
+            // 16-bit types, and the rescaling below (a round trip through tensor memory that has to wait for the previous
+            // product) becomes rare instead of happening whenever one of a warp's 32 rows sees a new maximum.
+            const float m_new = (bm - m) * args.c > 8.0f ? bm : m;  // m = -inf: the first visible block sets it
+            const float alpha = m_new != m ? ex2_approx((m - m_new) * args.c) : 1.0f;  // m = -inf: 0
+            if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+                // this stream's accumulator holds the sum up to block j - 1 relative to the old maxima: wait for that
+                // product to be complete, then scale the row in place
+                if (!mbar_wait(&pv_done[b ^ 1u], (((unsigned)(j - 1)) >> 1) & 1u, args.wait)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int cq = 0; cq < 4; ++cq) {
+                    uint32_t o[32];
+                    tmem_ld32(o_mine + cq * 32, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(o_mine + cq * 32, o);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            l *= alpha;
+            m = m_new;
+            const float mc = m * args.c;
             uint32_t packed[32];
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
                 float p0 = ex2_approx(fmaf(__uint_as_float(v[i >> 5][i & 31]), args.c, -mc));
@@ -1323,8 +1326,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (col0 + i > horizon) p0 = 0.0f;
                     if (col0 + i + 1 > horizon) p1 = 0.0f;
                 }
-                l += p0;
-                l += p1;
+                l4[i & 2] += p0;
+                l4[(i & 2) + 1] += p1;
                 if (KIND == 2) {
                     __half2 hh = __floats2half2_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
@@ -1333,46 +1336,59 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
                 }
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             // this buffer of P is free once the MMAs of block j - 2 have read it
-            if (!mbar_wait(&p_empty[pb], (((unsigned)j >> 1) & 1u) ^ 1u, args.wait)) { ok = false; break; }
-            unsigned char *prow = sP + (2 * pb + half) * ATT_TILE + row_local * 128;
+            if (!mbar_wait(&p_empty[b], ph ^ 1u, args.wait)) { ok = false; break; }
+            unsigned char *prow = sP + (2 * b + half) * ATT_TILE + row_local * 128;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch)
                 *reinterpret_cast<uint4 *>(prow + ((ch ^ (row_local & 7)) * 16)) =
                     make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[pb]);
+            if (lane == 0) mbar_arrive(&p_full[b]);
         }
-        red[half][row_local] = l;
+        // merge the two streams of a row: weights 2^((m_h - M) c), M = max(m_0, m_1).  The exchange goes through the K ring,
+        // which is dead by now: this warp has seen the last S complete, and every S MMA precedes it in the tensor pipe.
+        float (*red_m)[128] = reinterpret_cast<float (*)[128]>(sK);
+        float (*red_l)[128] = reinterpret_cast<float (*)[128]>(sK + 1024);
+        red_m[half][row_local] = m;
+        red_l[half][row_local] = l;
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        l = red[0][row_local] + red[1][row_local];
+        const float m0 = red_m[0][row_local], m1 = red_m[1][row_local];
+        const float mm = fmaxf(m0, m1);
+        const float w0 = m0 == -INFINITY ? 0.0f : ex2_approx((m0 - mm) * args.c);
+        const float w1 = m1 == -INFINITY ? 0.0f : ex2_approx((m1 - mm) * args.c);
+        const float lsum = w0 * red_l[0][row_local] + w1 * red_l[1][row_local];
         if (ok && mbar_wait(&o_full, 0, args.wait)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t v[2][32];
-            const uint32_t o_addr = tmem_o + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 64);
-            tmem_ld32_nowait(o_addr, v[0]);
-            tmem_ld32_nowait(o_addr + 32, v[1]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < args.T) {
-                const float inv = 1.0f / l;
-                uint16_t *dst = reinterpret_cast<uint16_t *>(args.out) + (size_t)row * args.ldo + (size_t)head * 128 + half * 64;
+            const float i0 = w0 / lsum, i1 = w1 / lsum;
+            uint16_t *dst = reinterpret_cast<uint16_t *>(args.out) + (size_t)row * args.ldo + (size_t)head * 128 + half * 64;
+#pragma unroll 1
+            for (int cq = 0; cq < 2; ++cq) {  // 32 output columns at a time
+                uint32_t a[32], bb[32];
+                tmem_ld32_nowait(lane_base + 256 + half * 64 + cq * 32, a);
+                tmem_ld32_nowait(lane_base + 384 + half * 64 + cq * 32, bb);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < args.T) {
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    uint32_t w[4];
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint32_t w[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = 8 * ch + 2 * e;
-                        const float f0 = __uint_as_float(v[i >> 5][i & 31]) * inv, f1 = __uint_as_float(v[(i + 1) >> 5][(i + 1) & 31]) * inv;
-                        if (KIND == 2) {
-                            __half2 hh = __floats2half2_rn(f0, f1);
-                            w[e] = *reinterpret_cast<uint32_t *>(&hh);
-                        } else {
-                            __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
-                            w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = 8 * ch + 2 * e;
+                            const float f0 = __uint_as_float(a[i]) * i0 + __uint_as_float(bb[i]) * i1;
+                            const float f1 = __uint_as_float(a[i + 1]) * i0 + __uint_as_float(bb[i + 1]) * i1;
+                            if (KIND == 2) {
+                                __half2 hh = __floats2half2_rn(f0, f1);
+                                w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                            } else {
+                                __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                                w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                            }
                         }
+                        *reinterpret_cast<uint4 *>(dst + cq * 32 + 8 * ch) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4 *>(dst + 8 * ch) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
