@@ -271,8 +271,9 @@ class PrefillStack:
             qkv4 = self.qkv.view(T, 3, Hl, 128)
             q, k, v = (qkv4[:, j].transpose(0, 1) for j in range(3))      # [Hl, T, 128] views, rows 3*dl apart
             if self.fused_attention:
-                # one kernel for the rank's heads: scores and probabilities never leave the SM
-                attention_prefill_(self.attn_rows, q, k, v, 1.0 / math.sqrt(128.0))
+                # one kernel for the rank's heads: scores and probabilities never leave the SM (a single rank owns
+                # every head and writes the rows the out projection reads: nothing to exchange)
+                attention_prefill_(self.attn_full.t if self.world == 1 else self.attn_rows, q, k, v, 1.0 / math.sqrt(128.0))
             else:
                 # q.k^T, one launch for the rank's heads; tiles beyond the causal horizon are skipped
                 matmul_causal_(self.scores, q, k, True, 1, 0)
@@ -281,7 +282,8 @@ class PrefillStack:
                 # p.v, [T, 128] right-hand side per head; every row tile stops at its horizon
                 matmul_causal_(self.attn_l, self.scores, v, False, 2, 0)
             if self.fused_attention:
-                self._gather(self.attn_full, self.attn_rows, d, 1)
+                if self.world > 1:
+                    self._gather(self.attn_full, self.attn_rows, d, 1)
             else:
                 self._gather(self.attn_full, self.attn_l, d, Hl)
             check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn_full.t.data_ptr(), BF16,
@@ -291,10 +293,15 @@ class PrefillStack:
                                                   cur.data_ptr(), self.proj_full.t.data_ptr(), lay["norm2"].data_ptr(), BF16, T,
                                                   d, self.eps, s))
             self._linear_local(self.h_l, lay["linear_in"], 2 * hl, d)
-            check(L.xn_mm_silu_mul(BF16, self.g_l.data_ptr(), self.h_l.data_ptr(), T, hl, s))
-            self._gather(self.gated_full, self.g_l, hid, 1)
-            check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.gated_full.t.data_ptr(), BF16,
-                                          T, hid, s))
+            if self.world == 1:
+                # a single rank holds whole rows of the gated activations: gate and split in one kernel
+                check(L.xn_mm_silu_mul_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.h_l.data_ptr(), BF16, T,
+                                                  hl, s))
+            else:
+                check(L.xn_mm_silu_mul(BF16, self.g_l.data_ptr(), self.h_l.data_ptr(), T, hl, s))
+                self._gather(self.gated_full, self.g_l, hid, 1)
+                check(L.xn_mm_split_rows_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.gated_full.t.data_ptr(),
+                                              BF16, T, hid, s))
             self._linear_gathered(self.proj_full, lay["linear_out"], d, hid)
             if li + 1 < len(self.layers):
                 check(L.xn_mm_add_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.x_out.data_ptr(),
