@@ -1109,9 +1109,11 @@ gemm_q8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 // Causal attention over a block of query rows as ONE kernel (prefill): scores never leave the SM.
 // One CTA per (head, 128-query block), heaviest blocks first; one pass over the visible 128-key blocks:
 //   S = Q K^T into tensor memory (two buffers); the softmax warps read it back, p = 2^((s - m) c) with
-//   c = scale * log2(e) and m the running row maximum, row sums in f32, P rounded to the element type and written
-//   into shared memory in the K-major 128-byte-swizzled layout of an A operand; O += P V accumulated in tensor memory
-//   (V is read as it lies in memory, keys x head_dim, as an MN-major B operand); at the end O / l, rounded, stored.
+//   c = scale * log2(e) and m the stream's reference point, row sums in f32, P rounded to the element type and written
+//   BACK into tensor memory over the scores it came from (a thread's row is its lane; two elements per column):
+//   O += P V takes its A operand from tensor memory and V from shared memory as it lies in memory (keys x head_dim,
+//   an MN-major B operand), accumulating in tensor memory; at the end O / l, rounded, stored.  Nothing but K, V and
+//   Q tiles ever touches shared memory.
 // Thread layout: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = softmax, two per tensor-memory lane
 // quarter.  A softmax thread owns one query row and ONE HALF of every key block (keys 0..63 or 64..127 of the block),
 // and the two halves are two independent online-softmax streams: each has its own running maximum, its own row sum
@@ -1140,6 +1142,15 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// D += A * B with the A operand in tensor memory (lane = row, two 16-bit elements per column, 8 columns per MMA)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -1149,9 +1160,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char *sQ = smem;                       // 2 tiles (head_dim halves)
     unsigned char *sK = sQ + 2 * ATT_TILE;          // 2 stages x 2 tiles
     unsigned char *sV = sK + 4 * ATT_TILE;          // 2 stages x 2 key halves x (2 blocks of 64 head_dim columns)
-    unsigned char *sP = sV + 4 * ATT_TILE;          // 2 buffers x 2 tiles (key halves)
     __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
-        p_empty[2], pv_done[2], o_full;
+        pv_done[2], o_full;
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1169,8 +1179,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
-            mbar_init(&p_full[i], 8); mbar_init(&p_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 1);
+            mbar_init(&p_full[i], 8);
             mbar_init(&pv_done[i], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1245,18 +1255,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int kh = 0; kh < 2; ++kh) {  // stream kh: O_kh += P[:, keys of half kh] V[keys of half kh]
-                    const uint64_t da = smem_desc(sP + (2 * b + kh) * ATT_TILE);
                     const uint64_t db = smem_desc_mn(sV + (2 * b + kh) * ATT_TILE, 64 * BKB);
 #pragma unroll
                     for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
-                        const uint64_t adv = (uint64_t)(ks * UMMA_KB >> 4);
                         const uint64_t badv = (uint64_t)((UMMA_KB / 2) * 128 >> 4);  // 16 key rows of 128 bytes per MMA
-                        umma<false>(tmem_o + kh * 128, da + adv, db + ks * badv, IDESC | (1u << 16), (j | ks) != 0);
+                        // P of stream kh sits in the first 32 columns of the stream's half of S[b]: 8 columns per MMA
+                        umma_ts(tmem_o + kh * 128, tmem_base + b * 128 + kh * 64 + ks * 8, db + ks * badv, IDESC | (1u << 16),
+                                (j | ks) != 0);
                     }
                 }
-                umma_commit(&p_empty[b]);
                 umma_commit(&v_empty[b]);
                 umma_commit(&pv_done[b]);
+                umma_commit(&s_empty[b]);  // S[b] (and the P inside it) is free once these products have read it
             }
             if (ok) umma_commit(&o_full);
         }
@@ -1277,9 +1287,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_ld32_nowait(s_addr + b * 128, v[0]);
             tmem_ld32_nowait(s_addr + b * 128 + 32, v[1]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[b]);
             const int col0 = j * 128 + half * 64;
             const bool full = col0 + 63 <= horizon;
             float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maximum is on the critical path
@@ -1337,14 +1344,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            // this buffer of P is free once the MMAs of block j - 2 have read it
-            if (!mbar_wait(&p_empty[b], ph ^ 1u, args.wait)) { ok = false; break; }
-            unsigned char *prow = sP + (2 * b + half) * ATT_TILE + row_local * 128;
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4 *>(prow + ((ch ^ (row_local & 7)) * 16)) =
-                    make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P goes back into tensor memory, over the first 32 columns of the scores this thread has just consumed
+            // (its row = its lane, two elements per column): the A operand of the P V product is read from there
+            tmem_st32(s_addr + b * 128, packed);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
@@ -1725,7 +1728,7 @@ int launch_attention_prefill(xn_dtype dt, void *out, size_t ldo, const void *q, 
     if (rc) return rc;
     rc = make_map_mn(&mv, v, 128, ctx, ld, heads, head_stride, &a.v_inner);
     if (rc) return rc;
-    const size_t smem = (size_t)14 * ATT_TILE + 1024;
+    const size_t smem = (size_t)10 * ATT_TILE + 1024;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(heads * a.nqb));
     cfg.blockDim = dim3(ATT_THREADS);
