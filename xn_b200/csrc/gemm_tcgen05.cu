@@ -1107,7 +1107,7 @@ gemm_q8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
 // ---------------------------------------------------------------------------------------------
 // Causal attention over a block of query rows as ONE kernel (prefill): scores never leave the SM.
-// One CTA per (head, 128-query block), heaviest blocks first; one pass over the visible 128-key blocks:
+// A work item is a (head, 128-query block) pair; one pass over its visible 128-key blocks:
 //   S = Q K^T into tensor memory (two buffers); the softmax warps read it back, p = 2^((s - m) c) with
 //   c = scale * log2(e) and m the stream's reference point, row sums in f32, P rounded to the element type and written
 //   BACK into tensor memory over the scores it came from (a thread's row is its lane; two elements per column):
@@ -1160,22 +1160,33 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     unsigned char *sQ = smem;                       // 2 tiles (head_dim halves)
     unsigned char *sK = sQ + 2 * ATT_TILE;          // 2 stages x 2 tiles
     unsigned char *sV = sK + 4 * ATT_TILE;          // 2 stages x 2 key halves x (2 blocks of 64 head_dim columns)
-    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
-        pv_done[2], o_full;
+    __shared__ __align__(8) uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2],
+        p_full[2], pv_done[2], o_full, o_empty;
     __shared__ uint32_t tmem_slot;
+    __shared__ float red_m[2][128], red_l[2][128];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heaviest query blocks first: block index 0 is the last query block of head 0
-    const int head = (int)(blockIdx.x % (unsigned)args.heads);
-    const int qb = args.nqb - 1 - (int)(blockIdx.x / (unsigned)args.heads);
-    const int q0 = qb * 128;
-    int nkb = (min(args.ctx - 1, q0 + 127 + args.off) >> 7) + 1;  // visible 128-key blocks
-    if (nkb < 1) nkb = 1;
+    // The kernel is persistent: CTA c works on items c, c + grid, ... of the list of (query block, head) pairs ordered
+    // by falling work (the last query block of every head first), so that every CTA gets the same share within a block
+    // or two, and the set-up, the first loads and the first scores of an item overlap the tail of the previous one.
+    // Every barrier is used once per key block or once per item; the roles keep running counts for the phases.
+    const int nitems = args.nqb * args.heads;
     constexpr uint32_t IDESC = KIND == 1 ? instr_desc(1, 1, 128) : instr_desc(0, 0, 128);
+    // Item k of this CTA: the list is dealt out in rounds of `grid` items, forwards in even rounds and backwards in odd
+    // ones, so a CTA that got the heaviest item of one round gets the lightest of the next.
+    auto first_item = [&](unsigned k) -> int {
+        return (int)(k * gridDim.x + ((k & 1u) ? gridDim.x - 1 - blockIdx.x : blockIdx.x));
+    };
+    auto item_geom = [&](int item, int &head, int &q0, int &nkb) {
+        head = (int)((unsigned)item % (unsigned)args.heads);
+        q0 = (args.nqb - 1 - (int)((unsigned)item / (unsigned)args.heads)) * 128;
+        nkb = (min(args.ctx - 1, q0 + 127 + args.off) >> 7) + 1;  // visible 128-key blocks
+        if (nkb < 1) nkb = 1;
+    };
 
     if (threadIdx.x == 0) {
-        mbar_init(&q_full, 1);
-        mbar_init(&o_full, 1);
+        mbar_init(&q_full, 1); mbar_init(&q_empty, 1);
+        mbar_init(&o_full, 1); mbar_init(&o_empty, 8);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
@@ -1202,33 +1213,39 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 0) {
         if (lane == 0) {
             bool ok = true;
-            mbar_expect_tx(&q_full, 2 * ATT_TILE);
-            for (int h = 0; h < 2; ++h)
-                tma_load_3d(sQ + h * ATT_TILE, &map_q, h * 64, args.q_inner ? head : q0, args.q_inner ? q0 : head, &q_full);
-            for (int j = 0; j < nkb && ok; ++j) {
-                const int s = j & 1;
-                const unsigned ph = (((unsigned)j >> 1) & 1u) ^ 1u;
-                if (!mbar_wait(&k_empty[s], ph, args.wait)) { ok = false; break; }
-                mbar_expect_tx(&k_full[s], 2 * ATT_TILE);
+            unsigned g = 0, n_item = 0;  // key blocks and items so far
+            for (int item = first_item(0); item < nitems && ok; item = first_item(++n_item)) {
+                int head, q0, nkb;
+                item_geom(item, head, q0, nkb);
+                if (!mbar_wait(&q_empty, (n_item & 1u) ^ 1u, args.wait)) { ok = false; break; }  // the previous item's scores are done
+                mbar_expect_tx(&q_full, 2 * ATT_TILE);
                 for (int h = 0; h < 2; ++h)
-                    tma_load_3d(sK + (2 * s + h) * ATT_TILE, &map_k, h * 64, args.k_inner ? head : j * 128,
-                                args.k_inner ? j * 128 : head, &k_full[s]);
-                if (!mbar_wait(&v_empty[s], ph, args.wait)) { ok = false; break; }
-                mbar_expect_tx(&v_full[s], 2 * ATT_TILE);
-                for (int kh = 0; kh < 2; ++kh)      // 64 keys each
-                    for (int nb = 0; nb < 2; ++nb)  // 64 head_dim columns each
-                        tma_load_3d(sV + (2 * s + kh) * ATT_TILE + nb * (64 * BKB), &map_v, nb * 64,
-                                    args.v_inner ? head : j * 128 + kh * 64, args.v_inner ? j * 128 + kh * 64 : head, &v_full[s]);
+                    tma_load_3d(sQ + h * ATT_TILE, &map_q, h * 64, args.q_inner ? head : q0, args.q_inner ? q0 : head, &q_full);
+                for (int j = 0; j < nkb && ok; ++j, ++g) {
+                    const int s = (int)(g & 1u);
+                    const unsigned ph = ((g >> 1) & 1u) ^ 1u;
+                    if (!mbar_wait(&k_empty[s], ph, args.wait)) { ok = false; break; }
+                    mbar_expect_tx(&k_full[s], 2 * ATT_TILE);
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_3d(sK + (2 * s + h) * ATT_TILE, &map_k, h * 64, args.k_inner ? head : j * 128,
+                                    args.k_inner ? j * 128 : head, &k_full[s]);
+                    if (!mbar_wait(&v_empty[s], ph, args.wait)) { ok = false; break; }
+                    mbar_expect_tx(&v_full[s], 2 * ATT_TILE);
+                    for (int kh = 0; kh < 2; ++kh)      // 64 keys each
+                        for (int nb = 0; nb < 2; ++nb)  // 64 head_dim columns each
+                            tma_load_3d(sV + (2 * s + kh) * ATT_TILE + nb * (64 * BKB), &map_v, nb * 64,
+                                        args.v_inner ? head : j * 128 + kh * 64, args.v_inner ? j * 128 + kh * 64 : head,
+                                        &v_full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = mbar_wait(&q_full, 0, args.wait);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // S[j & 1] = Q K_j^T
-            auto issue_s = [&](int j) -> bool {
-                const int b = j & 1;
-                const unsigned ph = ((unsigned)j >> 1) & 1u;
+            bool ok = true;
+            unsigned gs = 0, gp = 0, n_item = 0;  // scores issued, products issued, items so far
+            // S[gs & 1] = Q K^T for the next key block of the K ring
+            auto issue_s = [&]() -> bool {
+                const unsigned b = gs & 1u, ph = (gs >> 1) & 1u;
                 if (!mbar_wait(&k_full[b], ph, args.wait)) return false;
                 if (!mbar_wait(&s_empty[b], ph ^ 1u, args.wait)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1243,154 +1260,172 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 umma_commit(&k_empty[b]);
                 umma_commit(&s_full[b]);
+                ++gs;
                 return true;
             };
-            if (ok) ok = issue_s(0);
-            for (int j = 0; j < nkb && ok; ++j) {
-                if (j + 1 < nkb) ok = issue_s(j + 1);
-                if (!ok) break;
-                const int b = j & 1;
-                const unsigned ph = ((unsigned)j >> 1) & 1u;
-                if (!mbar_wait(&p_full[b], ph, args.wait) || !mbar_wait(&v_full[b], ph, args.wait)) { ok = false; break; }
+            for (int item = first_item(0); item < nitems && ok; item = first_item(++n_item)) {
+                int head, q0, nkb;
+                item_geom(item, head, q0, nkb);
+                if (!mbar_wait(&q_full, n_item & 1u, args.wait)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int kh = 0; kh < 2; ++kh) {  // stream kh: O_kh += P[:, keys of half kh] V[keys of half kh]
-                    const uint64_t db = smem_desc_mn(sV + (2 * b + kh) * ATT_TILE, 64 * BKB);
-#pragma unroll
-                    for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
-                        const uint64_t badv = (uint64_t)((UMMA_KB / 2) * 128 >> 4);  // 16 key rows of 128 bytes per MMA
-                        // P of stream kh sits in the first 32 columns of the stream's half of S[b]: 8 columns per MMA
-                        umma_ts(tmem_o + kh * 128, tmem_base + b * 128 + kh * 64 + ks * 8, db + ks * badv, IDESC | (1u << 16),
-                                (j | ks) != 0);
+                ok = issue_s();
+                if (ok && nkb == 1) umma_commit(&q_empty);
+                for (int j = 0; j < nkb && ok; ++j, ++gp) {
+                    if (j + 1 < nkb) {
+                        ok = issue_s();
+                        if (ok && j + 2 == nkb) umma_commit(&q_empty);  // the last scores of the item: Q may be replaced
                     }
+                    if (!ok) break;
+                    const unsigned b = gp & 1u, ph = (gp >> 1) & 1u;
+                    if (!mbar_wait(&p_full[b], ph, args.wait) || !mbar_wait(&v_full[b], ph, args.wait)) { ok = false; break; }
+                    // the first product of an item overwrites the accumulators: the previous item's rows must have been read
+                    if (j == 0 && !mbar_wait(&o_empty, (n_item & 1u) ^ 1u, args.wait)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int kh = 0; kh < 2; ++kh) {  // stream kh: O_kh += P[:, keys of half kh] V[keys of half kh]
+                        const uint64_t db = smem_desc_mn(sV + (2 * b + kh) * ATT_TILE, 64 * BKB);
+#pragma unroll
+                        for (int ks = 0; ks < BKB / UMMA_KB; ++ks) {
+                            const uint64_t badv = (uint64_t)((UMMA_KB / 2) * 128 >> 4);  // 16 key rows of 128 bytes per MMA
+                            // P of stream kh sits in the first 32 columns of the stream's half of S[b]: 8 columns per MMA
+                            umma_ts(tmem_o + kh * 128, tmem_base + b * 128 + kh * 64 + ks * 8, db + ks * badv, IDESC | (1u << 16),
+                                    (j | ks) != 0);
+                        }
+                    }
+                    umma_commit(&v_empty[b]);
+                    umma_commit(&pv_done[b]);
+                    umma_commit(&s_empty[b]);  // S[b] (and the P inside it) is free once these products have read it
                 }
-                umma_commit(&v_empty[b]);
-                umma_commit(&pv_done[b]);
-                umma_commit(&s_empty[b]);  // S[b] (and the P inside it) is free once these products have read it
+                if (ok) umma_commit(&o_full);
             }
-            if (ok) umma_commit(&o_full);
         }
     } else {
         const int q = warp & 3, half = (warp - 2) >> 2;
-        const int row_local = q * 32 + lane, row = q0 + row_local;
+        const int row_local = q * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         const uint32_t s_addr = lane_base + (uint32_t)(half * 64);
         const uint32_t o_mine = lane_base + 256 + (uint32_t)(half * 128);  // this stream's accumulator row
-        const int horizon = min(args.ctx - 1, row + args.off);             // last visible key of this row
         bool ok = true;
-        float m = -INFINITY, l = 0.0f;
-        for (int j = 0; j < nkb && ok; ++j) {
-            const unsigned b = (unsigned)j & 1u, ph = ((unsigned)j >> 1) & 1u;
-            if (!mbar_wait(&s_full[b], ph, args.wait)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t v[2][32];
-            tmem_ld32_nowait(s_addr + b * 128, v[0]);
-            tmem_ld32_nowait(s_addr + b * 128 + 32, v[1]);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            const int col0 = j * 128 + half * 64;
-            const bool full = col0 + 63 <= horizon;
-            float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maximum is on the critical path
-            if (full) {
+        unsigned g = 0, n_item = 0;
+        for (int item = first_item(0); item < nitems; item = first_item(++n_item)) {
+            int head, q0, nkb;
+            item_geom(item, head, q0, nkb);
+            const int row = q0 + row_local;
+            const int horizon = min(args.ctx - 1, row + args.off);  // last visible key of this row
+            float m = -INFINITY, l = 0.0f;
+            for (int j = 0; j < nkb && ok; ++j, ++g) {
+                const unsigned b = g & 1u, ph = (g >> 1) & 1u;
+                if (!mbar_wait(&s_full[b], ph, args.wait)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t v[2][32];
+                tmem_ld32_nowait(s_addr + b * 128, v[0]);
+                tmem_ld32_nowait(s_addr + b * 128 + 32, v[1]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = j * 128 + half * 64;
+                const bool full = col0 + 63 <= horizon;
+                if (!full) {  // a block that straddles the row's horizon: hidden scores become -inf (probability 0)
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (col0 + i > horizon) v[i >> 5][i & 31] = 0xff800000u;
+                }
+                float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maximum is on the critical path
 #pragma unroll
                 for (int i = 0; i < 64; ++i) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(v[i >> 5][i & 31]));
-            } else {
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (col0 + i <= horizon) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(v[i >> 5][i & 31]));
-            }
-            const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
-            // The reference point m of the stream's exponentials moves only when a block exceeds it by more than 2^8:
-            // any reference gives the same quotient at the end, probabilities up to 256 are harmless in f32 and in the
-            // 16-bit types, and the rescaling below (a round trip through tensor memory that has to wait for the previous
-            // product) becomes rare instead of happening whenever one of a warp's 32 rows sees a new maximum.
-            const float m_new = (bm - m) * args.c > 8.0f ? bm : m;  // m = -inf: the first visible block sets it
-            const float alpha = m_new != m ? ex2_approx((m - m_new) * args.c) : 1.0f;  // m = -inf: 0
-            if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
-                // this stream's accumulator holds the sum up to block j - 1 relative to the old maxima: wait for that
-                // product to be complete, then scale the row in place
-                if (!mbar_wait(&pv_done[b ^ 1u], (((unsigned)(j - 1)) >> 1) & 1u, args.wait)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
+                // The reference point m of the stream's exponentials moves only when a block exceeds it by more than 2^8:
+                // any reference gives the same quotient at the end, probabilities up to 256 are harmless in f32 and in the
+                // 16-bit types, and the rescaling below (a round trip through tensor memory that has to wait for the previous
+                // product) becomes rare instead of happening whenever one of a warp's 32 rows sees a new maximum.
+                const float m_new = (bm - m) * args.c > 8.0f ? bm : m;  // m = -inf: the first visible block sets it
+                const float alpha = m_new != m ? ex2_approx((m - m_new) * args.c) : 1.0f;  // m = -inf: 0
+                if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+                    // this stream's accumulator holds the sum up to block j - 1 relative to the old reference: wait for that
+                    // product to be complete, then scale the row in place
+                    if (!mbar_wait(&pv_done[b ^ 1u], ((g - 1) >> 1) & 1u, args.wait)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (int cq = 0; cq < 4; ++cq) {
-                    uint32_t o[32];
-                    tmem_ld32(o_mine + cq * 32, o);
+                    for (int cq = 0; cq < 4; ++cq) {
+                        uint32_t o[32];
+                        tmem_ld32(o_mine + cq * 32, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(o_mine + cq * 32, o);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(o_mine + cq * 32, o);
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 }
+                l *= alpha;
+                m = m_new;
+                const float mc = m == -INFINITY ? 0.0f : m * args.c;  // a stream that has seen no key yet: its scores are all -inf
+                uint32_t packed[32];
+                float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(v[i >> 5][i & 31]), args.c, -mc));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(v[(i + 1) >> 5][(i + 1) & 31]), args.c, -mc));
+                    l4[i & 2] += p0;
+                    l4[(i & 2) + 1] += p1;
+                    if (KIND == 2) {
+                        __half2 hh = __floats2half2_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
+                    } else {
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
+                    }
+                }
+                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                // P goes back into tensor memory, over the first 32 columns of the scores this thread has just consumed
+                // (its row = its lane, two elements per column): the A operand of the P V product is read from there
+                tmem_st32(s_addr + b * 128, packed);
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[b]);
             }
-            l *= alpha;
-            m = m_new;
-            const float mc = m * args.c;
-            uint32_t packed[32];
-            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-                float p0 = ex2_approx(fmaf(__uint_as_float(v[i >> 5][i & 31]), args.c, -mc));
-                float p1 = ex2_approx(fmaf(__uint_as_float(v[(i + 1) >> 5][(i + 1) & 31]), args.c, -mc));
-                if (!full) {
-                    if (col0 + i > horizon) p0 = 0.0f;
-                    if (col0 + i + 1 > horizon) p1 = 0.0f;
-                }
-                l4[i & 2] += p0;
-                l4[(i & 2) + 1] += p1;
-                if (KIND == 2) {
-                    __half2 hh = __floats2half2_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
-                } else {
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&hh);
-                }
-            }
-            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            // P goes back into tensor memory, over the first 32 columns of the scores this thread has just consumed
-            // (its row = its lane, two elements per column): the A operand of the P V product is read from there
-            tmem_st32(s_addr + b * 128, packed);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[b]);
-        }
-        // merge the two streams of a row: weights 2^((m_h - M) c), M = max(m_0, m_1).  The exchange goes through the K ring,
-        // which is dead by now: this warp has seen the last S complete, and every S MMA precedes it in the tensor pipe.
-        float (*red_m)[128] = reinterpret_cast<float (*)[128]>(sK);
-        float (*red_l)[128] = reinterpret_cast<float (*)[128]>(sK + 1024);
-        red_m[half][row_local] = m;
-        red_l[half][row_local] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        const float m0 = red_m[0][row_local], m1 = red_m[1][row_local];
-        const float mm = fmaxf(m0, m1);
-        const float w0 = m0 == -INFINITY ? 0.0f : ex2_approx((m0 - mm) * args.c);
-        const float w1 = m1 == -INFINITY ? 0.0f : ex2_approx((m1 - mm) * args.c);
-        const float lsum = w0 * red_l[0][row_local] + w1 * red_l[1][row_local];
-        if (ok && mbar_wait(&o_full, 0, args.wait)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float i0 = w0 / lsum, i1 = w1 / lsum;
-            uint16_t *dst = reinterpret_cast<uint16_t *>(args.out) + (size_t)row * args.ldo + (size_t)head * 128 + half * 64;
+            // merge the two streams of a row: weights 2^((m_h - M) c), M = max(m_0, m_1).  (Every softmax warp passes the
+            // two barriers of every item, also after a wait has run out: nobody is left waiting at them.)
+            red_m[half][row_local] = m;
+            red_l[half][row_local] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float m0 = red_m[0][row_local], m1 = red_m[1][row_local];
+            const float mm = fmaxf(m0, m1);
+            const float w0 = m0 == -INFINITY ? 0.0f : ex2_approx((m0 - mm) * args.c);
+            const float w1 = m1 == -INFINITY ? 0.0f : ex2_approx((m1 - mm) * args.c);
+            const float lsum = w0 * red_l[0][row_local] + w1 * red_l[1][row_local];
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the exchange arrays may be rewritten for the next item
+            if (ok && !mbar_wait(&o_full, n_item & 1u, args.wait)) ok = false;
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float i0 = w0 / lsum, i1 = w1 / lsum;
+                uint16_t *dst = reinterpret_cast<uint16_t *>(args.out) + (size_t)row * args.ldo + (size_t)head * 128 + half * 64;
 #pragma unroll 1
-            for (int cq = 0; cq < 2; ++cq) {  // 32 output columns at a time
-                uint32_t a[32], bb[32];
-                tmem_ld32_nowait(lane_base + 256 + half * 64 + cq * 32, a);
-                tmem_ld32_nowait(lane_base + 384 + half * 64 + cq * 32, bb);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < args.T) {
+                for (int cq = 0; cq < 2; ++cq) {  // 32 output columns at a time
+                    uint32_t a[32], bb[32];
+                    tmem_ld32_nowait(lane_base + 256 + half * 64 + cq * 32, a);
+                    tmem_ld32_nowait(lane_base + 384 + half * 64 + cq * 32, bb);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (cq == 1) {  // both accumulators of this item are in registers: the next item may overwrite them
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&o_empty);
+                    }
+                    if (row < args.T) {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint32_t w[4];
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int i = 8 * ch + 2 * e;
-                            const float f0 = __uint_as_float(a[i]) * i0 + __uint_as_float(bb[i]) * i1;
-                            const float f1 = __uint_as_float(a[i + 1]) * i0 + __uint_as_float(bb[i + 1]) * i1;
-                            if (KIND == 2) {
-                                __half2 hh = __floats2half2_rn(f0, f1);
-                                w[e] = *reinterpret_cast<uint32_t *>(&hh);
-                            } else {
-                                __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
-                                w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                            for (int e = 0; e < 4; ++e) {
+                                const int i = 8 * ch + 2 * e;
+                                const float f0 = __uint_as_float(a[i]) * i0 + __uint_as_float(bb[i]) * i1;
+                                const float f1 = __uint_as_float(a[i + 1]) * i0 + __uint_as_float(bb[i + 1]) * i1;
+                                if (KIND == 2) {
+                                    __half2 hh = __floats2half2_rn(f0, f1);
+                                    w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                                } else {
+                                    __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                                    w[e] = *reinterpret_cast<uint32_t *>(&hh);
+                                }
                             }
+                            *reinterpret_cast<uint4 *>(dst + cq * 32 + 8 * ch) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                        *reinterpret_cast<uint4 *>(dst + cq * 32 + 8 * ch) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
@@ -1730,7 +1765,8 @@ int launch_attention_prefill(xn_dtype dt, void *out, size_t ldo, const void *q, 
     if (rc) return rc;
     const size_t smem = (size_t)10 * ATT_TILE + 1024;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(heads * a.nqb));
+    const size_t items = heads * (size_t)a.nqb;
+    cfg.gridDim = dim3((unsigned)(items < (size_t)sm_count() ? items : (size_t)sm_count()));
     cfg.blockDim = dim3(ATT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
