@@ -675,6 +675,42 @@ __device__ __forceinline__ int unit_owner(int u, int uq, int ur) {  // the CTA w
     return u < big ? (int)((unsigned)u / (unsigned)(uq + 1)) : ur + (int)((unsigned)(u - big) / (unsigned)uq);
 }
 
+// The finisher's sum over a split tile's contributors for one lane quarter: ROWS activation rows x NC contributors per
+// round of loads, added in contributor order; x_scale comes from shared memory (s_xs), staged at kernel start.
+template <int KIND, int ROWS, int NC>
+__device__ __forceinline__ void skinny_reduce(const SkinnyArgs &args, const float *s_xs, float ws, int ch, int q, int lane,
+                                              int c_first, int c_last, int t0, int uq, int ur, size_t slot_elems) {
+    constexpr bool F8 = KIND == 0;
+    for (int m0 = 0; m0 < args.M; m0 += ROWS) {
+        float sum[ROWS];
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) sum[j] = 0.0f;
+        for (int cc0 = c_first; cc0 <= c_last; cc0 += NC) {
+            float tv[NC][ROWS];
+#pragma unroll
+            for (int d = 0; d < NC; ++d) {
+                const int cc = cc0 + d;
+                const bool on = cc <= c_last;
+                const int slot = on ? 2 * cc + (unit_begin(cc, uq, ur) >= t0 ? 0 : 1) : 0;
+                const float *src = args.partials + (size_t)slot * slot_elems + (size_t)m0 * BM + q * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < ROWS; ++j) tv[d][j] = (on && m0 + j < args.MB) ? __ldcg(src + (size_t)j * BM) : 0.0f;
+            }
+#pragma unroll
+            for (int d = 0; d < NC; ++d)
+#pragma unroll
+                for (int j = 0; j < ROWS; ++j) sum[j] += tv[d][j];
+        }
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j)
+            if (m0 + j < args.M) {
+                const float val = F8 ? ws * (s_xs[m0 + j] * sum[j]) : sum[j];
+                if (KIND == 2) reinterpret_cast<__half *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2half_rn(val);
+                else reinterpret_cast<__nv_bfloat16 *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2bfloat16_rn(val);
+            }
+    }
+}
+
 // KIND: 0 = fp8 pieces -> bf16 out (scaled), 1 = bf16 -> bf16, 2 = f16 -> f16 (one piece, no scales)
 template <int KIND>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -696,6 +732,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t full[8], empty[8], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_slot;
+    __shared__ float s_xs[64];  // x_scale of the (at most 64) activation rows
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (args.K + (KIND == 0 ? BKB : BKB / 2) - 1) / (KIND == 0 ? BKB : BKB / 2);
@@ -796,6 +833,11 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         bool ok = true;
         const size_t slot_elems = (size_t)args.MB * BM;
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (F8 && warp == 2) {
+            s_xs[lane] = lane < args.M ? __ldg(args.x_scale + lane) : 0.0f;
+            s_xs[lane + 32] = lane + 32 < args.M ? __ldg(args.x_scale + lane + 32) : 0.0f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         for (int u = u0; u < u1 && ok; ++t_local) {
             const int tile = (int)((unsigned)u / (unsigned)num_kb), kb0 = u - tile * num_kb;
             const int kb1 = min(num_kb, kb0 + (u1 - u));
@@ -836,7 +878,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                         for (int j = 0; j < 16; ++j) {
                             const int mrow = c + j;
                             if (mrow < args.M) {  // 32 lanes = 32 consecutive channels of one activation row
-                                const float val = F8 ? ws * (__ldg(args.x_scale + mrow) * __uint_as_float(v[j])) : __uint_as_float(v[j]);
+                                const float val = F8 ? ws * (s_xs[mrow] * __uint_as_float(v[j])) : __uint_as_float(v[j]);
                                 if (KIND == 2) reinterpret_cast<__half *>(args.y)[(size_t)mrow * args.ldy + ch] = __float2half_rn(val);
                                 else reinterpret_cast<__nv_bfloat16 *>(args.y)[(size_t)mrow * args.ldy + ch] = __float2bfloat16_rn(val);
                             }
@@ -866,36 +908,14 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     __threadfence();
                     if (lane == 0) args.counters[(size_t)tile * 4 + q] = 0;  // ready for the next launch
                     if (ch < args.N) {
-                        // 16 activation rows at a time, four contributors' loads in flight together; the
-                        // additions run in contributor (= k) order whatever the arrival order was
-                        for (int m0 = 0; m0 < args.M; m0 += 16) {
-                            float sum[16];
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) sum[j] = 0.0f;
-                            for (int cc0 = c_first; cc0 <= c_last; cc0 += 4) {
-                                float tv[4][16];
-#pragma unroll
-                                for (int d = 0; d < 4; ++d) {
-                                    const int cc = cc0 + d;
-                                    const bool on = cc <= c_last;
-                                    const int slot = on ? 2 * cc + (unit_begin(cc, uq, ur) >= t0 ? 0 : 1) : 0;
-                                    const float *src = args.partials + (size_t)slot * slot_elems + (size_t)m0 * BM + q * 32 + lane;
-#pragma unroll
-                                    for (int j = 0; j < 16; ++j) tv[d][j] = (on && m0 + j < args.MB) ? __ldcg(src + (size_t)j * BM) : 0.0f;
-                                }
-#pragma unroll
-                                for (int d = 0; d < 4; ++d)
-#pragma unroll
-                                    for (int j = 0; j < 16; ++j) sum[j] += tv[d][j];
-                            }
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (m0 + j < args.M) {
-                                    const float val = F8 ? ws * (__ldg(args.x_scale + m0 + j) * sum[j]) : sum[j];
-                                    if (KIND == 2) reinterpret_cast<__half *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2half_rn(val);
-                                    else reinterpret_cast<__nv_bfloat16 *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2bfloat16_rn(val);
-                                }
-                        }
+                        // This reduction is the tail of the kernel: every round of loads is an L2 round trip on the
+                        // critical path.  64 loads are in flight per round: two contributors x 32 rows when a tile has
+                        // at most two (wide weights: one round for 32 rows), four contributors x 16 rows otherwise.
+                        // The additions run in contributor (= k) order whatever the arrival order was.
+                        if (c_last - c_first < 2)
+                            skinny_reduce<KIND, 32, 2>(args, s_xs, ws, ch, q, lane, c_first, c_last, t0, uq, ur, slot_elems);
+                        else
+                            skinny_reduce<KIND, 16, 4>(args, s_xs, ws, ch, q, lane, c_first, c_last, t0, uq, ur, slot_elems);
                     }
                 }
             }
