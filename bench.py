@@ -446,7 +446,7 @@ def measure_prefill_stack(args, dev, world, rank, timed, torch, dist) -> dict:
            "nvlink_bytes_out_per_rank": st.exchanged_bytes_per_rank(),
            "route": "multimem.st through an NVLink multicast mapping" if st.proj_full.mc_ptr else
                     ("plain stores into peer buffers" if world > 1 else "one rank: no exchange"),
-           "variant": "W8A16", "attention": "causal, one kernel per layer for all heads of the rank (scores in tensor memory, probabilities in shared memory)"}
+           "variant": "W8A16", "attention": "causal, one kernel per layer for all heads of the rank (scores and probabilities in tensor memory)"}
     del st
     torch.cuda.empty_cache()
     return out
