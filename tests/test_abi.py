@@ -128,6 +128,27 @@ def test_row_op_and_scatter_validation_on_the_host(xn):
     assert lib.xn_mm_linear_fp8_noalloc(None, None, None, None, 65, 16, 128, 0, None) == 2
 
 
+def test_prefill_attention_validation_on_the_host(xn):
+    """xn_mm_attention_prefill refuses what its kernel cannot take before anything is launched."""
+    lib = xn.lib()
+    BF16, F32 = 2, 0
+    ok_args = dict(ldo=256, ld=768, hs=128, heads=2, hd=128, t=64, ctx=64)
+
+    def call(dtype=BF16, out=16, q=16, k=16, v=16, **kw):
+        a = dict(ok_args, **kw)
+        return lib.xn_mm_attention_prefill(dtype, out, a["ldo"], q, k, v, a["ld"], a["hs"], a["heads"], a["hd"], a["t"], a["ctx"],
+                                           0.1, None)
+
+    assert call(dtype=F32) == 1 and b"16-bit" in lib.xn_mm_last_error()
+    assert call(hd=64) == 1 and b"head_dim" in lib.xn_mm_last_error()
+    assert call(heads=0) == 0 and call(t=0) == 0                      # nothing to do
+    assert call(q=None) == 1 and b"null" in lib.xn_mm_last_error()
+    assert call(ctx=32) == 1 and b"context" in lib.xn_mm_last_error()  # fewer keys than query rows
+    assert call(ld=772) == 1 and call(hs=100) == 1 and call(q=18) == 1  # 16-byte alignment of pitches and pointers
+    assert call(ldo=128) == 1                                         # rows too short for two heads of 128
+    assert call(hs=64) == 1 and b"overlap" in lib.xn_mm_last_error()
+
+
 def test_entry_points_work_with_nvtx_ranges_switched_on():
     """XN_MM_NVTX=1 wraps every entry point in an NVTX range; without a profiler attached the ranges are no-ops and
     the host-only entry points behave as before (checked in a child process: the switch is read once)."""
