@@ -612,7 +612,7 @@ def main() -> None:
     # pinned host memory, quantizes them, runs the linear and copies the result back to pinned host memory.
     # The calls of a step are independent decode requests, so a serving loop spreads them over a few streams: the
     # copies of one call overlap the kernels of another (every call still pays its own copy in and copy out).
-    E2E_STREAMS = [torch.cuda.Stream() for _ in range(4)]
+    E2E_STREAMS = [torch.cuda.Stream() for _ in range(int(os.environ.get("XN_BENCH_E2E_STREAMS", "8")))]
     host_ys = {(m, i): torch.empty(m, N_OUT).pin_memory() for m in MS for i in range(R)}
 
     def step_e2e():
@@ -649,7 +649,7 @@ def main() -> None:
     e2e_steps = max(3, min(args.steps, 20))
     ms_e2e_eager = timed(step_e2e, e2e_steps)
 
-    # The same calls captured once in a CUDA graph -- copies in, quantizers, linears, copies out, forked over the four
+    # The same calls captured once in a CUDA graph -- copies in, quantizers, linears, copies out, forked over the
     # streams and joined -- and replayed every step, as a serving loop does with a step whose shapes repeat: what is
     # left per step is one graph launch instead of 72 x 4 driver calls from Python, and every step still copies its
     # inputs from and its results to pinned host memory.
@@ -746,9 +746,9 @@ def main() -> None:
                     "d2h_bytes_per_step": R * sum(m * N_OUT * 4 for m in MS), "steps": e2e_steps,
                     "ms_per_step": ms_e2e / e2e_steps, "calls_per_step": len(MS) * R,
                     "api": ("LinearQ4.forward_host -> xn_mm_linear_q4_host (copy in, quantize rows, linear, copy out), "
-                            "calls spread round-robin over 4 streams; the step's calls are captured once in a CUDA graph "
+                            "calls spread round-robin over 8 streams; the step's calls are captured once in a CUDA graph "
                             "(copies included) and replayed per step") if e2e_graph_ok else
-                           "LinearQ4.forward_host -> xn_mm_linear_q4_host, plain calls over 4 streams (graph replay differed)",
+                           "LinearQ4.forward_host -> xn_mm_linear_q4_host, plain calls over 8 streams (graph replay differed)",
                     "plain_calls_value": world * e2e_steps * len(MS) * R * wb / (ms_e2e_eager * 1e-3) / 1e9},
             "gpu_launches": args.steps * launches_per_step,
             "fp8_prefill_gemm": fp8_prefill,
