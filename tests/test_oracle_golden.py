@@ -27,7 +27,7 @@ def test_oracle_f32_vs_f64_noise_floor(oracle):
     a = oracle.gemm(oracle.F32, 4 * 64, x.reshape(-1), 0, w.reshape(-1), 0, 4, 64, 4096, 1, 0, 0, (1, 64), (1, 4096), (4096, 1), 0)
     b = oracle.gemm_f64(oracle.F32, x.reshape(-1), 0, w.reshape(-1), 0, 4, 64, 4096, 1, 0, 0, (1, 4096), (4096, 1))
     # strictly sequential f32 accumulation over k = 4096 is itself ~1e-4 away from the true value in
-    # this metric, which is why the f32 parity tests judge kernels against the f64-accumulated twin
+    # this metric, which is why the f32 parity tests compare kernels with the f64-accumulated twin
     assert oracle.rel_err(a, b) < 3e-4
     c = oracle.linear_f32_fast(x, w)
     assert oracle.rel_err(c, b) < 5e-5
