@@ -659,7 +659,7 @@ struct SkinnyArgs {
     int ldy;
     const float *x_scale, *w_scale;  // fp8 operands only
     float *partials;     // scratch: [2 * grid][MB][128] f32 partial accumulators of split tiles
-    unsigned *counters;  // scratch: [tiles][4] arrival counts per (tile, lane quarter); zero between launches
+    unsigned *counters;  // scratch: [tiles] arrival counts; zero between launches
     int M, N, K;
     int MB;      // MMA N dimension: M rounded up to 16
     int nstage;
@@ -671,7 +671,7 @@ struct SkinnyArgs {
 
 // Work is cut at k-stage granularity ("stream-K"): total = tiles * num_kb stage units, CTA c owns the
 // contiguous unit range [c*total/G, (c+1)*total/G), i.e. a run of segments (tile, kb0..kb1).  A tile
-// that is covered by several CTAs is finished by whichever of them arrives last (per lane quarter):
+// that is covered by several CTAs is finished by whichever of them arrives last:
 // every contributor stores its f32 partial to scratch, and the finisher adds all partials in k order
 // -- a fixed order, so the result does not depend on which CTA happens to be last.
 // (32-bit arithmetic only: a 64-bit division is ~100 dependent instructions, and the epilogue warps sit on
@@ -683,39 +683,75 @@ __device__ __forceinline__ int unit_owner(int u, int uq, int ur) {  // the CTA w
     return u < big ? (int)((unsigned)u / (unsigned)(uq + 1)) : ur + (int)((unsigned)(u - big) / (unsigned)uq);
 }
 
-// The finisher's sum over a split tile's contributors for one lane quarter: ROWS activation rows x NC contributors per
-// round of loads, added in contributor order; x_scale comes from shared memory (s_xs), staged at kernel start.
-template <int KIND, int ROWS, int NC>
-__device__ __forceinline__ void skinny_reduce(const SkinnyArgs &args, const float *s_xs, float ws, int ch, int q, int lane,
-                                              int c_first, int c_last, int t0, int uq, int ur, size_t slot_elems) {
+// The finisher's sum over a split tile's contributors.  The four epilogue warps of the CTA that arrived last share
+// the tile's rows (warp w takes rows w, w + 4, ...); a lane owns four consecutive channels, so one 128-bit load per
+// (row, contributor) and one 8-byte store per row replace four scalar ones -- the reduction is the tail of the
+// kernel and was bound by its own instruction count on one warp per scheduler.  RB rows x NC contributors are in
+// flight per round; the additions run in contributor (= k) order whatever the arrival order was.
+template <int KIND, int RB, int NC>
+__device__ __forceinline__ void skinny_reduce(const SkinnyArgs &args, const float *s_xs, int tile, int w, int lane, int c_first,
+                                              int c_last, int t0, int uq, int ur, size_t slot_elems) {
     constexpr bool F8 = KIND == 0;
-    for (int m0 = 0; m0 < args.M; m0 += ROWS) {
-        float sum[ROWS];
+    const int ch0 = tile * BM + 4 * lane;  // first of this lane's four channels
+    float ws[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    if (F8) {
 #pragma unroll
-        for (int j = 0; j < ROWS; ++j) sum[j] = 0.0f;
+        for (int i = 0; i < 4; ++i) ws[i] = ch0 + i < args.N ? __ldg(args.w_scale + ch0 + i) : 0.0f;
+    }
+    const bool vec_store = ch0 + 4 <= args.N && (args.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(args.y) & 7) == 0;
+    for (int m0 = w; m0 < args.M; m0 += 4 * RB) {
+        float4 sum[RB];
+#pragma unroll
+        for (int j = 0; j < RB; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int cc0 = c_first; cc0 <= c_last; cc0 += NC) {
-            float tv[NC][ROWS];
+            float4 tv[NC][RB];
 #pragma unroll
             for (int d = 0; d < NC; ++d) {
                 const int cc = cc0 + d;
                 const bool on = cc <= c_last;
                 const int slot = on ? 2 * cc + (unit_begin(cc, uq, ur) >= t0 ? 0 : 1) : 0;
-                const float *src = args.partials + (size_t)slot * slot_elems + (size_t)m0 * BM + q * 32 + lane;
+                const float *src = args.partials + (size_t)slot * slot_elems + 4 * lane;
 #pragma unroll
-                for (int j = 0; j < ROWS; ++j) tv[d][j] = (on && m0 + j < args.MB) ? __ldcg(src + (size_t)j * BM) : 0.0f;
+                for (int j = 0; j < RB; ++j) {
+                    const int row = m0 + 4 * j;
+                    tv[d][j] = (on && row < args.M) ? __ldcg(reinterpret_cast<const float4 *>(src + (size_t)row * BM))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
 #pragma unroll
             for (int d = 0; d < NC; ++d)
 #pragma unroll
-                for (int j = 0; j < ROWS; ++j) sum[j] += tv[d][j];
+                for (int j = 0; j < RB; ++j) {
+                    sum[j].x += tv[d][j].x; sum[j].y += tv[d][j].y; sum[j].z += tv[d][j].z; sum[j].w += tv[d][j].w;
+                }
         }
 #pragma unroll
-        for (int j = 0; j < ROWS; ++j)
-            if (m0 + j < args.M) {
-                const float val = F8 ? ws * (s_xs[m0 + j] * sum[j]) : sum[j];
-                if (KIND == 2) reinterpret_cast<__half *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2half_rn(val);
-                else reinterpret_cast<__nv_bfloat16 *>(args.y)[(size_t)(m0 + j) * args.ldy + ch] = __float2bfloat16_rn(val);
+        for (int j = 0; j < RB; ++j) {
+            const int row = m0 + 4 * j;
+            if (row >= args.M) continue;
+            const float xs = F8 ? s_xs[row] : 1.0f;
+            const float val[4] = {F8 ? ws[0] * (xs * sum[j].x) : sum[j].x, F8 ? ws[1] * (xs * sum[j].y) : sum[j].y,
+                                  F8 ? ws[2] * (xs * sum[j].z) : sum[j].z, F8 ? ws[3] * (xs * sum[j].w) : sum[j].w};
+            if (KIND == 2) {
+                __half *dst = reinterpret_cast<__half *>(args.y) + (size_t)row * args.ldy + ch0;
+                if (vec_store) {
+                    const __half2 lo = __floats2half2_rn(val[0], val[1]), hi = __floats2half2_rn(val[2], val[3]);
+                    *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+                } else {
+                    for (int i = 0; i < 4; ++i)
+                        if (ch0 + i < args.N) dst[i] = __float2half_rn(val[i]);
+                }
+            } else {
+                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(args.y) + (size_t)row * args.ldy + ch0;
+                if (vec_store) {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(val[0], val[1]), hi = __floats2bfloat162_rn(val[2], val[3]);
+                    *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+                } else {
+                    for (int i = 0; i < 4; ++i)
+                        if (ch0 + i < args.N) dst[i] = __float2bfloat16_rn(val[i]);
+                }
             }
+        }
     }
 }
 
@@ -741,6 +777,8 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     __shared__ __align__(8) uint64_t full[8], empty[8], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ float s_xs[64];  // x_scale of the (at most 64) activation rows
+    __shared__ int s_ok[2][4];  // per segment parity: has each epilogue warp seen its accumulator?
+    __shared__ int s_last;      // this CTA arrived last at the split tile of the current segment
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (args.K + (KIND == 0 ? BKB : BKB / 2) - 1) / (KIND == 0 ? BKB : BKB / 2);
@@ -855,7 +893,12 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             const bool whole = kb0 == 0 && kb1 == num_kb;
             const int acc = t_local & 1;
             const unsigned acc_ph = (unsigned)(t_local >> 1) & 1u;
-            if (!mbar_wait(&tmem_full[acc], acc_ph, args.wait)) { ok = false; break; }
+            // The four warps act together below (named barrier 1): a warp whose wait ran out still takes part in this
+            // segment's barrier, and all four leave the loop together.
+            const bool got = mbar_wait(&tmem_full[acc], acc_ph, args.wait);
+            if (lane == 0) s_ok[t_local & 1][q] = got ? 1 : 0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!(s_ok[t_local & 1][0] && s_ok[t_local & 1][1] && s_ok[t_local & 1][2] && s_ok[t_local & 1][3])) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int ch = tile * BM + q * 32 + lane;  // output channel of this lane
             const float ws = !F8 ? 1.0f : (ch < args.N ? __ldg(args.w_scale + ch) : 0.0f);
@@ -910,24 +953,20 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 const int t0 = tile * num_kb, t1 = t0 + num_kb;
                 const int c_first = unit_owner(t0, uq, ur), c_last = unit_owner(t1 - 1, uq, ur);
                 const unsigned ncontrib = (unsigned)(c_last - c_first + 1);
-                __threadfence();
-                __syncwarp();
-                unsigned old = 0;
-                if (lane == 0) old = atomicAdd(args.counters + (size_t)tile * 4 + q, 1u);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == ncontrib - 1) {  // last arriver of this quarter: reduce in k order and store
+                __threadfence();  // this warp's quarter of the partial is visible before the CTA is counted
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) s_last = atomicAdd(args.counters + tile, 1u) == ncontrib - 1 ? 1 : 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (s_last) {  // last arriver: reduce in k order and store
                     __threadfence();
-                    if (lane == 0) args.counters[(size_t)tile * 4 + q] = 0;  // ready for the next launch
-                    if (ch < args.N) {
-                        // This reduction is the tail of the kernel: every round of loads is an L2 round trip on the
-                        // critical path.  64 loads are in flight per round: two contributors x 32 rows when a tile has
-                        // at most two (wide weights: one round for 32 rows), four contributors x 16 rows otherwise.
-                        // The additions run in contributor (= k) order whatever the arrival order was.
-                        if (c_last - c_first < 2)
-                            skinny_reduce<KIND, 32, 2>(args, s_xs, ws, ch, q, lane, c_first, c_last, t0, uq, ur, slot_elems);
-                        else
-                            skinny_reduce<KIND, 16, 4>(args, s_xs, ws, ch, q, lane, c_first, c_last, t0, uq, ur, slot_elems);
-                    }
+                    if (warp == 2 && lane == 0) args.counters[tile] = 0;  // ready for the next launch
+                    // Every round of loads is an L2 round trip on the critical path at the end of the kernel: 16
+                    // 128-bit loads per lane are in flight per round (8 rows x 2 contributors when a tile has at most
+                    // two, 4 rows x 4 otherwise).
+                    if (c_last - c_first < 2)
+                        skinny_reduce<KIND, 8, 2>(args, s_xs, tile, warp - 2, lane, c_first, c_last, t0, uq, ur, slot_elems);
+                    else
+                        skinny_reduce<KIND, 4, 4>(args, s_xs, tile, warp - 2, lane, c_first, c_last, t0, uq, ur, slot_elems);
                 }
             }
             u += kb1 - kb0;
@@ -1703,7 +1742,8 @@ int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ld
     const int stage = BM * BKB + a.np * a.MB * BKB;
     // a ring of about 100 KB: two CTAs (this launch's and the next one's, see the kernel) fit an SM, and the
     // kernel is not bound by bytes in flight (3 to 8 stages measured the same)
-    a.nstage = (100 * 1024) / stage > 8 ? 8 : (100 * 1024) / stage;
+    static const int ring_kb = [] { const char *e = getenv("XN_SKINNY_RING_KB"); return e ? atoi(e) : 100; }();
+    a.nstage = (ring_kb * 1024) / stage > 8 ? 8 : (ring_kb * 1024) / stage;
     if (a.nstage < 2) a.nstage = 2;
     const int tiles = (int)((n + BM - 1) / BM);
     const int num_kb = (int)((k + BK - 1) / BK);
