@@ -466,25 +466,36 @@ def measure_decode(args, dev, world, rank, timed):
     except torch.cuda.OutOfMemoryError:
         return {"unavailable": "not enough free device memory for the 57 GB decode working set"}
     x = torch.randn(streams, 4096, device=dev).bfloat16()
-    st.step(x)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            st.step(x)
-    torch.cuda.synchronize()
-    for _ in range(3):
-        graph.replay()
-    ms = timed(graph.replay, args.decode_steps)
-    per_step = ms / args.decode_steps
+
+    def time_mode(mode):
+        st.attention = mode
+        st.step(x)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                st.step(x)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        ms_ = timed(graph.replay, args.decode_steps)
+        del graph
+        return ms_ / args.decode_steps, st.launches_per_step()
+
+    # the same step with cache append + attention + merge + e4m3 split as ONE launch per layer (identical results,
+    # fewer launches, measured slower at this size: every attention CTA then ends with a fence and an arrival)
+    fused_ms, fused_launches = time_mode("fused_one_launch")
+    per_step, launches = time_mode("separate")
     b = st.bytes_per_step()
     peak, kind = measured_peak_gbs()
     return {"ms_per_step": per_step, "steps_per_s_per_gpu": 1e3 / per_step, "streams_per_gpu": streams,
             "tokens_per_s_all_gpus": world * streams * 1e3 / per_step, "context": ctx,
             "bytes_per_step_per_gpu": b["total"], "gb_per_s_per_gpu": b["total"] / (per_step * 1e-3) / 1e9,
             "frac_of_hbm_peak": b["total"] / (per_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}",
-            "launches_per_step": st.launches_per_step(), "variant": "W8A16",
+            "launches_per_step": launches, "variant": "W8A16",
+            "one_launch_attention": {"ms_per_step": fused_ms, "launches_per_step": fused_launches,
+                                     "frac_of_hbm_peak": b["total"] / (fused_ms * 1e-3) / 1e9 / peak},
             "l2": "working set 57 GB per GPU, far larger than L2"}
 
 

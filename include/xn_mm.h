@@ -343,6 +343,27 @@ int xn_mm_decode_attention_split_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_sca
                                       const float *mask_or_null, size_t batch, size_t heads, size_t context,
                                       size_t head_dim, float scale, void *workspace, size_t workspace_bytes,
                                       void *stream);
+
+/* One launch for what a decode layer does between its input and output projections
+ * (xn-moshi/src/batched_transformer.rs:136-160 with xn-core/src/models/kv_cache.rs:352-366): xn_mm_kv_append2 of the
+ * new key / value rows (k_new, v_new: [batch, heads * 128] bf16 rows qkv_batch_stride elements apart, appended at
+ * context index index[batch]; an index outside [0, context) appends nothing), xn_mm_decode_attention_split over the
+ * caches with q taken at the same batch stride, the merge of the context slices and the e4m3 split of the output row,
+ * with results identical to the three separate calls.  x_hi / x_lo / x_scale may all be null (no pieces wanted).
+ * merge: where the merge of the slices and the split run -- 1 = inside the attention kernel (one launch: the CTA that
+ * arrives last at a (stream, head) merges, the one that finishes a stream's last head splits the row), 2 = as a second
+ * launch, 0 = the library decides (inside when every resident slot sees at most two CTAs; with many short slices the
+ * fence and arrival at the end of every CTA cost more than the second launch).
+ * workspace: xn_mm_decode_attention_append_workspace_bytes(batch, heads, context) bytes of device memory owned by the
+ * caller; the arrival counters of the merge live in the library's per-stream scratch, so calls on one device must be
+ * stream-ordered with the other calls that use that scratch. */
+size_t xn_mm_decode_attention_append_workspace_bytes(size_t batch, size_t heads, size_t context);
+int xn_mm_decode_attention_append_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *out_bf16, const void *q_bf16,
+                                       const void *k_new_bf16, const void *v_new_bf16, size_t qkv_batch_stride,
+                                       void *k_cache_bf16, void *v_cache_bf16, const int64_t *index,
+                                       const float *mask_or_null, size_t batch, size_t heads, size_t context,
+                                       size_t head_dim, float scale, int merge, void *workspace, size_t workspace_bytes,
+                                       void *stream);
 /* xn_mm_kv_append for the key and the value cache in one launch (same index, same source layout). */
 int xn_mm_kv_append2(xn_dtype dtype, void *k_cache, void *v_cache, const void *k_src, const void *v_src,
                      size_t src_batch_stride, const int64_t *index, size_t batch, size_t heads, size_t context,

@@ -132,6 +132,12 @@ extern "C" {
         v_cache_bf16: *const c_void, mask_or_null: *const f32, batch: usize, heads: usize, context: usize,
         head_dim: usize, scale: f32, workspace: *mut c_void, workspace_bytes: usize,
         stream: *mut c_void) -> c_int;
+    pub fn xn_mm_decode_attention_append_workspace_bytes(batch: usize, heads: usize, context: usize) -> usize;
+    pub fn xn_mm_decode_attention_append_e4m3(x_hi: *mut u8, x_lo: *mut u8, x_scale: *mut f32,
+        out_bf16: *mut c_void, q_bf16: *const c_void, k_new_bf16: *const c_void, v_new_bf16: *const c_void,
+        qkv_batch_stride: usize, k_cache_bf16: *mut c_void, v_cache_bf16: *mut c_void, index: *const i64,
+        mask_or_null: *const f32, batch: usize, heads: usize, context: usize, head_dim: usize, scale: f32,
+        merge: c_int, workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn xn_mm_kv_append2(dtype: XnDtype, k_cache: *mut c_void, v_cache: *mut c_void, k_src: *const c_void,
         v_src: *const c_void, src_batch_stride: usize, index: *const i64, batch: usize, heads: usize,
         context: usize, head_dim: usize, stream: *mut c_void) -> c_int;

@@ -146,6 +146,15 @@ def test_decoder_step_reduced_size(xn, oracle, cuda):
     # measured: rms 0.0075, max 0.032 of the output's rms (a wrong head or a skipped residual moves the rms error
     # to order one)
     assert err_rms < 1e-2 and err_max < 4.5e-2
+    # the other two ways of launching a layer's append + attention + merge + split give the same bits
+    for mode in ("fused", "fused_one_launch"):
+        for lay, (k0, v0) in zip(st.layers, caches):
+            lay["k"].copy_(k0)
+            lay["v"].copy_(v0)
+        st.attention = mode
+        y2 = st.step(x).float().cpu().numpy()
+        assert np.array_equal(y, y2), mode
+        assert st.launches_per_step() == 2 * (8 if mode == "fused_one_launch" or st._merge_in_kernel() else 9) + 1
 
 
 def test_decode_attention_full_width_slice(xn, oracle, cuda):
@@ -273,6 +282,78 @@ def test_attention_with_fused_e4m3_split_equals_the_two_calls(xn, cuda, B, H, ct
     assert torch.equal(out0, out1) and torch.equal(hi0, hi1) and torch.equal(xs0, xs1)
     if variant == 0:
         assert torch.equal(lo0, lo1)
+
+
+@pytest.mark.parametrize("merge", [0, 1, 2])
+@pytest.mark.parametrize("B,H,ctx,variant,masked", [(4, 32, 3000, 0, False), (2, 8, 700, 1, True), (40, 4, 96, 0, False),
+                                                     (3, 2, 33, 0, True)])
+def test_attention_with_fused_append_merge_and_split_equals_the_separate_calls(xn, cuda, B, H, ctx, variant, masked, merge):
+    """xn_mm_decode_attention_append_e4m3 == xn_mm_kv_append2, then xn_mm_decode_attention_split_e4m3, bit for bit:
+    caches, attention output, pieces and row scales; new rows landing in different slices (first row, last row,
+    somewhere inside, outside the cache = nothing appended); called twice in a row (the arrival counters are back at
+    zero after a launch); merge inside the attention kernel (1), as a second launch (2), or as the library decides (0)."""
+    L = xn.lib()
+    hd = 128
+    g = torch.Generator(device=cuda).manual_seed(7 * B + ctx)
+    sc = 1.0 / math.sqrt(hd)
+    u8 = dict(dtype=torch.uint8, device=cuda)
+    k0 = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    v0 = torch.randn(B, H, ctx, hd, generator=g, device=cuda).bfloat16()
+    pos = [ctx - 1, 0, ctx // 2 + 1, ctx + 5, -1, ctx // 3]
+    idx = torch.tensor([pos[i % len(pos)] for i in range(B)], dtype=torch.int64, device=cuda)
+    mask = None
+    if masked:
+        mask = torch.zeros(B, ctx, device=cuda)
+        mask[:, ::3] = -1e9
+        mask[0, :] = 0.0
+    mp = mask.data_ptr() if mask is not None else None
+    ws_a = int(L.xn_mm_decode_attention_workspace_bytes(B, H, ctx))
+    ws_b = int(L.xn_mm_decode_attention_append_workspace_bytes(B, H, ctx))
+    assert ws_b >= ws_a and ws_b >= B * H * (hd + 2) * 4
+    wsa = torch.empty(max(ws_a, 4), dtype=torch.uint8, device=cuda)
+    wsb = torch.empty(ws_b, dtype=torch.uint8, device=cuda)
+    k1, v1, k2, v2 = k0.clone(), v0.clone(), k0.clone(), v0.clone()
+    for rep in range(2):
+        qkv = torch.randn(B, 3 * H * hd, generator=g, device=cuda).bfloat16()
+        q, kn, vn = qkv.data_ptr(), qkv.data_ptr() + 2 * H * hd, qkv.data_ptr() + 4 * H * hd
+        out1 = torch.empty(B, H * hd, dtype=torch.bfloat16, device=cuda)
+        hi1, lo1, xs1 = torch.zeros(B, H * hd, **u8), torch.zeros(B, H * hd, **u8), torch.zeros(B, device=cuda)
+        xn._lib.check(L.xn_mm_kv_append2(2, k1.data_ptr(), v1.data_ptr(), kn, vn, 3 * H * hd, idx.data_ptr(), B, H, ctx, hd, None))
+        xn._lib.check(L.xn_mm_decode_attention_split_e4m3(hi1.data_ptr(), lo1.data_ptr() if variant == 0 else None, xs1.data_ptr(),
+                                                          out1.data_ptr(), q, 3 * H * hd, k1.data_ptr(), v1.data_ptr(), mp,
+                                                          B, H, ctx, hd, sc, wsa.data_ptr(), ws_a, None))
+        out2 = torch.empty_like(out1)
+        hi2, lo2, xs2 = torch.zeros(B, H * hd, **u8), torch.zeros(B, H * hd, **u8), torch.zeros(B, device=cuda)
+        xn._lib.check(L.xn_mm_decode_attention_append_e4m3(hi2.data_ptr(), lo2.data_ptr() if variant == 0 else None,
+                                                           xs2.data_ptr(), out2.data_ptr(), q, kn, vn, 3 * H * hd,
+                                                           k2.data_ptr(), v2.data_ptr(), idx.data_ptr(), mp, B, H, ctx, hd, sc,
+                                                           merge, wsb.data_ptr(), ws_b, None))
+        torch.cuda.synchronize()
+        assert torch.equal(k1, k2) and torch.equal(v1, v2), rep
+        assert torch.equal(out1, out2), rep
+        assert torch.equal(hi1, hi2) and torch.equal(xs1, xs2), rep
+        if variant == 0:
+            assert torch.equal(lo1, lo2), rep
+    # without pieces: the attention output alone
+    out3 = torch.empty_like(out2)
+    k3, v3 = k0.clone(), v0.clone()
+    xn._lib.check(L.xn_mm_decode_attention_append_e4m3(None, None, None, out3.data_ptr(), q, kn, vn, 3 * H * hd, k3.data_ptr(),
+                                                       v3.data_ptr(), idx.data_ptr(), mp, B, H, ctx, hd, sc, merge, wsb.data_ptr(),
+                                                       ws_b, None))
+    out4 = torch.empty_like(out2)
+    k4, v4 = k0.clone(), v0.clone()
+    xn._lib.check(L.xn_mm_kv_append2(2, k4.data_ptr(), v4.data_ptr(), kn, vn, 3 * H * hd, idx.data_ptr(), B, H, ctx, hd, None))
+    xn._lib.check(L.xn_mm_decode_attention_split(out4.data_ptr(), q, 3 * H * hd, k4.data_ptr(), v4.data_ptr(), mp, B, H, ctx, hd,
+                                                 sc, wsa.data_ptr(), ws_a, None))
+    torch.cuda.synchronize()
+    assert torch.equal(out3, out4) and torch.equal(k3, k4) and torch.equal(v3, v4)
+    # a workspace that is too small is refused on the host
+    assert L.xn_mm_decode_attention_append_e4m3(None, None, None, out3.data_ptr(), q, kn, vn, 3 * H * hd, k3.data_ptr(),
+                                                v3.data_ptr(), idx.data_ptr(), mp, B, H, ctx, hd, sc, merge, wsb.data_ptr(), 8,
+                                                None) == 4
+    assert L.xn_mm_decode_attention_append_e4m3(None, None, None, out3.data_ptr(), q, kn, vn, 3 * H * hd, k3.data_ptr(),
+                                                v3.data_ptr(), idx.data_ptr(), mp, B, H, ctx, hd, sc, 3, wsb.data_ptr(), ws_b,
+                                                None) == 1
 
 
 def test_kv_append2_equals_two_appends(xn, cuda):

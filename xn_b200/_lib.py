@@ -71,6 +71,8 @@ SIGNATURES = {
     "xn_mm_decode_attention_workspace_bytes": (_sz, [_sz, _sz, _sz]),
     "xn_mm_decode_attention_split": (_i, [_p, _p, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, C.c_float, _p, _sz, _p]),
     "xn_mm_decode_attention_split_e4m3": (_i, [_p, _p, _p, _p, _p, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, C.c_float, _p, _sz, _p]),
+    "xn_mm_decode_attention_append_workspace_bytes": (_sz, [_sz, _sz, _sz]),
+    "xn_mm_decode_attention_append_e4m3": (_i, [_p, _p, _p, _p, _p, _p, _p, _sz, _p, _p, _p, _p, _sz, _sz, _sz, _sz, C.c_float, _i, _p, _sz, _p]),
     "xn_mm_kv_append2": (_i, [_i, _p, _p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _p]),
     "xn_mm_softmax_causal": (_i, [_i, _p, _p, _sz, _sz, _sz, C.c_float, _i, _p]),
     "xn_mm_gemm_causal": (_i, [_i, _sz, _i, _p, _p, _sz, _p, _sz] + [_sz] * 12 + [_p]),

@@ -565,6 +565,214 @@ decode_attention_combine_split_kernel(__nv_bfloat16 *__restrict__ out, uint8_t *
 }
 
 
+// The row loop of the single-token attention for one half-warp: rows row_lo + group, + 8, ... below row_hi of a
+// (stream, head) cache, online softmax in f32, the loads of the next 8 * U rows in flight while this group's scores
+// and products are computed.  kl / vl point at this lane's 16 bytes of row 0; with NEW, row r_new is read from
+// knl / vnl (the key / value being appended) instead of the cache.
+template <bool NEW>
+__device__ __forceinline__ void attend_rows(const float (&qv)[8], const __nv_bfloat16 *kl, const __nv_bfloat16 *vl,
+                                            const __nv_bfloat16 *knl, const __nv_bfloat16 *vnl, int r_new,
+                                            const float *mrow, int row_lo, int row_hi, int group, float &m_run, float &l_run,
+                                            float (&acc)[8]) {
+    constexpr int U = 4;
+    uint4 kn[U], vn[U];
+    auto fetch = [&](int base) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = base + group + 8 * u;
+            if (r < row_hi) {
+                const bool is_new = NEW && r == r_new;
+                kn[u] = ldg_stream(is_new ? knl : kl + (size_t)r * HD);
+                vn[u] = ldg_stream(is_new ? vnl : vl + (size_t)r * HD);
+            } else {
+                kn[u] = make_uint4(0, 0, 0, 0);
+                vn[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    fetch(row_lo);
+    for (int base = row_lo; base < row_hi; base += 8 * U) {  // uniform trip count across the CTA
+        const int r0 = base + group;
+        uint4 kr[U], vr[U];
+        float sc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) { kr[u] = kn[u]; vr[u] = vn[u]; }
+        if (base + 8 * U < row_hi) fetch(base + 8 * U);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&kr[u]);
+            float d = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d = fmaf(qv[j], __bfloat162float(e[j]), d);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);  // within the half-warp
+            const int r = r0 + 8 * u;
+            if (r >= row_hi) d = -INFINITY;
+            else if (mrow) d += mrow[r];
+            sc[u] = d;
+        }
+        float m_new = m_run;
+#pragma unroll
+        for (int u = 0; u < U; ++u) m_new = fmaxf(m_new, sc[u]);
+        if (m_new == -INFINITY) continue;  // everything masked so far
+        const float corr = __expf(m_run - m_new);
+        l_run *= corr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= corr;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float p = __expf(sc[u] - m_new);
+            l_run += p;
+            const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&vr[u]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(p, __bfloat162float(e[j]), acc[j]);
+        }
+        m_run = m_new;
+    }
+}
+
+// One launch for what a decode layer does between its input and output projections: append the new key / value row
+// of every (stream, head) to the caches at index[stream], attend over the cache, merge the context slices, and split
+// the [streams, heads * 128] output row into e4m3 pieces -- xn_mm_kv_append2, xn_mm_decode_attention_split and the
+// merge + split kernel in one grid, with identical results.
+//   * The slice that holds row index[stream] takes that row from the new key / value instead of the cache and writes
+//     it to the cache on the way (no other CTA of the grid touches the row).
+//   * Every slice stores its (maximum, sum, output) record; the CTA that arrives last at a (stream, head) merges
+//     the records in slice order, and the CTA that finishes the last head of a stream splits the stream's row.  Both
+//     "last" decisions are arrival counters in library scratch, zero between launches; the merges run in a fixed
+//     order, so the result does not depend on which CTA happens to be last.
+template <bool MERGE>
+__global__ void __launch_bounds__(128, 5)   // five CTAs per SM, like the kernel it extends
+decode_attention_append_kernel(__nv_bfloat16 *__restrict__ out, uint8_t *__restrict__ hi, uint8_t *__restrict__ lo,
+                               float *__restrict__ xs, const __nv_bfloat16 *__restrict__ q,
+                               const __nv_bfloat16 *__restrict__ k_new, const __nv_bfloat16 *__restrict__ v_new,
+                               __nv_bfloat16 *__restrict__ kc, __nv_bfloat16 *__restrict__ vc,
+                               const int64_t *__restrict__ index, const float *__restrict__ mask, size_t heads, size_t context,
+                               size_t qkv_batch_stride, float scale, size_t rows_per_split, float *__restrict__ partial,
+                               unsigned *__restrict__ cnt_head, unsigned *__restrict__ cnt_stream) {
+    const size_t bh = blockIdx.x, b = bh / heads, h = bh % heads;
+    // 32-bit row indices (context < 2^31): the loop's live state must fit 96 registers with the new-row pointers
+    const int row_lo = (int)(blockIdx.y * rows_per_split);
+    const int row_hi = (int)(row_lo + rows_per_split < context ? row_lo + rows_per_split : context);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4, l16 = lane & 15;
+    const int group = warp * 2 + half;  // 8 half-warps stride over the rows
+    float qv[8];
+    {
+        const uint4 t = *reinterpret_cast<const uint4 *>(q + b * qkv_batch_stride + h * HD + l16 * 8);
+        const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qv[j] = __bfloat162float(e[j]) * scale;
+    }
+    const int64_t pidx = index[b];
+    const int r_new = (pidx >= 0 && (size_t)pidx < context) ? (int)pidx : -1;  // out of range: nothing appended
+    const float *mrow = mask ? mask + b * context : nullptr;
+    float m_run = -INFINITY, l_run = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // Only the slice that holds the appended row pays for it: there the row's source is selected per load (no
+    // branch inside the software pipeline), everywhere else the loop is the plain one.
+    if (r_new >= row_lo && r_new < row_hi) {
+        const __nv_bfloat16 *knl = k_new + b * qkv_batch_stride + h * HD + l16 * 8;
+        const __nv_bfloat16 *vnl = v_new + b * qkv_batch_stride + h * HD + l16 * 8;
+        attend_rows<true>(qv, kc + bh * context * HD + l16 * 8, vc + bh * context * HD + l16 * 8, knl, vnl, r_new, mrow, row_lo,
+                          row_hi, group, m_run, l_run, acc);
+        if (group == ((r_new - row_lo) & 7)) {  // the half-warp that read the row also writes it to the caches
+            const size_t off = (bh * context + (size_t)r_new) * HD + l16 * 8, noff = b * qkv_batch_stride + h * HD + l16 * 8;
+            *reinterpret_cast<uint4 *>(kc + off) = *reinterpret_cast<const uint4 *>(k_new + noff);
+            *reinterpret_cast<uint4 *>(vc + off) = *reinterpret_cast<const uint4 *>(v_new + noff);
+        }
+    } else {
+        attend_rows<false>(qv, kc + bh * context * HD + l16 * 8, vc + bh * context * HD + l16 * 8, nullptr, nullptr, -1, mrow,
+                           row_lo, row_hi, group, m_run, l_run, acc);
+    }
+    // merge the 8 half-warp states into the slice's record
+    __shared__ float sm_m[8], sm_l[8], sm_acc[8][HD];
+    __shared__ float red[32];
+    __shared__ int s_last;
+    if (l16 == 0) { sm_m[group] = m_run; sm_l[group] = l_run; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm_acc[group][l16 * 8 + j] = acc[j];
+    __syncthreads();
+    const int splits = (int)gridDim.y;
+    {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int gI = 0; gI < 8; ++gI) mx = fmaxf(mx, sm_m[gI]);
+        float l = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int gI = 0; gI < 8; ++gI) {
+            const float w = sm_m[gI] == -INFINITY ? 0.0f : __expf(sm_m[gI] - mx);
+            l += w * sm_l[gI];
+            o += w * sm_acc[gI][threadIdx.x];
+        }
+        float *p = partial + (bh * splits + blockIdx.y) * (HD + 2);
+        p[2 + threadIdx.x] = o;
+        if (threadIdx.x == 0) { p[0] = mx; p[1] = l; }
+    }
+    if (!MERGE) return;  // the merge + split kernel follows as its own launch
+    // last slice of this (stream, head)?
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(cnt_head + bh, 1u) == (unsigned)splits - 1 ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    {
+        const float *p = partial + bh * splits * (HD + 2);
+        float mx = -INFINITY;
+        for (int s2 = 0; s2 < splits; ++s2) mx = fmaxf(mx, __ldcg(p + (size_t)s2 * (HD + 2)));
+        float l = 0.0f, o = 0.0f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float m = __ldcg(p + (size_t)s2 * (HD + 2));
+            const float w = m == -INFINITY ? 0.0f : __expf(m - mx);
+            l += w * __ldcg(p + (size_t)s2 * (HD + 2) + 1);
+            o += w * __ldcg(p + (size_t)s2 * (HD + 2) + 2 + threadIdx.x);
+        }
+        out[bh * HD + threadIdx.x] = __float2bfloat16_rn(o / l);
+    }
+    // last head of this stream?
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        cnt_head[bh] = 0;  // ready for the next launch
+        s_last = atomicAdd(cnt_stream + b, 1u) == (unsigned)heads - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last || !hi) {
+        if (s_last && threadIdx.x == 0) cnt_stream[b] = 0;
+        return;
+    }
+    __threadfence();
+    if (threadIdx.x == 0) cnt_stream[b] = 0;
+    // e4m3 pieces of the stream's row: a thread owns 4 consecutive dimensions of every fourth head
+    const int items = (int)heads * (HD / 4);
+    const __nv_bfloat16 *row = out + b * heads * HD;
+    float amax = 0.0f;
+    for (int it = threadIdx.x; it < items; it += 128) {
+        const uint2 t = __ldcg(reinterpret_cast<const uint2 *>(row + (size_t)it * 4));
+        const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(e[j])));
+    }
+    amax = block_max2(amax, red);
+    const float scl = pow2_scale(amax), inv = 1.0f / scl;
+    if (threadIdx.x == 0) xs[b] = scl;
+    for (int it = threadIdx.x; it < items; it += 128) {
+        const uint2 t = __ldcg(reinterpret_cast<const uint2 *>(row + (size_t)it * 4));
+        const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&t);
+        uint8_t hh[4], ll[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float yv = __bfloat162float(e[j]) * inv;
+            hh[j] = (uint8_t)__nv_cvt_float_to_fp8(yv, __NV_SATFINITE, __NV_E4M3);
+            ll[j] = (uint8_t)__nv_cvt_float_to_fp8(yv - e4m3_f32(hh[j]), __NV_SATFINITE, __NV_E4M3);
+        }
+        const size_t off = b * heads * HD + (size_t)it * 4;
+        *reinterpret_cast<uint32_t *>(hi + off) = *reinterpret_cast<const uint32_t *>(hh);
+        if (lo) *reinterpret_cast<uint32_t *>(lo + off) = *reinterpret_cast<const uint32_t *>(ll);
+    }
+}
+
+
 // Causal attention probabilities for a block of T query rows against ctx keys (the last T keys are the block's
 // own): row i sees keys j <= i + (ctx - T).  y = softmax(T(s * scale)) over the visible keys with the roundings of
 // the unfused route (scores scaled and rounded to the element type, exp and quotient rounded as in softmax_kernel),
@@ -1030,6 +1238,83 @@ extern "C" int xn_mm_kv_append2(xn_dtype dtype, void *k_cache, void *v_cache, co
                                     (T *)k_cache, (T *)v_cache, (const T *)k_src, (const T *)v_src, index, heads, context, head_dim,
                                     src_batch_stride, total));
     XN_CHECK_CUDA(cudaGetLastError());
+    return XN_OK;
+}
+
+extern "C" size_t xn_mm_decode_attention_append_workspace_bytes(size_t batch, size_t heads, size_t context) {
+    if (batch == 0 || heads == 0 || context == 0) return 0;
+    return batch * heads * (size_t)attention_splits(batch, heads, context) * (HD + 2) * sizeof(float);
+}
+
+extern "C" int xn_mm_decode_attention_append_e4m3(uint8_t *x_hi, uint8_t *x_lo, float *x_scale, void *out_bf16,
+                                                  const void *q_bf16, const void *k_new_bf16, const void *v_new_bf16,
+                                                  size_t qkv_batch_stride, void *k_cache_bf16, void *v_cache_bf16,
+                                                  const int64_t *index, const float *mask_or_null, size_t batch, size_t heads,
+                                                  size_t context, size_t head_dim, float scale, int merge, void *workspace,
+                                                  size_t workspace_bytes, void *stream) {
+    XN_API_RANGE("xn_mm_decode_attention_append_e4m3");
+    XN_REQUIRE(merge >= 0 && merge <= 2, "decode_attention_append: merge=%d (0 = library decides, 1 = in the kernel, 2 = own launch)", merge);
+    XN_REQUIRE(head_dim == 128, "decode_attention_append: head_dim %zu is not supported (128 only)", head_dim);
+    if (batch == 0 || heads == 0) return XN_OK;
+    XN_REQUIRE(context > 0, "decode_attention_append: empty context");
+    XN_REQUIRE(out_bf16 && q_bf16 && k_new_bf16 && v_new_bf16 && k_cache_bf16 && v_cache_bf16 && index,
+               "decode_attention_append: null pointer");
+    XN_REQUIRE((x_hi != nullptr) == (x_scale != nullptr) && (x_hi || !x_lo), "decode_attention_append: pieces and scales go together");
+    XN_REQUIRE(aligned(q_bf16, 16) && aligned(k_new_bf16, 16) && aligned(v_new_bf16, 16) && aligned(k_cache_bf16, 16) &&
+                   aligned(v_cache_bf16, 16) && qkv_batch_stride % 8 == 0,
+               "decode_attention_append: q, the new rows and the caches must be 16-byte aligned (batch stride a multiple of 8)");
+    XN_REQUIRE(aligned(out_bf16, 8) && (!x_hi || aligned(x_hi, 4)) && (!x_lo || aligned(x_lo, 4)),
+               "decode_attention_append: output row must be 8-byte, pieces 4-byte aligned");
+    XN_REQUIRE(batch * heads <= 0x7fffffffull, "decode_attention_append: too many (stream, head) pairs");
+    XN_REQUIRE(context <= 0x7fffffffull, "decode_attention_append: context %zu too long", context);
+    int splits = attention_splits(batch, heads, context);
+    const size_t need = batch * heads * (size_t)splits * (HD + 2) * sizeof(float);
+    if (workspace_bytes < need || !workspace)
+        return fail(XN_ERR_WORKSPACE, "decode_attention_append: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    XN_REQUIRE(aligned(workspace, 4), "decode_attention_append: workspace must be 4-byte aligned");
+    const size_t rows_per_split = ((context + splits - 1) / splits + 31) / 32 * 32;
+    splits = (int)((context + rows_per_split - 1) / rows_per_split);
+    cudaStream_t st = (cudaStream_t)stream;
+    // Where the merge runs.  Inside the attention kernel every CTA ends with a fence and an arrival (about 1.4 us
+    // during which its slot streams nothing); with many short slices per slot that costs more than the merge kernel's
+    // launch saves (32 streams x 32 heads x 3000 rows, 4864 CTAs: decode step 10.83 ms merged in the kernel against
+    // 10.5 ms with the merge as its own launch), so the library fuses the merge only when a slot sees at most two CTAs.
+    bool in_kernel = batch * heads * (size_t)splits <= (size_t)sm_count() * 5 * 2;
+    if (merge) in_kernel = merge == 1;
+    if (in_kernel) {
+        SkinnyScratch sc;  // arrival counters: one per (stream, head), one per stream; zero between launches
+        if (int rc = skinny_scratch(st, 0, batch * heads + batch, &sc)) return rc;
+        decode_attention_append_kernel<true><<<dim3((unsigned)(batch * heads), (unsigned)splits), 128, 0, st>>>(
+            (__nv_bfloat16 *)out_bf16, x_hi, x_lo, x_scale, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_new_bf16,
+            (const __nv_bfloat16 *)v_new_bf16, (__nv_bfloat16 *)k_cache_bf16, (__nv_bfloat16 *)v_cache_bf16, index, mask_or_null,
+            heads, context, qkv_batch_stride, scale, rows_per_split, (float *)workspace, sc.counters, sc.counters + batch * heads);
+        XN_CHECK_CUDA(cudaGetLastError());
+        return XN_OK;
+    }
+    decode_attention_append_kernel<false><<<dim3((unsigned)(batch * heads), (unsigned)splits), 128, 0, st>>>(
+        (__nv_bfloat16 *)out_bf16, x_hi, x_lo, x_scale, (const __nv_bfloat16 *)q_bf16, (const __nv_bfloat16 *)k_new_bf16,
+        (const __nv_bfloat16 *)v_new_bf16, (__nv_bfloat16 *)k_cache_bf16, (__nv_bfloat16 *)v_cache_bf16, index, mask_or_null,
+        heads, context, qkv_batch_stride, scale, rows_per_split, (float *)workspace, nullptr, nullptr);
+    XN_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    if (x_hi && heads <= 64) {  // merge + e4m3 split of the whole row in one launch
+        cfg.gridDim = dim3((unsigned)batch);
+        cfg.blockDim = dim3(1024);
+        XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, xn::decode_attention_combine_split_kernel, (__nv_bfloat16 *)out_bf16, x_hi, x_lo,
+                                         x_scale, (const float *)workspace, splits, (int)heads));
+        return XN_OK;
+    }
+    cfg.gridDim = dim3((unsigned)(batch * heads));
+    cfg.blockDim = dim3(HD);
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, decode_attention_combine_kernel, (__nv_bfloat16 *)out_bf16, (const float *)workspace,
+                                     splits));
+    if (x_hi) return xn_mm_split_rows_e4m3(x_hi, x_lo, x_scale, out_bf16, XN_BF16, batch, heads * head_dim, stream);
     return XN_OK;
 }
 

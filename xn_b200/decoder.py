@@ -20,8 +20,16 @@ from ._lib import BF16, check, lib
 
 class DecoderStack:
     def __init__(self, n_layers: int, d_model: int, n_heads: int, ffn_hidden: int, streams: int, context: int,
-                 device, eps: float = 1e-5, seed: int = 4, variant: int = 0, kv_init: str = "normal"):
+                 device, eps: float = 1e-5, seed: int = 4, variant: int = 0, kv_init: str = "normal",
+                 attention: str = "separate"):
+        """attention: how a layer's cache append, attention, merge of the context slices and e4m3 split are launched.
+        "separate" = xn_mm_kv_append2 + xn_mm_decode_attention_split_e4m3 (three launches; the fastest at 32 streams x
+        3000 tokens), "fused" = xn_mm_decode_attention_append_e4m3 (one or two launches, the library decides where the
+        merge runs), "fused_one_launch" = the same with the merge forced into the attention kernel.  All three give
+        identical results."""
         assert d_model == n_heads * 128, "head_dim is 128"
+        assert attention in ("separate", "fused", "fused_one_launch")
+        self.attention = attention
         self.L, self.d, self.H, self.hid, self.B, self.ctx = n_layers, d_model, n_heads, ffn_hidden, streams, context
         self.eps, self.variant, self.dev = eps, variant, device
         g = torch.Generator(device=device).manual_seed(seed)
@@ -59,9 +67,9 @@ class DecoderStack:
         self.xs = torch.empty(B, dtype=torch.float32, device=device)
         self.qkv = torch.empty(B, 3 * d, **bf)
         self.attn = torch.empty(B, d, **bf)
-        # partial results of the context slices of the attention (empty when one slice per head fills the GPU)
-        self.attn_ws_bytes = int(lib().xn_mm_decode_attention_workspace_bytes(B, n_heads, context))
-        self.attn_ws = torch.empty(self.attn_ws_bytes, dtype=torch.uint8, device=device) if self.attn_ws_bytes else None
+        # (maximum, sum, output) records of the context slices of the attention
+        self.attn_ws_bytes = int(lib().xn_mm_decode_attention_append_workspace_bytes(B, n_heads, context))
+        self.attn_ws = torch.empty(self.attn_ws_bytes, dtype=torch.uint8, device=device)
         self.proj = torch.empty(B, d, **bf)
         self.h = torch.empty(B, 2 * hid, **bf)
         self.x_mid = torch.empty(B, d, **bf)
@@ -93,15 +101,26 @@ class DecoderStack:
                                                   lay["norm1"].data_ptr(), BF16, B, d, self.eps, s))
             self._linear(self.qkv, lay["in_proj"], B, 3 * d, d)
             q, kn, vn = self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * d, self.qkv.data_ptr() + 4 * d
-            check(L.xn_mm_kv_append2(BF16, lay["k"].data_ptr(), lay["v"].data_ptr(), kn, vn, 3 * d, self.pos.data_ptr(), B, H,
-                                     ctx, 128, s))
-            # attention over the cache; the merge of the context slices also writes the e4m3 pieces of the output row
-            check(L.xn_mm_decode_attention_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.attn.data_ptr(),
-                                                      q, 3 * d, lay["k"].data_ptr(), lay["v"].data_ptr(),
-                                                      self.mask.data_ptr() if self.mask is not None else None, B, H, ctx, 128,
-                                                      1.0 / math.sqrt(128.0),
-                                                      self.attn_ws.data_ptr() if self.attn_ws is not None else None,
-                                                      self.attn_ws_bytes, s))
+            if self.attention == "separate":
+                check(L.xn_mm_kv_append2(BF16, lay["k"].data_ptr(), lay["v"].data_ptr(), kn, vn, 3 * d, self.pos.data_ptr(), B, H,
+                                         ctx, 128, s))
+                # attention over the cache; the merge of the context slices also writes the e4m3 pieces of the output row
+                check(L.xn_mm_decode_attention_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(),
+                                                          self.attn.data_ptr(), q, 3 * d, lay["k"].data_ptr(),
+                                                          lay["v"].data_ptr(),
+                                                          self.mask.data_ptr() if self.mask is not None else None, B, H, ctx,
+                                                          128, 1.0 / math.sqrt(128.0), self.attn_ws.data_ptr(),
+                                                          self.attn_ws_bytes, s))
+            else:
+                # append the new key / value rows, attend over the cache, merge the context slices and write the e4m3
+                # pieces of the output row
+                check(L.xn_mm_decode_attention_append_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(),
+                                                           self.attn.data_ptr(), q, kn, vn, 3 * d, lay["k"].data_ptr(),
+                                                           lay["v"].data_ptr(), self.pos.data_ptr(),
+                                                           self.mask.data_ptr() if self.mask is not None else None, B, H, ctx,
+                                                           128, 1.0 / math.sqrt(128.0),
+                                                           1 if self.attention == "fused_one_launch" else 0,
+                                                           self.attn_ws.data_ptr(), self.attn_ws_bytes, s))
             self._linear(self.proj, lay["out_proj"], B, d, d)
             check(L.xn_mm_add_rms_norm_split_e4m3(self.hi.data_ptr(), self._lo(), self.xs.data_ptr(), self.x_mid.data_ptr(),
                                                   cur.data_ptr(), self.proj.data_ptr(), lay["norm2"].data_ptr(), BF16, B, d,
@@ -126,7 +145,17 @@ class DecoderStack:
         return {"weights": w, "kv": kv, "total": w + kv}
 
     def launches_per_step(self) -> int:
-        # per layer: in_proj, kv append (both caches), attention, merge of the context slices + e4m3 split (two launches
-        # when the context is not sliced), out_proj, add+norm, linear_in, silu*mul, linear_out, add+norm (plain add after
-        # the last layer); one norm up front
-        return self.L * 10 + 1
+        # per layer: in_proj, cache append + attention + merge of the context slices with the e4m3 split (three launches,
+        # two or one, see `attention`), out_proj, add+norm, linear_in, silu*mul, linear_out, add+norm (plain add after the last layer); one norm
+        # up front
+        per_layer = 10 if self.attention == "separate" else (8 if self._merge_in_kernel() else 9)
+        return self.L * per_layer + 1
+
+    def _merge_in_kernel(self) -> bool:
+        """The library's policy (xn_mm_decode_attention_append_e4m3): the merge of the context slices runs inside the
+        attention kernel when a resident slot sees at most two CTAs, otherwise as its own launch."""
+        if self.attention == "fused_one_launch":
+            return True
+        ctas = self.attn_ws_bytes // (130 * 4)  # one 130-float record per (stream, head, slice)
+        sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        return ctas <= sms * 5 * 2
