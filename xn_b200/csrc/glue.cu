@@ -1130,12 +1130,14 @@ extern "C" int xn_mm_kv_append(xn_dtype dtype, void *cache, const void *src, siz
 namespace {
 // Slices of the context per (stream, head).  The kernel keeps two sets of loads per warp in flight (96 registers:
 // five CTAs per SM), so 32 streams x 32 heads as one slice each would be 1024 CTAs on 740 slots -- a full wave and
-// a 38 % one.  The context is therefore cut until there are about eight CTAs per slot (the hardware hands the next
+// a 38 % one.  The context is therefore cut until there are six to seven CTAs per slot (the hardware hands the next
 // slice to whichever slot frees up first, so the tail is a fraction of one short slice), each slice at least 128
-// rows; the log-sum-exp combine of the slices moves a few MB.
+// rows; the log-sum-exp combine of the slices moves a few MB.  Measured on the 32-layer decode step (32 streams x
+// 32 heads x 3000 rows): 3 / 4 / 5 / 6 / 7 / 9 slices per head = 10.51 / 10.41 / 10.20-10.27 / 10.41 / 10.41 / 10.36 ms.
 int attention_splits(size_t batch, size_t heads, size_t context) {
     const size_t slots = (size_t)sm_count() * 5, bh = batch * heads;
-    size_t s = (slots * 8 + bh - 1) / bh;
+    static const size_t per_slot = [] { const char *e = getenv("XN_ATTN_CTAS_PER_SLOT"); return (size_t)(e ? atoi(e) : 6); }();
+    size_t s = (slots * per_slot + bh - 1) / bh;
     if (s > context / 128) s = context / 128;
     if (s > 32) s = 32;
     return s < 1 ? 1 : (int)s;
