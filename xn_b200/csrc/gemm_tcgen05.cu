@@ -1765,7 +1765,10 @@ int launch_skinny(void *y, size_t ldy, const void *x0, const void *x1, size_t ld
     if (tiles < sms && grid == sms) {
         const long long s_per_tile = sms / tiles;
         const long long aligned = tiles * (s_per_tile < num_kb ? s_per_tile : num_kb);
-        if (aligned * 100 >= (long long)sms * 60 && total / aligned >= 4) grid = aligned;
+        // S = 1 (whole tiles on 60-90 % of the SMs) trades a longer k loop for no reduction at all: that pays from
+        // 33 rows on (N = 12288: 20.0 us either way at 64 rows, 17.6 us whole against 16.2 us split at 32).
+        const bool whole_tiles = aligned == tiles;
+        if (aligned * 100 >= (long long)sms * 60 && total / aligned >= 4 && (!whole_tiles || a.MB > 32)) grid = aligned;
     }
     static const int force_grid = [] { const char *e = getenv("XN_SKINNY_GRID"); return e ? atoi(e) : 0; }();
     if (force_grid > 0 && force_grid <= sms && force_grid <= total) grid = force_grid;
