@@ -485,8 +485,8 @@ def measure_decode(args, dev, world, rank, timed):
 
     # the same step with cache append + attention + merge + e4m3 split as ONE launch per layer (identical results,
     # fewer launches, measured slower at this size: every attention CTA then ends with a fence and an arrival)
-    fused_ms, fused_launches = time_mode("fused_one_launch")
-    per_step, launches = time_mode("separate")
+    fused_ms, fused_launches = time_mode("fused_one_launch") if args.decode_attention == "both" else (None, None)
+    per_step, launches = time_mode("separate" if args.decode_attention == "both" else args.decode_attention)
     b = st.bytes_per_step()
     peak, kind = measured_peak_gbs()
     return {"ms_per_step": per_step, "steps_per_s_per_gpu": 1e3 / per_step, "streams_per_gpu": streams,
@@ -494,8 +494,9 @@ def measure_decode(args, dev, world, rank, timed):
             "bytes_per_step_per_gpu": b["total"], "gb_per_s_per_gpu": b["total"] / (per_step * 1e-3) / 1e9,
             "frac_of_hbm_peak": b["total"] / (per_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {kind}",
             "launches_per_step": launches, "variant": "W8A16",
-            "one_launch_attention": {"ms_per_step": fused_ms, "launches_per_step": fused_launches,
-                                     "frac_of_hbm_peak": b["total"] / (fused_ms * 1e-3) / 1e9 / peak},
+            "one_launch_attention": None if fused_ms is None else
+            {"ms_per_step": fused_ms, "launches_per_step": fused_launches,
+             "frac_of_hbm_peak": b["total"] / (fused_ms * 1e-3) / 1e9 / peak},
             "l2": "working set 57 GB per GPU, far larger than L2"}
 
 
@@ -515,6 +516,9 @@ def main() -> None:
     ap.add_argument("--no-decode", action="store_true", help="skip the decoder-stack step measurement")
     ap.add_argument("--decode-steps", type=int, default=8)
     ap.add_argument("--decode-only", action="store_true", help="measure only the decoder-stack step (profiling aid)")
+    ap.add_argument("--decode-attention", default="both", choices=["both", "separate", "fused", "fused_one_launch"],
+                    help="how a layer launches cache append + attention + merge + split; 'both' times the three-launch "
+                         "form (reported as the step) and the one-launch form beside it")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill stack (profiling aid)")
     ap.add_argument("--prefill-layers", type=int, default=32)
     args = ap.parse_args()
