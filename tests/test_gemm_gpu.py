@@ -255,6 +255,38 @@ def test_linear_bias_fused_in_the_tiled_epilogue(xn, oracle, cuda, dtype, m, n, 
     assert torch.equal(y, (y_plain.float() + b.float()).to(dtype))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k,bias", [(256, 4096, 4096, False), (200, 1000, 2048, True), (128, 4096, 11264, False),
+                                         (512, 2048, 1024, True), (65, 260, 8192, False)])
+def test_few_tiles_split_along_k(xn, oracle, cuda, dtype, m, n, k, bias):
+    """A hundred-odd rows against a narrow weight: the tiled kernel runs equal k chunks as its batch dimension and a
+    second kernel adds the f32 tile records in k order and applies the epilogue (bias included).  Against f64 on
+    sampled rows, deterministic from call to call, and the bias form bit-identical to product + broadcast_add."""
+    g = torch.Generator(device=cuda).manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g, device=cuda).to(dtype)
+    w = (torch.randn(n, k, generator=g, device=cuda) * 0.05).to(dtype)
+    y_plain = xn.Linear(w)(x)
+    y_again = xn.Linear(w)(x)
+    torch.cuda.synchronize()
+    assert torch.equal(y_plain, y_again)
+    rows = torch.arange(0, m, max(1, m // 37), device=cuda)
+    ref = (x[rows].double() @ w.double().t()).cpu().numpy()
+    assert oracle.rel_err(y_plain[rows].float().cpu().numpy(), ref) < 1e-2
+    # the last row and the last column are part of the product
+    ref_last = (x[-1:].double() @ w.double().t()).cpu().numpy()
+    assert oracle.rel_err(y_plain[-1:].float().cpu().numpy(), ref_last) < 1e-2
+    # plain matmul_t (no static-weight promise) takes the same route
+    y_mm = torch.empty_like(y_plain)
+    xn.ops.matmul_(y_mm, x, w, True)
+    torch.cuda.synchronize()
+    assert torch.equal(y_mm, y_plain)
+    if bias:
+        b = torch.randn(n, generator=g, device=cuda).to(dtype)
+        y = xn.Linear(w, b)(x)
+        torch.cuda.synchronize()
+        assert torch.equal(y, (y_plain.float() + b.float()).to(dtype))
+
+
 def test_dense_16bit_views_with_row_pitch(xn, oracle, cuda):
     """narrow()-ed operands: row pitches larger than k, non-zero offsets (multiples of 8 elements)."""
     g = torch.Generator(device=cuda).manual_seed(5)

@@ -214,6 +214,8 @@ struct GemmArgs {
     int rows2;            // NA = 2 instantiations: the two A tiles are rows [256 i, +128) and [256 i + 128, +128) of ONE matrix
                           // (a 256 x BN tile: both accumulator buffers belong to one tile, the B stage is read by two MMAs)
     int fast_store;       // one destination, no multicast, and every 16-byte output chunk of an interior tile is aligned
+    float *split_out;     // split-k launch: the batch index is a k chunk of ONE product and every tile leaves as an f32
+                          // record [chunk][tile][column group of 4][128 rows][4] for splitk_reduce_kernel
 };
 
 __device__ __forceinline__ bool tile_masked(const GemmArgs &a, int m_blk, int n_blk, int bn) {
@@ -239,6 +241,25 @@ template <int KIND, int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs &args, uint32_t tmem_base, int acc, int q, int lane, int m_row0,
                                               int n_blk, int g, unsigned char *slab, int c_begin, int c_end) {
     constexpr bool F8 = KIND == 0;
+    if (args.split_out) {
+        // raw f32 accumulators, a lane's row of every 4-column group next to its neighbours' rows: 512 contiguous
+        // bytes per warp store; scales, bias and rounding belong to the reduction over the chunks
+        const int num_n = (args.N + BN - 1) / BN, num_m = (args.M + BM - 1) / BM;
+        const size_t t = (size_t)g * num_m * num_n + (size_t)(m_row0 / BM) * num_n + n_blk;
+        float *rec = args.split_out + t * (size_t)(BN * BM) + (size_t)(q * 32 + lane) * 4;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; ++c) {
+            uint32_t v[32];
+            tmem_ld32(taddr + c * 32, v);
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4)
+                *reinterpret_cast<float4 *>(rec + (size_t)(c * 8 + j4) * (BM * 4)) =
+                    make_float4(__uint_as_float(v[4 * j4]), __uint_as_float(v[4 * j4 + 1]), __uint_as_float(v[4 * j4 + 2]),
+                                __uint_as_float(v[4 * j4 + 3]));
+        }
+        return;
+    }
     const int row = m_row0 + q * 32 + lane;
     float xs = 1.0f;
     if (F8 && row < args.M) xs = __ldg(args.x_scale + row);
@@ -1594,6 +1615,62 @@ int make_map_mn(CUtensorMap *map, const void *base, size_t n, size_t k, size_t l
     return XN_OK;
 }
 
+// Second half of a split-k product: y = epilogue(sum over the k chunks of the f32 tile records the tiled kernel left
+// in `rec`), the chunks added in k order.  A thread owns one row of a tile and one group of 4 columns; a CTA of 256
+// threads covers the tile's 128 rows x 2 column groups, so every record read is 512 contiguous bytes per warp.
+// Epilogue as in the tiled kernel: fp8 scales, or nn::Linear's bias added to the rounded product and rounded again.
+template <int KIND>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(void *__restrict__ y, int ldy, const float *__restrict__ rec, int chunks, int M, int N, int bn,
+                     const float *__restrict__ x_scale, const float *__restrict__ w_scale, const void *__restrict__ col_bias) {
+    constexpr bool F8 = KIND == 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int per_tile = bn / 8;  // CTAs per tile
+    const int t = blockIdx.x / per_tile, cg = (blockIdx.x - t * per_tile) * 2 + (threadIdx.x >> 7), r = threadIdx.x & 127;
+    const int num_n = (N + bn - 1) / bn, num_m = (M + BM - 1) / BM;
+    const int m_blk = t / num_n, n_blk = t - m_blk * num_n;
+    const int row = m_blk * BM + r, col = n_blk * bn + cg * 4;
+    if (row >= M || col >= N) return;
+    const size_t tile_elems = (size_t)bn * BM, chunk_elems = tile_elems * num_m * num_n;
+    const float *p = rec + (size_t)t * tile_elems + ((size_t)cg * BM + r) * 4;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < chunks; c0 += 4) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            v[j] = c0 + j < chunks ? __ldcg(reinterpret_cast<const float4 *>(p + (size_t)(c0 + j) * chunk_elems))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+    }
+    float val[4] = {sum.x, sum.y, sum.z, sum.w};
+    if (F8) {
+        const float xs = __ldg(x_scale + row);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) val[e] = (col + e < N ? __ldg(w_scale + col + e) : 0.0f) * (xs * val[e]);
+    }
+    uint16_t out[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (KIND == 2) {
+            __half h = __float2half_rn(val[e]);
+            if (col_bias && col + e < N) h = __float2half_rn(__half2float(h) + __half2float(reinterpret_cast<const __half *>(col_bias)[col + e]));
+            out[e] = *reinterpret_cast<const uint16_t *>(&h);
+        } else {
+            __nv_bfloat16 h = __float2bfloat16_rn(val[e]);
+            if (col_bias && col + e < N)
+                h = __float2bfloat16_rn(__bfloat162float(h) + __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(col_bias)[col + e]));
+            out[e] = *reinterpret_cast<const uint16_t *>(&h);
+        }
+    }
+    uint16_t *dst = reinterpret_cast<uint16_t *>(y) + (size_t)row * ldy + col;
+    if (col + 4 <= N && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+        *reinterpret_cast<uint2 *>(dst) = make_uint2((uint32_t)out[0] | ((uint32_t)out[1] << 16), (uint32_t)out[2] | ((uint32_t)out[3] << 16));
+    } else {
+        for (int e = 0; e < 4 && col + e < N; ++e) dst[e] = out[e];
+    }
+}
+
 struct BatchGeom { size_t batch = 1, a_stride = 0, b_stride = 0; };
 
 template <int KIND, int BN, int NA>
@@ -1657,6 +1734,40 @@ int launch_cfg(const void *a0, const void *a1, const void *b, size_t lda, size_t
     return XN_OK;
 }
 
+// Split-k for a product with too few 128 x 256 tiles to occupy the machine (a hundred-odd rows against a narrow
+// weight): `chunks` equal k ranges ride the tiled kernel's batch dimension (the operands' batch stride is the chunk
+// length along k), every (chunk, tile) leaves as an f32 record in library scratch, and splitk_reduce_kernel adds the
+// chunks in k order and applies the epilogue.  Narrow tiles would fill the SMs too, but every one of them re-reads the
+// whole A tile: 256 x 4096 x 4096 as 128 tiles of 128 x 64 pulls 196 MB through L2 for 36 MB of operands.
+template <int KIND, int NA>
+int launch_split_k(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args, int chunks,
+                   cudaStream_t st) {
+    constexpr int bn = 256;
+    const long long num_m = (args.M + BM - 1) / BM, num_n = (args.N + bn - 1) / bn;
+    void *scratch = nullptr;
+    if (int rc = library_scratch(st, (size_t)chunks * num_m * num_n * bn * BM * sizeof(float), &scratch)) return rc;
+    GemmArgs a2 = args;
+    a2.K = args.K / chunks;
+    a2.batch = chunks;
+    a2.split_out = static_cast<float *>(scratch);
+    a2.col_bias = nullptr;
+    BatchGeom bg;
+    bg.batch = (size_t)chunks; bg.a_stride = (size_t)a2.K; bg.b_stride = (size_t)a2.K;
+    if (int rc = launch_cfg<KIND, bn, NA>(a0, a1, b, lda, ldb, a2, st, bg)) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(num_m * num_n * (bn / 8)));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    XN_CHECK_CUDA(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<KIND>, args.y[0], args.ldy, (const float *)scratch, chunks, args.M,
+                                     args.N, bn, args.x_scale, args.w_scale, args.col_bias));
+    return XN_OK;
+}
+
 template <int KIND, int NA>
 int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_t ldb, const GemmArgs &args,
                 cudaStream_t st, const BatchGeom &bg = BatchGeom()) {
@@ -1667,6 +1778,22 @@ int launch_kind(const void *a0, const void *a1, const void *b, size_t lda, size_
     const int sms = sm_count();
     static const int force_bn = [] { const char *e = getenv("XN_GEMM_BN"); return e ? atoi(e) : 0; }();
     const long long m_tiles = (long long)((args.M + BM - 1) / BM) * args.batch;
+    if constexpr (KIND != 3) {
+        // split-k when 128 x 256 tiles would leave three quarters of the SMs idle and every chunk keeps >= 16 k stages
+        // (measured: two chunks gain nothing -- 512 x 4096 x 4096 bf16 25.2 us either way -- and chunks of 8 stages lose:
+        // fp8 W8A8 256 x 4096 x 4096 13.6 -> 15.0 us)
+        static const int force_split = [] { const char *e = getenv("XN_GEMM_SPLITK"); return e ? atoi(e) : -1; }();
+        constexpr int BKE = BKB / (KIND == 0 ? 1 : 2);
+        const long long t256 = m_tiles * ((args.N + 255) / 256);
+        if (force_split != 0 && args.batch == 1 && !args.causal && !args.a_bcast && args.ndst == 1 && !args.mc && !args.b_mn &&
+            !args.row_bias && !args.rows2 && args.col_offset == 0 && t256 * 4 <= sms && args.N >= 256) {
+            int chunks = 0;
+            for (int c = 8; c >= 4; c >>= 1)
+                if (c * t256 <= sms && args.K % (c * BKE) == 0 && args.K / (c * BKE) >= 16) { chunks = c; break; }
+            if (force_split > 1 && args.K % (force_split * BKE) == 0) chunks = force_split;
+            if (chunks >= 2) return launch_split_k<KIND, NA>(a0, a1, b, lda, ldb, args, chunks, st);
+        }
+    }
     int best = 256;
     long long best_cost = -1;
     const int bn_step = args.b_mn ? 64 : 32;  // an n-contiguous B arrives in 64-column blocks
