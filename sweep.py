@@ -113,6 +113,8 @@ def sweep_dense(out, dev, pk):
         shapes = [(4096, 4096, 4096), (8192, 8192, 8192), (1024, 12288, 4096), (256, 12288, 4096), (64, 12288, 4096)]
         if dt == torch.bfloat16:  # the reference's decode path: unquantized bf16 weights, decode-sized m
             shapes += [(m, n, k) for (n, k) in ((12288, 4096), (4096, 4096), (22528, 4096), (4096, 11264)) for m in (1, 16, 32)]
+            # a hundred-odd rows against the narrow weights: too few 128 x 256 tiles for the machine (split along k)
+            shapes += [(128, 4096, 4096), (256, 4096, 4096), (256, 4096, 11264)]
         for m, n, k in shapes:
             R = replicas_for(2 * n * k, hi=8)
             ws = [(torch.randn(n, k, device=dev) * 0.05).to(dt) for _ in range(R)]
