@@ -631,9 +631,10 @@ def main() -> None:
     host_ys = {(m, i): torch.empty(m, N_OUT).pin_memory() for m in MS for i in range(R)}
 
     def step_e2e():
+        # the three batch sizes interleaved, as mixed requests arrive: the copy-heavy M = 16 calls overlap the others
         n = 0
-        for m in MS:
-            for i, lin in enumerate(lins):
+        for i, lin in enumerate(lins):
+            for m in MS:
                 with torch.cuda.stream(E2E_STREAMS[n % len(E2E_STREAMS)]):
                     lin.forward_host(host_x[m], host_ys[(m, i)])
                 n += 1
@@ -674,8 +675,8 @@ def main() -> None:
             for st_ in E2E_STREAMS:
                 st_.wait_stream(side)
             n_call = 0
-            for m in MS:
-                for i, lin in enumerate(lins):
+            for i, lin in enumerate(lins):
+                for m in MS:
                     with torch.cuda.stream(E2E_STREAMS[n_call % len(E2E_STREAMS)]):
                         lin.forward_host(host_x[m], host_ys[(m, i)])
                     n_call += 1
@@ -761,8 +762,8 @@ def main() -> None:
                     "d2h_bytes_per_step": R * sum(m * N_OUT * 4 for m in MS), "steps": e2e_steps,
                     "ms_per_step": ms_e2e / e2e_steps, "calls_per_step": len(MS) * R,
                     "api": ("LinearQ4.forward_host -> xn_mm_linear_q4_host (copy in, quantize rows, linear, copy out), "
-                            "calls spread round-robin over 8 streams; the step's calls are captured once in a CUDA graph "
-                            "(copies included) and replayed per step") if e2e_graph_ok else
+                            "the three batch sizes interleaved and the calls spread round-robin over 8 streams; the step's "
+                            "calls are captured once in a CUDA graph (copies included) and replayed per step") if e2e_graph_ok else
                            "LinearQ4.forward_host -> xn_mm_linear_q4_host, plain calls over 8 streams (graph replay differed)",
                     "plain_calls_value": world * e2e_steps * len(MS) * R * wb / (ms_e2e_eager * 1e-3) / 1e9},
             "gpu_launches": args.steps * launches_per_step,
